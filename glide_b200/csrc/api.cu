@@ -1,0 +1,718 @@
+// C ABI (include/glide_b200.h): argument checks, scratch memory, stream and timing around
+// the kernel launchers. No compute happens on the host; there is no CPU fallback.
+#include <algorithm>
+#include <cfloat>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/glide_b200.h"
+#include "kernels.h"
+#include "scan.cuh"
+
+using namespace glide;
+
+struct glide_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    std::string error;
+    float last_ms = 0.0f;
+    void *ws = nullptr;  // scratch, grown on demand
+    size_t ws_bytes = 0;
+    unsigned long long *counters = nullptr;  // 3 x u64 on the device
+    bool counters_on = false;
+};
+
+namespace {
+
+int fail(glide_ctx *ctx, int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->error = buf;
+    return code;
+}
+
+#define GL_CUDA(ctx, call)                                                                          \
+    do {                                                                                            \
+        cudaError_t e_ = (call);                                                                    \
+        if (e_ != cudaSuccess)                                                                      \
+            return fail(ctx, e_ == cudaErrorMemoryAllocation ? GLIDE_ERR_NO_MEMORY : GLIDE_ERR_CUDA, \
+                        "%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__);       \
+    } while (0)
+
+#define GL_REQUIRE(ctx, cond, code, msg)               \
+    do {                                                \
+        if (!(cond)) return fail(ctx, code, "%s", msg); \
+    } while (0)
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t) 255; }
+
+int ensure_ws(glide_ctx *ctx, size_t bytes) {
+    if (bytes <= ctx->ws_bytes) return GLIDE_OK;
+    if (ctx->ws) {
+        GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        GL_CUDA(ctx, cudaFree(ctx->ws));
+        ctx->ws = nullptr;
+        ctx->ws_bytes = 0;
+    }
+    GL_CUDA(ctx, cudaMalloc(&ctx->ws, bytes));
+    ctx->ws_bytes = bytes;
+    return GLIDE_OK;
+}
+
+struct Bump {
+    char *base;
+    size_t off = 0;
+    explicit Bump(void *b) : base(static_cast<char *>(b)) {}
+    template<typename T>
+    T *take(size_t count) {
+        T *p = reinterpret_cast<T *>(base + off);
+        off += align256(count * sizeof(T));
+        return p;
+    }
+};
+
+int check_params(glide_ctx *ctx, const glide_search_params *p, uint32_t degree) {
+    GL_REQUIRE(ctx, p != nullptr, GLIDE_ERR_BAD_ARG, "search params are null");
+    GL_REQUIRE(ctx, p->beam >= 32 && p->beam % 32 == 0, GLIDE_ERR_BAD_ARG, "beam must be a positive multiple of 32");
+    GL_REQUIRE(ctx, p->beam <= 512, GLIDE_ERR_UNSUPPORTED, "Unsupported beam");               // kernel_config.cuh:47-48
+    GL_REQUIRE(ctx, degree >= 1 && degree <= 256, GLIDE_ERR_UNSUPPORTED, "Unsupported graph_degree");  // :59-60
+    GL_REQUIRE(ctx, p->max_iterations >= 1, GLIDE_ERR_BAD_ARG, "max_iterations must be >= 1");
+    GL_REQUIRE(ctx, p->hash_bit >= 4 && p->hash_bit <= 13, GLIDE_ERR_BAD_ARG, "hash_bit out of range");
+    GL_REQUIRE(ctx, p->hash_reset_interval >= 1, GLIDE_ERR_BAD_ARG, "hash_reset_interval must be >= 1");
+    return GLIDE_OK;
+}
+
+BeamParamsHost to_host(const glide_search_params *p) {
+    return BeamParamsHost{p->beam, p->max_iterations, p->min_iterations, p->hash_bit, p->hash_reset_interval};
+}
+
+struct Timed {
+    glide_ctx *ctx;
+    explicit Timed(glide_ctx *c) : ctx(c) { cudaEventRecord(ctx->ev_start, ctx->stream); }
+    int finish() {
+        cudaEventRecord(ctx->ev_stop, ctx->stream);
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) return fail(ctx, GLIDE_ERR_CUDA, "kernel execution failed: %s", cudaGetErrorString(e));
+        cudaEventElapsedTime(&ctx->last_ms, ctx->ev_start, ctx->ev_stop);
+        return GLIDE_OK;
+    }
+};
+
+unsigned long long *counters_or_null(glide_ctx *ctx) {
+    if (!ctx->counters_on) return nullptr;
+    cudaMemsetAsync(ctx->counters, 0, 3 * sizeof(unsigned long long), ctx->stream);
+    return ctx->counters;
+}
+
+uint64_t splitmix64(uint64_t &x) {
+    uint64_t z = (x += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+uint64_t gcd64(uint64_t a, uint64_t b) {
+    while (b) { const uint64_t t = a % b; a = b; b = t; }
+    return a;
+}
+
+}  // namespace
+
+extern "C" {
+
+int glide_ctx_create(int device, glide_ctx **out) {
+    if (!out) return GLIDE_ERR_BAD_ARG;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || device < 0 || device >= count) return GLIDE_ERR_CUDA;
+    glide_ctx *ctx = new (std::nothrow) glide_ctx();
+    if (!ctx) return GLIDE_ERR_NO_MEMORY;
+    ctx->device = device;
+    if (cudaSetDevice(device) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreate(&ctx->ev_start) != cudaSuccess || cudaEventCreate(&ctx->ev_stop) != cudaSuccess ||
+        cudaMalloc(&ctx->counters, 3 * sizeof(unsigned long long)) != cudaSuccess) {
+        delete ctx;
+        return GLIDE_ERR_CUDA;
+    }
+    *out = ctx;
+    return GLIDE_OK;
+}
+
+void glide_ctx_destroy(glide_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->counters) cudaFree(ctx->counters);
+    if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+    if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+const char *glide_last_error(const glide_ctx *ctx) { return ctx ? ctx->error.c_str() : "null context"; }
+void *glide_ctx_stream(glide_ctx *ctx) { return ctx ? (void *) ctx->stream : nullptr; }
+float glide_last_kernel_ms(const glide_ctx *ctx) { return ctx ? ctx->last_ms : 0.0f; }
+
+void glide_enable_counters(glide_ctx *ctx, int on) { if (ctx) ctx->counters_on = on != 0; }
+
+int glide_read_counters(glide_ctx *ctx, uint64_t out[3]) {
+    if (!ctx || !out) return GLIDE_ERR_BAD_ARG;
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    GL_CUDA(ctx, cudaMemcpyAsync(out, ctx->counters, 3 * sizeof(uint64_t), cudaMemcpyDeviceToHost, ctx->stream));
+    GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return GLIDE_OK;
+}
+
+// params.cuh:49-66
+uint32_t glide_calculate_hash_bitlen(uint32_t beam, uint32_t graph_degree, float max_fill_rate, uint32_t min_bitlen) {
+    const uint32_t max_visited = beam + graph_degree;
+    uint32_t lo = 8;
+    const uint32_t hi = 13;
+    if (lo < min_bitlen) lo = min_bitlen;
+    uint32_t bitlen = lo;
+    while (max_visited > (float) (1u << bitlen) * max_fill_rate) bitlen += 1;
+    if (bitlen > hi) bitlen = hi;
+    return bitlen;
+}
+
+// params.cuh:68-80
+uint32_t glide_calculate_hash_reset_interval(uint32_t beam, uint32_t graph_degree, float max_fill_rate,
+                                             uint32_t hash_bitlen) {
+    uint32_t interval = 1;
+    while (true) {
+        const uint32_t max_visited = beam + graph_degree * (interval + 1);
+        if (max_visited > (float) (1u << hash_bitlen) * max_fill_rate) break;
+        interval += 1;
+    }
+    return interval;
+}
+
+// params.cuh:82-99
+void glide_adjust_search_params(uint32_t min_iterations, uint32_t *max_iterations, uint32_t *beam) {
+    uint32_t m = *max_iterations;
+    if (*max_iterations == 0) m = (uint32_t) (1 + std::min(*beam * 1.1, *beam + 10.0));
+    if (*max_iterations < min_iterations) m = min_iterations;
+    if (*max_iterations < m) *max_iterations = m;
+    if (*beam % 32) *beam += 32 - (*beam % 32);
+}
+
+// ---- memory helpers ----------------------------------------------------------------------
+int glide_malloc(glide_ctx *ctx, size_t bytes, void **d_out) {
+    if (!ctx || !d_out) return GLIDE_ERR_BAD_ARG;
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    GL_CUDA(ctx, cudaMalloc(d_out, bytes ? bytes : 1));
+    return GLIDE_OK;
+}
+void glide_free(void *device_ptr) { if (device_ptr) cudaFree(device_ptr); }
+int glide_memcpy_h2d(glide_ctx *ctx, void *d_dst, const void *h_src, size_t bytes) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    GL_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return GLIDE_OK;
+}
+int glide_memcpy_d2h(glide_ctx *ctx, void *h_dst, const void *d_src, size_t bytes) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    GL_CUDA(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return GLIDE_OK;
+}
+int glide_memset_u32(glide_ctx *ctx, uint32_t *d_dst, uint32_t value, size_t count) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const uint8_t b = value & 0xff;
+    if (((value >> 8) & 0xff) == b && ((value >> 16) & 0xff) == b && (value >> 24) == b) {
+        GL_CUDA(ctx, cudaMemsetAsync(d_dst, b, count * 4, ctx->stream));
+    } else {
+        std::vector<uint32_t> h(count, value);
+        GL_CUDA(ctx, cudaMemcpyAsync(d_dst, h.data(), count * 4, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return GLIDE_OK;
+}
+
+// ---- partition ---------------------------------------------------------------------------
+int glide_kmeans_fit(glide_ctx *ctx, const float *d_sample, uint32_t n, uint32_t dim, uint32_t C, uint32_t max_iter,
+                     int metric, float *d_centroids, uint32_t *d_labels_or_null, uint32_t *iterations_run) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_sample && d_centroids && dim > 0, GLIDE_ERR_BAD_ARG, "kmeans: null pointer or zero dim");
+    GL_REQUIRE(ctx, C >= 1 && n >= C, GLIDE_ERR_BAD_ARG, "kmeans: fewer rows than centroids");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (max_iter == 0) max_iter = 25;
+    const size_t need = 4 * align256((size_t) n * 4) + align256(slot_scratch_words(n, C) * 4) +
+                        3 * align256((size_t) (C + 2) * 4) + align256(scan_tmp_bytes(C + 1)) + 256;
+    int rc = ensure_ws(ctx, need);
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    uint32_t *labels_a = b.take<uint32_t>(n), *labels_b = b.take<uint32_t>(n);
+    uint32_t *slot = b.take<uint32_t>(n), *members = b.take<uint32_t>(n);
+    uint32_t *hist = b.take<uint32_t>(slot_scratch_words(n, C));
+    uint32_t *cnt = b.take<uint32_t>(C + 2), *off = b.take<uint32_t>(C + 2), *changed = b.take<uint32_t>(C + 2);
+    void *scan_tmp = b.take<char>(scan_tmp_bytes(C + 1));
+    cudaStream_t st = ctx->stream;
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_centroids, d_sample, (size_t) C * dim * 4, cudaMemcpyDeviceToDevice, st));
+    GL_CUDA(ctx, cudaMemsetAsync(labels_b, 0xff, (size_t) n * 4, st));
+    uint32_t rounds = 0;
+    uint32_t *cur = labels_a, *prev = labels_b;
+    for (uint32_t it = 0; it < max_iter; it++) {
+        AssignArgs a{d_sample, n, dim, d_centroids, C, -1.0f, metric, cur, nullptr};
+        GL_CUDA(ctx, launch_assign(a, st));
+        GL_CUDA(ctx, launch_count_changed(cur, prev, n, changed, st));
+        uint32_t h_changed = 0;
+        GL_CUDA(ctx, cudaMemcpyAsync(&h_changed, changed, 4, cudaMemcpyDeviceToHost, st));
+        GL_CUDA(ctx, cudaStreamSynchronize(st));
+        rounds++;
+        std::swap(cur, prev);  // prev now holds the latest labels
+        if (h_changed == 0) break;
+        GL_CUDA(ctx, launch_slots(prev, n, C, slot, cnt, hist, st));
+        GL_CUDA(ctx, exclusive_scan_u32(cnt, C, off, scan_tmp, st));
+        GL_CUDA(ctx, launch_scatter_members(prev, slot, off, n, members, st));
+        GL_CUDA(ctx, launch_centroid_update(d_sample, dim, members, off, cnt, C, d_centroids, st));
+    }
+    if (d_labels_or_null) GL_CUDA(ctx, cudaMemcpyAsync(d_labels_or_null, prev, (size_t) n * 4, cudaMemcpyDeviceToDevice, st));
+    if (iterations_run) *iterations_run = rounds;
+    return timer.finish();
+}
+
+// Sample ids: an arithmetic progression modulo n with a seeded stride coprime to n, i.e.
+// floor(n*sample_factor) distinct rows spread over the whole set. (The reference shuffles
+// all ids with an unseeded generator and takes the first ones, partition.cuh:25-31.)
+static void sample_ids(uint32_t n, uint32_t sample_num, uint64_t seed, std::vector<uint32_t> &ids) {
+    uint64_t s = seed;
+    uint64_t stride = splitmix64(s) % n;
+    if (stride == 0) stride = 1;
+    while (gcd64(stride, n) != 1) stride = stride % n + 1;
+    const uint64_t offset = splitmix64(s) % n;
+    ids.resize(sample_num);
+    for (uint32_t i = 0; i < sample_num; i++) ids[i] = (uint32_t) ((offset + (uint64_t) i * stride) % n);
+}
+
+int glide_sample_ids(uint32_t n, uint32_t sample_num, uint64_t seed, uint32_t *h_out) {
+    if (!h_out || n == 0 || sample_num > n) return GLIDE_ERR_BAD_ARG;
+    std::vector<uint32_t> ids;
+    sample_ids(n, sample_num, seed, ids);
+    std::memcpy(h_out, ids.data(), (size_t) sample_num * 4);
+    return GLIDE_OK;
+}
+
+int glide_get_centroids(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, uint32_t C, float sample_factor,
+                        uint64_t seed, uint32_t max_iter, int metric, float *d_centroids, uint32_t *iterations_run) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_data && d_centroids && n > 0 && dim > 0, GLIDE_ERR_BAD_ARG, "get_centroids: bad argument");
+    const uint32_t sample_num = (uint32_t) ((double) n * sample_factor);  // partition.cuh:17
+    GL_REQUIRE(ctx, sample_num >= C && sample_num <= n, GLIDE_ERR_BAD_ARG,
+               "get_centroids: sample smaller than centroid_num (raise sample_factor)");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    std::vector<uint32_t> ids;
+    sample_ids(n, sample_num, seed, ids);
+    float *d_sample = nullptr;
+    uint32_t *d_ids = nullptr;
+    GL_CUDA(ctx, cudaMalloc(&d_sample, (size_t) sample_num * dim * 4));
+    cudaError_t e = cudaMalloc(&d_ids, (size_t) sample_num * 4);
+    if (e != cudaSuccess) { cudaFree(d_sample); return fail(ctx, GLIDE_ERR_NO_MEMORY, "cudaMalloc failed"); }
+    int rc = GLIDE_OK;
+    e = cudaMemcpyAsync(d_ids, ids.data(), (size_t) sample_num * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = launch_gather_rows(d_data, d_ids, sample_num, dim, d_sample, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) rc = fail(ctx, GLIDE_ERR_CUDA, "sample gather failed: %s", cudaGetErrorString(e));
+    if (rc == GLIDE_OK) rc = glide_kmeans_fit(ctx, d_sample, sample_num, dim, C, max_iter, metric, d_centroids, nullptr, iterations_run);
+    cudaFree(d_sample);
+    cudaFree(d_ids);
+    return rc;
+}
+
+int glide_define_partition(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, const float *d_centroids,
+                           uint32_t C, float boundary_factor, int metric, uint32_t *d_segment_index,
+                           uint32_t *h_segment_start, uint32_t *h_segment_length) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_data && d_centroids && d_segment_index && h_segment_start && h_segment_length, GLIDE_ERR_BAD_ARG,
+               "define_partition: null pointer");
+    GL_REQUIRE(ctx, n > 0 && dim > 0 && C >= 1, GLIDE_ERR_BAD_ARG, "define_partition: zero size");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t need = 4 * align256((size_t) n * 4) + align256(slot_scratch_words(n, C) * 4) + align256((size_t) (C + 1) * 4) + 256;
+    int rc = ensure_ws(ctx, need);
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    uint32_t *nearest = b.take<uint32_t>(n), *bkey = b.take<uint32_t>(n), *slot = b.take<uint32_t>(n), *bslot = b.take<uint32_t>(n);
+    uint32_t *hist = b.take<uint32_t>(slot_scratch_words(n, C));
+    uint32_t *totals = b.take<uint32_t>(C + 1);
+    cudaStream_t st = ctx->stream;
+    Timed timer(ctx);
+    AssignArgs a{d_data, n, dim, d_centroids, C, boundary_factor, metric, nearest, bkey};
+    GL_CUDA(ctx, launch_assign(a, st));
+    GL_CUDA(ctx, launch_slots(nearest, n, C, slot, totals, hist, st));
+    GL_CUDA(ctx, launch_slots(bkey, n, 1, bslot, totals + C, hist, st));
+    GL_CUDA(ctx, launch_pack_seg_index(nearest, slot, bslot, n, d_segment_index, st));
+    GL_CUDA(ctx, cudaMemcpyAsync(h_segment_length, totals, (size_t) (C + 1) * 4, cudaMemcpyDeviceToHost, st));
+    rc = timer.finish();
+    if (rc) return rc;
+    uint32_t start = 0;  // partition.cuh:111-115
+    for (uint32_t i = 0; i <= C; i++) {
+        h_segment_start[i] = start;
+        start += h_segment_length[i];
+    }
+    return GLIDE_OK;
+}
+
+int glide_reorder(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, const uint32_t *d_segment_index,
+                  const uint32_t *h_segment_start, uint32_t C, float *d_reorder_data, uint32_t *d_map) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_data && d_segment_index && h_segment_start && d_reorder_data && d_map, GLIDE_ERR_BAD_ARG,
+               "reorder: null pointer");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    int rc = ensure_ws(ctx, align256((size_t) (C + 1) * 4));
+    if (rc) return rc;
+    uint32_t *d_start = static_cast<uint32_t *>(ctx->ws);
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_start, h_segment_start, (size_t) (C + 1) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, launch_reorder(d_data, n, dim, d_segment_index, d_start, d_reorder_data, d_map, ctx->stream));
+    return timer.finish();
+}
+
+int glide_preprocess(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, uint32_t C, float boundary_factor,
+                     float sample_factor, int metric, uint64_t seed, float *d_centroids, uint32_t *h_segment_start,
+                     uint32_t *h_segment_length, float **d_reorder_data_out, uint32_t **d_map_out,
+                     uint32_t *reorder_num_out) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_reorder_data_out && d_map_out && reorder_num_out, GLIDE_ERR_BAD_ARG, "preprocess: null output");
+    *d_reorder_data_out = nullptr;
+    *d_map_out = nullptr;
+    float total_ms = 0.0f;
+    int rc = glide_get_centroids(ctx, d_data, n, dim, C, sample_factor, seed, 0, metric, d_centroids, nullptr);
+    if (rc) return rc;
+    total_ms += ctx->last_ms;
+    uint32_t *d_seg_index = nullptr;
+    GL_CUDA(ctx, cudaMalloc(&d_seg_index, (size_t) n * 3 * 4));
+    rc = glide_define_partition(ctx, d_data, n, dim, d_centroids, C, boundary_factor, metric, d_seg_index,
+                                h_segment_start, h_segment_length);
+    total_ms += ctx->last_ms;
+    if (rc) { cudaFree(d_seg_index); return rc; }
+    const uint32_t reorder_num = n + h_segment_length[C];  // partition.cuh:182
+    float *d_reorder = nullptr;
+    uint32_t *d_map = nullptr;
+    cudaError_t e = cudaMalloc(&d_reorder, (size_t) reorder_num * dim * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&d_map, (size_t) reorder_num * 4);
+    if (e != cudaSuccess) {
+        cudaFree(d_seg_index); cudaFree(d_reorder);
+        return fail(ctx, GLIDE_ERR_NO_MEMORY, "preprocess: cudaMalloc failed: %s", cudaGetErrorString(e));
+    }
+    rc = glide_reorder(ctx, d_data, n, dim, d_seg_index, h_segment_start, C, d_reorder, d_map);
+    total_ms += ctx->last_ms;
+    cudaFree(d_seg_index);
+    if (rc) { cudaFree(d_reorder); cudaFree(d_map); return rc; }
+    *d_reorder_data_out = d_reorder;
+    *d_map_out = d_map;
+    *reorder_num_out = reorder_num;
+    ctx->last_ms = total_ms;
+    return GLIDE_OK;
+}
+
+// ---- kNN -----------------------------------------------------------------------------------
+int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, uint32_t dim,
+                    const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t S, uint32_t knn_degree,
+                    uint32_t max_iterations, float termination_threshold, uint32_t sample, uint64_t seed, int metric,
+                    int32_t *d_knn, uint32_t *iterations_run) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_reorder_data && h_segment_start && h_segment_length && d_knn, GLIDE_ERR_BAD_ARG, "build_nnd: null pointer");
+    GL_REQUIRE(ctx, rows > 0 && dim > 0 && S >= 1, GLIDE_ERR_BAD_ARG, "build_nnd: zero size");
+    GL_REQUIRE(ctx, knn_degree >= 1 && knn_degree <= 64, GLIDE_ERR_UNSUPPORTED, "build_nnd: knn_degree must be <= 64");
+    if (max_iterations == 0) max_iterations = 20;              // params.cuh:20
+    if (termination_threshold < 0) termination_threshold = 1e-4f;  // params.cuh:21
+    if (sample == 0) sample = 32;
+    GL_REQUIRE(ctx, sample <= 32, GLIDE_ERR_UNSUPPORTED, "build_nnd: sample must be <= 32");
+    uint64_t covered = 0;
+    for (uint32_t s = 0; s < S; s++) {
+        GL_REQUIRE(ctx, h_segment_start[s] == covered, GLIDE_ERR_BAD_ARG, "build_nnd: segments must tile the rows in order");
+        covered += h_segment_length[s];
+    }
+    GL_REQUIRE(ctx, covered == rows, GLIDE_ERR_BAD_ARG, "build_nnd: segment lengths do not sum to the row count");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const uint32_t K = knn_degree <= 32 ? 32 : 64;
+    const size_t nnd_bytes = nnd_workspace_bytes(rows, K, sample);
+    int rc = ensure_ws(ctx, nnd_bytes + 2 * align256((size_t) S * 4));
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    uint32_t *d_start = b.take<uint32_t>(S), *d_len = b.take<uint32_t>(S);
+    void *work = b.take<char>(nnd_bytes);
+    // empty segments (C == 1 leaves the boundary segment empty, partition_kernel.cuh:58) need no launch
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_start, h_segment_start, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(d_len, h_segment_length, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    NndArgs a{};
+    a.data = d_reorder_data; a.rows = rows; a.dim = dim;
+    a.seg_start = d_start; a.seg_len = d_len; a.S = S;
+    a.K = K; a.sample = sample; a.max_iterations = max_iterations; a.termination_threshold = termination_threshold;
+    a.seed = seed; a.metric = metric; a.workspace = work; a.workspace_bytes = nnd_bytes;
+    a.out_knn = d_knn; a.out_degree = knn_degree; a.iterations_run = iterations_run; a.stage_ms = nullptr;
+    GL_CUDA(ctx, run_nn_descent(a, ctx->stream));
+    return timer.finish();
+}
+
+int glide_bruteforce_knn(glide_ctx *ctx, const float *d_base, uint32_t n, const float *d_queries, uint32_t q,
+                         uint32_t dim, uint32_t k, int metric, uint32_t *d_out_ids, float *d_out_dists) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_base && d_queries && d_out_ids, GLIDE_ERR_BAD_ARG, "bruteforce_knn: null pointer");
+    GL_REQUIRE(ctx, n > 0 && dim > 0, GLIDE_ERR_BAD_ARG, "bruteforce_knn: zero size");
+    GL_REQUIRE(ctx, k >= 1 && k <= 128 && k <= n, GLIDE_ERR_UNSUPPORTED, "bruteforce_knn: k must be in [1, min(128, n)]");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const uint32_t splits = bruteforce_default_splits(n, q);
+    int rc = ensure_ws(ctx, bruteforce_scratch_bytes(q, k, splits) + 256);
+    if (rc) return rc;
+    Timed timer(ctx);
+    GL_CUDA(ctx, launch_bruteforce(d_base, n, d_queries, q, dim, k, metric, splits, ctx->ws, d_out_ids, d_out_dists, ctx->stream));
+    return timer.finish();
+}
+
+// ---- graph build ---------------------------------------------------------------------------
+int glide_start_point_select(const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t S,
+                             const uint32_t *h_map, uint64_t seed, uint32_t *h_local, uint32_t *h_original) {
+    if (!h_segment_start || !h_segment_length || !h_local) return GLIDE_ERR_BAD_ARG;
+    uint64_t s = seed;
+    for (uint32_t i = 0; i < S; i++) {  // glide_impl.cuh:59-68
+        const uint32_t len = h_segment_length[i];
+        const uint32_t id = len ? (uint32_t) (splitmix64(s) % len) : 0;  // an empty segment (C == 1) gets 0
+        h_local[i] = id;
+        if (i + 1 != S && h_original && h_map) h_original[i] = h_map[h_segment_start[i] + id];
+    }
+    return GLIDE_OK;
+}
+
+int glide_subgraph_build_and_merge(glide_ctx *ctx, const float *d_reorder_data, uint32_t reorder_num, uint32_t dim,
+                                   const uint32_t *d_knn, uint32_t knn_degree, const uint32_t *h_segment_start,
+                                   const uint32_t *h_segment_length, uint32_t S, const uint32_t *d_start_points_local,
+                                   const uint32_t *d_map, uint32_t num, uint32_t graph_degree,
+                                   const glide_search_params *p, float relaxant_factor, int metric, int skip_boundary,
+                                   uint32_t *d_graph) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_reorder_data && d_knn && h_segment_start && h_segment_length && d_start_points_local && d_map && d_graph,
+               GLIDE_ERR_BAD_ARG, "subgraph_build_and_merge: null pointer");
+    GL_REQUIRE(ctx, S >= 1 && num <= reorder_num && dim > 0, GLIDE_ERR_BAD_ARG, "subgraph_build_and_merge: bad sizes");
+    int rc = check_params(ctx, p, knn_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, graph_degree >= 1 && graph_degree <= 256, GLIDE_ERR_UNSUPPORTED, "Unsupported graph_degree");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = ensure_ws(ctx, 2 * align256((size_t) S * 4));
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    uint32_t *d_start = b.take<uint32_t>(S), *d_len = b.take<uint32_t>(S);
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_start, h_segment_start, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(d_len, h_segment_length, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    BuildArgs a{};
+    a.mode = kModeBuild;
+    a.data = d_reorder_data; a.dim = dim; a.graph_in = d_knn; a.in_degree = knn_degree;
+    a.graph_out = d_graph; a.out_degree = graph_degree;
+    a.seg_start = d_start; a.seg_len = d_len; a.S = S; a.start_points = d_start_points_local; a.map = d_map;
+    a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
+    a.counters = counters_or_null(ctx);
+    GL_CUDA(ctx, launch_build(a, ctx->stream));
+    const uint32_t boundary_num = reorder_num - num;
+    if (!skip_boundary && boundary_num > 0) {  // glide_impl.cuh:149-187
+        a.mode = kModeBoundary;
+        a.fixed_segment = S - 1;
+        a.first = num;
+        a.count = boundary_num;
+        GL_CUDA(ctx, launch_build(a, ctx->stream));
+    }
+    return timer.finish();
+}
+
+int glide_reverse_graph(glide_ctx *ctx, uint32_t *d_graph, uint32_t num, uint32_t graph_degree) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_graph && num > 0, GLIDE_ERR_BAD_ARG, "reverse_graph: bad argument");
+    GL_REQUIRE(ctx, graph_degree >= 1 && graph_degree <= 256, GLIDE_ERR_UNSUPPORTED, "Unsupported graph_degree");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t need = 2 * align256((size_t) (num + 1) * 4) + align256((size_t) num * graph_degree * 8) +
+                        align256(reverse_scan_tmp_bytes(num)) + 256;
+    int rc = ensure_ws(ctx, need);
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    ReverseArgs a{};
+    a.graph = d_graph; a.num = num; a.degree = graph_degree;
+    a.counts = b.take<uint32_t>(num + 1);
+    a.offsets = b.take<uint32_t>(num + 1);
+    a.edges = b.take<unsigned long long>((size_t) num * graph_degree);
+    a.scan_tmp = b.take<char>(reverse_scan_tmp_bytes(num));
+    Timed timer(ctx);
+    GL_CUDA(ctx, launch_reverse(a, ctx->stream));
+    return timer.finish();
+}
+
+static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                         uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
+                         const glide_search_params *p, float relaxant_factor, int metric) {
+    GL_REQUIRE(ctx, d_data && d_graph && d_start_points && num > 0 && dim > 0, GLIDE_ERR_BAD_ARG, "refine: bad argument");
+    int rc = check_params(ctx, p, graph_degree);
+    if (rc) return rc;
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t graph_bytes = (size_t) num * graph_degree * 4;
+    rc = ensure_ws(ctx, align256(graph_bytes));
+    if (rc) return rc;
+    uint32_t *snapshot = static_cast<uint32_t *>(ctx->ws);
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(snapshot, d_graph, graph_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    BuildArgs a{};
+    a.mode = mode;
+    a.data = d_data; a.dim = dim; a.graph_in = snapshot; a.in_degree = graph_degree;
+    a.graph_out = d_graph; a.out_degree = graph_degree;
+    a.start_points = d_start_points; a.centroids = d_centroids; a.C = C;
+    a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
+    a.counters = counters_or_null(ctx);
+    GL_CUDA(ctx, launch_build(a, ctx->stream));
+    return timer.finish();
+}
+
+int glide_refine(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                 uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
+                 const glide_search_params *p, float relaxant_factor, int metric) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_centroids && C >= 1, GLIDE_ERR_BAD_ARG, "refine: centroids missing");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
+    return refine_common(ctx, kModeRefine, d_data, num, dim, d_graph, graph_degree, d_centroids, C, d_start_points, p,
+                         relaxant_factor, metric);
+}
+
+// ---- search ----------------------------------------------------------------------------------
+int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph,
+                 uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
+                 const float *d_queries, uint32_t q, const glide_search_params *p, int metric, uint32_t *d_out_ids,
+                 float *d_out_dists) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_data && d_graph && d_centroids && d_start_points && d_queries && d_out_ids && d_out_dists,
+               GLIDE_ERR_BAD_ARG, "search: null pointer");
+    GL_REQUIRE(ctx, num > 0 && dim > 0 && C >= 1, GLIDE_ERR_BAD_ARG, "search: zero size");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
+    int rc = check_params(ctx, p, graph_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, p->top_k >= 1 && p->top_k <= p->beam, GLIDE_ERR_BAD_ARG, "search: top_k must be in [1, beam]");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    SearchArgs a{};
+    a.data = d_data; a.graph = d_graph; a.degree = graph_degree; a.dim = dim;
+    a.queries = d_queries; a.Q = q; a.top_k = p->top_k; a.metric = metric; a.p = to_host(p);
+    a.centroids = d_centroids; a.C = C; a.start_points = d_start_points;
+    a.out_ids = d_out_ids; a.out_dists = d_out_dists;
+    a.counters = counters_or_null(ctx);
+    Timed timer(ctx);
+    GL_CUDA(ctx, launch_search(a, ctx->stream));
+    return timer.finish();
+}
+
+int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph,
+                      uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
+                      const float *h_queries, uint32_t q, const glide_search_params *p, int metric,
+                      uint32_t *h_out_ids, float *h_out_dists) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, h_queries && h_out_ids && h_out_dists && p, GLIDE_ERR_BAD_ARG, "search_host: null pointer");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t qb = align256((size_t) q * dim * 4), rb = align256((size_t) q * p->top_k * 4);
+    int rc = ensure_ws(ctx, qb + 2 * rb);
+    if (rc) return rc;
+    char *w = static_cast<char *>(ctx->ws);
+    float *d_q = reinterpret_cast<float *>(w);
+    uint32_t *d_ids = reinterpret_cast<uint32_t *>(w + qb);
+    float *d_dists = reinterpret_cast<float *>(w + qb + rb);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_q, h_queries, (size_t) q * dim * 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = glide_search(ctx, d_data, num, dim, d_graph, graph_degree, d_centroids, C, d_start_points, d_q, q, p, metric,
+                      d_ids, d_dists);
+    if (rc) return rc;
+    GL_CUDA(ctx, cudaMemcpyAsync(h_out_ids, d_ids, (size_t) q * p->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(h_out_dists, d_dists, (size_t) q * p->top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return GLIDE_OK;
+}
+
+// ---- large path ------------------------------------------------------------------------------
+int glide_select_segments(glide_ctx *ctx, const float *d_queries, uint32_t q, uint32_t dim, const float *d_centroids,
+                          uint32_t C, uint32_t min_segment_num, float boundary_factor, int metric, uint32_t *d_out) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_queries && d_centroids && d_out && dim > 0 && C >= 1, GLIDE_ERR_BAD_ARG, "select_segments: bad argument");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroid_size");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    SelectSegmentArgs a{d_queries, q, dim, d_centroids, C, min_segment_num, boundary_factor, metric, d_out};
+    Timed timer(ctx);
+    GL_CUDA(ctx, launch_select_segments(a, ctx->stream));
+    return timer.finish();
+}
+
+int glide_search_on_sub(glide_ctx *ctx, const float *d_data, uint32_t dim, const uint32_t *d_graph,
+                        uint32_t graph_degree, const uint32_t *d_map, uint32_t start_point, const float *d_queries,
+                        uint32_t q, const uint32_t *d_segment_ids, uint32_t segment_num, uint32_t segment_id,
+                        const glide_search_params *p, int metric, uint32_t *d_final_ids, float *d_final_dists) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_data && d_graph && d_map && d_queries && d_segment_ids && d_final_ids && d_final_dists,
+               GLIDE_ERR_BAD_ARG, "search_on_sub: null pointer");
+    int rc = check_params(ctx, p, graph_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, p->top_k >= 1 && p->top_k <= 128 && p->top_k <= p->beam, GLIDE_ERR_UNSUPPORTED, "Unsupported topk");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    SearchArgs a{};
+    a.data = d_data; a.graph = d_graph; a.degree = graph_degree; a.dim = dim;
+    a.queries = d_queries; a.Q = q; a.top_k = p->top_k; a.metric = metric; a.p = to_host(p);
+    a.C = 1; a.out_ids = d_final_ids; a.out_dists = d_final_dists;
+    a.segment_ids = d_segment_ids; a.segment_num = segment_num; a.segment_id = segment_id;
+    a.start_point = start_point; a.map = d_map;
+    a.counters = counters_or_null(ctx);
+    Timed timer(ctx);
+    GL_CUDA(ctx, launch_search(a, ctx->stream));
+    return timer.finish();
+}
+
+int glide_build_partition(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_knn,
+                          uint32_t knn_degree, uint32_t start_point, uint32_t graph_degree,
+                          const glide_search_params *p, float relaxant_factor, int metric, uint32_t *d_graph) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_data && d_knn && d_graph && num > 0 && dim > 0, GLIDE_ERR_BAD_ARG, "build_partition: bad argument");
+    int rc = check_params(ctx, p, knn_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, graph_degree >= 1 && graph_degree <= 256, GLIDE_ERR_UNSUPPORTED, "Unsupported graph_degree");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = ensure_ws(ctx, 3 * 256);
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    uint32_t *d_start = b.take<uint32_t>(1), *d_len = b.take<uint32_t>(1), *d_sp = b.take<uint32_t>(1);
+    const uint32_t zero = 0;
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_start, &zero, 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(d_len, &num, 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(d_sp, &start_point, 4, cudaMemcpyHostToDevice, ctx->stream));
+    BuildArgs a{};
+    a.mode = kModeBuild;
+    a.data = d_data; a.dim = dim; a.graph_in = d_knn; a.in_degree = knn_degree;
+    a.graph_out = d_graph; a.out_degree = graph_degree;
+    a.seg_start = d_start; a.seg_len = d_len; a.S = 1; a.start_points = d_sp; a.map = nullptr;
+    a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
+    a.counters = counters_or_null(ctx);
+    GL_CUDA(ctx, launch_build(a, ctx->stream));
+    return timer.finish();
+}
+
+int glide_refine_partition(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                           uint32_t graph_degree, uint32_t start_point, const glide_search_params *p,
+                           float relaxant_factor, int metric) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    uint32_t *d_sp = nullptr;
+    GL_CUDA(ctx, cudaMalloc(&d_sp, 4));
+    cudaError_t e = cudaMemcpy(d_sp, &start_point, 4, cudaMemcpyHostToDevice);
+    int rc = (e == cudaSuccess) ? refine_common(ctx, kModeRefineRow, d_data, num, dim, d_graph, graph_degree, nullptr, 1,
+                                                d_sp, p, relaxant_factor, metric)
+                                : fail(ctx, GLIDE_ERR_CUDA, "cudaMemcpy failed: %s", cudaGetErrorString(e));
+    cudaFree(d_sp);
+    return rc;
+}
+
+}  // extern "C"

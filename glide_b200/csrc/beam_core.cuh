@@ -1,0 +1,295 @@
+// Warp-per-query greedy beam search core, shared by query search, subgraph build,
+// boundary build, refinement and the large-path per-partition search.
+//
+// Behaviour (what is computed, in which order ties fall) follows the reference's
+// search loop, search_kernel.cuh:393-490 and graph_kernel.cuh:5-68. Layout does not:
+// the beam lives in registers for the whole search (NB pairs per lane, position
+// j = NB*lane + i), candidates pass through a small per-warp shared-memory strip,
+// and several warps (= several independent queries) share a CTA with no CTA-wide
+// barrier inside the loop.
+#pragma once
+
+#include "common.cuh"
+
+namespace glide {
+
+struct BeamParams {
+    uint32_t beam;            // multiple of 32, <= 32*NB
+    uint32_t max_iterations;
+    uint32_t min_iterations;
+    uint32_t hash_bit;
+    uint32_t hash_reset_interval;
+};
+
+// Per-warp shared memory strip. All offsets in 4-byte words; query first so that it
+// is 16-byte aligned.
+struct WarpStrip {
+    float *query;        // dim_pad floats
+    uint32_t *cand_id;   // 32*NC
+    float *cand_dist;    // 32*NC
+    uint32_t *visited;   // 1 << hash_bit
+    uint32_t *extra;     // mode-specific scratch (centroid list, pool, rows)
+};
+
+__host__ __device__ inline uint32_t dim_pad4(uint32_t dim) { return (dim + 3u) & ~3u; }
+
+__host__ __device__ inline uint32_t strip_words_base(uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
+    return dim_pad4(dim) + 2 * max_cand + (1u << hash_bit);
+}
+
+__device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
+    WarpStrip s;
+    s.query = reinterpret_cast<float *>(base);
+    s.cand_id = base + dim_pad4(dim);
+    s.cand_dist = reinterpret_cast<float *>(s.cand_id + max_cand);
+    s.visited = s.cand_id + 2 * max_cand;
+    s.extra = s.visited + (1u << hash_bit);
+    return s;
+}
+
+__device__ __forceinline__ void load_query(float *q_smem, const float *q_global, uint32_t dim) {
+    const uint32_t lane = lane_id();
+    if ((dim & 3u) == 0) {
+        const float4 *src = reinterpret_cast<const float4 *>(q_global);
+        float4 *dst = reinterpret_cast<float4 *>(q_smem);
+        for (uint32_t c = lane; c < (dim >> 2); c += 32) dst[c] = __ldg(src + c);
+    } else {
+        for (uint32_t i = lane; i < dim; i += 32) q_smem[i] = __ldg(q_global + i);
+    }
+    __syncwarp();
+}
+
+// Distances of the query to every valid candidate (cand_id[i] != kInvalid, and
+// != skip_id), written to cand_dist[i]; other slots get FLT_MAX. Candidates keep
+// their slot, which decides how ties fall in the sort that follows. Returns the
+// number of rows read by this warp (for the traffic counters).
+__device__ __forceinline__ uint32_t score_candidates(const WarpStrip &s, uint32_t count, uint32_t skip_id,
+                                                     const float *__restrict__ data, uint32_t dim, int metric) {
+    const uint32_t lane = lane_id();
+    const uint32_t team = lane / kTeam;
+    uint32_t rows = 0;
+    for (uint32_t base = 0; base < count; base += 32) {
+        const uint32_t i = base + lane;
+        const uint32_t id = (i < count) ? s.cand_id[i] : kInvalid;
+        const bool valid = (id != kInvalid) && (id != skip_id);
+        if (i < count && !valid) s.cand_dist[i] = FLT_MAX;
+        const uint32_t mask = __ballot_sync(kFullMask, valid);
+        const uint32_t n = __popc(mask);
+        rows += n;
+        for (uint32_t g = 0; g < n; g += kTeamsPerWarp) {
+            const uint32_t rank = g + team;
+            const bool active = rank < n;
+            const uint32_t src_lane = active ? __fns(mask, 0, rank + 1) : 0;
+            const uint32_t row_id = __shfl_sync(kFullMask, id, src_lane);
+            const float part = team_partial(s.query, data + (uint64_t) row_id * dim, dim, active);
+            const float sum = team_fold(part);
+            if (active && (lane & (kTeam - 1)) == 0) s.cand_dist[base + src_lane] = finish_metric(sum, metric);
+        }
+    }
+    __syncwarp();
+    return rows;
+}
+
+// search_kernel.cuh:362-391: read the parent's adjacency row, keep ids that are new
+// to the visited set (and are not own_id), then score them.
+__device__ __forceinline__ uint32_t expand_parent(const WarpStrip &s, uint32_t parent, uint32_t own_id,
+                                                  const uint32_t *__restrict__ graph, uint32_t degree,
+                                                  uint32_t hash_bit, const float *__restrict__ data,
+                                                  uint32_t dim, int metric) {
+    for (uint32_t i = lane_id(); i < degree; i += 32) {
+        uint32_t nb = kInvalid;
+        if (parent != kInvalid) nb = __ldg(graph + (uint64_t) parent * degree + i);
+        const uint32_t flag = (nb != kInvalid && nb != own_id) ? visited_insert(s.visited, hash_bit, nb) : 0;
+        s.cand_id[i] = flag ? nb : kInvalid;
+    }
+    __syncwarp();
+    return score_candidates(s, degree, kInvalid, data, dim, metric);
+}
+
+// search_kernel.cuh:336-360: seed from a start point's row. exclude_id keeps its
+// slot but gets distance FLT_MAX.
+__device__ __forceinline__ uint32_t seed_from_row(const WarpStrip &s, uint32_t start_point, uint32_t exclude_id,
+                                                  const uint32_t *__restrict__ graph, uint32_t degree,
+                                                  uint32_t hash_bit, const float *__restrict__ data,
+                                                  uint32_t dim, int metric) {
+    for (uint32_t i = lane_id(); i < degree; i += 32) {
+        const uint32_t index = __ldg(graph + (uint64_t) start_point * degree + i);
+        const uint32_t flag = (index != kInvalid) ? visited_insert(s.visited, hash_bit, index) : 0;
+        s.cand_id[i] = flag ? index : kInvalid;
+    }
+    __syncwarp();
+    return score_candidates(s, degree, exclude_id, data, dim, metric);
+}
+
+// search_kernel.cuh:258-269: distances to all centroids, sorted with the network of
+// width max_centroid (power of two >= C, >= 32); returns the nearest centroid's id.
+// scratch: 2 * max_centroid words.
+__device__ __forceinline__ uint32_t nearest_centroid(const float *q_smem, const float *__restrict__ centroids,
+                                                     uint32_t C, uint32_t max_centroid, uint32_t dim, int metric,
+                                                     uint32_t *scratch) {
+    const uint32_t lane = lane_id(), team = lane / kTeam;
+    const uint32_t n = max_centroid / 32;
+    float *ck = reinterpret_cast<float *>(scratch);
+    uint32_t *cv = scratch + max_centroid;
+    // element j starts in lane j%32, register j/32, i.e. network position n*(j%32) + j/32
+    for (uint32_t j = lane; j < max_centroid; j += 32) {
+        const uint32_t e = n * (j % 32) + j / 32;
+        ck[e] = FLT_MAX;
+        cv[e] = kInvalid;
+    }
+    __syncwarp();
+    for (uint32_t c0 = 0; c0 < C; c0 += kTeamsPerWarp) {
+        const uint32_t c = c0 + team;
+        const bool active = c < C;
+        const float part = team_partial(q_smem, centroids + (uint64_t) (active ? c : 0) * dim, dim, active);
+        const float sum = team_fold(part);
+        if (active && (lane & (kTeam - 1)) == 0) {
+            const uint32_t e = n * (c % 32) + c / 32;
+            ck[e] = finish_metric(sum, metric);
+            cv[e] = c;
+        }
+    }
+    __syncwarp();
+    warp_sort_smem(ck, cv, n);
+    return cv[0];
+}
+
+// The search loop proper. On return bk/bv hold the beam (ascending, position
+// j = NB*lane + i, ids still carrying the explored flag). Returns the number of
+// expansions; *rows_read accumulates data rows fetched.
+template<int NB, int NC>
+__device__ __forceinline__ uint32_t beam_loop(float (&bk)[NB], uint32_t (&bv)[NB], const WarpStrip &s,
+                                              const BeamParams &p, uint32_t own_id,
+                                              const uint32_t *__restrict__ graph, uint32_t degree,
+                                              const float *__restrict__ data, uint32_t dim, int metric,
+                                              uint32_t *rows_read) {
+    const uint32_t lane = lane_id();
+    constexpr uint32_t MAXB = 32u * NB;
+    uint32_t iter = 0;
+    bool terminate = false;
+    uint32_t rows = 0;
+    while (true) {
+        // -- sort the candidates (search_kernel.cuh:9-37) --
+        {
+            float ck[NC];
+            uint32_t cv[NC];
+#pragma unroll
+            for (int i = 0; i < NC; i++) {
+                const uint32_t j = lane + 32u * i;
+                ck[i] = (j < degree) ? s.cand_dist[j] : FLT_MAX;
+                cv[i] = (j < degree) ? s.cand_id[j] : kInvalid;
+            }
+            warp_sort<NC>(ck, cv);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < NC; i++) {
+                const uint32_t j = NC * lane + i;
+                if (j < degree && j < p.beam) {
+                    s.cand_dist[j] = ck[i];
+                    s.cand_id[j] = cv[i];
+                }
+            }
+            __syncwarp();
+        }
+        // -- merge into the beam (search_kernel.cuh:97-147) --
+        if (iter == 0) {
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                const bool take = (j < p.beam) && (j < degree);
+                bk[i] = take ? s.cand_dist[j] : FLT_MAX;
+                bv[i] = take ? s.cand_id[j] : kInvalid;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                const uint32_t k = MAXB - 1 - j;
+                if (k < p.beam && k < degree) {
+                    const float c = s.cand_dist[k];
+                    if (bk[i] > c) {
+                        bk[i] = c;
+                        bv[i] = s.cand_id[k];
+                    }
+                }
+            }
+            warp_merge_final<NB>(bk, bv);
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                if (j >= p.beam) {  // the reference keeps only `beam` slots between iterations
+                    bk[i] = FLT_MAX;
+                    bv[i] = kInvalid;
+                }
+            }
+        }
+        __syncwarp();
+        const bool reset = ((iter + 1) % p.hash_reset_interval) == 0;
+        if (reset) {
+            visited_clear(s.visited, p.hash_bit);
+            __syncwarp();
+        }
+        if (iter + 1 == p.max_iterations) break;
+        // -- first beam slot not yet expanded (search_kernel.cuh:292-325) --
+        uint32_t parent = kInvalid;
+        {
+            int first = -1;
+#pragma unroll
+            for (int i = NB - 1; i >= 0; i--)
+                if ((bv[i] & kExplored) == 0) first = i;
+            const uint32_t has = __ballot_sync(kFullMask, first >= 0);
+            if (has == 0) {
+                terminate = true;
+            } else {
+                const uint32_t src = __ffs(has) - 1;
+                uint32_t mine = kInvalid;
+                if (lane == src) {
+#pragma unroll
+                    for (int i = 0; i < NB; i++)
+                        if (i == first) {
+                            mine = bv[i];
+                            bv[i] |= kExplored;
+                        }
+                }
+                parent = __shfl_sync(kFullMask, mine, src);
+            }
+        }
+        if (reset) {  // search_kernel.cuh:327-334
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                if (j < p.beam) visited_insert(s.visited, p.hash_bit, bv[i] & kClean);
+            }
+            __syncwarp();
+        }
+        if (terminate && iter >= p.min_iterations) break;
+        rows += expand_parent(s, parent, own_id, graph, degree, p.hash_bit, data, dim, metric);
+        iter++;
+    }
+    if (rows_read) *rows_read += rows;
+    return iter;
+}
+
+}  // namespace glide
+
+// Binds run-time (beam, degree) size classes to template instances; the classes are the
+// reference's ladders (kernel_config.cuh:36-61): beam <=64/128/256/512, degree <=64/128/256.
+#define GLIDE_DISPATCH_NB_NC(FN, nb, nc, ...)                                              \
+    do {                                                                                   \
+        if (nc == 2) {                                                                     \
+            if (nb == 2) return FN<2, 2>(__VA_ARGS__);                                     \
+            if (nb == 4) return FN<4, 2>(__VA_ARGS__);                                     \
+            if (nb == 8) return FN<8, 2>(__VA_ARGS__);                                     \
+            return FN<16, 2>(__VA_ARGS__);                                                 \
+        } else if (nc == 4) {                                                              \
+            if (nb == 2) return FN<2, 4>(__VA_ARGS__);                                     \
+            if (nb == 4) return FN<4, 4>(__VA_ARGS__);                                     \
+            if (nb == 8) return FN<8, 4>(__VA_ARGS__);                                     \
+            return FN<16, 4>(__VA_ARGS__);                                                 \
+        } else {                                                                           \
+            if (nb == 2) return FN<2, 8>(__VA_ARGS__);                                     \
+            if (nb == 4) return FN<4, 8>(__VA_ARGS__);                                     \
+            if (nb == 8) return FN<8, 8>(__VA_ARGS__);                                     \
+            return FN<16, 8>(__VA_ARGS__);                                                 \
+        }                                                                                  \
+    } while (0)

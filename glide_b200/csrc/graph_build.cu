@@ -1,0 +1,558 @@
+// Graph construction kernels: per-point beam search over the kNN subgraph +
+// occlusion pruning (reference build_kernel, graph_kernel.cuh:249-316), boundary
+// partition build + merge (:160-247, :318-376), reverse-edge insertion (:378-453) and
+// refinement of rows that still have holes (:455-673). Large-path variants
+// (:675-821) are the same kernels with one segment and no id map.
+//
+// One warp owns one point from search to row write; the beam stays in registers and
+// is spilled to the warp's shared strip only for pruning.
+#include "beam_core.cuh"
+#include "kernels.h"
+#include "scan.cuh"
+
+namespace glide {
+
+namespace {
+
+struct BuildDev {
+    BuildArgs a;
+    uint32_t max_centroid;
+    uint32_t strip_words;
+    uint32_t max_beam;    // 32*NB
+    uint32_t max_degree;  // round_up32(out_degree)
+};
+
+// Extra strip layout (words): pool_id[max_beam] pool_dist[max_beam] flags[max_beam]
+// picks[max_degree] row[max_degree] bits[max_degree/32]; the centroid scratch
+// (2*max_centroid) aliases the start of it (used before the pool exists).
+struct PruneStrip {
+    uint32_t *pool_id;
+    float *pool_dist;
+    uint32_t *flags;
+    uint32_t *picks;
+    uint32_t *row;
+    uint32_t *bits;
+};
+
+__host__ __device__ inline uint32_t prune_strip_words(uint32_t max_beam, uint32_t max_degree) {
+    return 3 * max_beam + 2 * max_degree + max_degree / 32;
+}
+
+__device__ __forceinline__ PruneStrip make_prune_strip(uint32_t *extra, uint32_t max_beam, uint32_t max_degree) {
+    PruneStrip ps;
+    ps.pool_id = extra;
+    ps.pool_dist = reinterpret_cast<float *>(extra + max_beam);
+    ps.flags = extra + 2 * max_beam;
+    ps.picks = extra + 3 * max_beam;
+    ps.row = ps.picks + max_degree;
+    ps.bits = ps.row + max_degree;
+    return ps;
+}
+
+// Spill the beam into the pool, flags cleared (graph_kernel.cuh:65-67), dropping
+// unfilled slots: the reference would dereference them as data rows
+// (graph_kernel.cuh:92,104); with a full beam this is the identity. Returns pool size.
+template<int NB>
+__device__ __forceinline__ uint32_t spill_pool(const float (&bk)[NB], const uint32_t (&bv)[NB], uint32_t beam,
+                                               const PruneStrip &ps) {
+    const uint32_t lane = lane_id();
+#pragma unroll
+    for (int i = 0; i < NB; i++) {
+        const uint32_t j = NB * lane + i;
+        if (j < beam) {
+            ps.pool_id[j] = bv[i] & kClean;
+            ps.pool_dist[j] = bk[i];
+        }
+    }
+    __syncwarp();
+    uint32_t next = 0;
+    for (uint32_t base = 0; base < beam; base += 32) {
+        const uint32_t i = base + lane;
+        const uint32_t id = (i < beam) ? ps.pool_id[i] : kPadClean;
+        const float dist = (i < beam) ? ps.pool_dist[i] : FLT_MAX;
+        const bool keep = (id != kPadClean);
+        const uint32_t mask = __ballot_sync(kFullMask, keep);
+        __syncwarp();
+        if (keep) {
+            const uint32_t pos = next + __popc(mask & ((1u << lane) - 1));
+            ps.pool_id[pos] = id;
+            ps.pool_dist[pos] = dist;
+        }
+        next += __popc(mask);
+        __syncwarp();
+    }
+    return next;
+}
+
+// For pool entries [from, P): flags[i] = !(alpha * d(center, pool[i]) < pool_dist[i]),
+// the occlusion test of graph_kernel.cuh:103-114. The centre row is staged in `q`.
+__device__ __forceinline__ uint32_t occlusion_flags(const PruneStrip &ps, uint32_t from, uint32_t P, float *q,
+                                                    const float *__restrict__ data, uint32_t center, uint32_t dim,
+                                                    float alpha, int metric) {
+    const uint32_t lane = lane_id(), team = lane / kTeam;
+    load_query(q, data + (uint64_t) center * dim, dim);
+    uint32_t rows = 0;
+    for (uint32_t i0 = from; i0 < P; i0 += kTeamsPerWarp) {
+        const uint32_t i = i0 + team;
+        const bool active = i < P;
+        const uint32_t id = active ? ps.pool_id[i] : 0;
+        const float part = team_partial(q, data + (uint64_t) id * dim, dim, active);
+        const float sum = team_fold(part);
+        if (active && (lane & (kTeam - 1)) == 0) {
+            const float d = finish_metric(sum, metric);
+            ps.flags[i] = (alpha * d < ps.pool_dist[i]) ? 0u : 1u;
+        }
+    }
+    rows += (P > from) ? (P - from) : 0;
+    __syncwarp();
+    return rows;
+}
+
+// Stable compaction of pool entries [from, P) whose flag is set; returns new size.
+__device__ __forceinline__ uint32_t compact_pool(const PruneStrip &ps, uint32_t from, uint32_t P) {
+    const uint32_t lane = lane_id();
+    uint32_t next = 0;
+    for (uint32_t base = from & ~31u; base < P; base += 32) {
+        const uint32_t i = base + lane;
+        const bool keep = (i >= from) && (i < P) && (ps.flags[i] != 0);
+        const uint32_t id = keep ? ps.pool_id[i] : 0;
+        const float dist = keep ? ps.pool_dist[i] : 0.0f;
+        const uint32_t mask = __ballot_sync(kFullMask, keep);
+        __syncwarp();
+        if (keep) {
+            const uint32_t pos = next + __popc(mask & ((1u << lane) - 1));
+            ps.pool_id[pos] = id;
+            ps.pool_dist[pos] = dist;
+        }
+        next += __popc(mask);
+        __syncwarp();
+    }
+    return next;
+}
+
+// graph_kernel.cuh:70-143. picks[0..degree) receives pool-relative ids, unused slots
+// kInvalid. Returns rows read.
+__device__ __forceinline__ uint32_t sync_prune(const PruneStrip &ps, uint32_t P, float *q,
+                                               const float *__restrict__ data, uint32_t dim, uint32_t degree,
+                                               uint32_t max_degree, float alpha, int metric) {
+    const uint32_t lane = lane_id();
+    for (uint32_t i = lane; i < max_degree; i += 32) ps.picks[i] = kInvalid;
+    __syncwarp();
+    uint32_t nsize = 0, rows = 0;
+    while (nsize < degree && P > 0) {
+        const uint32_t center = ps.pool_id[0];
+        if (lane == 0) ps.picks[nsize] = center;
+        nsize++;
+        if (lane == 0) ps.flags[0] = 0;
+        rows += occlusion_flags(ps, 1, P, q, data, center, dim, alpha, metric);
+        P = compact_pool(ps, 0, P);
+    }
+    __syncwarp();
+    return rows;
+}
+
+// graph_kernel.cuh:455-578: like sync_prune, but the next centre is the first pool
+// entry that is neither the point itself nor already in its row, only entries from
+// that position on are tested, and at most `need` picks are made.
+__device__ __forceinline__ uint32_t sync_prune_refine(const PruneStrip &ps, uint32_t P, float *q,
+                                                      const float *__restrict__ data, uint32_t dim,
+                                                      uint32_t point_id, uint32_t degree, uint32_t max_degree,
+                                                      uint32_t need, float alpha, int metric) {
+    const uint32_t lane = lane_id();
+    for (uint32_t i = lane; i < max_degree; i += 32) ps.picks[i] = kInvalid;
+    __syncwarp();
+    uint32_t nsize = 0, rows = 0;
+    while (nsize < need && P > 0) {
+        // select_point (:455-492)
+        uint32_t pos = kInvalid;
+        for (uint32_t base = 0; base < P && pos == kInvalid; base += 32) {
+            const uint32_t i = base + lane;
+            bool ok = false;
+            if (i < P) {
+                const uint32_t id = ps.pool_id[i];
+                if (id != kInvalid && id != point_id) {
+                    ok = true;
+                    for (uint32_t j = 0; j < degree; j++)
+                        if (ps.row[j] == id) { ok = false; break; }
+                }
+            }
+            const uint32_t mask = __ballot_sync(kFullMask, ok);
+            if (mask) pos = base + __ffs(mask) - 1;
+        }
+        if (pos == kInvalid) break;
+        const uint32_t center = ps.pool_id[pos];
+        if (lane == 0) ps.picks[nsize] = center;
+        nsize++;
+        rows += occlusion_flags(ps, pos, P, q, data, center, dim, alpha, metric);
+        P = compact_pool(ps, pos, P);
+    }
+    __syncwarp();
+    return rows;
+}
+
+// map_to_graph_boundary, graph_kernel.cuh:160-247. ps.picks holds the pruned result
+// in reorder ids, ps.row the existing row. Writes the merged row to `out`.
+__device__ __forceinline__ void boundary_merge(const PruneStrip &ps, const uint32_t *__restrict__ map,
+                                               uint32_t degree, uint32_t max_degree, uint32_t *out) {
+    const uint32_t lane = lane_id();
+    for (uint32_t i = lane; i < max_degree / 32; i += 32) ps.bits[i] = 0;
+    __syncwarp();
+    uint32_t valid_num = 0, rep_num = 0;
+    for (uint32_t base = 0; base < max_degree; base += 32) {
+        const uint32_t i = base + lane;
+        const bool valid = (i < degree) && (ps.picks[i] != kInvalid);
+        const uint32_t index = valid ? __ldg(map + ps.picks[i]) : kInvalid;
+        bool non_rep = true;
+        uint32_t j = 0;
+        if (valid) {
+            for (j = 0; j < degree; j++) {
+                const uint32_t e = ps.row[j];
+                if (e == kInvalid) break;
+                if (e == index) { non_rep = false; break; }
+            }
+        }
+        const uint32_t m1 = __ballot_sync(kFullMask, valid && non_rep);
+        const uint32_t m2 = __ballot_sync(kFullMask, valid && !non_rep);
+        __syncwarp();
+        if (valid && non_rep) ps.picks[valid_num + __popc(m1 & ((1u << lane) - 1))] = index;
+        if (valid && !non_rep) atomicOr(&ps.bits[j / 32], 1u << (j % 32));
+        valid_num += __popc(m1);
+        rep_num += __popc(m2);
+        __syncwarp();
+    }
+    if (rep_num >= degree / 2) {
+        uint32_t pos_num = 0;
+        for (uint32_t base = 0; base < max_degree && pos_num < valid_num; base += 32) {
+            const uint32_t i = base + lane;
+            const bool empty = (i < degree) && (ps.row[i] == kInvalid);
+            const uint32_t mask = __ballot_sync(kFullMask, empty);
+            if (empty) {
+                const uint32_t pos = pos_num + __popc(mask & ((1u << lane) - 1));
+                if (pos < valid_num) out[i] = ps.picks[pos];
+            }
+            pos_num += __popc(mask);
+        }
+    } else {
+        const uint32_t max_need = degree / 2 - rep_num;
+        const uint32_t need = valid_num < max_need ? valid_num : max_need;
+        uint32_t pos_num = 0;
+        for (uint32_t base = 0; base < max_degree && pos_num < need; base += 32) {
+            const uint32_t gi = max_degree - 1 - (base + lane);
+            const bool in_range = gi < degree;
+            const bool rep = in_range && ((ps.bits[gi / 32] >> (gi % 32)) & 1u);
+            const bool empty = in_range && (ps.row[gi] == kInvalid);
+            const bool ok = in_range && (empty || !rep);
+            const uint32_t mask = __ballot_sync(kFullMask, ok);
+            if (ok) {
+                const uint32_t pos = pos_num + __popc(mask & ((1u << lane) - 1));
+                if (pos < need) out[gi] = ps.picks[pos];
+            }
+            pos_num += __popc(mask);
+        }
+    }
+}
+
+template<int NB, int NC>
+__global__ void __launch_bounds__(256) build_kernel(const BuildDev d) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    const BuildArgs &a = d.a;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const uint32_t t = blockIdx.x * warps_per_cta + warp;
+    if (t >= a.count) return;
+    const uint32_t point = a.first + t;
+    const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
+    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, 32u * NC, p.hash_bit);
+    PruneStrip ps = make_prune_strip(s.extra, d.max_beam, d.max_degree);
+    const uint32_t degree = a.out_degree;
+
+    uint32_t rows = 0, prune_rows = 0, iters = 0;
+    float bk[NB];
+    uint32_t bv[NB];
+
+    if (a.mode == kModeBuild || a.mode == kModeBoundary) {
+        uint32_t seg = a.fixed_segment;
+        if (a.mode == kModeBuild) {  // graph_kernel.cuh:276-282
+            for (seg = 0; seg < a.S; seg++)
+                if (point < a.seg_start[seg] + a.seg_len[seg]) break;
+            if (seg == a.S) return;
+        }
+        const uint32_t seg_start = a.seg_start[seg];
+        const float *pdata = a.data + (uint64_t) seg_start * a.dim;
+        const uint32_t *pknn = a.graph_in + (uint64_t) seg_start * a.in_degree;
+        load_query(s.query, a.data + (uint64_t) point * a.dim, a.dim);
+        visited_clear(s.visited, p.hash_bit);
+        __syncwarp();
+        // The seed step compares the row's partition-local ids with the point's reorder
+        // id, as the reference does (graph_kernel.cuh:295-298).
+        rows += seed_from_row(s, a.start_points[seg], point, pknn, a.in_degree, p.hash_bit, pdata, a.dim, a.metric);
+        iters = beam_loop<NB, NC>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows);
+        const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
+        prune_rows = sync_prune(ps, P, s.query, pdata, a.dim, degree, d.max_degree, a.alpha, a.metric);
+        const uint32_t orig = a.map ? a.map[point] : point;
+        uint32_t *out = a.graph_out + (uint64_t) orig * degree;
+        if (a.mode == kModeBuild) {  // map_to_graph_sub / map_to_graph (:145-158)
+            for (uint32_t i = lane; i < degree; i += 32) {
+                const uint32_t id = ps.picks[i];
+                out[i] = (id == kInvalid) ? kInvalid : (a.map ? a.map[id + seg_start] : id + seg_start);
+            }
+        } else {
+            for (uint32_t i = lane; i < d.max_degree; i += 32) {
+                ps.row[i] = (i < degree) ? out[i] : kInvalid;
+                if (ps.picks[i] != kInvalid) ps.picks[i] += seg_start;
+            }
+            __syncwarp();
+            boundary_merge(ps, a.map, degree, d.max_degree, out);
+        }
+    } else {
+        // refine (graph_kernel.cuh:580-673, :730-821). Searches read graph_in, rows are
+        // written to graph_out; the caller passes a snapshot as graph_in so that results
+        // do not depend on the order in which points finish.
+        const uint32_t *in_row = a.graph_in + (uint64_t) point * degree;
+        uint32_t *out = a.graph_out + (uint64_t) point * degree;
+        uint32_t need = 0;
+        for (uint32_t base = 0; base < d.max_degree; base += 32) {
+            const uint32_t i = base + lane;
+            const uint32_t e = (i < degree) ? __ldg(in_row + i) : kInvalid;
+            ps.row[i] = e;
+            need += __popc(__ballot_sync(kFullMask, (i < degree) && (e == kInvalid)));
+        }
+        __syncwarp();
+        if (need == 0) {
+            if (out != in_row)
+                for (uint32_t i = lane; i < degree; i += 32) out[i] = ps.row[i];
+            return;
+        }
+        load_query(s.query, a.data + (uint64_t) point * a.dim, a.dim);
+        visited_clear(s.visited, p.hash_bit);
+        __syncwarp();
+        if (a.mode == kModeRefine) {
+            // the centroid scratch sits past the row copy so that it survives
+            uint32_t *scratch = s.extra + prune_strip_words(d.max_beam, d.max_degree);
+            const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, scratch);
+            rows += seed_from_row(s, a.start_points[c], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
+                                  a.metric);
+        } else {
+            rows += seed_from_row(s, a.start_points[0], point, a.graph_in, degree, p.hash_bit, a.data, a.dim,
+                                  a.metric);
+        }
+        iters = beam_loop<NB, NC>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows);
+        const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
+        prune_rows = sync_prune_refine(ps, P, s.query, a.data, a.dim, point, degree, d.max_degree, need, a.alpha,
+                                       a.metric);
+        uint32_t pos_num = 0;  // :660-671: holes, front to back
+        for (uint32_t base = 0; base < d.max_degree; base += 32) {
+            const uint32_t i = base + lane;
+            const bool hole = (i < degree) && (ps.row[i] == kInvalid);
+            const uint32_t mask = __ballot_sync(kFullMask, hole);
+            if (i < degree) out[i] = hole ? ps.picks[pos_num + __popc(mask & ((1u << lane) - 1))] : ps.row[i];
+            pos_num += __popc(mask);
+        }
+    }
+    if (a.counters && lane == 0) {
+        atomicAdd(a.counters + 0, (unsigned long long) rows);
+        atomicAdd(a.counters + 1, (unsigned long long) iters);
+        atomicAdd(a.counters + 2, (unsigned long long) prune_rows);
+    }
+}
+
+uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
+    uint32_t m = lo;
+    while (m < x) m <<= 1;
+    return m;
+}
+
+template<int NB, int NC>
+cudaError_t launch_build_t(const BuildDev &d, uint32_t warps_per_cta, size_t smem_bytes, cudaStream_t stream) {
+    auto kernel = build_kernel<NB, NC>;
+    if (smem_bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+        if (e != cudaSuccess) return e;
+    }
+    const uint32_t grid = (d.a.count + warps_per_cta - 1) / warps_per_cta;
+    kernel<<<grid, warps_per_cta * 32, smem_bytes, stream>>>(d);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Reverse edges (graph_kernel.cuh:378-453). The reference appends with atomics from
+// `degree` concurrent launches, so which sources a crowded node keeps is arbitrary.
+// Here every node keeps the `degree` smallest (rank, source) pairs, i.e. the outcome of
+// the reference when its launches run one after another in ascending thread order:
+// edges are bucketed by destination (count, scan, fill) and each bucket is reduced by
+// one warp with a bitonic selection, so the result does not depend on arrival order.
+// ---------------------------------------------------------------------------
+__global__ void reverse_count_kernel(const uint32_t *__restrict__ graph, uint32_t num, uint32_t degree,
+                                     uint32_t *counts) {
+    const uint64_t e = (uint64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (uint64_t) num * degree) return;
+    const uint32_t dst = graph[e];
+    if (dst < num) atomicAdd(counts + dst, 1u);
+}
+
+__global__ void reverse_fill_kernel(const uint32_t *__restrict__ graph, uint32_t num, uint32_t degree,
+                                    const uint32_t *__restrict__ offsets, uint32_t *cursor,
+                                    unsigned long long *edges) {
+    const uint64_t e = (uint64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (uint64_t) num * degree) return;
+    const uint32_t dst = graph[e];
+    if (dst >= num) return;
+    const uint32_t src = (uint32_t) (e / degree), rank = (uint32_t) (e % degree);
+    const uint32_t slot = atomicAdd(cursor + dst, 1u);
+    edges[offsets[dst] + slot] = ((unsigned long long) rank << 32) | src;
+}
+
+// 64-bit compare-exchange network over the 32 lanes of a warp (one key per lane).
+__device__ __forceinline__ unsigned long long warp_sort_u64(unsigned long long key) {
+    const uint32_t lane = lane_id();
+#pragma unroll
+    for (uint32_t size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+        for (uint32_t stride = size >> 1; stride >= 1; stride >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(kFullMask, key, stride);
+            const bool asc = (size == 32) || ((lane & size) == 0);
+            const bool lower = (lane & stride) == 0;
+            const bool keep_small = (lower == asc);
+            if (keep_small ? (other < key) : (other > key)) key = other;
+        }
+    }
+    return key;
+}
+
+__device__ __forceinline__ uint32_t lower_bound_u64(const unsigned long long *a, uint32_t n, unsigned long long key) {
+    uint32_t lo = 0, hi = n;
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (a[mid] < key) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+// One warp per node: keep the smallest (rank, src) keys among incoming edges whose
+// source is not already in the node's row ("have" test, :395-405), as many as the row
+// has holes, then fill the holes front to back in that order (insert_reverse_kernel,
+// :416-453). Chunks of 32 incoming keys are sorted in registers and merged into a
+// sorted shared list by rank counting, so no step depends on arrival order.
+__global__ void __launch_bounds__(256) reverse_insert_kernel(uint32_t *graph, uint32_t num, uint32_t degree,
+                                                             const uint32_t *__restrict__ offsets,
+                                                             const unsigned long long *__restrict__ edges,
+                                                             uint32_t max_degree) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const uint32_t node = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (node >= num) return;
+    // strip (words): keepA[2*max_degree] keepB[2*max_degree] chunk[64] row[max_degree]
+    uint32_t *strip = smem + (size_t) warp * (5 * max_degree + 64);
+    unsigned long long *cur = reinterpret_cast<unsigned long long *>(strip);
+    unsigned long long *nxt = cur + max_degree;
+    unsigned long long *chunk = nxt + max_degree;
+    uint32_t *row = strip + 4 * max_degree + 64;
+    uint32_t holes = 0;
+    for (uint32_t base = 0; base < max_degree; base += 32) {
+        const uint32_t i = base + lane;
+        const uint32_t e = (i < degree) ? graph[(uint64_t) node * degree + i] : kInvalid;
+        row[i] = e;
+        holes += __popc(__ballot_sync(kFullMask, (i < degree) && (e == kInvalid)));
+    }
+    __syncwarp();
+    const uint32_t begin = offsets[node], cnt = offsets[node + 1] - begin;
+    if (holes == 0 || cnt == 0) return;
+    const unsigned long long *in = edges + begin;
+    const uint32_t cap = holes;  // holes <= degree, the reference's list capacity
+    uint32_t kept = 0;
+    for (uint32_t base = 0; base < cnt; base += 32) {
+        const uint32_t i = base + lane;
+        unsigned long long key = ~0ull;
+        if (i < cnt) {
+            key = in[i];
+            const uint32_t src = (uint32_t) key;
+            for (uint32_t j = 0; j < degree; j++)
+                if (row[j] == src) { key = ~0ull; break; }
+            if (kept == cap && key != ~0ull && key > cur[cap - 1]) key = ~0ull;  // cannot enter
+        }
+        const uint32_t any = __ballot_sync(kFullMask, key != ~0ull);
+        if (any == 0) continue;
+        const uint32_t n_valid = __popc(any);
+        key = warp_sort_u64(key);  // valid keys first, ascending
+        chunk[lane] = key;
+        __syncwarp();
+        if (lane < n_valid) {
+            const uint32_t pos = lane + lower_bound_u64(cur, kept, key);
+            if (pos < cap) nxt[pos] = key;
+        }
+        for (uint32_t k = lane; k < kept; k += 32) {
+            const unsigned long long kk = cur[k];
+            const uint32_t pos = k + lower_bound_u64(chunk, n_valid, kk);
+            if (pos < cap) nxt[pos] = kk;
+        }
+        __syncwarp();
+        kept = (kept + n_valid < cap) ? kept + n_valid : cap;
+        unsigned long long *t = cur; cur = nxt; nxt = t;
+    }
+    uint32_t pos_num = 0;
+    for (uint32_t base = 0; base < max_degree && pos_num < kept; base += 32) {
+        const uint32_t i = base + lane;
+        const bool hole = (i < degree) && (row[i] == kInvalid);
+        const uint32_t mask = __ballot_sync(kFullMask, hole);
+        if (hole) {
+            const uint32_t pos = pos_num + __popc(mask & ((1u << lane) - 1));
+            if (pos < kept) graph[(uint64_t) node * degree + i] = (uint32_t) cur[pos];
+        }
+        pos_num += __popc(mask);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
+    if (a.count == 0) return cudaSuccess;
+    BuildDev d;
+    d.a = a;
+    d.max_centroid = pow2_at_least(a.C ? a.C : 1, 32);
+    const uint32_t max_beam = a.p.beam <= 64 ? 64 : (a.p.beam <= 128 ? 128 : (a.p.beam <= 256 ? 256 : 512));
+    const uint32_t max_cand = a.in_degree <= 64 ? 64 : (a.in_degree <= 128 ? 128 : 256);
+    d.max_beam = max_beam;
+    d.max_degree = round_up32(a.out_degree);
+    uint32_t extra = prune_strip_words(max_beam, d.max_degree);
+    if (a.mode == kModeRefine) extra += 2 * d.max_centroid;
+    d.strip_words = (strip_words_base(a.dim, max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
+    const size_t strip_bytes = (size_t) d.strip_words * 4;
+    uint32_t warps = 8;
+    while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;
+    if (strip_bytes * warps > 200 * 1024) return cudaErrorInvalidValue;
+    const int nb = max_beam / 32, nc = max_cand / 32;
+    GLIDE_DISPATCH_NB_NC(launch_build_t, nb, nc, d, warps, strip_bytes * warps, stream);
+}
+
+}  // namespace glide
+
+namespace glide {
+
+size_t reverse_scan_tmp_bytes(uint32_t num) { return scan_tmp_bytes(num); }
+
+cudaError_t launch_reverse(const ReverseArgs &a, cudaStream_t stream) {
+    if (a.num == 0) return cudaSuccess;
+    const uint64_t edges = (uint64_t) a.num * a.degree;
+    const uint32_t threads = 256;
+    const uint32_t blocks = (uint32_t) ((edges + threads - 1) / threads);
+    cudaError_t e = cudaMemsetAsync(a.counts, 0, (size_t) (a.num + 1) * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+    reverse_count_kernel<<<blocks, threads, 0, stream>>>(a.graph, a.num, a.degree, a.counts);
+    e = exclusive_scan_u32(a.counts, a.num, a.offsets, a.scan_tmp, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(a.counts, 0, (size_t) (a.num + 1) * sizeof(uint32_t), stream);  // reused as fill cursor
+    if (e != cudaSuccess) return e;
+    reverse_fill_kernel<<<blocks, threads, 0, stream>>>(a.graph, a.num, a.degree, a.offsets, a.counts, a.edges);
+    const uint32_t max_degree = round_up32(a.degree);
+    const uint32_t warps = 8;
+    const size_t smem_bytes = (size_t) warps * (5 * max_degree + 64) * 4;
+    if (smem_bytes > 48 * 1024) {
+        e = cudaFuncSetAttribute(reverse_insert_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+        if (e != cudaSuccess) return e;
+    }
+    reverse_insert_kernel<<<(a.num + warps - 1) / warps, warps * 32, smem_bytes, stream>>>(
+        a.graph, a.num, a.degree, a.offsets, a.edges, max_degree);
+    return cudaGetLastError();
+}
+
+}  // namespace glide

@@ -1,0 +1,151 @@
+// Internal launcher interface between the C-ABI layer (api.cu) and the kernel
+// translation units. Every launcher enqueues on `stream`, returns cudaError_t from
+// the launch (no synchronisation) and never allocates.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace glide {
+
+struct BeamParamsHost {
+    uint32_t beam, max_iterations, min_iterations, hash_bit, hash_reset_interval;
+};
+
+// ---- search.cu -----------------------------------------------------------
+struct SearchArgs {
+    const float *data;           // n x dim
+    const uint32_t *graph;       // n x degree
+    uint32_t degree, dim;
+    const float *queries;        // Q x dim
+    uint32_t Q, top_k;
+    int metric;
+    BeamParamsHost p;
+    // routed (small path): nearest centroid -> start point
+    const float *centroids;      // C x dim
+    uint32_t C;
+    const uint32_t *start_points;
+    uint32_t *out_ids;           // Q x top_k
+    float *out_dists;            // Q x top_k
+    // per-partition (large path): only queries routed to segment_id run
+    const uint32_t *segment_ids; // Q x segment_num, or nullptr for the small path
+    uint32_t segment_num, segment_id, start_point;
+    const uint32_t *map;         // local id -> global id (large path)
+    unsigned long long *counters;  // [0] data rows read, [1] expansions; may be nullptr
+};
+cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream);
+
+struct SelectSegmentArgs {
+    const float *queries;
+    uint32_t Q, dim;
+    const float *centroids;
+    uint32_t C, min_segment_num;
+    float boundary_factor;
+    int metric;
+    uint32_t *out;  // Q x C
+};
+cudaError_t launch_select_segments(const SelectSegmentArgs &a, cudaStream_t stream);
+
+// ---- graph_build.cu ------------------------------------------------------
+enum BuildMode : int { kModeBuild = 0, kModeBoundary = 1, kModeRefine = 2, kModeRefineRow = 3 };
+
+struct BuildArgs {
+    int mode;
+    const float *data;
+    uint32_t dim;
+    const uint32_t *graph_in;  // kNN graph (build/boundary) or the merged graph snapshot (refine)
+    uint32_t in_degree;
+    uint32_t *graph_out;
+    uint32_t out_degree;
+    const uint32_t *seg_start, *seg_len;  // device, S entries (build/boundary)
+    uint32_t S;
+    const uint32_t *start_points;  // build: partition-local per segment; refine: per centroid, graph ids
+    const uint32_t *map;           // reorder id -> original id; nullptr = identity
+    const float *centroids;        // refine
+    uint32_t C;
+    uint32_t first, count;         // point range handled by this launch
+    uint32_t fixed_segment;        // boundary: the segment every point belongs to
+    float alpha;
+    int metric;
+    BeamParamsHost p;
+    unsigned long long *counters;  // [0] rows read in search, [1] expansions, [2] rows read in pruning
+};
+cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream);
+
+struct ReverseArgs {
+    uint32_t *graph;   // num x degree, updated in place
+    uint32_t num, degree;
+    // scratch: counts[num+1], offsets[num+1] u32; edges: u64 [num*degree]
+    uint32_t *counts;
+    uint32_t *offsets;
+    unsigned long long *edges;
+    void *scan_tmp;       // >= reverse_scan_tmp_bytes(num)
+};
+size_t reverse_scan_tmp_bytes(uint32_t num);
+cudaError_t launch_reverse(const ReverseArgs &a, cudaStream_t stream);
+
+// ---- partition.cu --------------------------------------------------------
+cudaError_t launch_gather_rows(const float *data, const uint32_t *ids, uint32_t count, uint32_t dim, float *out,
+                               cudaStream_t stream);
+struct AssignArgs {
+    const float *data;
+    uint32_t n, dim;
+    const float *centroids;
+    uint32_t C;
+    float boundary_factor;  // < 0: no boundary test (large path, k-means)
+    int metric;
+    uint32_t *nearest;      // n
+    uint32_t *is_boundary;  // n: 0 for a boundary point, 0xffffffff otherwise (a slot key); may be nullptr
+};
+cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream);
+
+// Deterministic slots: slot[p] = number of q < p with key[q] == key[p] (keys < K,
+// key == 0xffffffff means "none" and yields slot 0xffffffff); totals[K] = counts.
+// scratch: block_hist words = slot_scratch_words(n, K).
+size_t slot_scratch_words(uint32_t n, uint32_t K);
+cudaError_t launch_slots(const uint32_t *key, uint32_t n, uint32_t K, uint32_t *slot, uint32_t *totals,
+                         uint32_t *scratch, cudaStream_t stream);
+cudaError_t launch_reorder(const float *data, uint32_t n, uint32_t dim, const uint32_t *seg_index,
+                           const uint32_t *seg_start_dev, float *reorder_data, uint32_t *map, cudaStream_t stream);
+cudaError_t launch_pack_seg_index(const uint32_t *nearest, const uint32_t *slot, const uint32_t *bslot, uint32_t n,
+                                  uint32_t *seg_index, cudaStream_t stream);
+// k-means centroid update: members of cluster c are member_ids[off[c] .. off[c]+cnt[c]) in ascending row order.
+cudaError_t launch_centroid_update(const float *sample, uint32_t dim, const uint32_t *member_ids,
+                                   const uint32_t *off, const uint32_t *cnt, uint32_t C, float *centroids,
+                                   cudaStream_t stream);
+cudaError_t launch_scatter_members(const uint32_t *label, const uint32_t *slot, const uint32_t *off, uint32_t n,
+                                   uint32_t *member_ids, cudaStream_t stream);
+cudaError_t launch_count_changed(const uint32_t *a, const uint32_t *b, uint32_t n, uint32_t *count,
+                                 cudaStream_t stream);
+
+// ---- bruteforce.cu -------------------------------------------------------
+size_t bruteforce_scratch_bytes(uint32_t Q, uint32_t k, uint32_t splits);
+uint32_t bruteforce_default_splits(uint32_t n, uint32_t Q);
+cudaError_t launch_bruteforce(const float *base, uint32_t n, const float *queries, uint32_t Q, uint32_t dim,
+                              uint32_t k, int metric, uint32_t splits, void *scratch, uint32_t *out_ids,
+                              float *out_dists, cudaStream_t stream);
+
+// ---- nn_descent.cu -------------------------------------------------------
+struct NndArgs {
+    const float *data;   // rows x dim (reorder space)
+    uint32_t rows, dim;
+    const uint32_t *seg_start, *seg_len;  // device, S entries
+    uint32_t S;
+    uint32_t K;          // list width (multiple of 32, <= 64)
+    uint32_t sample;     // new/old samples per direction (<= 32)
+    uint32_t max_iterations;
+    float termination_threshold;
+    uint64_t seed;
+    int metric;
+    // state (device): lists keys u64 [rows*K]; proposal slots u64 [rows*P]; samples
+    void *workspace;
+    size_t workspace_bytes;
+    int32_t *out_knn;    // rows x out_degree, partition-local ids
+    uint32_t out_degree;
+    uint32_t *iterations_run;  // host pointer, may be nullptr
+    float *stage_ms;           // host pointer [3] (sample, join, merge), may be nullptr
+};
+size_t nnd_workspace_bytes(uint32_t rows, uint32_t K, uint32_t sample);
+cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream);
+
+}  // namespace glide

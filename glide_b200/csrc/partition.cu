@@ -1,0 +1,257 @@
+// Partition stage kernels: sample gather (reference sample_kernel,
+// partition_kernel.cuh:7-20), nearest-centroid assignment with the boundary test
+// (define_partition_kernel, :22-66), order-independent slot assignment replacing the
+// reference's atomics (:57-60), the permuted copy (reorder_kernel, :68-100) and the
+// Lloyd centroid update used in place of cuVS kmeans::fit (partition.cuh:48-54).
+#include "beam_core.cuh"
+#include "kernels.h"
+
+namespace glide {
+
+namespace {
+
+__global__ void gather_rows_kernel(const float *__restrict__ data, const uint32_t *__restrict__ ids, uint32_t count,
+                                   uint32_t dim, float *__restrict__ out) {
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = lane_id();
+    if (warp >= count) return;
+    const float *src = data + (uint64_t) ids[warp] * dim;
+    float *dst = out + (uint64_t) warp * dim;
+    if ((dim & 3u) == 0) {
+        for (uint32_t c = lane; c < (dim >> 2); c += 32)
+            reinterpret_cast<float4 *>(dst)[c] = __ldg(reinterpret_cast<const float4 *>(src) + c);
+    } else {
+        for (uint32_t i = lane; i < dim; i += 32) dst[i] = __ldg(src + i);
+    }
+}
+
+// A warp per point: distances to all centroids, network sort, nearest + boundary flag.
+__global__ void __launch_bounds__(256) assign_kernel(const AssignArgs a, uint32_t max_centroid, uint32_t strip_words) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const uint32_t p = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (p >= a.n) return;
+    uint32_t *base = smem + (size_t) warp * strip_words;
+    float *query = reinterpret_cast<float *>(base);
+    uint32_t *scratch = base + dim_pad4(a.dim);
+    load_query(query, a.data + (uint64_t) p * a.dim, a.dim);
+    const uint32_t c0 = nearest_centroid(query, a.centroids, a.C, max_centroid, a.dim, a.metric, scratch);
+    if (lane == 0) {
+        a.nearest[p] = c0;
+        if (a.is_boundary) {
+            const float *ck = reinterpret_cast<const float *>(scratch);
+            // partition_kernel.cuh:58-60
+            a.is_boundary[p] = (a.boundary_factor >= 0.0f && a.C > 1 && ck[1] / ck[0] <= a.boundary_factor) ? 0u : kInvalid;
+        }
+    }
+}
+
+constexpr uint32_t kSlotBlock = 256;
+
+// pass 1: per-block histogram of keys
+__global__ void __launch_bounds__(kSlotBlock) slot_hist_kernel(const uint32_t *__restrict__ key, uint32_t n, uint32_t K,
+                                                                uint32_t *block_hist) {
+    extern __shared__ uint32_t hist[];
+    for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) hist[k] = 0;
+    __syncthreads();
+    const uint32_t i = blockIdx.x * kSlotBlock + threadIdx.x;
+    if (i < n) {
+        const uint32_t k = key[i];
+        if (k < K) atomicAdd(&hist[k], 1u);
+    }
+    __syncthreads();
+    for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) block_hist[(uint64_t) blockIdx.x * K + k] = hist[k];
+}
+
+// pass 2: per key, exclusive prefix over blocks (in place); totals[k] = count
+__global__ void slot_prefix_kernel(uint32_t *block_hist, uint32_t blocks, uint32_t K, uint32_t *totals) {
+    const uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= K) return;
+    uint32_t run = 0;
+    for (uint32_t b = 0; b < blocks; b++) {
+        const uint32_t v = block_hist[(uint64_t) b * K + k];
+        block_hist[(uint64_t) b * K + k] = run;
+        run += v;
+    }
+    totals[k] = run;
+}
+
+// pass 3: slot = block prefix + rank among earlier points of the block with the same
+// key. Warps take turns in ascending order so that ranks follow the point index.
+__global__ void __launch_bounds__(kSlotBlock) slot_rank_kernel(const uint32_t *__restrict__ key, uint32_t n, uint32_t K,
+                                                                const uint32_t *__restrict__ block_hist,
+                                                                uint32_t *slot) {
+    extern __shared__ uint32_t run[];
+    for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) run[k] = block_hist[(uint64_t) blockIdx.x * K + k];
+    __syncthreads();
+    const uint32_t i = blockIdx.x * kSlotBlock + threadIdx.x;
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const uint32_t k = (i < n) ? key[i] : kInvalid;
+    const bool valid = k < K;
+    for (uint32_t w = 0; w < kSlotBlock / 32; w++) {
+        if (warp == w) {
+            const uint32_t peers = __match_any_sync(kFullMask, k);
+            if (valid) {
+                const uint32_t rank = __popc(peers & ((1u << lane) - 1));
+                slot[i] = run[k] + rank;
+            } else if (i < n) {
+                slot[i] = kInvalid;
+            }
+            __syncwarp();
+            if (valid && lane == (uint32_t) (__ffs(peers) - 1)) run[k] += __popc(peers);
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void reorder_kernel(const float *__restrict__ data, uint32_t n, uint32_t dim,
+                               const uint32_t *__restrict__ seg_index, const uint32_t *__restrict__ seg_start,
+                               float *__restrict__ out, uint32_t *__restrict__ map) {
+    const uint32_t p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = lane_id();
+    if (p >= n) return;
+    const uint32_t r = seg_start[seg_index[3 * (uint64_t) p]] + seg_index[3 * (uint64_t) p + 1];
+    const uint32_t b = seg_index[3 * (uint64_t) p + 2];
+    const float *src = data + (uint64_t) p * dim;
+    float *d0 = out + (uint64_t) r * dim;
+    float *d1 = (b != kInvalid) ? out + (uint64_t) (n + b) * dim : nullptr;
+    if ((dim & 3u) == 0) {
+        for (uint32_t c = lane; c < (dim >> 2); c += 32) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(src) + c);
+            reinterpret_cast<float4 *>(d0)[c] = v;
+            if (d1) reinterpret_cast<float4 *>(d1)[c] = v;
+        }
+    } else {
+        for (uint32_t i = lane; i < dim; i += 32) {
+            const float v = __ldg(src + i);
+            d0[i] = v;
+            if (d1) d1[i] = v;
+        }
+    }
+    if (lane == 0) {
+        map[r] = p;
+        if (d1) map[n + b] = p;
+    }
+}
+
+__global__ void pack_seg_index_kernel(const uint32_t *__restrict__ nearest, const uint32_t *__restrict__ slot,
+                                      const uint32_t *__restrict__ bslot, uint32_t n, uint32_t *seg_index) {
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n) return;
+    seg_index[3 * (uint64_t) p] = nearest[p];
+    seg_index[3 * (uint64_t) p + 1] = slot[p];
+    seg_index[3 * (uint64_t) p + 2] = bslot ? bslot[p] : kInvalid;
+}
+
+__global__ void scatter_members_kernel(const uint32_t *__restrict__ label, const uint32_t *__restrict__ slot,
+                                       const uint32_t *__restrict__ off, uint32_t n, uint32_t *member_ids) {
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n) return;
+    member_ids[off[label[p]] + slot[p]] = p;
+}
+
+// centroid c = (sum of its members in ascending row order) / count, fp32; an empty
+// cluster keeps its centroid.
+__global__ void centroid_update_kernel(const float *__restrict__ sample, uint32_t dim,
+                                       const uint32_t *__restrict__ member_ids, const uint32_t *__restrict__ off,
+                                       const uint32_t *__restrict__ cnt, float *centroids) {
+    const uint32_t c = blockIdx.x;
+    const uint32_t count = cnt[c];
+    if (count == 0) return;
+    const uint32_t *members = member_ids + off[c];
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t m = 0; m < count; m++) acc = acc + __ldg(sample + (uint64_t) members[m] * dim + d);
+        centroids[(uint64_t) c * dim + d] = acc / (float) count;
+    }
+}
+
+__global__ void count_changed_kernel(const uint32_t *__restrict__ a, const uint32_t *__restrict__ b, uint32_t n,
+                                     uint32_t *count) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool diff = (i < n) && (a[i] != b[i]);
+    const uint32_t m = __ballot_sync(kFullMask, diff);
+    if (lane_id() == 0 && m) atomicAdd(count, (uint32_t) __popc(m));
+}
+
+uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
+    uint32_t m = lo;
+    while (m < x) m <<= 1;
+    return m;
+}
+
+}  // namespace
+
+cudaError_t launch_gather_rows(const float *data, const uint32_t *ids, uint32_t count, uint32_t dim, float *out,
+                               cudaStream_t stream) {
+    if (count == 0) return cudaSuccess;
+    const uint32_t warps = 8;
+    gather_rows_kernel<<<(count + warps - 1) / warps, warps * 32, 0, stream>>>(data, ids, count, dim, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream) {
+    if (a.n == 0) return cudaSuccess;
+    const uint32_t max_centroid = pow2_at_least(a.C, 32);
+    const uint32_t strip_words = (dim_pad4(a.dim) + 2 * max_centroid + 3u) & ~3u;
+    uint32_t warps = 8;
+    while (warps > 1 && (size_t) strip_words * 4 * warps > 96 * 1024) warps >>= 1;
+    const size_t smem_bytes = (size_t) strip_words * 4 * warps;
+    if (smem_bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+        if (e != cudaSuccess) return e;
+    }
+    assign_kernel<<<(a.n + warps - 1) / warps, warps * 32, smem_bytes, stream>>>(a, max_centroid, strip_words);
+    return cudaGetLastError();
+}
+
+size_t slot_scratch_words(uint32_t n, uint32_t K) { return (size_t) ((n + kSlotBlock - 1) / kSlotBlock) * K; }
+
+cudaError_t launch_slots(const uint32_t *key, uint32_t n, uint32_t K, uint32_t *slot, uint32_t *totals,
+                         uint32_t *scratch, cudaStream_t stream) {
+    if (n == 0) return cudaMemsetAsync(totals, 0, K * sizeof(uint32_t), stream);
+    const uint32_t blocks = (n + kSlotBlock - 1) / kSlotBlock;
+    slot_hist_kernel<<<blocks, kSlotBlock, K * sizeof(uint32_t), stream>>>(key, n, K, scratch);
+    slot_prefix_kernel<<<(K + 127) / 128, 128, 0, stream>>>(scratch, blocks, K, totals);
+    slot_rank_kernel<<<blocks, kSlotBlock, K * sizeof(uint32_t), stream>>>(key, n, K, scratch, slot);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_reorder(const float *data, uint32_t n, uint32_t dim, const uint32_t *seg_index,
+                           const uint32_t *seg_start_dev, float *reorder_data, uint32_t *map, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    const uint32_t warps = 8;
+    reorder_kernel<<<(n + warps - 1) / warps, warps * 32, 0, stream>>>(data, n, dim, seg_index, seg_start_dev,
+                                                                       reorder_data, map);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_pack_seg_index(const uint32_t *nearest, const uint32_t *slot, const uint32_t *bslot, uint32_t n,
+                                  uint32_t *seg_index, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    pack_seg_index_kernel<<<(n + 255) / 256, 256, 0, stream>>>(nearest, slot, bslot, n, seg_index);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_members(const uint32_t *label, const uint32_t *slot, const uint32_t *off, uint32_t n,
+                                   uint32_t *member_ids, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    scatter_members_kernel<<<(n + 255) / 256, 256, 0, stream>>>(label, slot, off, n, member_ids);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_centroid_update(const float *sample, uint32_t dim, const uint32_t *member_ids,
+                                   const uint32_t *off, const uint32_t *cnt, uint32_t C, float *centroids,
+                                   cudaStream_t stream) {
+    const uint32_t threads = dim < 1024 ? ((dim + 31) / 32) * 32 : 1024;
+    centroid_update_kernel<<<C, threads, 0, stream>>>(sample, dim, member_ids, off, cnt, centroids);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_count_changed(const uint32_t *a, const uint32_t *b, uint32_t n, uint32_t *count,
+                                 cudaStream_t stream) {
+    cudaError_t e = cudaMemsetAsync(count, 0, sizeof(uint32_t), stream);
+    if (e != cudaSuccess || n == 0) return e;
+    count_changed_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a, b, n, count);
+    return cudaGetLastError();
+}
+
+}  // namespace glide

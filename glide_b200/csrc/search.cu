@@ -1,0 +1,217 @@
+// Query search kernels: the small path's routed search (reference search_kernel,
+// search_kernel.cuh:393-490), the large path's query routing (select_segment_kernel,
+// :546-607) and per-partition search with running top-k merge (search_on_sub_kernel +
+// result_merge, :609-765).
+#include "beam_core.cuh"
+#include "kernels.h"
+
+namespace glide {
+
+namespace {
+
+struct SearchDev {
+    SearchArgs a;
+    uint32_t max_centroid;
+    uint32_t max_topk;
+    uint32_t strip_words;
+};
+
+// Last bitonic phase on a shared array of 32*n pairs (the input must be bitonic).
+__device__ inline void warp_merge_final_smem(float *k, uint32_t *v, uint32_t n_per_lane) {
+    const uint32_t total = 32u * n_per_lane, lane = lane_id();
+    for (uint32_t stride = total >> 1; stride >= 1; stride >>= 1) {
+        for (uint32_t p = lane; p < total / 2; p += 32) {
+            const uint32_t lo = ((p / stride) * 2 * stride) + (p % stride);
+            const uint32_t hi = lo + stride;
+            const float k0 = k[lo], k1 = k[hi];
+            if ((k0 != k1) && !(k0 < k1)) {
+                k[lo] = k1; k[hi] = k0;
+                const uint32_t t = v[lo]; v[lo] = v[hi]; v[hi] = t;
+            }
+        }
+        __syncwarp();
+    }
+}
+
+template<int NB, int NC>
+__global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    const SearchArgs &a = d.a;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const uint32_t q = blockIdx.x * warps_per_cta + warp;
+    if (q >= a.Q) return;
+    const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
+    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, 32u * NC, p.hash_bit);
+
+    const bool sub = (a.segment_ids != nullptr);
+    if (sub) {  // search_kernel.cuh:676-692: skip queries not routed to this partition
+        bool routed = false;
+        if (lane == 0) {
+            for (uint32_t i = 0; i < a.segment_num; i++) {
+                const uint32_t sid = a.segment_ids[(uint64_t) q * a.segment_num + i];
+                if (sid == a.segment_id) { routed = true; break; }
+                if (sid == kInvalid) break;
+            }
+        }
+        routed = __shfl_sync(kFullMask, routed ? 1 : 0, 0) != 0;
+        if (!routed) return;
+    }
+
+    load_query(s.query, a.queries + (uint64_t) q * a.dim, a.dim);
+    visited_clear(s.visited, p.hash_bit);
+    __syncwarp();
+
+    uint32_t rows = 0;
+    uint32_t start_node;
+    if (!sub) {
+        const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, s.extra);
+        start_node = a.start_points[c];
+    } else {
+        start_node = a.start_point;
+    }
+    rows += seed_from_row(s, start_node, kInvalid, a.graph, a.degree, p.hash_bit, a.data, a.dim, a.metric);
+
+    float bk[NB];
+    uint32_t bv[NB];
+    const uint32_t iters = beam_loop<NB, NC>(bk, bv, s, p, kInvalid, a.graph, a.degree, a.data, a.dim, a.metric, &rows);
+
+    if (!sub) {
+#pragma unroll
+        for (int i = 0; i < NB; i++) {
+            const uint32_t j = NB * lane + i;
+            if (j < a.top_k) {
+                a.out_ids[(uint64_t) q * a.top_k + j] = bv[i] & kClean;
+                a.out_dists[(uint64_t) q * a.top_k + j] = bk[i];
+            }
+        }
+    } else {
+        // result_merge (search_kernel.cuh:609-651): fold the first top_k beam entries
+        // into the running result with a network of width max_topk.
+        const uint32_t M = d.max_topk, n = M / 32;
+        float *mk = reinterpret_cast<float *>(s.extra);
+        uint32_t *mv = s.extra + M;
+        float *rk = reinterpret_cast<float *>(s.extra + 2 * M);  // this partition's result, by beam position
+        uint32_t *rv = s.extra + 3 * M;
+#pragma unroll
+        for (int i = 0; i < NB; i++) {
+            const uint32_t j = NB * lane + i;
+            if (j < a.top_k) {
+                rk[j] = bk[i];
+                const uint32_t id = bv[i] & kClean;
+                rv[j] = (id == kPadClean) ? kInvalid : a.map[id];  // an unfilled slot has no global id
+            }
+        }
+        float *fd = a.out_dists + (uint64_t) q * a.top_k;
+        uint32_t *fi = a.out_ids + (uint64_t) q * a.top_k;
+        for (uint32_t j = lane; j < M; j += 32) {
+            mk[j] = (j < a.top_k) ? fd[j] : FLT_MAX;
+            mv[j] = (j < a.top_k) ? fi[j] : kInvalid;
+        }
+        __syncwarp();
+        for (uint32_t j = lane; j < M; j += 32) {
+            const uint32_t k = M - 1 - j;
+            if (k < a.top_k && mk[j] > rk[k]) {
+                mk[j] = rk[k];
+                mv[j] = rv[k];
+            }
+        }
+        __syncwarp();
+        warp_merge_final_smem(mk, mv, n);
+        for (uint32_t j = lane; j < a.top_k; j += 32) {
+            fd[j] = mk[j];
+            fi[j] = mv[j];
+        }
+    }
+    if (a.counters && lane == 0) {
+        atomicAdd(a.counters + 0, (unsigned long long) rows);
+        atomicAdd(a.counters + 1, (unsigned long long) iters);
+    }
+}
+
+// select_segment_kernel (search_kernel.cuh:546-607): a warp per query.
+__global__ void __launch_bounds__(128) select_segment_kernel(const SelectSegmentArgs a, uint32_t max_centroid,
+                                                             uint32_t strip_words) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const uint32_t q = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (q >= a.Q) return;
+    uint32_t *base = smem + (size_t) warp * strip_words;
+    float *query = reinterpret_cast<float *>(base);
+    uint32_t *scratch = base + dim_pad4(a.dim);
+    load_query(query, a.queries + (uint64_t) q * a.dim, a.dim);
+    nearest_centroid(query, a.centroids, a.C, max_centroid, a.dim, a.metric, scratch);
+    const float *ck = reinterpret_cast<const float *>(scratch);
+    const uint32_t *cv = scratch + max_centroid;
+    uint32_t *out = a.out + (uint64_t) q * a.C;
+    const float d0 = ck[0];
+    uint32_t allow_num = 0;
+    for (uint32_t base_i = 0; base_i < a.C; base_i += 32) {
+        const uint32_t i = base_i + lane;
+        const bool allow = (i < a.C) && (ck[i] / d0 <= a.boundary_factor);
+        if (i < a.C) out[i] = allow ? cv[i] : kInvalid;
+        allow_num += __popc(__ballot_sync(kFullMask, allow));
+    }
+    __syncwarp();
+    if (allow_num < a.min_segment_num) {
+        const uint32_t need = a.min_segment_num - allow_num;
+        for (uint32_t i = lane; i < need; i += 32)
+            if (allow_num + i < a.C) out[allow_num + i] = cv[allow_num + i];
+    }
+}
+
+uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
+    uint32_t m = lo;
+    while (m < x) m <<= 1;
+    return m;
+}
+
+template<int NB, int NC>
+cudaError_t launch_search_t(const SearchDev &d, uint32_t warps_per_cta, size_t smem_bytes, cudaStream_t stream) {
+    auto kernel = search_kernel<NB, NC>;
+    if (smem_bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+        if (e != cudaSuccess) return e;
+    }
+    const uint32_t grid = (d.a.Q + warps_per_cta - 1) / warps_per_cta;
+    kernel<<<grid, warps_per_cta * 32, smem_bytes, stream>>>(d);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
+    if (a.Q == 0) return cudaSuccess;
+    SearchDev d;
+    d.a = a;
+    d.max_centroid = pow2_at_least(a.C, 32);
+    d.max_topk = a.top_k <= 32 ? 32 : (a.top_k <= 64 ? 64 : 128);  // kernel_config.cuh:309-319
+    // same size ladders as kernel_config.cuh:190-204 so that ties fall identically
+    const uint32_t max_beam = a.p.beam <= 64 ? 64 : (a.p.beam <= 128 ? 128 : (a.p.beam <= 256 ? 256 : 512));
+    const uint32_t max_cand = a.degree <= 64 ? 64 : (a.degree <= 128 ? 128 : 256);
+    const uint32_t extra = a.segment_ids ? 4 * d.max_topk : 2 * d.max_centroid;
+    d.strip_words = (strip_words_base(a.dim, max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
+    const size_t strip_bytes = (size_t) d.strip_words * 4;
+    uint32_t warps = 8;
+    while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;
+    if (strip_bytes * warps > 200 * 1024) return cudaErrorInvalidValue;
+    const int nb = max_beam / 32, nc = max_cand / 32;
+    GLIDE_DISPATCH_NB_NC(launch_search_t, nb, nc, d, warps, strip_bytes * warps, stream);
+}
+
+cudaError_t launch_select_segments(const SelectSegmentArgs &a, cudaStream_t stream) {
+    if (a.Q == 0) return cudaSuccess;
+    const uint32_t max_centroid = pow2_at_least(a.C, 32);
+    const uint32_t strip_words = (dim_pad4(a.dim) + 2 * max_centroid + 3u) & ~3u;
+    const uint32_t warps = 4;
+    const size_t smem_bytes = (size_t) strip_words * 4 * warps;
+    if (smem_bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(select_segment_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int) smem_bytes);
+        if (e != cudaSuccess) return e;
+    }
+    select_segment_kernel<<<(a.Q + warps - 1) / warps, warps * 32, smem_bytes, stream>>>(a, max_centroid, strip_words);
+    return cudaGetLastError();
+}
+
+}  // namespace glide

@@ -1,0 +1,109 @@
+"""Seeded synthetic data sets with the shapes and value ranges of the benchmark configs.
+
+They stand in for the public ANN benchmark sets the reference was measured on (none of
+whose records are used): generation is counter-based (Philox), chunked by rows, so any
+row range can be produced without materialising the whole set, and the same seed gives
+the same bytes on every machine.
+
+Order of generation: centres, then base rows in row order, then queries.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+_CHUNK = 65536
+
+
+@dataclass(frozen=True)
+class DatasetSpec:
+    name: str
+    n: int
+    dim: int
+    n_queries: int
+    kind: str            # "uniform" | "int_mixture" | "scaled_mixture" | "unit_mixture"
+    centres: int
+    metric: str          # "Euclidean" | "Cosine"
+    graph_degree: int
+    seed: int
+
+
+CONFIGS = {
+    # tiny correctness build: 10,000 x 32 i.i.d. uniform[0,1), 1,000 queries, degree 32
+    "cfg0": DatasetSpec("cfg0", 10_000, 32, 1_000, "uniform", 0, "Euclidean", 32, 0),
+    # 1M x 128: 1,024-centre mixture, centres U[0,120], sigma 20, rounded, clipped to [0,218]
+    "cfg1": DatasetSpec("cfg1", 1_000_000, 128, 10_000, "int_mixture", 1024, "Euclidean", 32, 1),
+    # 1M x 960: 256 centres N(0,1), sigma 0.3, each row scaled by U[0.5,1.5]
+    "cfg2": DatasetSpec("cfg2", 1_000_000, 960, 1_000, "scaled_mixture", 256, "Euclidean", 64, 2),
+    # 10M x 96 cosine: 4,096 centres N(0,1), sigma 0.5, rows normalised
+    "cfg3": DatasetSpec("cfg3", 10_000_000, 96, 10_000, "unit_mixture", 4096, "Cosine", 32, 3),
+    # 100M x 128: as cfg1 with 16,384 centres
+    "cfg4": DatasetSpec("cfg4", 100_000_000, 128, 10_000, "int_mixture", 16384, "Euclidean", 32, 4),
+}
+
+
+def scaled(spec: DatasetSpec, n: int, n_queries: int | None = None) -> DatasetSpec:
+    """The same distribution with fewer rows (parity tests run on slices of the big configs)."""
+    return DatasetSpec(spec.name + f"_n{n}", n, spec.dim, spec.n_queries if n_queries is None else n_queries,
+                       spec.kind, spec.centres, spec.metric, spec.graph_degree, spec.seed)
+
+
+def _rng(seed: int, stream: int, chunk: int) -> np.random.Generator:
+    # key = (seed, stream), counter starts at chunk * 2^64: disjoint counter ranges per chunk
+    return np.random.Generator(np.random.Philox(key=[seed, stream], counter=[0, chunk, 0, 0]))
+
+
+def centres(spec: DatasetSpec) -> np.ndarray | None:
+    if spec.kind == "uniform":
+        return None
+    g = _rng(spec.seed, 0, 0)
+    if spec.kind == "int_mixture":
+        return g.uniform(0.0, 120.0, size=(spec.centres, spec.dim)).astype(np.float32)
+    return g.standard_normal(size=(spec.centres, spec.dim), dtype=np.float32)
+
+
+def _rows(spec: DatasetSpec, cent: np.ndarray | None, stream: int, first: int, count: int) -> np.ndarray:
+    out = np.empty((count, spec.dim), np.float32)
+    done = 0
+    while done < count:
+        row = first + done
+        chunk, off = divmod(row, _CHUNK)
+        take = min(count - done, _CHUNK - off)
+        g = _rng(spec.seed, stream, chunk)
+        if spec.kind == "uniform":
+            block = g.random(size=(_CHUNK, spec.dim), dtype=np.float32)[off:off + take]
+        else:
+            comp = g.integers(0, spec.centres, size=_CHUNK)[off:off + take]
+            noise = g.standard_normal(size=(_CHUNK, spec.dim), dtype=np.float32)[off:off + take]
+            if spec.kind == "int_mixture":
+                block = np.clip(np.rint(cent[comp] + np.float32(20.0) * noise), 0.0, 218.0)
+            elif spec.kind == "scaled_mixture":
+                scale = g.uniform(0.5, 1.5, size=_CHUNK).astype(np.float32)[off:off + take]
+                block = (cent[comp] + np.float32(0.3) * noise) * scale[:, None]
+            elif spec.kind == "unit_mixture":
+                block = cent[comp] + np.float32(0.5) * noise
+                block /= np.linalg.norm(block, axis=1, keepdims=True).astype(np.float32)
+            else:
+                raise ValueError(spec.kind)
+        out[done:done + take] = block
+        done += take
+    return out
+
+
+def base_rows(spec: DatasetSpec, first: int = 0, count: int | None = None, cent: np.ndarray | None = None) -> np.ndarray:
+    count = spec.n - first if count is None else count
+    if cent is None:
+        cent = centres(spec)
+    return _rows(spec, cent, 1, first, count)
+
+
+def queries(spec: DatasetSpec, cent: np.ndarray | None = None) -> np.ndarray:
+    if cent is None:
+        cent = centres(spec)
+    return _rows(spec, cent, 2, 0, spec.n_queries)
+
+
+def make(spec: DatasetSpec) -> tuple[np.ndarray, np.ndarray]:
+    cent = centres(spec)
+    return base_rows(spec, cent=cent), queries(spec, cent=cent)

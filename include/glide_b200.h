@@ -1,0 +1,189 @@
+/*
+ * glide_b200 — C ABI of the B200-native GLIDE hot path.
+ *
+ * A drop-in for the stages of owlet-hub/GLIDE's pipeline: partition -> kNN graph ->
+ * graph build/refine -> search (small, GPU-resident variant and large, per-partition
+ * variant). Every entry point takes plain pointers and sizes; pointers named d_* are
+ * device pointers, h_* host pointers. Matrices are row-major; ids are uint32_t; an
+ * empty graph slot is 0xffffffff. All calls return 0 on success or a negative
+ * glide_status; glide_last_error() gives the message of the last failure on a context.
+ * Work is enqueued on the context's stream and the call returns after that stream has
+ * been synchronised unless stated otherwise.
+ *
+ * Each declaration names the reference interface it replaces (paths relative to the
+ * reference's src/ directory).
+ */
+#ifndef GLIDE_B200_H
+#define GLIDE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct glide_ctx glide_ctx;
+
+typedef enum {
+    GLIDE_OK = 0,
+    GLIDE_ERR_BAD_ARG = -1,      /* null pointer, zero size, inconsistent sizes */
+    GLIDE_ERR_UNSUPPORTED = -2,  /* beam > 512, degree > 256, ... (kernel_config.cuh:47-48, :59-60) */
+    GLIDE_ERR_CUDA = -3,         /* a CUDA call failed; see glide_last_error */
+    GLIDE_ERR_NO_MEMORY = -4,
+    GLIDE_ERR_IO = -5
+} glide_status;
+
+enum { GLIDE_METRIC_EUCLIDEAN = 0, GLIDE_METRIC_COSINE = 1 }; /* params.cuh:5-8 */
+
+/* SearchParameter, params.cuh:37-47, after adjust_search_params / calculate_hash_* (:49-99). */
+typedef struct {
+    uint32_t top_k;
+    uint32_t beam;                /* multiple of 32, <= 512 */
+    uint32_t max_iterations;      /* >= 1 */
+    uint32_t min_iterations;
+    uint32_t hash_bit;            /* 8..13 */
+    uint32_t hash_reset_interval; /* >= 1 */
+} glide_search_params;
+
+/* ---- context ------------------------------------------------------------------------- */
+/* The reference hard-codes cudaSetDevice(1) in every main (small_build.cu:33); here the
+ * device is a parameter. Creates one stream. */
+int glide_ctx_create(int device, glide_ctx **out);
+void glide_ctx_destroy(glide_ctx *ctx);
+const char *glide_last_error(const glide_ctx *ctx);
+/* cudaStream_t of the context, for callers that enqueue their own work around the calls. */
+void *glide_ctx_stream(glide_ctx *ctx);
+/* Elapsed device milliseconds of the kernels of the most recent call on this context
+ * (the reference's timing convention: cudaEvent pairs around kernels, glide_impl.cuh:144-147). */
+float glide_last_kernel_ms(const glide_ctx *ctx);
+
+/* Parameter helpers: params.cuh:49-66, :68-80, :82-99. */
+uint32_t glide_calculate_hash_bitlen(uint32_t beam, uint32_t graph_degree, float max_fill_rate, uint32_t min_bitlen);
+uint32_t glide_calculate_hash_reset_interval(uint32_t beam, uint32_t graph_degree, float max_fill_rate,
+                                             uint32_t hash_bitlen);
+void glide_adjust_search_params(uint32_t min_iterations, uint32_t *max_iterations, uint32_t *beam);
+
+/* ---- partition stage (partition.cuh) ---------------------------------------------------- */
+/* get_centroids, partition.cuh:8-59: sample floor(n*sample_factor) rows (seeded shuffle)
+ * and fit `centroid_num` centroids with Lloyd iterations (the reference calls cuVS
+ * kmeans::fit). d_centroids: centroid_num x dim. */
+int glide_get_centroids(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, uint32_t centroid_num,
+                        float sample_factor, uint64_t seed, uint32_t max_iter, int metric, float *d_centroids,
+                        uint32_t *iterations_run);
+/* The sample rows get_centroids draws: an arithmetic progression modulo n with a seeded
+ * stride coprime to n (the reference shuffles all ids, partition.cuh:25-31). */
+int glide_sample_ids(uint32_t n, uint32_t sample_num, uint64_t seed, uint32_t *h_out);
+/* k-means on rows already selected (the fit itself), for callers that sample themselves. */
+int glide_kmeans_fit(glide_ctx *ctx, const float *d_sample, uint32_t n, uint32_t dim, uint32_t centroid_num,
+                     uint32_t max_iter, int metric, float *d_centroids, uint32_t *d_labels_or_null,
+                     uint32_t *iterations_run);
+/* define_partition, partition.cuh:61-116 (+ kernel partition_kernel.cuh:22-66).
+ * d_segment_index: n x 3 (segment, slot, boundary slot or 0xffffffff); h_segment_start /
+ * h_segment_length: centroid_num+1 entries, the last one is the boundary segment.
+ * boundary_factor < 0 disables the boundary test (large path, partition_kernel.cuh:122-162).
+ * Slots follow ascending row id (the reference's come from atomics and are arbitrary). */
+int glide_define_partition(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, const float *d_centroids,
+                           uint32_t centroid_num, float boundary_factor, int metric, uint32_t *d_segment_index,
+                           uint32_t *h_segment_start, uint32_t *h_segment_length);
+/* reorder, partition.cuh:118-157 (+ kernel partition_kernel.cuh:68-100).
+ * d_reorder_data: (n + boundary) x dim, d_map: n + boundary. */
+int glide_reorder(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, const uint32_t *d_segment_index,
+                  const uint32_t *h_segment_start, uint32_t centroid_num, float *d_reorder_data, uint32_t *d_map);
+/* preprocess, partition.cuh:159-193: the three steps above. The caller does not know the
+ * boundary count in advance, so the outputs are allocated by the library (cudaMalloc) and
+ * owned by the caller, who frees them with glide_free. */
+int glide_preprocess(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, uint32_t centroid_num,
+                     float boundary_factor, float sample_factor, int metric, uint64_t seed, float *d_centroids,
+                     uint32_t *h_segment_start, uint32_t *h_segment_length, float **d_reorder_data_out,
+                     uint32_t **d_map_out, uint32_t *reorder_num_out);
+void glide_free(void *device_ptr);
+
+/* ---- kNN stage -------------------------------------------------------------------------- */
+/* build_nnd, nn_descent.cuh:1405-1467: per-partition kNN graph of the reordered rows,
+ * partition-local ids, h_or_d knn: rows x knn_degree int32. knn_degree <= 64.
+ * max_iterations 0 -> 20 and termination_threshold < 0 -> 1e-4 (params.cuh:20-21).
+ * sample 0 -> 32. */
+int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, uint32_t dim,
+                    const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t segment_num,
+                    uint32_t knn_degree, uint32_t max_iterations, float termination_threshold, uint32_t sample,
+                    uint64_t seed, int metric, int32_t *d_knn, uint32_t *iterations_run);
+/* Exact kNN by brute force: the ground truth (the reference reads it from a file,
+ * small_search.cu:88). k <= 128. d_out_dists may be null. */
+int glide_bruteforce_knn(glide_ctx *ctx, const float *d_base, uint32_t n, const float *d_queries, uint32_t q,
+                         uint32_t dim, uint32_t k, int metric, uint32_t *d_out_ids, float *d_out_dists);
+
+/* ---- graph build stage (glide_impl.cuh) ------------------------------------------------- */
+/* start_point_select, glide_impl.cuh:43-73: one member per segment drawn from `seed`.
+ * h_local: segment_num partition-local ids; h_original: centroid_num original ids. */
+int glide_start_point_select(const uint32_t *h_segment_start, const uint32_t *h_segment_length,
+                             uint32_t segment_num, const uint32_t *h_map, uint64_t seed, uint32_t *h_local,
+                             uint32_t *h_original);
+/* subgraph_build_and_merge, glide_impl.cuh:75-192: build_kernel over the `num` main rows
+ * then build_boundary_kernel over the boundary copies. d_graph: num x graph_degree, every
+ * slot must be 0xffffffff on entry. d_start_points_local: segment_num entries. */
+int glide_subgraph_build_and_merge(glide_ctx *ctx, const float *d_reorder_data, uint32_t reorder_num, uint32_t dim,
+                                   const uint32_t *d_knn, uint32_t knn_degree, const uint32_t *h_segment_start,
+                                   const uint32_t *h_segment_length, uint32_t segment_num,
+                                   const uint32_t *d_start_points_local, const uint32_t *d_map, uint32_t num,
+                                   uint32_t graph_degree, const glide_search_params *p, float relaxant_factor,
+                                   int metric, int skip_boundary, uint32_t *d_graph);
+/* reverse_graph, glide_impl.cuh:194-256. In place. */
+int glide_reverse_graph(glide_ctx *ctx, uint32_t *d_graph, uint32_t num, uint32_t graph_degree);
+/* refine, glide_impl.cuh:258-317. In place (a snapshot is taken internally). */
+int glide_refine(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                 uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
+                 const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor, int metric);
+
+/* ---- search stage ----------------------------------------------------------------------- */
+/* GLIDE::search, glide_impl.cuh:370-454 (search_kernel, search_kernel.cuh:393-490).
+ * Device pointers; results Q x top_k. */
+int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph,
+                 uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
+                 const uint32_t *d_start_points, const float *d_queries, uint32_t q, const glide_search_params *p,
+                 int metric, uint32_t *d_out_ids, float *d_out_dists);
+/* Same call with HOST query and result buffers (copies inside), the shape of the
+ * reference's small_search main (small_search.cu:113-117 upload, glide_impl.cuh:450-453
+ * download). */
+int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph,
+                      uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
+                      const uint32_t *d_start_points, const float *h_queries, uint32_t q,
+                      const glide_search_params *p, int metric, uint32_t *h_out_ids, float *h_out_dists);
+/* Traffic counters of the last search/build/refine call when enabled: rows read during
+ * search, expansions, rows read during pruning. */
+void glide_enable_counters(glide_ctx *ctx, int on);
+int glide_read_counters(glide_ctx *ctx, uint64_t out[3]);
+
+/* ---- large path (glide_large_impl.cuh) -------------------------------------------------- */
+/* select_segment_kernel, search_kernel.cuh:546-607; d_out: q x centroid_num. */
+int glide_select_segments(glide_ctx *ctx, const float *d_queries, uint32_t q, uint32_t dim,
+                          const float *d_centroids, uint32_t centroid_num, uint32_t min_segment_num,
+                          float boundary_factor, int metric, uint32_t *d_out);
+/* search_on_sub_kernel, search_kernel.cuh:653-765: search one resident partition and fold
+ * its results into the running top-k (d_final_*: q x top_k, initialised by the caller to
+ * FLT_MAX / 0xffffffff before the first partition). */
+int glide_search_on_sub(glide_ctx *ctx, const float *d_data, uint32_t dim, const uint32_t *d_graph,
+                        uint32_t graph_degree, const uint32_t *d_map, uint32_t start_point,
+                        const float *d_queries, uint32_t q, const uint32_t *d_segment_ids, uint32_t segment_num,
+                        uint32_t segment_id, const glide_search_params *p, int metric, uint32_t *d_final_ids,
+                        float *d_final_dists);
+/* build_for_large_kernel / refine_for_large_kernel, graph_kernel.cuh:675-821: one resident
+ * partition, local ids, no map. */
+int glide_build_partition(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_knn,
+                          uint32_t knn_degree, uint32_t start_point, uint32_t graph_degree,
+                          const glide_search_params *p, float relaxant_factor, int metric, uint32_t *d_graph);
+int glide_refine_partition(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                           uint32_t graph_degree, uint32_t start_point, const glide_search_params *p,
+                           float relaxant_factor, int metric);
+
+/* ---- device memory helpers for hosts without their own CUDA binding --------------------- */
+int glide_malloc(glide_ctx *ctx, size_t bytes, void **d_out);
+int glide_memcpy_h2d(glide_ctx *ctx, void *d_dst, const void *h_src, size_t bytes);
+int glide_memcpy_d2h(glide_ctx *ctx, void *h_dst, const void *d_src, size_t bytes);
+int glide_memset_u32(glide_ctx *ctx, uint32_t *d_dst, uint32_t value, size_t count);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GLIDE_B200_H */
