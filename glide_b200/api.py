@@ -238,6 +238,100 @@ def start_point_select(h_segment_start, h_segment_length, h_map, seed: int):
     return local, original[:s - 1]
 
 
+def subgraph_build_and_merge(ctx: Context, d_reorder_data, d_knn, h_segment_start, h_segment_length,
+                             d_start_points_local, d_map, num: int, d_graph, p: SearchParameter,
+                             relaxant_factor: float, metric: Metric = Metric.Euclidean, skip_boundary: bool = False):
+    """glide_impl.cuh:75-192 on caller-owned buffers; d_graph (num x degree) must be all 0xffffffff."""
+    seg_start = np.ascontiguousarray(h_segment_start, np.uint32)
+    seg_len = np.ascontiguousarray(h_segment_length, np.uint32)
+    pc = _params_c(p)
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_subgraph_build_and_merge(
+        ctx.handle, _ptr(d_reorder_data), d_reorder_data.shape[0], d_reorder_data.shape[1], _ptr(d_knn),
+        d_knn.shape[1], _ptr(seg_start), _ptr(seg_len), seg_start.size, _ptr(d_start_points_local), _ptr(d_map), num,
+        d_graph.shape[1], C.byref(pc), relaxant_factor, int(metric), 1 if skip_boundary else 0, _ptr(d_graph)))
+    return ctx.last_kernel_seconds
+
+
+def reverse_graph(ctx: Context, d_graph):
+    """glide_impl.cuh:194-256, in place."""
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_reverse_graph(ctx.handle, _ptr(d_graph), d_graph.shape[0], d_graph.shape[1]))
+    return ctx.last_kernel_seconds
+
+
+def refine(ctx: Context, d_data, d_graph, d_centroids, d_start_points, p: SearchParameter, relaxant_factor: float,
+           metric: Metric = Metric.Euclidean):
+    """glide_impl.cuh:258-317, in place."""
+    pc = _params_c(p)
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_refine(ctx.handle, _ptr(d_data), d_data.shape[0], d_data.shape[1], _ptr(d_graph),
+                                   d_graph.shape[1], _ptr(d_centroids), d_centroids.shape[0], _ptr(d_start_points),
+                                   C.byref(pc), relaxant_factor, int(metric)))
+    return ctx.last_kernel_seconds
+
+
+def search(ctx: Context, d_data, d_graph, d_centroids, d_start_points, d_queries, p: SearchParameter,
+           metric: Metric = Metric.Euclidean):
+    """glide_impl.cuh:370-454 on caller-owned device buffers. Returns (d_ids, d_dists, seconds)."""
+    q = d_queries.shape[0]
+    d_ids = _u32_tensor(ctx, (q, p.top_k))
+    d_dists = ctx.empty((q, p.top_k), torch.float32)
+    pc = _params_c(p)
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_search(ctx.handle, _ptr(d_data), d_data.shape[0], d_data.shape[1], _ptr(d_graph),
+                                   d_graph.shape[1], _ptr(d_centroids), d_centroids.shape[0], _ptr(d_start_points),
+                                   _ptr(d_queries), q, C.byref(pc), int(metric), _ptr(d_ids), _ptr(d_dists)))
+    return d_ids, d_dists, ctx.last_kernel_seconds
+
+
+def select_segments(ctx: Context, d_queries, d_centroids, min_segment_num: int, boundary_factor: float,
+                    metric: Metric = Metric.Euclidean):
+    """search_kernel.cuh:546-607. Returns d_segment_ids [Q, C]."""
+    q, dim = d_queries.shape
+    c = d_centroids.shape[0]
+    out = _u32_tensor(ctx, (q, c))
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_select_segments(ctx.handle, _ptr(d_queries), q, dim, _ptr(d_centroids), c, min_segment_num,
+                                            boundary_factor, int(metric), _ptr(out)))
+    return out
+
+
+def search_on_sub(ctx: Context, d_data, d_graph, d_map, start_point: int, d_queries, d_segment_ids, segment_id: int,
+                  p: SearchParameter, d_final_ids, d_final_dists, metric: Metric = Metric.Euclidean):
+    """search_kernel.cuh:653-765: one resident partition, folds into the running top-k."""
+    pc = _params_c(p)
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_search_on_sub(ctx.handle, _ptr(d_data), d_data.shape[1], _ptr(d_graph), d_graph.shape[1],
+                                          _ptr(d_map), start_point, _ptr(d_queries), d_queries.shape[0],
+                                          _ptr(d_segment_ids), d_segment_ids.shape[1], segment_id, C.byref(pc),
+                                          int(metric), _ptr(d_final_ids), _ptr(d_final_dists)))
+    return ctx.last_kernel_seconds
+
+
+def build_partition(ctx: Context, d_data, d_knn, start_point: int, graph_degree: int, p: SearchParameter,
+                    relaxant_factor: float, metric: Metric = Metric.Euclidean):
+    """build_for_large_kernel, graph_kernel.cuh:675-728. Returns d_graph [num, graph_degree], local ids."""
+    num, dim = d_data.shape
+    d_graph = _u32_tensor(ctx, (num, graph_degree))
+    d_graph.fill_(-1)
+    pc = _params_c(p)
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_build_partition(ctx.handle, _ptr(d_data), num, dim, _ptr(d_knn), d_knn.shape[1], start_point,
+                                            graph_degree, C.byref(pc), relaxant_factor, int(metric), _ptr(d_graph)))
+    return d_graph
+
+
+def refine_partition(ctx: Context, d_data, d_graph, start_point: int, p: SearchParameter, relaxant_factor: float,
+                     metric: Metric = Metric.Euclidean):
+    """refine_for_large_kernel, graph_kernel.cuh:730-821, in place."""
+    pc = _params_c(p)
+    ctx.sync_inputs()
+    ctx.check(ctx.lib.glide_refine_partition(ctx.handle, _ptr(d_data), d_data.shape[0], d_data.shape[1], _ptr(d_graph),
+                                             d_graph.shape[1], start_point, C.byref(pc), relaxant_factor, int(metric)))
+    return ctx.last_kernel_seconds
+
+
 def calculate_recall(neighbors: np.ndarray, truth: np.ndarray, top_k: int) -> float:
     """small_search.cu:14-36: mean over queries of |result[:k] ∩ truth[:k]| / k."""
     nb = np.asarray(neighbors)[:, :top_k]

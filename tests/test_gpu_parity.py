@@ -1,0 +1,334 @@
+"""GPU parity tests: every CUDA stage, called through the C ABI, against the CPU oracle on the
+same seeded inputs. Ids are compared bit for bit; distances bit for bit too, because the
+oracle restates the kernels' summation order (a tolerance of 1e-5 relative is what the
+reference's own order differs by and is asserted separately)."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import oracle
+from glide_b200 import api
+from glide_b200.params import Metric, NNDescentParameter, SearchParameter
+
+pytestmark = pytest.mark.gpu
+INVALID = 0xFFFFFFFF
+
+
+def dev(ctx, a, dtype=None):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint32:
+        return api.from_u32(ctx, a)
+    return torch.from_numpy(a).to(ctx.torch_device)
+
+
+def sp_from(o: oracle.SearchParams) -> SearchParameter:
+    return SearchParameter(top_k=o.top_k, beam=o.beam, max_iterations=o.max_iterations,
+                           min_iterations=o.min_iterations, hash_bit=o.hash_bit,
+                           hash_reset_interval=o.hash_reset_interval)
+
+
+CASES = {
+    "uniform16": dict(kind="uniform", n=3000, dim=16, nq=200, metric=oracle.EUCLIDEAN),
+    "int128": dict(kind="int", n=3000, dim=128, nq=200, metric=oracle.EUCLIDEAN),     # exact ties occur
+    "unit96": dict(kind="unit", n=2500, dim=96, nq=150, metric=oracle.COSINE),
+    "uniform30": dict(kind="uniform", n=1500, dim=30, nq=100, metric=oracle.EUCLIDEAN),  # dim % 4 != 0
+}
+_cache = {}
+
+
+def case(name):
+    if name not in _cache:
+        c = CASES[name]
+        base, queries = helpers.small_dataset(c["kind"], c["n"], c["dim"], c["nq"])
+        P = helpers.oracle_pipeline(base, metric=c["metric"])
+        _cache[name] = (base, queries, P)
+    return _cache[name]
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+@pytest.mark.parametrize("beam", [32, 64, 100, 256])
+def test_search_matches_oracle(gpu_ctx, name, beam):
+    base, queries, P = case(name)
+    metric = P["metric"]
+    o = oracle.SearchParams.derive(beam, P["graph"].shape[1], top_k=10)
+    want_ids, want_d = oracle.search(base, P["graph"], P["centroids"], P["orig_sp"], queries, o, metric)
+    d_ids, d_d, _ = api.search(gpu_ctx, dev(gpu_ctx, base), dev(gpu_ctx, P["graph"]), dev(gpu_ctx, P["centroids"]),
+                               dev(gpu_ctx, P["orig_sp"]), dev(gpu_ctx, queries), sp_from(o), Metric(metric))
+    got_ids, got_d = api.to_u32(d_ids), d_d.cpu().numpy()
+    assert np.array_equal(got_ids, want_ids)
+    assert np.array_equal(got_d, want_d)
+    # and within 1e-5 relative of the reference's own summation order
+    ref_ids, ref_d = oracle.search(base, P["graph"], P["centroids"], P["orig_sp"], queries, o, metric,
+                                   order=oracle.ORDER_REF)
+    same = (ref_ids == got_ids)
+    assert same.mean() > 0.99
+    assert np.allclose(got_d[same], ref_d[same], rtol=1e-5)
+
+
+def test_search_host_entry_point(gpu_ctx):
+    base, queries, P = case("int128")
+    o = oracle.SearchParams.derive(64, 16, top_k=10)
+    want_ids, want_d = oracle.search(base, P["graph"], P["centroids"], P["orig_sp"], queries, o)
+    index = api.GLIDE(gpu_ctx, 16, base, P["centroids"])
+    index.load(P["graph"], P["orig_sp"])
+    ids, d = index.search_host(sp_from(o), queries)
+    assert np.array_equal(ids, want_ids) and np.array_equal(d, want_d)
+    ids2, d2, seconds = index.search(sp_from(o), dev(gpu_ctx, queries))
+    assert np.array_equal(ids2, want_ids) and np.array_equal(d2, want_d) and seconds > 0
+
+
+@pytest.mark.parametrize("name", ["uniform16", "int128", "unit96", "uniform30"])
+def test_define_partition_and_reorder_match_oracle(gpu_ctx, name):
+    base, _, P = case(name)
+    metric = Metric(P["metric"])
+    d_base = dev(gpu_ctx, base)
+    d_seg, seg_start, seg_len = api.define_partition(gpu_ctx, d_base, dev(gpu_ctx, P["centroids"]), 1.1, metric)
+    assert np.array_equal(api.to_u32(d_seg), P["seg_index"])
+    assert np.array_equal(seg_start, P["seg_start"]) and np.array_equal(seg_len, P["seg_len"])
+    d_re, d_map = api.reorder(gpu_ctx, d_base, d_seg, seg_start, int(seg_len[-1]))
+    assert np.array_equal(api.to_u32(d_map), P["mapping"])
+    assert np.array_equal(d_re.cpu().numpy(), P["reorder_data"])
+
+
+def test_define_partition_without_boundary_and_single_centroid(gpu_ctx):
+    base, _, P = case("uniform16")
+    d_base = dev(gpu_ctx, base)
+    d_seg, seg_start, seg_len = api.define_partition(gpu_ctx, d_base, dev(gpu_ctx, P["centroids"]), -1.0)
+    want = oracle.define_partition(base, P["centroids"], -1.0)
+    assert np.array_equal(api.to_u32(d_seg), want[0]) and seg_len[-1] == 0
+    one = base.mean(axis=0, keepdims=True)
+    d_seg, seg_start, seg_len = api.define_partition(gpu_ctx, d_base, dev(gpu_ctx, one), 1.1)
+    assert seg_len.tolist() == [base.shape[0], 0]
+    assert np.array_equal(api.to_u32(d_seg)[:, 1], np.arange(base.shape[0]))
+
+
+@pytest.mark.parametrize("name,c", [("int128", 8), ("uniform16", 5), ("unit96", 6)])
+def test_kmeans_matches_oracle(gpu_ctx, name, c):
+    base, _, P = case(name)
+    sample = base[:1200]
+    want_c, want_l, want_r = oracle.kmeans(sample, c, 25, metric=P["metric"])
+    d_c, d_l, rounds = api.kmeans_fit(gpu_ctx, dev(gpu_ctx, sample), c, 25, Metric(P["metric"]))
+    assert rounds == want_r
+    assert np.array_equal(api.to_u32(d_l), want_l)
+    assert np.array_equal(d_c.cpu().numpy(), want_c)
+
+
+def test_get_centroids_uses_seeded_sample(gpu_ctx):
+    base, _, _ = case("int128")
+    ids = api.sample_ids(base.shape[0], 600, 3)
+    want_c, _, _ = oracle.kmeans(base[ids], 4, 25)
+    d_c, _ = api.get_centroids(gpu_ctx, dev(gpu_ctx, base), 4, 0.2, seed=3)
+    assert np.array_equal(d_c.cpu().numpy(), want_c)
+
+
+@pytest.mark.parametrize("name", ["uniform16", "int128", "unit96", "uniform30"])
+def test_build_boundary_reverse_refine_match_oracle(gpu_ctx, name):
+    base, _, P = case(name)
+    metric = Metric(P["metric"])
+    n = base.shape[0]
+    d_re, d_knn = dev(gpu_ctx, P["reorder_data"]), dev(gpu_ctx, P["knn"].view(np.uint32))
+    d_map, d_local = dev(gpu_ctx, P["mapping"]), dev(gpu_ctx, P["local_sp"])
+    pb = sp_from(P["p_build"])
+    g = api._u32_tensor(gpu_ctx, (n, 16)); g.fill_(-1)
+    api.subgraph_build_and_merge(gpu_ctx, d_re, d_knn, P["seg_start"], P["seg_len"], d_local, d_map, n, g, pb,
+                                 P["alpha"], metric, skip_boundary=True)
+    assert np.array_equal(api.to_u32(g), P["after_build"])
+    g.fill_(-1)
+    api.subgraph_build_and_merge(gpu_ctx, d_re, d_knn, P["seg_start"], P["seg_len"], d_local, d_map, n, g, pb,
+                                 P["alpha"], metric)
+    assert np.array_equal(api.to_u32(g), P["after_boundary"])
+    api.reverse_graph(gpu_ctx, g)
+    assert np.array_equal(api.to_u32(g), P["after_reverse"])
+    api.refine(gpu_ctx, dev(gpu_ctx, base), g, dev(gpu_ctx, P["centroids"]), dev(gpu_ctx, P["orig_sp"]),
+               sp_from(P["p_refine"]), P["alpha"], metric)
+    assert np.array_equal(api.to_u32(g), P["graph"])
+
+
+def test_build_with_wider_graph_than_knn(gpu_ctx):
+    # graph_degree 48 > knn_degree 16, beam 64: rows keep holes that reverse edges and refinement fill
+    base, _, P = case("uniform16")
+    n = base.shape[0]
+    o = oracle.SearchParams.derive(64, 16)
+    want = oracle.build_rows(P["reorder_data"], P["knn"].view(np.uint32), P["seg_start"], P["seg_len"], P["local_sp"],
+                             P["mapping"], n, 48, o, 1.05)
+    oracle.build_boundary(P["reorder_data"], P["knn"].view(np.uint32), n, int(P["local_sp"][-1]), P["mapping"], want,
+                          o, 1.05)
+    g = api._u32_tensor(gpu_ctx, (n, 48)); g.fill_(-1)
+    api.subgraph_build_and_merge(gpu_ctx, dev(gpu_ctx, P["reorder_data"]), dev(gpu_ctx, P["knn"].view(np.uint32)),
+                                 P["seg_start"], P["seg_len"], dev(gpu_ctx, P["local_sp"]), dev(gpu_ctx, P["mapping"]),
+                                 n, g, sp_from(o), 1.05)
+    assert np.array_equal(api.to_u32(g), want)
+    oracle.reverse_graph(want)
+    api.reverse_graph(gpu_ctx, g)
+    assert np.array_equal(api.to_u32(g), want)
+    o2 = oracle.SearchParams.derive(128, 16)
+    want2 = oracle.refine(base, want, P["centroids"], P["orig_sp"], o2, 1.05)
+    api.refine(gpu_ctx, dev(gpu_ctx, base), g, dev(gpu_ctx, P["centroids"]), dev(gpu_ctx, P["orig_sp"]), sp_from(o2), 1.05)
+    assert np.array_equal(api.to_u32(g), want2)
+
+
+def test_reverse_graph_on_hub_heavy_graph(gpu_ctx):
+    # many rows point at a few hubs, rows mostly empty: exercises capacity and ordering
+    rng = np.random.default_rng(0)
+    n, deg = 5000, 32
+    g = np.full((n, deg), INVALID, np.uint32)
+    for p in range(n):
+        k = rng.integers(1, 6)
+        row = np.unique(np.concatenate([rng.integers(0, 8, 2), rng.integers(0, n, k)]))
+        row = row[row != p][:deg]
+        g[p, :row.size] = rng.permutation(row)
+    want = oracle.reverse_graph(g.copy())
+    d_g = dev(gpu_ctx, g)
+    api.reverse_graph(gpu_ctx, d_g)
+    assert np.array_equal(api.to_u32(d_g), want)
+
+
+@pytest.mark.parametrize("name", ["int128", "uniform30"])
+def test_bruteforce_knn_matches_oracle(gpu_ctx, name):
+    base, queries, P = case(name)
+    want_ids, want_d = oracle.bruteforce_knn(base, queries, 10, P["metric"])
+    ids, d = api.bruteforce_knn(gpu_ctx, dev(gpu_ctx, base), dev(gpu_ctx, queries), 10, Metric(P["metric"]))
+    ids, d = api.to_u32(ids), d.cpu().numpy()
+    assert np.allclose(d, want_d, rtol=1e-5)
+    if name == "int128":  # exact arithmetic: ids must agree, ties broken by id on both sides
+        assert np.array_equal(ids, want_ids)
+    else:
+        assert (ids == want_ids).mean() > 0.995
+
+
+def test_bruteforce_knn_large_k_and_ragged_sizes(gpu_ctx):
+    rng = np.random.default_rng(2)
+    base = rng.integers(0, 50, (777, 20)).astype(np.float32)
+    queries = rng.integers(0, 50, (65, 20)).astype(np.float32)
+    want_ids, _ = oracle.bruteforce_knn(base, queries, 100)
+    ids, _ = api.bruteforce_knn(gpu_ctx, dev(gpu_ctx, base), dev(gpu_ctx, queries), 100)
+    assert np.array_equal(api.to_u32(ids), want_ids)
+
+
+def knn_recall(knn, exact, k):
+    hits = 0
+    for r in range(knn.shape[0]):
+        hits += len(set(knn[r, :k].tolist()) & set(exact[r, :k].tolist()))
+    return hits / (knn.shape[0] * k)
+
+
+@pytest.mark.parametrize("name", ["uniform16", "int128", "unit96"])
+def test_nn_descent_graph_recall_and_invariants(gpu_ctx, name):
+    base, _, P = case(name)
+    rd, seg_start, seg_len = P["reorder_data"], P["seg_start"], P["seg_len"]
+    metric = Metric(P["metric"])
+    d_knn, rounds, seconds = api.build_nnd(gpu_ctx, NNDescentParameter(32), dev(gpu_ctx, rd), seg_start, seg_len, metric,
+                                           seed=1)
+    knn = d_knn.cpu().numpy()
+    assert knn.shape == (rd.shape[0], 32) and 1 <= rounds <= 20
+    exact = helpers.exact_partition_knn(rd, seg_start, seg_len, 10, P["metric"])
+    # ids are partition-local, no self loops, no duplicates
+    for s, l in zip(seg_start, seg_len):
+        part = knn[int(s):int(s) + int(l)]
+        assert part.min() >= 0 and part.max() < int(l)
+    rows = np.arange(rd.shape[0])
+    local = rows - np.repeat(seg_start, seg_len)
+    assert not (knn == local[:, None]).any()
+    assert all(len(set(r.tolist())) == 32 for r in knn[::53])
+    assert knn_recall(knn, exact, 10) >= 0.95
+    # reproducible
+    d_knn2, rounds2, _ = api.build_nnd(gpu_ctx, NNDescentParameter(32), dev(gpu_ctx, rd), seg_start, seg_len, metric, seed=1)
+    assert rounds2 == rounds and torch.equal(d_knn, d_knn2)
+
+
+def test_large_path_stages_match_oracle(gpu_ctx):
+    base, queries = helpers.small_dataset("uniform", 1500, 16, 60, seed=5)
+    C = 3
+    centroids, _, _ = oracle.kmeans(base[:300], C, 10)
+    seg_index, seg_start, seg_len = oracle.define_partition(base, centroids, -1.0)
+    rd, mapping = oracle.reorder(base, seg_index, seg_start, 0)
+    want_routes = oracle.select_segments(queries, centroids, 2, 1.2)
+    d_q = dev(gpu_ctx, queries)
+    d_routes = api.select_segments(gpu_ctx, d_q, dev(gpu_ctx, centroids), 2, 1.2)
+    assert np.array_equal(api.to_u32(d_routes), want_routes)
+    o = oracle.SearchParams.derive(64, 16)
+    ob = oracle.SearchParams.derive(64, 16)
+    want_ids = np.full((60, 10), INVALID, np.uint32)
+    want_d = np.full((60, 10), np.finfo(np.float32).max, np.float32)
+    d_fi = dev(gpu_ctx, want_ids.copy())
+    d_fd = dev(gpu_ctx, want_d.copy())
+    for s in range(C):
+        lo, ln = int(seg_start[s]), int(seg_len[s])
+        part = rd[lo:lo + ln]
+        knn = helpers.exact_partition_knn(part, np.array([0], np.uint32), np.array([ln], np.uint32), 16, oracle.EUCLIDEAN)
+        # build_for_large / refine_for_large on the resident partition
+        one = np.array([0], np.uint32)
+        want_g = oracle.build_rows(part, knn.view(np.uint32), one, np.array([ln], np.uint32), np.array([5], np.uint32),
+                                   np.arange(ln, dtype=np.uint32), ln, 24, ob, 1.05)
+        d_part = dev(gpu_ctx, part)
+        d_g = api.build_partition(gpu_ctx, d_part, dev(gpu_ctx, knn.view(np.uint32)), 5, 24, sp_from(ob), 1.05)
+        assert np.array_equal(api.to_u32(d_g), want_g)
+        oracle.search_on_sub(part, want_g, mapping[lo:lo + ln], 5, queries, want_routes, s, o, want_ids, want_d)
+        api.search_on_sub(gpu_ctx, d_part, d_g, dev(gpu_ctx, mapping[lo:lo + ln]), 5, d_q, d_routes, s, sp_from(o),
+                          d_fi, d_fd)
+    assert np.array_equal(api.to_u32(d_fi), want_ids)
+    assert np.array_equal(d_fd.cpu().numpy(), want_d)
+
+
+def test_unsupported_shapes_are_rejected(gpu_ctx):
+    base, queries, P = case("uniform16")
+    index = api.GLIDE(gpu_ctx, 16, base, P["centroids"])
+    index.load(P["graph"], P["orig_sp"])
+    bad = SearchParameter(top_k=10, beam=544, max_iterations=10, hash_bit=11, hash_reset_interval=1)
+    with pytest.raises(api.UnsupportedError):  # kernel_config.cuh:47-48 "Unsupported beam"
+        index.search(bad, dev(gpu_ctx, queries))
+    with pytest.raises(api.GlideError):
+        index.search(SearchParameter(top_k=10, beam=48, max_iterations=10, hash_bit=8, hash_reset_interval=1),
+                     dev(gpu_ctx, queries))
+    with pytest.raises(api.GlideError):  # top_k > beam
+        index.search(SearchParameter(top_k=40, beam=32, max_iterations=10, hash_bit=8, hash_reset_interval=1),
+                     dev(gpu_ctx, queries))
+    # the context stays usable after a rejected call
+    ok = SearchParameter(top_k=10, beam=32).derive(16)
+    ids, _, _ = index.search(ok, dev(gpu_ctx, queries))
+    assert ids.shape == (queries.shape[0], 10)
+
+
+def test_empty_query_batch(gpu_ctx):
+    base, queries, P = case("uniform16")
+    index = api.GLIDE(gpu_ctx, 16, base, P["centroids"])
+    index.load(P["graph"], P["orig_sp"])
+    ids, d, _ = index.search(SearchParameter(top_k=10, beam=32).derive(16), dev(gpu_ctx, queries[:0]))
+    assert ids.shape == (0, 10) and d.shape == (0, 10)
+
+
+def test_cfg0_pipeline_recall(gpu_ctx):
+    """Tiny correctness build: 10,000 x 32 uniform, degree 32, NN-descent 8 iterations, one partition."""
+    from glide_b200 import datasets, pipeline
+    spec = datasets.CONFIGS["cfg0"]
+    base, queries = datasets.make(spec)
+    cfg = pipeline.BuildConfig(centroid_num=1, knn_degree=32, graph_degree=32, nnd_max_iterations=8, seed=0)
+    res = pipeline.build_small(gpu_ctx, dev(gpu_ctx, base), cfg, keep_intermediates=True)
+    assert res.h_segment_length.tolist() == [10000, 0]
+    gt = oracle.bruteforce_knn(base, queries, 10, want_dists=False)
+    # kNN graph quality
+    exact = helpers.exact_partition_knn(res.d_reorder_data.cpu().numpy(), res.h_segment_start, res.h_segment_length, 10, 0)
+    assert knn_recall(res.d_knn.cpu().numpy(), exact, 10) >= 0.9
+    graph = api.to_u32(res.index.graph_view())
+    assert (graph != INVALID).all(axis=1).mean() > 0.99
+    recalls = {}
+    for beam in (32, 64, 128):
+        sp = pipeline.derive_search_params(beam, 32)
+        ids, dists, _ = res.index.search(sp, dev(gpu_ctx, queries))
+        recalls[beam] = api.calculate_recall(ids, gt, 10)
+        o = oracle.SearchParams(sp.beam, sp.max_iterations, sp.min_iterations, sp.hash_bit, sp.hash_reset_interval, 10)
+        want_ids, want_d = oracle.search(base, graph, res.index.centroid_view().cpu().numpy(),
+                                         api.to_u32(res.index.start_point_view()), queries, o)
+        assert np.array_equal(ids, want_ids) and np.array_equal(dists, want_d)
+    assert recalls[64] >= 0.95 and recalls[128] >= recalls[64] - 1e-6
+    # the GPU-built graph equals the oracle's graph built from the same kNN graph and start points
+    P = dict(rd=res.d_reorder_data.cpu().numpy(), knn=res.d_knn.cpu().numpy().view(np.uint32), mp=api.to_u32(res.d_map))
+    p_knn, p_ref = pipeline.derive_build_search_params(cfg)
+    local, original = api.start_point_select(res.h_segment_start, res.h_segment_length, P["mp"], cfg.seed)
+    ok = oracle.SearchParams(p_knn.beam, p_knn.max_iterations, 0, p_knn.hash_bit, p_knn.hash_reset_interval)
+    orf = oracle.SearchParams(p_ref.beam, p_ref.max_iterations, 0, p_ref.hash_bit, p_ref.hash_reset_interval)
+    want = oracle.build_rows(P["rd"], P["knn"], res.h_segment_start, res.h_segment_length, local, P["mp"], 10000, 32, ok, 1.05)
+    oracle.reverse_graph(want)
+    want = oracle.refine(base, want, res.index.centroid_view().cpu().numpy(), original, orf, 1.05)
+    assert np.array_equal(graph, want)
