@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: build seconds and search QPS at recall@10 >= 0.95.
+
+    python bench.py --gpus N --steps K --warmup W [--config cfg1] [--impl reference]
+
+A step is one pass of the search kernel over one batch of Q queries (10,000 for cfg1)
+at the smallest beam of a fixed ladder that reaches recall@10 >= 0.95 against exact
+kNN; the index is built once before the timed region and its stage times are reported
+under "build". `value` is queries/s with queries resident in HBM (sum over ranks / max
+time over ranks); `e2e` is the same through the host-buffer entry point with the H2D
+and D2H copies inside the timed region. Under torchrun every rank holds a replica of the
+index and searches its own query batch (weak scaling, no data-path collective).
+
+`--impl reference`: the reference is CUDA-only and cannot be built here, so this arm
+times exact brute-force kNN (recall 1.0) on the host cores, a bounded sample of queries
+per step.
+
+Data are seeded synthetic stand-ins with the shapes and value ranges of the named config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BEAM_LADDER = [10, 15, 20, 25, 30, 35, 40, 45, 50, 60, 70, 80, 100, 120, 150, 200, 256, 384, 512]
+TARGET_RECALL = 0.95
+TOP_K = 10
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="cfg1")
+    ap.add_argument("--rows", type=int, default=0, help="use only the first ROWS base rows (debugging; marks the run reduced)")
+    ap.add_argument("--queries", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the host baseline sample")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms during the timed region."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.device_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def load_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def make_data(args):
+    from glide_b200 import datasets
+    spec = datasets.CONFIGS[args.config]
+    reduced = False
+    if args.rows and args.rows < spec.n:
+        spec = datasets.scaled(spec, args.rows, args.queries or spec.n_queries)
+        reduced = True
+    elif args.queries:
+        spec = datasets.scaled(spec, spec.n, args.queries)
+    return spec, reduced
+
+
+def cpu_bruteforce_qps(base, queries, seconds_target, metric):
+    """Exact kNN on all host cores over a bounded sample of the queries."""
+    import oracle
+    cores = oracle.max_threads()
+    probe = min(len(queries), max(cores, 8))
+    t0 = time.perf_counter()
+    oracle.bruteforce_knn(base, queries[:probe], TOP_K, metric, threads=cores, want_dists=False)
+    per_query = (time.perf_counter() - t0) / probe
+    sample = int(min(len(queries), max(probe, seconds_target / max(per_query, 1e-9))))
+    t0 = time.perf_counter()
+    oracle.bruteforce_knn(base, queries[:sample], TOP_K, metric, threads=cores, want_dists=False)
+    dt = time.perf_counter() - t0
+    return sample / dt, cores, sample, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from glide_b200 import datasets
+    oracle.build()
+    spec, reduced = make_data(args)
+    cent = datasets.centres(spec)
+    base = datasets.base_rows(spec, cent=cent)
+    queries = datasets.queries(spec, cent=cent)
+    metric = oracle.EUCLIDEAN if spec.metric == "Euclidean" else oracle.COSINE
+    cores = oracle.max_threads()
+    # size one step at about cpu_seconds / (steps + warmup)
+    probe = min(len(queries), max(cores, 8))
+    t0 = time.perf_counter()
+    oracle.bruteforce_knn(base, queries[:probe], TOP_K, metric, threads=cores, want_dists=False)
+    per_query = (time.perf_counter() - t0) / probe
+    budget = max(args.cpu_seconds * 4, 20.0) / max(args.steps + args.warmup, 1)
+    sample = int(min(len(queries), max(probe, budget / max(per_query, 1e-9))))
+    for _ in range(args.warmup):
+        oracle.bruteforce_knn(base, queries[:sample], TOP_K, metric, threads=cores, want_dists=False)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        lo = (s * sample) % max(len(queries) - sample + 1, 1)
+        oracle.bruteforce_knn(base, queries[lo:lo + sample], TOP_K, metric, threads=cores, want_dists=False)
+    dt = time.perf_counter() - t0
+    qps = args.steps * sample / dt
+    line = {
+        "impl": "reference", "metric": "search QPS @ recall@10>=0.95", "value": qps, "unit": "queries/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{spec.name}: {spec.n}x{spec.dim} fp32 {spec.metric}, {spec.n_queries} queries, k={TOP_K}",
+                   "reduced": reduced, "l2": "base set larger than L2"},
+        "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port",
+                         "sample": f"exact brute-force kNN (recall 1.0), {sample} queries per step on {cores} host threads"},
+        "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "recall_at_10": 1.0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from glide_b200 import api, datasets, pipeline
+    from glide_b200.params import Metric
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = api.Context(local_rank)
+    dev = ctx.torch_device
+
+    spec, reduced = make_data(args)
+    metric = Metric.parse(spec.metric)
+    cent = datasets.centres(spec)
+    base = datasets.base_rows(spec, cent=cent)
+    # every rank searches its own batch from the same distribution (weak scaling)
+    qspec = datasets.DatasetSpec(spec.name, spec.n, spec.dim, spec.n_queries, spec.kind, spec.centres, spec.metric,
+                                 spec.graph_degree, spec.seed + 1000 * rank)
+    queries = datasets.queries(spec, cent=cent) if rank == 0 else datasets._rows(qspec, cent, 2 + rank, 0, spec.n_queries)
+    d_base = torch.from_numpy(base).to(dev)
+    d_queries = torch.from_numpy(queries).to(dev)
+    Q = queries.shape[0]
+
+    # ---- build (untimed region of the step loop, reported on its own) ----
+    cfg = pipeline.BuildConfig(metric=metric, graph_degree=spec.graph_degree, knn_degree=32,
+                               centroid_num=1 if spec.n <= 20000 else 10, seed=spec.seed)
+    t0 = time.perf_counter()
+    res = pipeline.build_small(ctx, d_base, cfg)
+    build_wall = time.perf_counter() - t0
+    index = res.index
+
+    # ---- ground truth: exact kNN on the GPU, checked against the host on a few queries ----
+    gt_ids, _ = api.bruteforce_knn(ctx, d_base, d_queries, TOP_K, metric)
+    gt = api.to_u32(gt_ids)
+    gt_seconds = ctx.last_kernel_seconds
+
+    # ---- smallest ladder beam reaching the target recall ----
+    chosen, curve = None, []
+    for beam in BEAM_LADDER:
+        sp = pipeline.derive_search_params(beam, spec.graph_degree, TOP_K)
+        ids, _, sec = index.search(sp, d_queries)
+        rec = api.calculate_recall(ids, gt, TOP_K)
+        curve.append({"beam": beam, "recall": round(rec, 4), "qps": round(Q / sec, 1)})
+        if rec >= TARGET_RECALL:
+            chosen = (beam, sp, rec)
+            break
+    if chosen is None:
+        beam = BEAM_LADDER[-1]
+        chosen = (beam, pipeline.derive_search_params(beam, spec.graph_degree, TOP_K), curve[-1]["recall"])
+    beam, sp, recall = chosen
+
+    # ---- traffic counters of one search pass (untimed) ----
+    ctx.enable_counters(True)
+    index.search(sp, d_queries)
+    rows_read, expansions, _ = ctx.read_counters()
+    ctx.enable_counters(False)
+    C = index.centroid_num()
+    algo_bytes = (rows_read * spec.dim * 4 + expansions * spec.graph_degree * 4 +
+                  Q * (spec.dim * 4 + C * spec.dim * 4 + spec.graph_degree * 4 + TOP_K * 8))
+
+    flush = torch.empty(512 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)  # 512 MB > 126 MB L2
+
+    def flush_l2():
+        flush.add_(1.0)
+        torch.cuda.synchronize(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    d_ids = api._u32_tensor(ctx, (Q, TOP_K))
+    d_dists = ctx.empty((Q, TOP_K), torch.float32)
+    pc = api._params_c(sp)
+    import ctypes as C_
+
+    def search_once():
+        ctx.check(ctx.lib.glide_search(ctx.handle, d_base.data_ptr(), index.num(), index.dim(), index.d_graph.data_ptr(),
+                                       index.graph_degree(), index.d_centroids.data_ptr(), C,
+                                       index.d_start_points.data_ptr(), d_queries.data_ptr(), Q, C_.byref(pc),
+                                       int(metric), d_ids.data_ptr(), d_dists.data_ptr()))
+        return ctx.lib.glide_last_kernel_ms(ctx.handle)
+
+    for _ in range(args.warmup):
+        flush_l2()
+        search_once()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    kernel_ms = 0.0
+    for _ in range(args.steps):
+        flush_l2()
+        kernel_ms += search_once()   # CUDA events on the launching stream, around the kernel
+    barrier()
+    # ---- end to end through the host-buffer entry point (pinned host memory) ----
+    h_q = torch.from_numpy(queries).pin_memory()
+    h_ids = torch.empty((Q, TOP_K), dtype=torch.int32).pin_memory()
+    h_d = torch.empty((Q, TOP_K), dtype=torch.float32).pin_memory()
+
+    def search_host_once():
+        ctx.check(ctx.lib.glide_search_host(ctx.handle, d_base.data_ptr(), index.num(), index.dim(),
+                                            index.d_graph.data_ptr(), index.graph_degree(),
+                                            index.d_centroids.data_ptr(), C, index.d_start_points.data_ptr(),
+                                            h_q.data_ptr(), Q, C_.byref(pc), int(metric), h_ids.data_ptr(),
+                                            h_d.data_ptr()))
+
+    for _ in range(args.warmup):
+        flush_l2()
+        search_host_once()
+    e2e_s = 0.0
+    barrier()
+    for _ in range(args.steps):
+        flush_l2()
+        t0 = time.perf_counter()
+        search_host_once()   # returns after the results are in host memory
+        e2e_s += time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_recall = api.calculate_recall(h_ids.numpy().view(np.uint32), gt, TOP_K)
+
+    t = torch.tensor([kernel_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    max_kernel_ms, max_e2e_ms = float(t[0]), float(t[1])
+    qps = world * Q * args.steps / (max_kernel_ms / 1e3)
+    e2e_qps = world * Q * args.steps / (max_e2e_ms / 1e3)
+
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        achieved = algo_bytes / (kernel_ms / args.steps / 1e3) / 1e9
+        line = {
+            "metric": "search QPS @ recall@10>=0.95", "value": qps, "unit": "queries/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": max_kernel_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{spec.name}: {spec.n}x{spec.dim} fp32 {spec.metric}, {Q} queries per rank, "
+                                   f"k={TOP_K}, graph degree {spec.graph_degree}, {cfg.centroid_num} partitions",
+                       "beam": beam, "beam_rounded": sp.beam, "max_iterations": sp.max_iterations, "reduced": reduced,
+                       "l2": "512 MB buffer rewritten between timed iterations",
+                       "multi_gpu": "one index replica and one query batch per rank" if world > 1 else "single GPU"},
+            "recall_at_10": round(recall, 4),
+            "build": {"seconds": round(res.total_seconds, 4), "wall_seconds": round(build_wall, 3),
+                      "stages": {k: round(v, 4) for k, v in res.seconds.items()}, "nnd_rounds": res.nnd_rounds,
+                      "ground_truth_seconds": round(gt_seconds, 4)},
+            "recall_curve": curve,
+            "e2e": {"value": e2e_qps, "unit": "queries/s", "h2d_bytes_per_step": Q * spec.dim * 4,
+                    "d2h_bytes_per_step": Q * TOP_K * 8, "recall_at_10": round(e2e_recall, 4)},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "search_kernel", "algorithmic_bytes_per_launch": int(algo_bytes),
+                         "rows_read_per_launch": int(rows_read), "expansions_per_launch": int(expansions)},
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            import oracle
+            ometric = oracle.EUCLIDEAN if spec.metric == "Euclidean" else oracle.COSINE
+            cqps, cores, sample, dt = cpu_bruteforce_qps(base, queries, args.cpu_seconds, ometric)
+            # the same sample validates the GPU ground truth
+            ref = oracle.bruteforce_knn(base, queries[:min(sample, 64)], TOP_K, ometric, want_dists=False)
+            line["cpu_baseline"] = {"value": cqps, "unit": "queries/s", "cores": cores, "kind": "port",
+                                    "sample": f"exact brute-force kNN (recall 1.0) of {sample} queries in {dt:.1f} s",
+                                    "gt_agreement": float((ref == gt[:ref.shape[0]]).mean())}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    ctx.close()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

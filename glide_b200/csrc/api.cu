@@ -592,6 +592,7 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
                  const float *d_queries, uint32_t q, const glide_search_params *p, int metric, uint32_t *d_out_ids,
                  float *d_out_dists) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
+    if (q == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }  // an empty batch is valid and launches nothing
     GL_REQUIRE(ctx, d_data && d_graph && d_centroids && d_start_points && d_queries && d_out_ids && d_out_dists,
                GLIDE_ERR_BAD_ARG, "search: null pointer");
     GL_REQUIRE(ctx, num > 0 && dim > 0 && C >= 1, GLIDE_ERR_BAD_ARG, "search: zero size");
@@ -616,6 +617,7 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
                       const float *h_queries, uint32_t q, const glide_search_params *p, int metric,
                       uint32_t *h_out_ids, float *h_out_dists) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
+    if (q == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
     GL_REQUIRE(ctx, h_queries && h_out_ids && h_out_dists && p, GLIDE_ERR_BAD_ARG, "search_host: null pointer");
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t qb = align256((size_t) q * dim * 4), rb = align256((size_t) q * p->top_k * 4);
