@@ -32,12 +32,12 @@ SIGNATURES = {
     "glide_adjust_search_params": (None, [u32, P(u32), P(u32)]),
     "glide_get_centroids": (i32, [vp, vp, u32, u32, u32, f32, u64, u32, i32, vp, P(u32)]),
     "glide_sample_ids": (i32, [u32, u32, u64, vp]),
-    "glide_kmeans_fit": (i32, [vp, vp, u32, u32, u32, u32, i32, vp, vp, P(u32)]),
+    "glide_kmeans_fit": (i32, [vp, vp, u32, u32, u32, u32, i32, i32, vp, vp, P(u32)]),
     "glide_define_partition": (i32, [vp, vp, u32, u32, vp, u32, f32, i32, vp, vp, vp]),
     "glide_reorder": (i32, [vp, vp, u32, u32, vp, vp, u32, vp, vp]),
     "glide_preprocess": (i32, [vp, vp, u32, u32, u32, f32, f32, i32, u64, vp, vp, vp, P(vp), P(vp), P(u32)]),
     "glide_free": (None, [vp]),
-    "glide_build_nnd": (i32, [vp, vp, u32, u32, vp, vp, u32, u32, u32, f32, u32, u64, i32, vp, P(u32)]),
+    "glide_build_nnd": (i32, [vp, vp, u32, u32, vp, vp, u32, u32, u32, f32, u32, u32, u64, i32, vp, P(u32)]),
     "glide_bruteforce_knn": (i32, [vp, vp, u32, vp, u32, u32, u32, i32, vp, vp]),
     "glide_start_point_select": (i32, [vp, vp, u32, vp, u64, vp, vp]),
     "glide_subgraph_build_and_merge": (i32, [vp, vp, u32, u32, vp, u32, vp, vp, u32, vp, vp, u32, u32,

@@ -136,13 +136,13 @@ def get_centroids(ctx: Context, d_data: torch.Tensor, centroid_num: int, sample_
 
 
 def kmeans_fit(ctx: Context, d_sample: torch.Tensor, centroid_num: int, max_iter: int = 0,
-               metric: Metric = Metric.Euclidean):
+               metric: Metric = Metric.Euclidean, init: int = 1):
     n, dim = d_sample.shape
     d_centroids = ctx.empty((centroid_num, dim), torch.float32)
     d_labels = _u32_tensor(ctx, (n,))
     rounds = C.c_uint32(0)
     ctx.sync_inputs()
-    ctx.check(ctx.lib.glide_kmeans_fit(ctx.handle, _ptr(d_sample), n, dim, centroid_num, max_iter, int(metric),
+    ctx.check(ctx.lib.glide_kmeans_fit(ctx.handle, _ptr(d_sample), n, dim, centroid_num, max_iter, int(metric), init,
                                        _ptr(d_centroids), _ptr(d_labels), C.byref(rounds)))
     return d_centroids, d_labels, rounds.value
 
@@ -191,11 +191,13 @@ def preprocess(ctx: Context, param: PartitionParameter, d_data: torch.Tensor, se
 
 
 def build_nnd(ctx: Context, param: NNDescentParameter, d_data: torch.Tensor, h_segment_start: np.ndarray,
-              h_segment_length: np.ndarray, metric: Metric = Metric.Euclidean, seed: int = 0, sample: int = 0):
+              h_segment_length: np.ndarray, metric: Metric = Metric.Euclidean, seed: int = 0, sample: int = 0,
+              exact_max_rows: int = 0xFFFFFFFF):
     """``build_nnd`` of nn_descent.cuh:1405-1467. Returns (d_knn int32 [rows, degree], rounds, seconds).
 
     As in the reference the output degree is min(graph_degree, intermediate_graph_degree)
-    (nn_descent.cuh:1423-1425) and ids are partition-local.
+    (nn_descent.cuh:1423-1425) and ids are partition-local. Partitions of at most
+    ``exact_max_rows`` rows are solved exactly by all pairs (default 16384; 0 = descent everywhere).
     """
     rows, dim = d_data.shape
     degree = min(param.graph_degree, param.intermediate_graph_degree)
@@ -205,8 +207,8 @@ def build_nnd(ctx: Context, param: NNDescentParameter, d_data: torch.Tensor, h_s
     seg_len = np.ascontiguousarray(h_segment_length, np.uint32)
     ctx.sync_inputs()
     ctx.check(ctx.lib.glide_build_nnd(ctx.handle, _ptr(d_data), rows, dim, _ptr(seg_start), _ptr(seg_len), seg_start.size,
-                                      degree, param.max_iterations, param.termination_threshold, sample, seed,
-                                      int(metric), _ptr(d_knn), C.byref(rounds)))
+                                      degree, param.max_iterations, param.termination_threshold, sample,
+                                      exact_max_rows, seed, int(metric), _ptr(d_knn), C.byref(rounds)))
     return d_knn, rounds.value, ctx.last_kernel_seconds
 
 

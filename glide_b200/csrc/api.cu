@@ -244,7 +244,7 @@ int glide_memset_u32(glide_ctx *ctx, uint32_t *d_dst, uint32_t value, size_t cou
 
 // ---- partition ---------------------------------------------------------------------------
 int glide_kmeans_fit(glide_ctx *ctx, const float *d_sample, uint32_t n, uint32_t dim, uint32_t C, uint32_t max_iter,
-                     int metric, float *d_centroids, uint32_t *d_labels_or_null, uint32_t *iterations_run) {
+                     int metric, int init, float *d_centroids, uint32_t *d_labels_or_null, uint32_t *iterations_run) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
     GL_REQUIRE(ctx, d_sample && d_centroids && dim > 0, GLIDE_ERR_BAD_ARG, "kmeans: null pointer or zero dim");
     GL_REQUIRE(ctx, C >= 1 && n >= C, GLIDE_ERR_BAD_ARG, "kmeans: fewer rows than centroids");
@@ -252,7 +252,8 @@ int glide_kmeans_fit(glide_ctx *ctx, const float *d_sample, uint32_t n, uint32_t
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
     if (max_iter == 0) max_iter = 25;
     const size_t need = 4 * align256((size_t) n * 4) + align256(slot_scratch_words(n, C) * 4) +
-                        3 * align256((size_t) (C + 2) * 4) + align256(scan_tmp_bytes(C + 1)) + 256;
+                        3 * align256((size_t) (C + 2) * 4) + align256(scan_tmp_bytes(C + 1)) + 256 +
+                        align256(farthest_first_scratch_bytes(n));
     int rc = ensure_ws(ctx, need);
     if (rc) return rc;
     Bump b(ctx->ws);
@@ -261,9 +262,14 @@ int glide_kmeans_fit(glide_ctx *ctx, const float *d_sample, uint32_t n, uint32_t
     uint32_t *hist = b.take<uint32_t>(slot_scratch_words(n, C));
     uint32_t *cnt = b.take<uint32_t>(C + 2), *off = b.take<uint32_t>(C + 2), *changed = b.take<uint32_t>(C + 2);
     void *scan_tmp = b.take<char>(scan_tmp_bytes(C + 1));
+    void *ff_tmp = b.take<char>(farthest_first_scratch_bytes(n));
     cudaStream_t st = ctx->stream;
     Timed timer(ctx);
-    GL_CUDA(ctx, cudaMemcpyAsync(d_centroids, d_sample, (size_t) C * dim * 4, cudaMemcpyDeviceToDevice, st));
+    if (init == 0) {
+        GL_CUDA(ctx, cudaMemcpyAsync(d_centroids, d_sample, (size_t) C * dim * 4, cudaMemcpyDeviceToDevice, st));
+    } else {
+        GL_CUDA(ctx, launch_farthest_first(d_sample, n, dim, C, d_centroids, ff_tmp, st));
+    }
     GL_CUDA(ctx, cudaMemsetAsync(labels_b, 0xff, (size_t) n * 4, st));
     uint32_t rounds = 0;
     uint32_t *cur = labels_a, *prev = labels_b;
@@ -328,7 +334,7 @@ int glide_get_centroids(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_
     if (e == cudaSuccess) e = launch_gather_rows(d_data, d_ids, sample_num, dim, d_sample, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) rc = fail(ctx, GLIDE_ERR_CUDA, "sample gather failed: %s", cudaGetErrorString(e));
-    if (rc == GLIDE_OK) rc = glide_kmeans_fit(ctx, d_sample, sample_num, dim, C, max_iter, metric, d_centroids, nullptr, iterations_run);
+    if (rc == GLIDE_OK) rc = glide_kmeans_fit(ctx, d_sample, sample_num, dim, C, max_iter, metric, 1, d_centroids, nullptr, iterations_run);
     cudaFree(d_sample);
     cudaFree(d_ids);
     return rc;
@@ -424,8 +430,8 @@ int glide_preprocess(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t d
 // ---- kNN -----------------------------------------------------------------------------------
 int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, uint32_t dim,
                     const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t S, uint32_t knn_degree,
-                    uint32_t max_iterations, float termination_threshold, uint32_t sample, uint64_t seed, int metric,
-                    int32_t *d_knn, uint32_t *iterations_run) {
+                    uint32_t max_iterations, float termination_threshold, uint32_t sample, uint32_t exact_max_rows,
+                    uint64_t seed, int metric, int32_t *d_knn, uint32_t *iterations_run) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
     GL_REQUIRE(ctx, d_reorder_data && h_segment_start && h_segment_length && d_knn, GLIDE_ERR_BAD_ARG, "build_nnd: null pointer");
     GL_REQUIRE(ctx, rows > 0 && dim > 0 && S >= 1, GLIDE_ERR_BAD_ARG, "build_nnd: zero size");
@@ -442,19 +448,33 @@ int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, 
     GL_REQUIRE(ctx, covered == rows, GLIDE_ERR_BAD_ARG, "build_nnd: segment lengths do not sum to the row count");
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
     const uint32_t K = knn_degree <= 32 ? 32 : 64;
-    const size_t nnd_bytes = nnd_workspace_bytes(rows, K, sample);
-    int rc = ensure_ws(ctx, nnd_bytes + 2 * align256((size_t) S * 4));
+    // partitions of at most exact_max_rows rows: all pairs; larger ones: NN-descent
+    if (exact_max_rows == 0xffffffffu) exact_max_rows = 16384;
+    const uint32_t tile_count = segment_knn_tile_count(h_segment_length, S, exact_max_rows);
+    bool need_nnd = false;
+    for (uint32_t s = 0; s < S; s++) need_nnd = need_nnd || h_segment_length[s] > exact_max_rows;
+    const size_t nnd_bytes = need_nnd ? nnd_workspace_bytes(rows, K, sample) : 0;
+    int rc = ensure_ws(ctx, nnd_bytes + 2 * align256((size_t) S * 4) + align256((size_t) tile_count * 12) + 256);
     if (rc) return rc;
     Bump b(ctx->ws);
     uint32_t *d_start = b.take<uint32_t>(S), *d_len = b.take<uint32_t>(S);
+    uint32_t *d_tiles = b.take<uint32_t>((size_t) tile_count * 3 + 1);
     void *work = b.take<char>(nnd_bytes);
+    std::vector<uint32_t> h_tiles((size_t) tile_count * 3 + 1);
+    segment_knn_fill_tiles(h_segment_start, h_segment_length, S, exact_max_rows, h_tiles.data());
     // empty segments (C == 1 leaves the boundary segment empty, partition_kernel.cuh:58) need no launch
     Timed timer(ctx);
     GL_CUDA(ctx, cudaMemcpyAsync(d_start, h_segment_start, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
     GL_CUDA(ctx, cudaMemcpyAsync(d_len, h_segment_length, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if (iterations_run) *iterations_run = 0;
+    if (tile_count) {
+        GL_CUDA(ctx, cudaMemcpyAsync(d_tiles, h_tiles.data(), (size_t) tile_count * 12, cudaMemcpyHostToDevice, ctx->stream));
+        GL_CUDA(ctx, launch_segment_knn(d_reorder_data, dim, d_tiles, tile_count, knn_degree, d_knn, ctx->stream));
+    }
+    if (!need_nnd) return timer.finish();
     NndArgs a{};
     a.data = d_reorder_data; a.rows = rows; a.dim = dim;
-    a.seg_start = d_start; a.seg_len = d_len; a.S = S;
+    a.seg_start = d_start; a.seg_len = d_len; a.S = S; a.min_seg_len = exact_max_rows + 1;
     a.K = K; a.sample = sample; a.max_iterations = max_iterations; a.termination_threshold = termination_threshold;
     a.seed = seed; a.metric = metric; a.workspace = work; a.workspace_bytes = nnd_bytes;
     a.out_knn = d_knn; a.out_degree = knn_degree; a.iterations_run = iterations_run; a.stage_ms = nullptr;

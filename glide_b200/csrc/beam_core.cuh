@@ -121,12 +121,19 @@ __device__ __forceinline__ uint32_t seed_from_row(const WarpStrip &s, uint32_t s
     return score_candidates(s, degree, exclude_id, data, dim, metric);
 }
 
-// search_kernel.cuh:258-269: distances to all centroids, sorted with the network of
-// width max_centroid (power of two >= C, >= 32); returns the nearest centroid's id.
-// scratch: 2 * max_centroid words.
+// search_kernel.cuh:258-269: distances to all centroids, ordered as the reference's
+// network of width max_centroid (power of two >= C, >= 32) orders them; returns the nearest
+// centroid's id. scratch: 2 * max_centroid words (keys then ids). What is valid afterwards
+// depends on `need`: kNearestOnly - nothing else; kTopTwo - keys[0], keys[1], ids[0];
+// kSorted - both arrays fully sorted. When the smallest distance is unique the first two
+// need no sort (position 0 of the sorted list is the minimum whatever the network does);
+// a tie at the minimum falls back to the full network so that the reference's tie order
+// is reproduced.
+enum CentroidNeed : int { kNearestOnly = 0, kTopTwo = 1, kSorted = 2 };
+
 __device__ __forceinline__ uint32_t nearest_centroid(const float *q_smem, const float *__restrict__ centroids,
                                                      uint32_t C, uint32_t max_centroid, uint32_t dim, int metric,
-                                                     uint32_t *scratch) {
+                                                     uint32_t *scratch, int need) {
     const uint32_t lane = lane_id(), team = lane / kTeam;
     const uint32_t n = max_centroid / 32;
     float *ck = reinterpret_cast<float *>(scratch);
@@ -150,6 +157,35 @@ __device__ __forceinline__ uint32_t nearest_centroid(const float *q_smem, const 
         }
     }
     __syncwarp();
+    if (need != kSorted) {
+        float m0 = FLT_MAX;
+        for (uint32_t e = lane; e < max_centroid; e += 32)
+            if (cv[e] != kInvalid && ck[e] < m0) m0 = ck[e];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) m0 = fminf(m0, __shfl_xor_sync(kFullMask, m0, off));
+        uint32_t cnt = 0, pos = 0;
+        for (uint32_t e = lane; e < max_centroid; e += 32)
+            if (cv[e] != kInvalid && ck[e] == m0) { cnt++; pos = e; }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            cnt += __shfl_xor_sync(kFullMask, cnt, off);
+            pos = max(pos, __shfl_xor_sync(kFullMask, pos, off));
+        }
+        if (cnt == 1) {
+            const uint32_t id = cv[pos];
+            if (need == kTopTwo) {
+                float m1 = FLT_MAX;
+                for (uint32_t e = lane; e < max_centroid; e += 32)
+                    if (e != pos && cv[e] != kInvalid && ck[e] < m1) m1 = ck[e];
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) m1 = fminf(m1, __shfl_xor_sync(kFullMask, m1, off));
+                __syncwarp();
+                if (lane == 0) { ck[0] = m0; ck[1] = m1; cv[0] = id; }
+                __syncwarp();
+            }
+            return id;
+        }
+    }
     warp_sort_smem(ck, cv, n);
     return cv[0];
 }

@@ -173,6 +173,143 @@ __global__ void __launch_bounds__(128) bruteforce_merge_kernel(const Cand *__res
     }
 }
 
+// ---------------------------------------------------------------------------
+// Per-partition exact kNN graph: every row against all rows of its own partition. This
+// is the kNN stage for partitions small enough that all pairs cost less than NN-descent
+// would. A CTA owns up to 64 rows of one partition (tile table built on the host) and
+// walks that partition in tiles of 128 rows; rows beating the current k-th best are
+// queued as 64-bit keys (distance bits | local id), and after every tile one warp per row
+// sorts its queue in registers and folds it into the row's sorted list with one bitonic
+// merge. Output: partition-local ids, self excluded, nearest first.
+// ---------------------------------------------------------------------------
+constexpr u64 kNoKey = ((u64) 0x7f7fffffu << 32) | 0xffffffffull;
+
+struct SegTile {
+    uint32_t seg_start, seg_len, first;  // rows [seg_start + first, +64) of the segment
+};
+
+template<int NL>  // list width = 32 * NL
+__global__ void __launch_bounds__(256, 2) segment_knn_kernel(const float *__restrict__ data, uint32_t dim,
+                                                             const SegTile *__restrict__ tiles, int32_t *out,
+                                                             uint32_t out_degree) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    constexpr uint32_t L = 32u * NL;
+    float *Qs = reinterpret_cast<float *>(smem);                 // [kKT][kQPad]
+    float *Bs = Qs + kKT * kQPad;                                // [kKT][kBPad]
+    u64 *lists = reinterpret_cast<u64 *>(Bs + kKT * kBPad);      // [kQT][L]
+    u64 *queue = lists + kQT * L;                                // [kQT][kBT]
+    uint32_t *qcount = reinterpret_cast<uint32_t *>(queue + kQT * kBT);  // [kQT]
+
+    const SegTile t = tiles[blockIdx.x];
+    const uint32_t tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
+    const uint32_t tx = tid & 15, ty = tid >> 4;
+    const float *seg = data + (uint64_t) t.seg_start * dim;
+    const uint32_t nq = min((uint32_t) kQT, t.seg_len - t.first);
+
+    for (uint32_t i = tid; i < kQT * L; i += 256) lists[i] = kNoKey;
+    if (tid < kQT) qcount[tid] = 0;
+    __syncthreads();
+
+    for (uint32_t r0 = 0; r0 < t.seg_len; r0 += kBT) {
+        float acc[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+        for (uint32_t k0 = 0; k0 < dim; k0 += kKT) {
+            for (uint32_t e = tid; e < kQT * kKT; e += 256) {
+                const uint32_t row = e / kKT, kk = e % kKT;
+                const uint32_t d = k0 + kk;
+                Qs[kk * kQPad + row] = (row < nq && d < dim) ? __ldg(seg + (uint64_t) (t.first + row) * dim + d) : 0.0f;
+            }
+            for (uint32_t e = tid; e < kBT * kKT; e += 256) {
+                const uint32_t row = e / kKT, kk = e % kKT;
+                const uint32_t r = r0 + row, d = k0 + kk;
+                Bs[kk * kBPad + row] = (r < t.seg_len && d < dim) ? __ldg(seg + (uint64_t) r * dim + d) : 0.0f;
+            }
+            __syncthreads();
+#pragma unroll 8
+            for (int kk = 0; kk < kKT; kk++) {
+                const float4 qa = *reinterpret_cast<const float4 *>(Qs + kk * kQPad + 4 * ty);
+                const float4 b0 = *reinterpret_cast<const float4 *>(Bs + kk * kBPad + 8 * tx);
+                const float4 b1 = *reinterpret_cast<const float4 *>(Bs + kk * kBPad + 8 * tx + 4);
+                const float qv[4] = {qa.x, qa.y, qa.z, qa.w};
+                const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const float df = qv[i] - bv[j];
+                        acc[i][j] = __fmaf_rn(df, df, acc[i][j]);
+                    }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t ql = 4 * ty + i;
+            if (ql >= nq) continue;
+            const u64 thr = lists[ql * L + L - 1];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const uint32_t r = r0 + 8 * tx + j;
+                if (r >= t.seg_len || r == t.first + ql) continue;
+                const u64 key = ((u64) __float_as_uint(acc[i][j]) << 32) | r;
+                if (key < thr) queue[ql * kBT + atomicAdd(&qcount[ql], 1u)] = key;
+            }
+        }
+        __syncthreads();
+        for (uint32_t ql = warp; ql < nq; ql += 8) {
+            const uint32_t m = qcount[ql];
+            if (m == 0) continue;
+            u64 *q = queue + ql * kBT;
+            u64 *list = lists + ql * L;
+            // sort the queue (<= 128 keys) ascending, in place
+            if (m <= 32) {
+                u64 k1[1] = {lane < m ? q[lane] : kNoKey};
+                sort_u64<1>(k1);
+                __syncwarp();
+                q[lane] = k1[0];
+                for (uint32_t j = 32 + lane; j < L; j += 32) q[j] = kNoKey;
+            } else {
+                u64 k4[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) k4[i] = (4 * lane + i < m) ? q[4 * lane + i] : kNoKey;
+                sort_u64<4>(k4);
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; i++) q[4 * lane + i] = k4[i];
+            }
+            __syncwarp();
+            // the L smallest of list and queue: list[j] against queue[L-1-j], then one merge phase
+            u64 keys[NL];
+#pragma unroll
+            for (int i = 0; i < NL; i++) {
+                const uint32_t j = NL * lane + i;
+                const u64 a = list[j], b = q[L - 1 - j];
+                keys[i] = a < b ? a : b;
+            }
+            phase_u64<NL>(keys, L, true);
+#pragma unroll
+            for (int i = 0; i < NL; i++) list[NL * lane + i] = keys[i];
+            if (lane == 0) qcount[ql] = 0;
+        }
+        __syncthreads();
+    }
+    for (uint32_t i = tid; i < nq * out_degree; i += 256) {
+        const uint32_t ql = i / out_degree, j = i % out_degree;
+        const uint32_t id = (uint32_t) lists[ql * L + j];
+        const uint64_t flat = (uint64_t) (t.seg_start + t.first + ql) * out_degree + j;
+        uint32_t u = (uint32_t) flat;  // xorshift32, utils.cuh:14-19, as nn_descent.cuh:1384-1391 pads short rows
+        u ^= u >> 13; u ^= u << 27; u ^= u >> 5; u *= 0x9E3779B9u;
+        out[flat] = (int32_t) (id < t.seg_len ? id : u % t.seg_len);
+    }
+}
+
+size_t segment_knn_smem_bytes(uint32_t L) {
+    return (size_t) (kKT * kQPad + kKT * kBPad) * 4 + (size_t) kQT * L * 8 + (size_t) kQT * kBT * 8 + kQT * 4;
+}
+
 size_t tile_smem_bytes(uint32_t k) {
     return (size_t) (kKT * kQPad + kKT * kBPad + 2 * kQT * k + 2 * kQT * kBT + kQT) * 4;
 }
@@ -211,6 +348,41 @@ cudaError_t launch_bruteforce(const float *base, uint32_t n, const float *querie
     const uint32_t warps = 4;
     bruteforce_merge_kernel<<<(Q + warps - 1) / warps, warps * 32, (size_t) warps * 2 * k * 4, stream>>>(
         static_cast<const Cand *>(scratch), Q, k, splits, metric, out_ids, out_dists);
+    return cudaGetLastError();
+}
+
+uint32_t segment_knn_tile_count(const uint32_t *h_seg_len, uint32_t S, uint32_t max_len) {
+    uint32_t tiles = 0;
+    for (uint32_t s = 0; s < S; s++)
+        if (h_seg_len[s] > 0 && h_seg_len[s] <= max_len) tiles += (h_seg_len[s] + kQT - 1) / kQT;
+    return tiles;
+}
+
+void segment_knn_fill_tiles(const uint32_t *h_seg_start, const uint32_t *h_seg_len, uint32_t S, uint32_t max_len,
+                            uint32_t *h_tiles) {
+    SegTile *t = reinterpret_cast<SegTile *>(h_tiles);
+    for (uint32_t s = 0; s < S; s++) {
+        if (h_seg_len[s] == 0 || h_seg_len[s] > max_len) continue;
+        for (uint32_t first = 0; first < h_seg_len[s]; first += kQT) *t++ = SegTile{h_seg_start[s], h_seg_len[s], first};
+    }
+}
+
+cudaError_t launch_segment_knn(const float *data, uint32_t dim, const uint32_t *d_tiles, uint32_t tile_count,
+                               uint32_t out_degree, int32_t *out, cudaStream_t stream) {
+    if (tile_count == 0) return cudaSuccess;
+    if (out_degree == 0 || out_degree > 64) return cudaErrorInvalidValue;
+    const uint32_t L = out_degree <= 32 ? 32 : 64;
+    const size_t smem_bytes = segment_knn_smem_bytes(L);
+    cudaError_t e;
+    if (L == 32) {
+        e = cudaFuncSetAttribute(segment_knn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+        if (e != cudaSuccess) return e;
+        segment_knn_kernel<1><<<tile_count, 256, smem_bytes, stream>>>(data, dim, reinterpret_cast<const SegTile *>(d_tiles), out, out_degree);
+    } else {
+        e = cudaFuncSetAttribute(segment_knn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+        if (e != cudaSuccess) return e;
+        segment_knn_kernel<2><<<tile_count, 256, smem_bytes, stream>>>(data, dim, reinterpret_cast<const SegTile *>(d_tiles), out, out_degree);
+    }
     return cudaGetLastError();
 }
 

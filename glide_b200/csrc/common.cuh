@@ -193,6 +193,42 @@ __device__ __forceinline__ uint32_t visited_insert(uint32_t *table, uint32_t bit
     return 0;
 }
 
+typedef unsigned long long u64;
+
+// ---- u64 bitonic network, N keys per lane, position e = N*lane + i -------------
+template<int N>
+__device__ __forceinline__ void phase_u64(u64 (&k)[N], uint32_t size, bool final_phase) {
+    const uint32_t lane = lane_id();
+    for (uint32_t stride = size >> 1; stride >= (uint32_t) N; stride >>= 1) {
+        const uint32_t ls = stride / N;
+        const bool asc = final_phase || (((N * lane) & size) == 0);
+        const bool keep_small = ((lane & ls) == 0) == asc;
+#pragma unroll
+        for (int i = 0; i < N; i++) {
+            const u64 o = __shfl_xor_sync(kFullMask, k[i], ls);
+            if (keep_small ? (o < k[i]) : (o > k[i])) k[i] = o;
+        }
+    }
+#pragma unroll
+    for (int stride = N / 2; stride >= 1; stride >>= 1) {
+        if ((uint32_t) stride > (size >> 1)) continue;
+#pragma unroll
+        for (int i = 0; i < N; i++) {
+            const int j = i ^ stride;
+            if (i < j) {
+                const bool asc = final_phase || (((N * lane + i) & size) == 0);
+                const u64 a = k[i], b = k[j];
+                if ((a > b) == asc && a != b) { k[i] = b; k[j] = a; }
+            }
+        }
+    }
+}
+template<int N>
+__device__ __forceinline__ void sort_u64(u64 (&k)[N]) {
+#pragma unroll
+    for (uint32_t size = 2; size <= 32u * N; size <<= 1) phase_u64<N>(k, size, size == 32u * N);
+}
+
 __host__ __device__ constexpr uint32_t round_up32(uint32_t x) { return (x + 31u) & ~31u; }
 
 }  // namespace glide

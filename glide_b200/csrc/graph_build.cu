@@ -329,7 +329,8 @@ __global__ void __launch_bounds__(256) build_kernel(const BuildDev d) {
         if (a.mode == kModeRefine) {
             // the centroid scratch sits past the row copy so that it survives
             uint32_t *scratch = s.extra + prune_strip_words(d.max_beam, d.max_degree);
-            const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, scratch);
+            const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, scratch,
+                                                kNearestOnly);
             rows += seed_from_row(s, a.start_points[c], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
                                   a.metric);
         } else {

@@ -115,6 +115,10 @@ cudaError_t launch_centroid_update(const float *sample, uint32_t dim, const uint
                                    cudaStream_t stream);
 cudaError_t launch_scatter_members(const uint32_t *label, const uint32_t *slot, const uint32_t *off, uint32_t n,
                                    uint32_t *member_ids, cudaStream_t stream);
+// k-means initialisation by farthest-first traversal of the sample rows.
+size_t farthest_first_scratch_bytes(uint32_t n);
+cudaError_t launch_farthest_first(const float *sample, uint32_t n, uint32_t dim, uint32_t C, float *centroids,
+                                  void *scratch, cudaStream_t stream);
 cudaError_t launch_count_changed(const uint32_t *a, const uint32_t *b, uint32_t n, uint32_t *count,
                                  cudaStream_t stream);
 
@@ -125,12 +129,21 @@ cudaError_t launch_bruteforce(const float *base, uint32_t n, const float *querie
                               uint32_t k, int metric, uint32_t splits, void *scratch, uint32_t *out_ids,
                               float *out_dists, cudaStream_t stream);
 
+// Exact kNN graph of every partition of at most max_len rows (all pairs inside the
+// partition). Tiles: 3 words each (segment start, segment length, first row), built on the host.
+uint32_t segment_knn_tile_count(const uint32_t *h_seg_len, uint32_t S, uint32_t max_len);
+void segment_knn_fill_tiles(const uint32_t *h_seg_start, const uint32_t *h_seg_len, uint32_t S, uint32_t max_len,
+                            uint32_t *h_tiles);
+cudaError_t launch_segment_knn(const float *data, uint32_t dim, const uint32_t *d_tiles, uint32_t tile_count,
+                               uint32_t out_degree, int32_t *out, cudaStream_t stream);
+
 // ---- nn_descent.cu -------------------------------------------------------
 struct NndArgs {
     const float *data;   // rows x dim (reorder space)
     uint32_t rows, dim;
     const uint32_t *seg_start, *seg_len;  // device, S entries
     uint32_t S;
+    uint32_t min_seg_len;  // partitions with fewer rows are skipped (handled by the exact all-pairs kernel)
     uint32_t K;          // list width (multiple of 32, <= 64)
     uint32_t sample;     // new/old samples per direction (<= 32)
     uint32_t max_iterations;

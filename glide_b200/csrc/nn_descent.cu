@@ -23,8 +23,6 @@ namespace glide {
 
 namespace {
 
-typedef unsigned long long u64;
-
 constexpr uint32_t kP = 32;             // proposal slots per row
 constexpr uint32_t kBestSlots = 4;      // partners kept per participant per join
 constexpr uint32_t kMaxS = 32;          // samples per direction
@@ -43,46 +41,13 @@ __host__ __device__ __forceinline__ uint32_t hash32(uint32_t x) {
     return x;
 }
 
-// ---- u64 bitonic network, N keys per lane, position e = N*lane + i -------------
-template<int N>
-__device__ __forceinline__ void phase_u64(u64 (&k)[N], uint32_t size, bool final_phase) {
-    const uint32_t lane = lane_id();
-    for (uint32_t stride = size >> 1; stride >= (uint32_t) N; stride >>= 1) {
-        const uint32_t ls = stride / N;
-        const bool asc = final_phase || (((N * lane) & size) == 0);
-        const bool keep_small = ((lane & ls) == 0) == asc;
-#pragma unroll
-        for (int i = 0; i < N; i++) {
-            const u64 o = __shfl_xor_sync(kFullMask, k[i], ls);
-            if (keep_small ? (o < k[i]) : (o > k[i])) k[i] = o;
-        }
-    }
-#pragma unroll
-    for (int stride = N / 2; stride >= 1; stride >>= 1) {
-        if ((uint32_t) stride > (size >> 1)) continue;
-#pragma unroll
-        for (int i = 0; i < N; i++) {
-            const int j = i ^ stride;
-            if (i < j) {
-                const bool asc = final_phase || (((N * lane + i) & size) == 0);
-                const u64 a = k[i], b = k[j];
-                if ((a > b) == asc && a != b) { k[i] = b; k[j] = a; }
-            }
-        }
-    }
-}
-template<int N>
-__device__ __forceinline__ void sort_u64(u64 (&k)[N]) {
-#pragma unroll
-    for (uint32_t size = 2; size <= 32u * N; size <<= 1) phase_u64<N>(k, size, size == 32u * N);
-}
-
 struct NndDev {
     const float *data;
     uint32_t rows, dim;
     const uint32_t *seg_start, *seg_len, *row_segment;
     uint32_t K, S;
     uint32_t seed;
+    uint32_t min_len;  // rows of shorter partitions are skipped by every kernel
     u64 *lists;       // rows x K, ascending
     u64 *props;       // rows x kP
     uint32_t *new_s;  // rows x 2S  (forward | reverse)
@@ -112,6 +77,7 @@ __global__ void __launch_bounds__(256) nnd_init_kernel(const NndDev d) {
     float *dists = reinterpret_cast<float *>(ids + K);
     const uint32_t seg = d.row_segment[row];
     const uint32_t start = d.seg_start[seg], len = d.seg_len[seg], self = row - start;
+    if (len < d.min_len) return;
     load_query(query, d.data + (uint64_t) row * d.dim, d.dim);
     uint32_t stride = 1;
     if (len > 2) {
@@ -153,6 +119,7 @@ __global__ void __launch_bounds__(256) nnd_sample_kernel(const NndDev d) {
     if (row >= d.rows) return;
     const uint32_t K = d.K, S = d.S;
     const uint32_t seg = d.row_segment[row];
+    if (d.seg_len[seg] < d.min_len) return;
     const uint32_t start = d.seg_start[seg], self = row - start;
     u64 *list = d.lists + (uint64_t) row * K;
     uint32_t *fnew = d.new_s + (uint64_t) row * 2 * S;
@@ -210,6 +177,7 @@ __global__ void __launch_bounds__(256) nnd_join_kernel(const NndDev d) {
     const uint32_t tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
     const uint32_t S = d.S, K = d.K;
     const uint32_t seg = d.row_segment[row];
+    if (d.seg_len[seg] < d.min_len) return;
     const uint32_t start = d.seg_start[seg];
 
     // raw ids: [0,2S) new, [2S,4S) old
@@ -339,6 +307,7 @@ __global__ void __launch_bounds__(256) nnd_merge_kernel(const NndDev d) {
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= d.rows) return;
+    if (d.seg_len[d.row_segment[row]] < d.min_len) return;
     constexpr uint32_t K = 32u * NK;
     u64 *list = d.lists + (uint64_t) row * K;
     u64 keys[NK];
@@ -387,6 +356,7 @@ __global__ void nnd_output_kernel(const NndDev d, int32_t *out, uint32_t out_deg
     if (t >= (uint64_t) d.rows * out_degree) return;
     const uint32_t row = (uint32_t) (t / out_degree), j = (uint32_t) (t % out_degree);
     const uint32_t len = d.seg_len[d.row_segment[row]];
+    if (len < d.min_len) return;
     const uint32_t id = key_id(d.lists[(uint64_t) row * d.K + j]);
     out[t] = (int32_t) ((id < len) ? id : xorshift32((uint32_t) t) % len);
 }
@@ -418,6 +388,7 @@ cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream) {
     d.data = a.data; d.rows = a.rows; d.dim = a.dim;
     d.seg_start = a.seg_start; d.seg_len = a.seg_len;
     d.K = a.K; d.S = a.sample; d.seed = (uint32_t) (a.seed * 0x9E3779B97F4A7C15ull >> 32);
+    d.min_len = a.min_seg_len;
     char *w = static_cast<char *>(a.workspace);
     d.lists = reinterpret_cast<u64 *>(w); w += align256((size_t) a.rows * a.K * 8);
     d.props = reinterpret_cast<u64 *>(w); w += align256((size_t) a.rows * kP * 8);

@@ -34,7 +34,8 @@ __global__ void __launch_bounds__(256) assign_kernel(const AssignArgs a, uint32_
     float *query = reinterpret_cast<float *>(base);
     uint32_t *scratch = base + dim_pad4(a.dim);
     load_query(query, a.data + (uint64_t) p * a.dim, a.dim);
-    const uint32_t c0 = nearest_centroid(query, a.centroids, a.C, max_centroid, a.dim, a.metric, scratch);
+    const uint32_t c0 = nearest_centroid(query, a.centroids, a.C, max_centroid, a.dim, a.metric, scratch,
+                                         a.is_boundary ? kTopTwo : kNearestOnly);
     if (lane == 0) {
         a.nearest[p] = c0;
         if (a.is_boundary) {
@@ -172,6 +173,82 @@ __global__ void count_changed_kernel(const uint32_t *__restrict__ a, const uint3
     if (lane_id() == 0 && m) atomicAdd(count, (uint32_t) __popc(m));
 }
 
+// ---- farthest-first traversal (k-means initialisation) ---------------------------------
+// Step t: mind2[i] = min(mind2[i], |x_i - c_{t-1}|^2) for every sample row, and the row
+// with the largest mind2 (lowest row on ties) becomes c_t. One kernel updates and reduces
+// per block, a one-block kernel picks the winner and copies its row.
+constexpr uint32_t kFfRowsPerBlock = 256;
+
+__device__ __forceinline__ u64 ff_key(float v, uint32_t row) {
+    return ((u64) __float_as_uint(v) << 32) | (u64) (0xffffffffu - row);
+}
+
+__global__ void __launch_bounds__(256) ff_update_kernel(const float *__restrict__ sample, uint32_t n, uint32_t dim,
+                                                        const float *__restrict__ centre, float *mind2,
+                                                        u64 *block_best) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    __shared__ u64 warp_best[8];
+    float *c = reinterpret_cast<float *>(smem);
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) c[i] = centre[i];
+    __syncthreads();
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id(), team = lane / kTeam;
+    const uint32_t row0 = blockIdx.x * kFfRowsPerBlock;
+    u64 best = 0;
+    for (uint32_t r = warp * kTeamsPerWarp; r < kFfRowsPerBlock; r += 8 * kTeamsPerWarp) {
+        const uint32_t row = row0 + r + team;
+        const bool active = row < n;
+        const float part = team_partial(c, sample + (uint64_t) (active ? row : 0) * dim, dim, active);
+        const float d = team_fold(part);
+        if (active) {
+            float m = mind2[row];
+            if (d < m) m = d;
+            if ((lane & (kTeam - 1)) == 0) mind2[row] = m;
+            const u64 k = ff_key(m, row);
+            if (k > best) best = k;
+        }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const u64 o = __shfl_xor_sync(kFullMask, best, off);
+        if (o > best) best = o;
+    }
+    if (lane == 0) warp_best[warp] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 b = warp_best[0];
+        for (int w = 1; w < 8; w++) if (warp_best[w] > b) b = warp_best[w];
+        block_best[blockIdx.x] = b;
+    }
+}
+
+__global__ void __launch_bounds__(256) ff_pick_kernel(const float *__restrict__ sample, uint32_t dim,
+                                                      const u64 *__restrict__ block_best, uint32_t blocks,
+                                                      float *next_centre) {
+    __shared__ u64 warp_best[8];
+    __shared__ uint32_t winner;
+    u64 best = 0;
+    for (uint32_t i = threadIdx.x; i < blocks; i += blockDim.x) if (block_best[i] > best) best = block_best[i];
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const u64 o = __shfl_xor_sync(kFullMask, best, off);
+        if (o > best) best = o;
+    }
+    if (lane_id() == 0) warp_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 b = warp_best[0];
+        for (int w = 1; w < 8; w++) if (warp_best[w] > b) b = warp_best[w];
+        winner = 0xffffffffu - (uint32_t) b;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) next_centre[i] = sample[(uint64_t) winner * dim + i];
+}
+
+__global__ void fill_f32_kernel(float *p, uint32_t n, float v) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
 uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
     uint32_t m = lo;
     while (m < x) m <<= 1;
@@ -251,6 +328,26 @@ cudaError_t launch_count_changed(const uint32_t *a, const uint32_t *b, uint32_t 
     cudaError_t e = cudaMemsetAsync(count, 0, sizeof(uint32_t), stream);
     if (e != cudaSuccess || n == 0) return e;
     count_changed_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a, b, n, count);
+    return cudaGetLastError();
+}
+
+size_t farthest_first_scratch_bytes(uint32_t n) {
+    return (size_t) n * 4 + 256 + (size_t) ((n + kFfRowsPerBlock - 1) / kFfRowsPerBlock) * 8 + 256;
+}
+
+cudaError_t launch_farthest_first(const float *sample, uint32_t n, uint32_t dim, uint32_t C, float *centroids,
+                                  void *scratch, cudaStream_t stream) {
+    float *mind2 = static_cast<float *>(scratch);
+    u64 *block_best = reinterpret_cast<u64 *>(static_cast<char *>(scratch) + (((size_t) n * 4 + 255) & ~(size_t) 255));
+    const uint32_t blocks = (n + kFfRowsPerBlock - 1) / kFfRowsPerBlock;
+    fill_f32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(mind2, n, FLT_MAX);
+    cudaError_t e = cudaMemcpyAsync(centroids, sample, (size_t) dim * 4, cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return e;
+    const size_t smem = (size_t) dim_pad4(dim) * 4;
+    for (uint32_t t = 0; t < C; t++) {
+        ff_update_kernel<<<blocks, 256, smem, stream>>>(sample, n, dim, centroids + (uint64_t) t * dim, mind2, block_best);
+        if (t + 1 < C) ff_pick_kernel<<<1, 256, 0, stream>>>(sample, dim, block_best, blocks, centroids + (uint64_t) (t + 1) * dim);
+    }
     return cudaGetLastError();
 }
 

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
     uint32_t rows = 0;
     uint32_t start_node;
     if (!sub) {
-        const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, s.extra);
+        const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, s.extra, kNearestOnly);
         start_node = a.start_points[c];
     } else {
         start_node = a.start_point;
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(128) select_segment_kernel(const SelectSegment
     float *query = reinterpret_cast<float *>(base);
     uint32_t *scratch = base + dim_pad4(a.dim);
     load_query(query, a.queries + (uint64_t) q * a.dim, a.dim);
-    nearest_centroid(query, a.centroids, a.C, max_centroid, a.dim, a.metric, scratch);
+    nearest_centroid(query, a.centroids, a.C, max_centroid, a.dim, a.metric, scratch, kSorted);
     const float *ck = reinterpret_cast<const float *>(scratch);
     const uint32_t *cv = scratch + max_centroid;
     uint32_t *out = a.out + (uint64_t) q * a.C;

@@ -28,6 +28,7 @@ class BuildConfig:
     nnd_max_iterations: int = 20
     nnd_termination_threshold: float = 0.0001
     nnd_sample: int = 0
+    exact_knn_max_rows: int = 0xFFFFFFFF   # partitions up to this size get an exact all-pairs kNN graph
     seed: int = 0
 
 
@@ -71,7 +72,7 @@ def build_small(ctx: api.Context, d_data: torch.Tensor, cfg: BuildConfig, keep_i
     seg_start, seg_len = pre["h_segment_start"], pre["h_segment_length"]
     nnd = NNDescentParameter(cfg.knn_degree, cfg.nnd_max_iterations, cfg.nnd_termination_threshold)
     d_knn, rounds, knn_seconds = api.build_nnd(ctx, nnd, pre["d_reorder_data"], seg_start, seg_len, cfg.metric,
-                                               cfg.seed, cfg.nnd_sample)
+                                               cfg.seed, cfg.nnd_sample, cfg.exact_knn_max_rows)
     seconds["knn"] = knn_seconds
     index = api.GLIDE(ctx, cfg.graph_degree, d_data, pre["d_centroids"], cfg.metric)
     p_knn, p_refine = derive_build_search_params(cfg)

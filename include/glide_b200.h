@@ -65,18 +65,21 @@ uint32_t glide_calculate_hash_reset_interval(uint32_t beam, uint32_t graph_degre
 void glide_adjust_search_params(uint32_t min_iterations, uint32_t *max_iterations, uint32_t *beam);
 
 /* ---- partition stage (partition.cuh) ---------------------------------------------------- */
-/* get_centroids, partition.cuh:8-59: sample floor(n*sample_factor) rows (seeded shuffle)
- * and fit `centroid_num` centroids with Lloyd iterations (the reference calls cuVS
- * kmeans::fit). d_centroids: centroid_num x dim. */
+/* get_centroids, partition.cuh:8-59: sample floor(n*sample_factor) rows (seeded) and fit
+ * `centroid_num` centroids: farthest-first initialisation, then Lloyd iterations (the
+ * reference calls cuVS kmeans::fit, whose arithmetic is not part of its tree).
+ * d_centroids: centroid_num x dim. */
 int glide_get_centroids(glide_ctx *ctx, const float *d_data, uint32_t n, uint32_t dim, uint32_t centroid_num,
                         float sample_factor, uint64_t seed, uint32_t max_iter, int metric, float *d_centroids,
                         uint32_t *iterations_run);
 /* The sample rows get_centroids draws: an arithmetic progression modulo n with a seeded
  * stride coprime to n (the reference shuffles all ids, partition.cuh:25-31). */
 int glide_sample_ids(uint32_t n, uint32_t sample_num, uint64_t seed, uint32_t *h_out);
-/* k-means on rows already selected (the fit itself), for callers that sample themselves. */
+/* k-means on rows already selected (the fit itself), for callers that sample themselves.
+ * init 0: the first centroid_num rows; init 1: farthest-first traversal of the rows (what
+ * glide_get_centroids uses). Lloyd rounds stop after max_iter (0 -> 25) or when no label changes. */
 int glide_kmeans_fit(glide_ctx *ctx, const float *d_sample, uint32_t n, uint32_t dim, uint32_t centroid_num,
-                     uint32_t max_iter, int metric, float *d_centroids, uint32_t *d_labels_or_null,
+                     uint32_t max_iter, int metric, int init, float *d_centroids, uint32_t *d_labels_or_null,
                      uint32_t *iterations_run);
 /* define_partition, partition.cuh:61-116 (+ kernel partition_kernel.cuh:22-66).
  * d_segment_index: n x 3 (segment, slot, boundary slot or 0xffffffff); h_segment_start /
@@ -103,11 +106,13 @@ void glide_free(void *device_ptr);
 /* build_nnd, nn_descent.cuh:1405-1467: per-partition kNN graph of the reordered rows,
  * partition-local ids, h_or_d knn: rows x knn_degree int32. knn_degree <= 64.
  * max_iterations 0 -> 20 and termination_threshold < 0 -> 1e-4 (params.cuh:20-21).
- * sample 0 -> 32. */
+ * sample 0 -> 32. Partitions of at most exact_max_rows rows get their EXACT kNN graph from
+ * an all-pairs kernel (cheaper than descent at that size); larger ones run NN-descent.
+ * exact_max_rows 0xffffffff -> 16384, 0 -> NN-descent everywhere. */
 int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, uint32_t dim,
                     const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t segment_num,
                     uint32_t knn_degree, uint32_t max_iterations, float termination_threshold, uint32_t sample,
-                    uint64_t seed, int metric, int32_t *d_knn, uint32_t *iterations_run);
+                    uint32_t exact_max_rows, uint64_t seed, int metric, int32_t *d_knn, uint32_t *iterations_run);
 /* Exact kNN by brute force: the ground truth (the reference reads it from a file,
  * small_search.cu:88). k <= 128. d_out_dists may be null. */
 int glide_bruteforce_knn(glide_ctx *ctx, const float *d_base, uint32_t n, const float *d_queries, uint32_t q,

@@ -241,12 +241,12 @@ def bruteforce_knn(base, queries, k, metric=EUCLIDEAN, threads=0, want_dists=Tru
     return (ids, dists) if want_dists else ids
 
 
-def kmeans(sample, c, max_iter=25, order=ORDER_TEAM, metric=EUCLIDEAN):
+def kmeans(sample, c, max_iter=25, order=ORDER_TEAM, metric=EUCLIDEAN, init=1):
     sample = _f32(sample)
     cent = np.empty((c, sample.shape[1]), np.float32)
     labels = np.empty(sample.shape[0], np.uint32)
     rounds = lib().orc_kmeans(_p(sample), u32(sample.shape[0]), u32(sample.shape[1]), u32(c), u32(max_iter),
-                              i32(metric), i32(order), _p(cent), _p(labels))
+                              i32(metric), i32(order), i32(init), _p(cent), _p(labels))
     if rounds < 0:
         raise ValueError("orc_kmeans: fewer rows than centroids")
     return cent, labels, rounds

@@ -1042,16 +1042,38 @@ int orc_bruteforce_knn(const float *base, uint32_t n, const float *queries, uint
 // Lloyd k-means. The reference calls cuvs::cluster::kmeans::fit (cuVS branch-24.08,
 // partition.cpp call site partition.cuh:48-54) whose arithmetic is not in the
 // reference tree: PARITY UNPINNED. This restates this repository's own
-// deterministic variant: centroids start as the first C sample rows; each round
+// deterministic variant: centroids start as the first C sample rows (init 0) or as a
+// farthest-first traversal of the sample (init 1); each round
 // assigns every row to its nearest centroid (the partition stage's rule: distances
 // in `metric`/`order`, sorted with the warp network), then recomputes each centroid as the fp32 sum of its members in
 // ascending row order divided by the count (an empty cluster keeps its centroid);
 // stops after max_iter rounds or when no assignment changes. Returns rounds run.
 // ---------------------------------------------------------------------------
 int orc_kmeans(const float *sample, uint32_t n, uint32_t dim, uint32_t C, uint32_t max_iter, int metric,
-               int order, float *centroids, uint32_t *labels_out) {
+               int order, int init, float *centroids, uint32_t *labels_out) {
     if (n < C) return -1;
-    std::memcpy(centroids, sample, (uint64_t) C * dim * sizeof(float));
+    if (init == 0) {
+        std::memcpy(centroids, sample, (uint64_t) C * dim * sizeof(float));
+    } else {
+        // farthest-first traversal: start from row 0, then repeatedly take the row whose
+        // squared distance to its nearest chosen centroid is largest (lowest row on ties)
+        std::vector<float> mind2(n, kMaxF);
+        uint32_t next = 0;
+        for (uint32_t t = 0; t < C; t++) {
+            std::memcpy(centroids + (uint64_t) t * dim, sample + (uint64_t) next * dim, dim * sizeof(float));
+            const float *c = centroids + (uint64_t) t * dim;
+            parallel_for(n, 0, [&](int64_t p) {
+                const float d = sq_sum(sample + (uint64_t) p * dim, c, dim, order);
+                if (d < mind2[p]) mind2[p] = d;
+            });
+            float best = -1.0f;
+            for (uint32_t p = 0; p < n; p++)
+                if (mind2[p] > best) {
+                    best = mind2[p];
+                    next = p;
+                }
+        }
+    }
     std::vector<uint32_t> labels(n, kInvalid);
     int rounds = 0;
     for (uint32_t it = 0; it < max_iter; it++) {

@@ -48,7 +48,7 @@ def oracle_pipeline(base, centroid_num=4, boundary_factor=1.1, knn_degree=16, gr
     n, dim = base.shape
     rng = np.random.default_rng(seed)
     sample = base[rng.permutation(n)[:max(centroid_num * 20, 64)]]
-    centroids, _, _ = oracle.kmeans(sample, centroid_num, 10, order=order, metric=metric)
+    centroids, _, _ = oracle.kmeans(sample, centroid_num, 10, order=order, metric=metric, init=0)
     seg_index, seg_start, seg_len = oracle.define_partition(base, centroids, boundary_factor, metric, order)
     reorder_data, mapping = oracle.reorder(base, seg_index, seg_start, int(seg_len[centroid_num]))
     knn = exact_partition_knn(reorder_data, seg_start, seg_len, knn_degree, metric)

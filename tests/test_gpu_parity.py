@@ -103,12 +103,13 @@ def test_define_partition_without_boundary_and_single_centroid(gpu_ctx):
     assert np.array_equal(api.to_u32(d_seg)[:, 1], np.arange(base.shape[0]))
 
 
-@pytest.mark.parametrize("name,c", [("int128", 8), ("uniform16", 5), ("unit96", 6)])
-def test_kmeans_matches_oracle(gpu_ctx, name, c):
+@pytest.mark.parametrize("init", [0, 1])
+@pytest.mark.parametrize("name,c", [("int128", 8), ("uniform16", 5), ("unit96", 6), ("int128", 40)])
+def test_kmeans_matches_oracle(gpu_ctx, name, c, init):
     base, _, P = case(name)
     sample = base[:1200]
-    want_c, want_l, want_r = oracle.kmeans(sample, c, 25, metric=P["metric"])
-    d_c, d_l, rounds = api.kmeans_fit(gpu_ctx, dev(gpu_ctx, sample), c, 25, Metric(P["metric"]))
+    want_c, want_l, want_r = oracle.kmeans(sample, c, 25, metric=P["metric"], init=init)
+    d_c, d_l, rounds = api.kmeans_fit(gpu_ctx, dev(gpu_ctx, sample), c, 25, Metric(P["metric"]), init)
     assert rounds == want_r
     assert np.array_equal(api.to_u32(d_l), want_l)
     assert np.array_equal(d_c.cpu().numpy(), want_c)
@@ -219,7 +220,7 @@ def test_nn_descent_graph_recall_and_invariants(gpu_ctx, name):
     rd, seg_start, seg_len = P["reorder_data"], P["seg_start"], P["seg_len"]
     metric = Metric(P["metric"])
     d_knn, rounds, seconds = api.build_nnd(gpu_ctx, NNDescentParameter(32), dev(gpu_ctx, rd), seg_start, seg_len, metric,
-                                           seed=1)
+                                           seed=1, exact_max_rows=0)
     knn = d_knn.cpu().numpy()
     assert knn.shape == (rd.shape[0], 32) and 1 <= rounds <= 20
     exact = helpers.exact_partition_knn(rd, seg_start, seg_len, 10, P["metric"])
@@ -233,8 +234,46 @@ def test_nn_descent_graph_recall_and_invariants(gpu_ctx, name):
     assert all(len(set(r.tolist())) == 32 for r in knn[::53])
     assert knn_recall(knn, exact, 10) >= 0.95
     # reproducible
-    d_knn2, rounds2, _ = api.build_nnd(gpu_ctx, NNDescentParameter(32), dev(gpu_ctx, rd), seg_start, seg_len, metric, seed=1)
+    d_knn2, rounds2, _ = api.build_nnd(gpu_ctx, NNDescentParameter(32), dev(gpu_ctx, rd), seg_start, seg_len, metric, seed=1,
+                                       exact_max_rows=0)
     assert rounds2 == rounds and torch.equal(d_knn, d_knn2)
+
+
+@pytest.mark.parametrize("name,degree", [("int128", 32), ("uniform16", 16), ("unit96", 48), ("uniform30", 32)])
+def test_exact_partition_knn_kernel(gpu_ctx, name, degree):
+    base, _, P = case(name)
+    rd, seg_start, seg_len = P["reorder_data"], P["seg_start"], P["seg_len"]
+    d_knn, rounds, _ = api.build_nnd(gpu_ctx, NNDescentParameter(degree), dev(gpu_ctx, rd), seg_start, seg_len,
+                                     Metric(P["metric"]))
+    knn = d_knn.cpu().numpy()
+    assert rounds == 0 and knn.shape == (rd.shape[0], degree)
+    exact = helpers.exact_partition_knn(rd, seg_start, seg_len, degree, P["metric"])
+    if name == "int128":   # exact arithmetic: identical, ties by ascending id
+        assert np.array_equal(knn, exact)
+    else:                  # a different summation order may swap near-ties
+        assert (knn == exact).mean() > 0.995
+        assert knn_recall(knn, exact, degree) > 0.999
+
+
+def test_mixed_exact_and_descent_partitions(gpu_ctx):
+    # partitions above the threshold run NN-descent, the others the all-pairs kernel
+    base, _, P = case("int128")
+    rd, seg_start, seg_len = P["reorder_data"], P["seg_start"], P["seg_len"]
+    threshold = int(np.sort(seg_len)[len(seg_len) // 2])
+    d_knn, rounds, _ = api.build_nnd(gpu_ctx, NNDescentParameter(32), dev(gpu_ctx, rd), seg_start, seg_len,
+                                     exact_max_rows=threshold, seed=2)
+    knn = d_knn.cpu().numpy()
+    exact = helpers.exact_partition_knn(rd, seg_start, seg_len, 32, 0)
+    assert rounds >= 1
+    for s, l in zip(seg_start, seg_len):
+        s, l = int(s), int(l)
+        if l == 0:
+            continue
+        if l <= threshold:
+            assert np.array_equal(knn[s:s + l], exact[s:s + l])
+        else:
+            assert knn_recall(knn[s:s + l], exact[s:s + l], 10) >= 0.95
+            assert knn[s:s + l].max() < l
 
 
 def test_large_path_stages_match_oracle(gpu_ctx):
@@ -303,7 +342,8 @@ def test_cfg0_pipeline_recall(gpu_ctx):
     from glide_b200 import datasets, pipeline
     spec = datasets.CONFIGS["cfg0"]
     base, queries = datasets.make(spec)
-    cfg = pipeline.BuildConfig(centroid_num=1, knn_degree=32, graph_degree=32, nnd_max_iterations=8, seed=0)
+    cfg = pipeline.BuildConfig(centroid_num=1, knn_degree=32, graph_degree=32, nnd_max_iterations=8, seed=0,
+                               sample_factor=0.05, exact_knn_max_rows=0)
     res = pipeline.build_small(gpu_ctx, dev(gpu_ctx, base), cfg, keep_intermediates=True)
     assert res.h_segment_length.tolist() == [10000, 0]
     gt = oracle.bruteforce_knn(base, queries, 10, want_dists=False)
