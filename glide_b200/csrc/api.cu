@@ -580,16 +580,21 @@ static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t
     if (rc) return rc;
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t graph_bytes = (size_t) num * graph_degree * 4;
-    rc = ensure_ws(ctx, align256(graph_bytes));
+    rc = ensure_ws(ctx, align256(graph_bytes) + align256((size_t) num * 4));
     if (rc) return rc;
     uint32_t *snapshot = static_cast<uint32_t *>(ctx->ws);
+    uint32_t *route = reinterpret_cast<uint32_t *>(static_cast<char *>(ctx->ws) + align256(graph_bytes));
     Timed timer(ctx);
     GL_CUDA(ctx, cudaMemcpyAsync(snapshot, d_graph, graph_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (mode == kModeRefine) {
+        AssignArgs r{d_data, num, dim, d_centroids, C, -1.0f, metric, route, nullptr};
+        GL_CUDA(ctx, launch_assign(r, ctx->stream));
+    }
     BuildArgs a{};
     a.mode = mode;
     a.data = d_data; a.dim = dim; a.graph_in = snapshot; a.in_degree = graph_degree;
     a.graph_out = d_graph; a.out_degree = graph_degree;
-    a.start_points = d_start_points; a.centroids = d_centroids; a.C = C;
+    a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route;
     a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
     a.counters = counters_or_null(ctx);
     GL_CUDA(ctx, launch_build(a, ctx->stream));
@@ -621,13 +626,18 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
     if (rc) return rc;
     GL_REQUIRE(ctx, p->top_k >= 1 && p->top_k <= p->beam, GLIDE_ERR_BAD_ARG, "search: top_k must be in [1, beam]");
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = ensure_ws(ctx, align256((size_t) q * 4));
+    if (rc) return rc;
+    uint32_t *route = static_cast<uint32_t *>(ctx->ws);
     SearchArgs a{};
     a.data = d_data; a.graph = d_graph; a.degree = graph_degree; a.dim = dim;
     a.queries = d_queries; a.Q = q; a.top_k = p->top_k; a.metric = metric; a.p = to_host(p);
-    a.centroids = d_centroids; a.C = C; a.start_points = d_start_points;
+    a.centroids = d_centroids; a.C = C; a.start_points = d_start_points; a.route = route;
     a.out_ids = d_out_ids; a.out_dists = d_out_dists;
     a.counters = counters_or_null(ctx);
     Timed timer(ctx);
+    AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr};
+    GL_CUDA(ctx, launch_assign(r, ctx->stream));
     GL_CUDA(ctx, launch_search(a, ctx->stream));
     return timer.finish();
 }
@@ -640,10 +650,12 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
     if (q == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
     GL_REQUIRE(ctx, h_queries && h_out_ids && h_out_dists && p, GLIDE_ERR_BAD_ARG, "search_host: null pointer");
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    // layout: [route (used by glide_search)] [queries] [ids] [dists]
+    const size_t route_b = align256((size_t) q * 4);
     const size_t qb = align256((size_t) q * dim * 4), rb = align256((size_t) q * p->top_k * 4);
-    int rc = ensure_ws(ctx, qb + 2 * rb);
+    int rc = ensure_ws(ctx, route_b + qb + 2 * rb);
     if (rc) return rc;
-    char *w = static_cast<char *>(ctx->ws);
+    char *w = static_cast<char *>(ctx->ws) + route_b;
     float *d_q = reinterpret_cast<float *>(w);
     uint32_t *d_ids = reinterpret_cast<uint32_t *>(w + qb);
     float *d_dists = reinterpret_cast<float *>(w + qb + rb);

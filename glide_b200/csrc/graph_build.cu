@@ -23,8 +23,7 @@ struct BuildDev {
 };
 
 // Extra strip layout (words): pool_id[max_beam] pool_dist[max_beam] flags[max_beam]
-// picks[max_degree] row[max_degree] bits[max_degree/32]; the centroid scratch
-// (2*max_centroid) aliases the start of it (used before the pool exists).
+// picks[max_degree] row[max_degree] bits[max_degree/32].
 struct PruneStrip {
     uint32_t *pool_id;
     float *pool_dist;
@@ -327,11 +326,8 @@ __global__ void __launch_bounds__(256) build_kernel(const BuildDev d) {
         visited_clear(s.visited, p.hash_bit);
         __syncwarp();
         if (a.mode == kModeRefine) {
-            // the centroid scratch sits past the row copy so that it survives
-            uint32_t *scratch = s.extra + prune_strip_words(d.max_beam, d.max_degree);
-            const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, scratch,
-                                                kNearestOnly);
-            rows += seed_from_row(s, a.start_points[c], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
+            // routed by the pre-pass (search_kernel.cuh:258-269 via graph_kernel.cuh:638-642)
+            rows += seed_from_row(s, a.start_points[a.route[point]], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
                                   a.metric);
         } else {
             rows += seed_from_row(s, a.start_points[0], point, a.graph_in, degree, p.hash_bit, a.data, a.dim,
@@ -515,7 +511,6 @@ cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
     d.max_beam = max_beam;
     d.max_degree = round_up32(a.out_degree);
     uint32_t extra = prune_strip_words(max_beam, d.max_degree);
-    if (a.mode == kModeRefine) extra += 2 * d.max_centroid;
     d.strip_words = (strip_words_base(a.dim, max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;

@@ -24,6 +24,7 @@ struct SearchArgs {
     // routed (small path): nearest centroid -> start point
     const float *centroids;      // C x dim
     uint32_t C;
+    const uint32_t *route;       // Q: nearest centroid of every query (launch_assign)
     const uint32_t *start_points;
     uint32_t *out_ids;           // Q x top_k
     float *out_dists;            // Q x top_k
@@ -63,6 +64,7 @@ struct BuildArgs {
     const uint32_t *map;           // reorder id -> original id; nullptr = identity
     const float *centroids;        // refine
     uint32_t C;
+    const uint32_t *route;         // refine: nearest centroid of every point (launch_assign)
     uint32_t first, count;         // point range handled by this launch
     uint32_t fixed_segment;        // boundary: the segment every point belongs to
     float alpha;

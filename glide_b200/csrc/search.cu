@@ -65,8 +65,8 @@ __global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
     uint32_t rows = 0;
     uint32_t start_node;
     if (!sub) {
-        const uint32_t c = nearest_centroid(s.query, a.centroids, a.C, d.max_centroid, a.dim, a.metric, s.extra, kNearestOnly);
-        start_node = a.start_points[c];
+        // the nearest centroid was found by the routing pre-pass (search_kernel.cuh:258-269)
+        start_node = a.start_points[a.route[q]];
     } else {
         start_node = a.start_point;
     }
@@ -189,7 +189,7 @@ cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
     // same size ladders as kernel_config.cuh:190-204 so that ties fall identically
     const uint32_t max_beam = a.p.beam <= 64 ? 64 : (a.p.beam <= 128 ? 128 : (a.p.beam <= 256 ? 256 : 512));
     const uint32_t max_cand = a.degree <= 64 ? 64 : (a.degree <= 128 ? 128 : 256);
-    const uint32_t extra = a.segment_ids ? 4 * d.max_topk : 2 * d.max_centroid;
+    const uint32_t extra = a.segment_ids ? 4 * d.max_topk : 0;
     d.strip_words = (strip_words_base(a.dim, max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;
