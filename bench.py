@@ -250,8 +250,10 @@ def run_ours(args):
     rows_read, expansions, _ = ctx.read_counters()
     ctx.enable_counters(False)
     C = index.centroid_num()
+    # algorithmic bytes of the search kernel: every data row it scores, one adjacency row per
+    # expansion (+ the seed row), the query vector and the results
     algo_bytes = (rows_read * spec.dim * 4 + expansions * spec.graph_degree * 4 +
-                  Q * (spec.dim * 4 + C * spec.dim * 4 + spec.graph_degree * 4 + TOP_K * 8))
+                  Q * (spec.dim * 4 + spec.graph_degree * 4 + TOP_K * 8))
 
     flush = torch.empty(512 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)  # 512 MB > 126 MB L2
 
@@ -274,8 +276,10 @@ def run_ours(args):
                                        index.graph_degree(), index.d_centroids.data_ptr(), C,
                                        index.d_start_points.data_ptr(), d_queries.data_ptr(), Q, C_.byref(pc),
                                        int(metric), d_ids.data_ptr(), d_dists.data_ptr()))
-        return ctx.lib.glide_last_kernel_ms(ctx.handle)
+        ctx.lib.glide_last_search_split_ms(ctx.handle, split)
+        return ctx.lib.glide_last_kernel_ms(ctx.handle), split[0], split[1]
 
+    split = (C_.c_float * 2)()
     for _ in range(args.warmup):
         flush_l2()
         search_once()
@@ -283,10 +287,13 @@ def run_ours(args):
     barrier()
     if rank == 0:
         sampler.start()
-    kernel_ms = 0.0
+    kernel_ms = route_ms = search_ms = 0.0
     for _ in range(args.steps):
         flush_l2()
-        kernel_ms += search_once()   # CUDA events on the launching stream, around the kernel
+        total, r_ms, s_ms = search_once()   # CUDA events on the launching stream, around the kernels
+        kernel_ms += total
+        route_ms += r_ms
+        search_ms += s_ms
     barrier()
     # ---- end to end through the host-buffer entry point (pinned host memory) ----
     h_q = torch.from_numpy(queries).pin_memory()
@@ -323,7 +330,7 @@ def run_ours(args):
 
     if rank == 0:
         peak, peak_kind = load_peaks()
-        achieved = algo_bytes / (kernel_ms / args.steps / 1e3) / 1e9
+        achieved = algo_bytes / (search_ms / args.steps / 1e3) / 1e9
         line = {
             "metric": "search QPS @ recall@10>=0.95", "value": qps, "unit": "queries/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": max_kernel_ms / args.steps,
@@ -340,7 +347,9 @@ def run_ours(args):
             "recall_curve": curve,
             "e2e": {"value": e2e_qps, "unit": "queries/s", "h2d_bytes_per_step": Q * spec.dim * 4,
                     "d2h_bytes_per_step": Q * TOP_K * 8, "recall_at_10": round(e2e_recall, 4)},
-            "gpu_launches": args.steps,
+            "gpu_launches": 2 * args.steps,
+            "kernels_ms_per_step": {"route(assign_kernel)": round(route_ms / args.steps, 4),
+                                    "search_kernel": round(search_ms / args.steps, 4)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
                          "kernel": "search_kernel", "algorithmic_bytes_per_launch": int(algo_bytes),

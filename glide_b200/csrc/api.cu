@@ -18,7 +18,8 @@ using namespace glide;
 struct glide_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
-    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr, ev_mid = nullptr;
+    float split_ms[2] = {0.0f, 0.0f};  // last glide_search: routing pre-pass, search kernel
     std::string error;
     float last_ms = 0.0f;
     void *ws = nullptr;  // scratch, grown on demand
@@ -139,6 +140,7 @@ int glide_ctx_create(int device, glide_ctx **out) {
     ctx->device = device;
     if (cudaSetDevice(device) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_start) != cudaSuccess || cudaEventCreate(&ctx->ev_stop) != cudaSuccess ||
+        cudaEventCreate(&ctx->ev_mid) != cudaSuccess ||
         cudaMalloc(&ctx->counters, 3 * sizeof(unsigned long long)) != cudaSuccess) {
         delete ctx;
         return GLIDE_ERR_CUDA;
@@ -155,6 +157,7 @@ void glide_ctx_destroy(glide_ctx *ctx) {
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
     if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
+    if (ctx->ev_mid) cudaEventDestroy(ctx->ev_mid);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -162,6 +165,12 @@ void glide_ctx_destroy(glide_ctx *ctx) {
 const char *glide_last_error(const glide_ctx *ctx) { return ctx ? ctx->error.c_str() : "null context"; }
 void *glide_ctx_stream(glide_ctx *ctx) { return ctx ? (void *) ctx->stream : nullptr; }
 float glide_last_kernel_ms(const glide_ctx *ctx) { return ctx ? ctx->last_ms : 0.0f; }
+
+void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]) {
+    if (!ctx || !out) return;
+    out[0] = ctx->split_ms[0];
+    out[1] = ctx->split_ms[1];
+}
 
 void glide_enable_counters(glide_ctx *ctx, int on) { if (ctx) ctx->counters_on = on != 0; }
 
@@ -638,8 +647,13 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
     Timed timer(ctx);
     AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr};
     GL_CUDA(ctx, launch_assign(r, ctx->stream));
+    GL_CUDA(ctx, cudaEventRecord(ctx->ev_mid, ctx->stream));
     GL_CUDA(ctx, launch_search(a, ctx->stream));
-    return timer.finish();
+    rc = timer.finish();
+    if (rc) return rc;
+    cudaEventElapsedTime(&ctx->split_ms[0], ctx->ev_start, ctx->ev_mid);
+    cudaEventElapsedTime(&ctx->split_ms[1], ctx->ev_mid, ctx->ev_stop);
+    return GLIDE_OK;
 }
 
 int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph,

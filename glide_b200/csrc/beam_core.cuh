@@ -28,13 +28,14 @@ struct WarpStrip {
     uint32_t *cand_id;   // 32*NC
     float *cand_dist;    // 32*NC
     uint32_t *visited;   // 1 << hash_bit
-    uint32_t *extra;     // mode-specific scratch (centroid list, pool, rows)
+    uint32_t *work;      // 32*NC: slots of the candidates to score
+    uint32_t *extra;     // mode-specific scratch (pool, rows, merge buffers)
 };
 
 __host__ __device__ inline uint32_t dim_pad4(uint32_t dim) { return (dim + 3u) & ~3u; }
 
 __host__ __device__ inline uint32_t strip_words_base(uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
-    return dim_pad4(dim) + 2 * max_cand + (1u << hash_bit);
+    return dim_pad4(dim) + 3 * max_cand + (1u << hash_bit);
 }
 
 __device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
@@ -43,7 +44,8 @@ __device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, ui
     s.cand_id = base + dim_pad4(dim);
     s.cand_dist = reinterpret_cast<float *>(s.cand_id + max_cand);
     s.visited = s.cand_id + 2 * max_cand;
-    s.extra = s.visited + (1u << hash_bit);
+    s.work = s.visited + (1u << hash_bit);
+    s.extra = s.work + max_cand;
     return s;
 }
 
@@ -61,33 +63,42 @@ __device__ __forceinline__ void load_query(float *q_smem, const float *q_global,
 
 // Distances of the query to every valid candidate (cand_id[i] != kInvalid, and
 // != skip_id), written to cand_dist[i]; other slots get FLT_MAX. Candidates keep
-// their slot, which decides how ties fall in the sort that follows. Returns the
-// number of rows read by this warp (for the traffic counters).
+// their slot, which decides how ties fall in the sort that follows. Valid slots are
+// compacted into the strip's work list so that the four teams always have rows to
+// stream, two rows per team in flight. Returns the number of rows read by this warp
+// (for the traffic counters).
 __device__ __forceinline__ uint32_t score_candidates(const WarpStrip &s, uint32_t count, uint32_t skip_id,
                                                      const float *__restrict__ data, uint32_t dim, int metric) {
     const uint32_t lane = lane_id();
     const uint32_t team = lane / kTeam;
-    uint32_t rows = 0;
+    const bool team_lead = (lane & (kTeam - 1)) == 0;
+    uint32_t n = 0;
     for (uint32_t base = 0; base < count; base += 32) {
         const uint32_t i = base + lane;
         const uint32_t id = (i < count) ? s.cand_id[i] : kInvalid;
         const bool valid = (id != kInvalid) && (id != skip_id);
         if (i < count && !valid) s.cand_dist[i] = FLT_MAX;
         const uint32_t mask = __ballot_sync(kFullMask, valid);
-        const uint32_t n = __popc(mask);
-        rows += n;
-        for (uint32_t g = 0; g < n; g += kTeamsPerWarp) {
-            const uint32_t rank = g + team;
-            const bool active = rank < n;
-            const uint32_t src_lane = active ? __fns(mask, 0, rank + 1) : 0;
-            const uint32_t row_id = __shfl_sync(kFullMask, id, src_lane);
-            const float part = team_partial(s.query, data + (uint64_t) row_id * dim, dim, active);
-            const float sum = team_fold(part);
-            if (active && (lane & (kTeam - 1)) == 0) s.cand_dist[base + src_lane] = finish_metric(sum, metric);
+        if (valid) s.work[n + __popc(mask & ((1u << lane) - 1))] = i;
+        n += __popc(mask);
+    }
+    __syncwarp();
+    for (uint32_t g = 0; g < n; g += 2 * kTeamsPerWarp) {
+        const uint32_t r0 = g + team, r1 = g + kTeamsPerWarp + team;
+        const bool a0 = r0 < n, a1 = r1 < n;
+        const uint32_t slot0 = a0 ? s.work[r0] : 0, slot1 = a1 ? s.work[r1] : 0;
+        const uint32_t id0 = a0 ? s.cand_id[slot0] : 0, id1 = a1 ? s.cand_id[slot1] : 0;
+        float p0, p1;
+        team_partial2(s.query, data + (uint64_t) id0 * dim, data + (uint64_t) id1 * dim, dim, a0, a1, p0, p1);
+        const float s0 = team_fold(p0);
+        const float s1 = team_fold(p1);
+        if (team_lead) {
+            if (a0) s.cand_dist[slot0] = finish_metric(s0, metric);
+            if (a1) s.cand_dist[slot1] = finish_metric(s1, metric);
         }
     }
     __syncwarp();
-    return rows;
+    return n;
 }
 
 // search_kernel.cuh:362-391: read the parent's adjacency row, keep ids that are new

@@ -80,6 +80,40 @@ __device__ __forceinline__ float team_partial(const float *__restrict__ q, const
     return acc;
 }
 
+// Two rows at once (same arithmetic per row as team_partial): the loads of both rows are
+// issued before either is consumed.
+__device__ __forceinline__ void team_partial2(const float *__restrict__ q, const float *__restrict__ row0,
+                                              const float *__restrict__ row1, uint32_t dim, bool active0,
+                                              bool active1, float &out0, float &out1) {
+    const uint32_t t = threadIdx.x & (kTeam - 1);
+    float acc0 = 0.0f, acc1 = 0.0f;
+    if (active0 && active1 && (dim & 3u) == 0) {
+        const uint32_t chunks = dim >> 2;
+        const float4 *q4 = reinterpret_cast<const float4 *>(q);
+        const float4 *r4 = reinterpret_cast<const float4 *>(row0);
+        const float4 *s4 = reinterpret_cast<const float4 *>(row1);
+        uint32_t c = t;
+        for (; c + kTeam < chunks; c += 2 * kTeam) {
+            const float4 b0 = __ldg(r4 + c), b1 = __ldg(r4 + c + kTeam);
+            const float4 d0 = __ldg(s4 + c), d1 = __ldg(s4 + c + kTeam);
+            const float4 qa = q4[c], qb = q4[c + kTeam];
+            acc0 = sq_acc4(qa, b0, acc0); acc1 = sq_acc4(qa, d0, acc1);
+            acc0 = sq_acc4(qb, b1, acc0); acc1 = sq_acc4(qb, d1, acc1);
+        }
+        for (; c < chunks; c += kTeam) {
+            const float4 b = __ldg(r4 + c), d = __ldg(s4 + c);
+            const float4 qa = q4[c];
+            acc0 = sq_acc4(qa, b, acc0);
+            acc1 = sq_acc4(qa, d, acc1);
+        }
+    } else {
+        acc0 = team_partial(q, row0, dim, active0);
+        acc1 = team_partial(q, row1, dim, active1);
+    }
+    out0 = acc0;
+    out1 = acc1;
+}
+
 __device__ __forceinline__ float finish_metric(float s, int metric) {
     return metric == kEuclidean ? sqrtf(s) : s;
 }

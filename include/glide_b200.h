@@ -154,6 +154,9 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
                       uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
                       const uint32_t *d_start_points, const float *h_queries, uint32_t q,
                       const glide_search_params *p, int metric, uint32_t *h_out_ids, float *h_out_dists);
+/* Device milliseconds of the two kernels of the last glide_search on this context:
+ * out[0] the routing pre-pass (nearest centroid per query), out[1] the search kernel. */
+void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]);
 /* Traffic counters of the last search/build/refine call when enabled: rows read during
  * search, expansions, rows read during pruning. */
 void glide_enable_counters(glide_ctx *ctx, int on);
