@@ -65,7 +65,7 @@ __device__ __forceinline__ void load_query(float *q_smem, const float *q_global,
 // != skip_id), written to cand_dist[i]; other slots get FLT_MAX. Candidates keep
 // their slot, which decides how ties fall in the sort that follows. Valid slots are
 // compacted into the strip's work list so that the four teams always have rows to
-// stream, two rows per team in flight. Returns the number of rows read by this warp
+// stream. Returns the number of rows read by this warp
 // (for the traffic counters).
 __device__ __forceinline__ uint32_t score_candidates(const WarpStrip &s, uint32_t count, uint32_t skip_id,
                                                      const float *__restrict__ data, uint32_t dim, int metric) {
@@ -83,19 +83,14 @@ __device__ __forceinline__ uint32_t score_candidates(const WarpStrip &s, uint32_
         n += __popc(mask);
     }
     __syncwarp();
-    for (uint32_t g = 0; g < n; g += 2 * kTeamsPerWarp) {
-        const uint32_t r0 = g + team, r1 = g + kTeamsPerWarp + team;
-        const bool a0 = r0 < n, a1 = r1 < n;
-        const uint32_t slot0 = a0 ? s.work[r0] : 0, slot1 = a1 ? s.work[r1] : 0;
-        const uint32_t id0 = a0 ? s.cand_id[slot0] : 0, id1 = a1 ? s.cand_id[slot1] : 0;
-        float p0, p1;
-        team_partial2(s.query, data + (uint64_t) id0 * dim, data + (uint64_t) id1 * dim, dim, a0, a1, p0, p1);
-        const float s0 = team_fold(p0);
-        const float s1 = team_fold(p1);
-        if (team_lead) {
-            if (a0) s.cand_dist[slot0] = finish_metric(s0, metric);
-            if (a1) s.cand_dist[slot1] = finish_metric(s1, metric);
-        }
+    for (uint32_t g = 0; g < n; g += kTeamsPerWarp) {
+        const uint32_t r = g + team;
+        const bool active = r < n;
+        const uint32_t slot = active ? s.work[r] : 0;
+        const uint32_t id = active ? s.cand_id[slot] : 0;
+        const float part = team_partial(s.query, data + (uint64_t) id * dim, dim, active);
+        const float sum = team_fold(part);
+        if (active && team_lead) s.cand_dist[slot] = finish_metric(sum, metric);
     }
     __syncwarp();
     return n;

@@ -34,7 +34,7 @@ __device__ inline void warp_merge_final_smem(float *k, uint32_t *v, uint32_t n_p
 }
 
 template<int NB, int NC>
-__global__ void __launch_bounds__(256, 4) search_kernel(const SearchDev d) {
+__global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
     extern __shared__ __align__(16) uint32_t smem[];
     const SearchArgs &a = d.a;
     const uint32_t warps_per_cta = blockDim.x >> 5;
