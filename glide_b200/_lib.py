@@ -46,6 +46,7 @@ SIGNATURES = {
     "glide_refine": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32]),
     "glide_search": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_search_host": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
+    "glide_search_static_scratch": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_last_search_split_ms": (None, [vp, P(f32)]),
     "glide_enable_counters": (None, [vp, i32]),
     "glide_read_counters": (i32, [vp, P(u64)]),

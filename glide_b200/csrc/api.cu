@@ -683,6 +683,61 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
     return GLIDE_OK;
 }
 
+// ---- search without any allocation -----------------------------------------------------------
+// Some hosts must not allocate device memory at call time: a serving loop whose device memory
+// is handed out once by its own pool and where a cudaMalloc would stall every stream of the
+// device, or a process that runs close to the memory limit and cannot risk a growing scratch
+// arena. glide_search needs one word of scratch per query (the partition each query is routed
+// to); here that scratch is a fixed array inside the library image, so the call touches no
+// allocator. Every GPU that loads the library carries the array until the process exits.
+constexpr uint32_t kStaticRouteCapacity = 65536;  // queries per call (256 KB of device memory)
+static __device__ __align__(256) uint32_t g_static_route[kStaticRouteCapacity];
+
+namespace {
+constexpr int kMaxDevices = 64;
+uint32_t *g_static_route_ptr[kMaxDevices] = {};  // device address of g_static_route, per device
+}  // namespace
+
+int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim,
+                                const uint32_t *d_graph, uint32_t graph_degree, const float *d_centroids, uint32_t C,
+                                const uint32_t *d_start_points, const float *d_queries, uint32_t q,
+                                const glide_search_params *p, int metric, uint32_t *d_out_ids, float *d_out_dists) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    if (q == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
+    GL_REQUIRE(ctx, q <= kStaticRouteCapacity, GLIDE_ERR_UNSUPPORTED,
+               "search_static_scratch: more than 65536 queries in one call; split the batch or use glide_search");
+    GL_REQUIRE(ctx, d_data && d_graph && d_centroids && d_start_points && d_queries && d_out_ids && d_out_dists,
+               GLIDE_ERR_BAD_ARG, "search_static_scratch: null pointer");
+    GL_REQUIRE(ctx, num > 0 && dim > 0 && C >= 1, GLIDE_ERR_BAD_ARG, "search_static_scratch: zero size");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
+    GL_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kMaxDevices, GLIDE_ERR_UNSUPPORTED,
+               "search_static_scratch: device index beyond 63");
+    int rc = check_params(ctx, p, graph_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, p->top_k >= 1 && p->top_k <= p->beam, GLIDE_ERR_BAD_ARG, "search: top_k must be in [1, beam]");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    // First call on this device: resolve the array's device address. In host code the symbol is
+    // only a handle, never an address a kernel may use.
+    uint32_t *route = g_static_route_ptr[ctx->device];
+    if (!route) {
+        void *addr = nullptr;
+        GL_CUDA(ctx, cudaGetSymbolAddress(&addr, g_static_route));
+        route = static_cast<uint32_t *>(addr);
+        g_static_route_ptr[ctx->device] = route;
+    }
+    SearchArgs a{};
+    a.data = d_data; a.graph = d_graph; a.degree = graph_degree; a.dim = dim;
+    a.queries = d_queries; a.Q = q; a.top_k = p->top_k; a.metric = metric; a.p = to_host(p);
+    a.centroids = d_centroids; a.C = C; a.start_points = d_start_points; a.route = route;
+    a.out_ids = d_out_ids; a.out_dists = d_out_dists;
+    a.counters = counters_or_null(ctx);
+    Timed timer(ctx);
+    AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr};
+    GL_CUDA(ctx, launch_assign(r, ctx->stream));
+    GL_CUDA(ctx, launch_search(a, ctx->stream));
+    return timer.finish();
+}
+
 // ---- large path ------------------------------------------------------------------------------
 int glide_select_segments(glide_ctx *ctx, const float *d_queries, uint32_t q, uint32_t dim, const float *d_centroids,
                           uint32_t C, uint32_t min_segment_num, float boundary_factor, int metric, uint32_t *d_out) {

@@ -154,6 +154,21 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
                       uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
                       const uint32_t *d_start_points, const float *h_queries, uint32_t q,
                       const glide_search_params *p, int metric, uint32_t *h_out_ids, float *h_out_dists);
+/* glide_search for hosts that must not allocate at call time (a serving loop whose device
+ * memory comes from its own pool and where a cudaMalloc would stall the device; a process
+ * running near the memory limit). It has no counterpart in the reference. Same arguments and
+ * results as glide_search; the per-query scratch (one word per query: the partition it is routed
+ * to) is a fixed 256 KB array inside the library image, held by every GPU that loads the library
+ * until the process exits, so at most 65,536 queries per call (more: GLIDE_ERR_UNSUPPORTED).
+ * The call uses no cudaMalloc/cudaFree and no allocating library routine. The first call on a
+ * device looks up the array's device address; make that call before starting any stream
+ * capture. All calls on one device share the array (it needs no clearing: every word used is
+ * written first), so two such calls that overlap on the GPU race; serialise them. */
+int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim,
+                                const uint32_t *d_graph, uint32_t graph_degree, const float *d_centroids,
+                                uint32_t centroid_num, const uint32_t *d_start_points, const float *d_queries,
+                                uint32_t q, const glide_search_params *p, int metric, uint32_t *d_out_ids,
+                                float *d_out_dists);
 /* Device milliseconds of the two kernels of the last glide_search on this context:
  * out[0] the routing pre-pass (nearest centroid per query), out[1] the search kernel. */
 void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]);
