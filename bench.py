@@ -8,8 +8,10 @@ at the smallest beam of a fixed ladder that reaches recall@10 >= 0.95 against ex
 kNN; the index is built once before the timed region and its stage times are reported
 under "build". `value` is queries/s with queries resident in HBM (sum over ranks / max
 time over ranks); `e2e` is the same through the host-buffer entry point with the H2D
-and D2H copies inside the timed region. Under torchrun every rank holds a replica of the
-index and searches its own query batch (weak scaling, no data-path collective).
+and D2H copies inside the timed region. Under torchrun the index build is sharded over the
+ranks (row ranges of the subgraph build and of refinement, rows exchanged over NCCL), every rank
+ends with the full index and searches its own query batch (weak scaling of the timed step, no
+collective inside it).
 
 `--impl reference`: the reference is CUDA-only and cannot be built here, so this arm
 times exact brute-force kNN (recall 1.0) on the host cores, a bounded sample of queries
@@ -220,7 +222,10 @@ def run_ours(args):
                                centroid_num=centroid_num, sample_factor=0.1 if centroid_num > 32 else 0.01,
                                seed=spec.seed)
     t0 = time.perf_counter()
-    res = pipeline.build_small(ctx, d_base, cfg)
+    if world > 1:   # subgraph build and refinement split over the ranks, rows exchanged over NCCL
+        res = pipeline.build_small_sharded(ctx, d_base, cfg, dist, world, rank)
+    else:
+        res = pipeline.build_small(ctx, d_base, cfg)
     build_wall = time.perf_counter() - t0
     index = res.index
 
@@ -339,7 +344,8 @@ def run_ours(args):
                                    f"k={TOP_K}, graph degree {spec.graph_degree}, {cfg.centroid_num} partitions",
                        "beam": beam, "beam_rounded": sp.beam, "max_iterations": sp.max_iterations, "reduced": reduced,
                        "l2": "512 MB buffer rewritten between timed iterations",
-                       "multi_gpu": "one index replica and one query batch per rank" if world > 1 else "single GPU"},
+                       "multi_gpu": ("build sharded by row ranges (NCCL row exchange), then one full index and one "
+                                     "query batch per rank") if world > 1 else "single GPU"},
             "recall_at_10": round(recall, 4),
             "build": {"seconds": round(res.total_seconds, 4), "wall_seconds": round(build_wall, 3),
                       "stages": {k: round(v, 4) for k, v in res.seconds.items()}, "nnd_rounds": res.nnd_rounds,

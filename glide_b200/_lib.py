@@ -42,7 +42,10 @@ SIGNATURES = {
     "glide_start_point_select": (i32, [vp, vp, u32, vp, u64, vp, vp]),
     "glide_subgraph_build_and_merge": (i32, [vp, vp, u32, u32, vp, u32, vp, vp, u32, vp, vp, u32, u32,
                                              P(SearchParamsC), f32, i32, i32, vp]),
+    "glide_subgraph_build_range": (i32, [vp, vp, u32, u32, vp, u32, vp, vp, u32, vp, vp, u32, u32,
+                                         P(SearchParamsC), f32, i32, u32, u32, vp]),
     "glide_reverse_graph": (i32, [vp, vp, u32, u32]),
+    "glide_refine_range": (i32, [vp, vp, u32, u32, vp, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32, u32]),
     "glide_refine": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32]),
     "glide_search": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_search_host": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),

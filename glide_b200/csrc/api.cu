@@ -560,6 +560,51 @@ int glide_subgraph_build_and_merge(glide_ctx *ctx, const float *d_reorder_data, 
     return timer.finish();
 }
 
+int glide_subgraph_build_range(glide_ctx *ctx, const float *d_reorder_data, uint32_t reorder_num, uint32_t dim,
+                               const uint32_t *d_knn, uint32_t knn_degree, const uint32_t *h_segment_start,
+                               const uint32_t *h_segment_length, uint32_t S, const uint32_t *d_start_points_local,
+                               const uint32_t *d_map, uint32_t num, uint32_t graph_degree,
+                               const glide_search_params *p, float relaxant_factor, int metric, uint32_t first_row,
+                               uint32_t row_count, uint32_t *d_graph) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_reorder_data && d_knn && h_segment_start && h_segment_length && d_start_points_local && d_map && d_graph,
+               GLIDE_ERR_BAD_ARG, "subgraph_build_range: null pointer");
+    GL_REQUIRE(ctx, S >= 1 && num <= reorder_num && dim > 0, GLIDE_ERR_BAD_ARG, "subgraph_build_range: bad sizes");
+    GL_REQUIRE(ctx, (uint64_t) first_row + row_count <= reorder_num, GLIDE_ERR_BAD_ARG, "subgraph_build_range: range beyond the rows");
+    int rc = check_params(ctx, p, knn_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, graph_degree >= 1 && graph_degree <= 256, GLIDE_ERR_UNSUPPORTED, "Unsupported graph_degree");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = ensure_ws(ctx, 2 * align256((size_t) S * 4));
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    uint32_t *d_start = b.take<uint32_t>(S), *d_len = b.take<uint32_t>(S);
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_start, h_segment_start, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(d_len, h_segment_length, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    BuildArgs a{};
+    a.data = d_reorder_data; a.dim = dim; a.graph_in = d_knn; a.in_degree = knn_degree;
+    a.graph_out = d_graph; a.out_degree = graph_degree;
+    a.seg_start = d_start; a.seg_len = d_len; a.S = S; a.start_points = d_start_points_local; a.map = d_map;
+    a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
+    a.counters = counters_or_null(ctx);
+    const uint32_t end = first_row + row_count;
+    if (first_row < num) {  // main rows: build_kernel
+        a.mode = kModeBuild;
+        a.first = first_row;
+        a.count = (end < num ? end : num) - first_row;
+        GL_CUDA(ctx, launch_build(a, ctx->stream));
+    }
+    if (end > num) {  // boundary copies: build_boundary_kernel
+        a.mode = kModeBoundary;
+        a.fixed_segment = S - 1;
+        a.first = first_row > num ? first_row : num;
+        a.count = end - a.first;
+        GL_CUDA(ctx, launch_build(a, ctx->stream));
+    }
+    return timer.finish();
+}
+
 int glide_reverse_graph(glide_ctx *ctx, uint32_t *d_graph, uint32_t num, uint32_t graph_degree) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
     GL_REQUIRE(ctx, d_graph && num > 0, GLIDE_ERR_BAD_ARG, "reverse_graph: bad argument");
@@ -605,6 +650,36 @@ static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t
     a.graph_out = d_graph; a.out_degree = graph_degree;
     a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route;
     a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
+    a.counters = counters_or_null(ctx);
+    GL_CUDA(ctx, launch_build(a, ctx->stream));
+    return timer.finish();
+}
+
+int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph_in,
+                       uint32_t *d_graph_out, uint32_t graph_degree, const float *d_centroids, uint32_t C,
+                       const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor, int metric,
+                       uint32_t first, uint32_t count) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_data && d_graph_in && d_graph_out && d_graph_in != d_graph_out && d_centroids && d_start_points,
+               GLIDE_ERR_BAD_ARG, "refine_range: null pointer, or input and output graph are the same buffer");
+    GL_REQUIRE(ctx, num > 0 && dim > 0 && C >= 1 && (uint64_t) first + count <= num, GLIDE_ERR_BAD_ARG, "refine_range: bad sizes");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
+    int rc = check_params(ctx, p, graph_degree);
+    if (rc) return rc;
+    if (count == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = ensure_ws(ctx, align256((size_t) count * 4));
+    if (rc) return rc;
+    uint32_t *route = static_cast<uint32_t *>(ctx->ws);
+    Timed timer(ctx);
+    AssignArgs r{d_data + (size_t) first * dim, count, dim, d_centroids, C, -1.0f, metric, route, nullptr};
+    GL_CUDA(ctx, launch_assign(r, ctx->stream));
+    BuildArgs a{};
+    a.mode = kModeRefine;
+    a.data = d_data; a.dim = dim; a.graph_in = d_graph_in; a.in_degree = graph_degree;
+    a.graph_out = d_graph_out; a.out_degree = graph_degree;
+    a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route; a.route_first = first;
+    a.first = first; a.count = count; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
     a.counters = counters_or_null(ctx);
     GL_CUDA(ctx, launch_build(a, ctx->stream));
     return timer.finish();

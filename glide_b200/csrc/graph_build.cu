@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(256) build_kernel(const BuildDev d) {
         __syncwarp();
         if (a.mode == kModeRefine) {
             // routed by the pre-pass (search_kernel.cuh:258-269 via graph_kernel.cuh:638-642)
-            rows += seed_from_row(s, a.start_points[a.route[point]], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
+            rows += seed_from_row(s, a.start_points[a.route[point - a.route_first]], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
                                   a.metric);
         } else {
             rows += seed_from_row(s, a.start_points[0], point, a.graph_in, degree, p.hash_bit, a.data, a.dim,

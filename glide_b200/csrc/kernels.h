@@ -64,7 +64,8 @@ struct BuildArgs {
     const uint32_t *map;           // reorder id -> original id; nullptr = identity
     const float *centroids;        // refine
     uint32_t C;
-    const uint32_t *route;         // refine: nearest centroid of every point (launch_assign)
+    const uint32_t *route;         // refine: nearest centroid of points route_first, route_first+1, ... (launch_assign)
+    uint32_t route_first;
     uint32_t first, count;         // point range handled by this launch
     uint32_t fixed_segment;        // boundary: the segment every point belongs to
     float alpha;

@@ -133,12 +133,30 @@ int glide_subgraph_build_and_merge(glide_ctx *ctx, const float *d_reorder_data, 
                                    const uint32_t *d_start_points_local, const uint32_t *d_map, uint32_t num,
                                    uint32_t graph_degree, const glide_search_params *p, float relaxant_factor,
                                    int metric, int skip_boundary, uint32_t *d_graph);
+/* The same two kernels for reorder rows [first_row, first_row + row_count) only: rows below
+ * `num` run build_kernel, rows from `num` on are boundary copies and run build_boundary_kernel
+ * (the rows they merge into must already hold their build_kernel result). This is how the
+ * build is sharded across GPUs; the reference launches whole ranges (glide_impl.cuh:114-187). */
+int glide_subgraph_build_range(glide_ctx *ctx, const float *d_reorder_data, uint32_t reorder_num, uint32_t dim,
+                               const uint32_t *d_knn, uint32_t knn_degree, const uint32_t *h_segment_start,
+                               const uint32_t *h_segment_length, uint32_t segment_num,
+                               const uint32_t *d_start_points_local, const uint32_t *d_map, uint32_t num,
+                               uint32_t graph_degree, const glide_search_params *p, float relaxant_factor,
+                               int metric, uint32_t first_row, uint32_t row_count, uint32_t *d_graph);
 /* reverse_graph, glide_impl.cuh:194-256. In place. */
 int glide_reverse_graph(glide_ctx *ctx, uint32_t *d_graph, uint32_t num, uint32_t graph_degree);
 /* refine, glide_impl.cuh:258-317. In place (a snapshot is taken internally). */
 int glide_refine(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
                  uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
                  const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor, int metric);
+
+/* refine for points [first, first + count): searches read d_graph_in (the graph before
+ * refinement), the refined rows are written to d_graph_out (a different buffer; rows outside
+ * the range are not touched). glide_impl.cuh:284-312 launches the whole range. */
+int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph_in,
+                       uint32_t *d_graph_out, uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
+                       const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor,
+                       int metric, uint32_t first, uint32_t count);
 
 /* ---- search stage ----------------------------------------------------------------------- */
 /* GLIDE::search, glide_impl.cuh:370-454 (search_kernel, search_kernel.cuh:393-490).

@@ -372,3 +372,48 @@ def test_cfg0_pipeline_recall(gpu_ctx):
     oracle.reverse_graph(want)
     want = oracle.refine(base, want, res.index.centroid_view().cpu().numpy(), original, orf, 1.05)
     assert np.array_equal(graph, want)
+
+
+def test_sharded_build_with_one_rank_equals_plain_build(gpu_ctx):
+    from glide_b200 import pipeline
+    base, _ = helpers.small_dataset("int", 4000, 32, 10, seed=9)
+    cfg = pipeline.BuildConfig(centroid_num=4, knn_degree=16, graph_degree=16, build_beam=32, refine_beam=64,
+                               sample_factor=0.1, boundary_factor=1.15, seed=3)
+    a = pipeline.build_small(gpu_ctx, dev(gpu_ctx, base), cfg)
+    b = pipeline.build_small_sharded(gpu_ctx, dev(gpu_ctx, base), cfg)
+    assert a.h_segment_length[-1] > 0   # the boundary path is exercised
+    assert torch.equal(a.index.graph_view(), b.index.graph_view())
+    assert torch.equal(a.index.start_point_view(), b.index.start_point_view())
+
+
+def _sharded_rank(rank, world, port, out_dir):
+    import os
+    import torch.distributed as dist
+    from glide_b200 import pipeline
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ctx = api.Context(rank)
+    base, _ = helpers.small_dataset("int", 4000, 32, 10, seed=9)
+    cfg = pipeline.BuildConfig(centroid_num=4, knn_degree=16, graph_degree=16, build_beam=32, refine_beam=64,
+                               sample_factor=0.1, boundary_factor=1.15, seed=3)
+    d = torch.from_numpy(base).to(ctx.torch_device)
+    plain = pipeline.build_small(ctx, d, cfg)
+    shard = pipeline.build_small_sharded(ctx, d, cfg, dist, world, rank)
+    ok = torch.equal(plain.index.graph_view(), shard.index.graph_view())
+    open(os.path.join(out_dir, f"rank{rank}.txt"), "w").write("ok" if ok else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+    ctx.close()
+
+
+def test_sharded_build_on_two_gpus_equals_plain_build(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import os
+    import torch.multiprocessing as mp
+    port = 29400 + os.getpid() % 500
+    mp.spawn(_sharded_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert open(tmp_path / "rank0.txt").read() == "ok" and open(tmp_path / "rank1.txt").read() == "ok"
