@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libglide_b200.so")
+# GLIDE_B200_LIB selects another build of the same library (A/B comparisons of kernel variants)
+LIB_PATH = os.environ.get("GLIDE_B200_LIB") or os.path.join(_HERE, "libglide_b200.so")
 
 u32, u64, i32, f32, vp = C.c_uint32, C.c_uint64, C.c_int, C.c_float, C.c_void_p
 P = C.POINTER

@@ -64,14 +64,12 @@ __device__ __forceinline__ void load_query(float *q_smem, const float *q_global,
 // Distances of the query to every valid candidate (cand_id[i] != kInvalid, and
 // != skip_id), written to cand_dist[i]; other slots get FLT_MAX. Candidates keep
 // their slot, which decides how ties fall in the sort that follows. Valid slots are
-// compacted into the strip's work list so that the four teams always have rows to
-// stream. Returns the number of rows read by this warp
+// compacted into the strip's work list and scored by warp_rows (whole-warp row loads,
+// several rows in flight). Returns the number of rows read by this warp
 // (for the traffic counters).
 __device__ __forceinline__ uint32_t score_candidates(const WarpStrip &s, uint32_t count, uint32_t skip_id,
                                                      const float *__restrict__ data, uint32_t dim, int metric) {
     const uint32_t lane = lane_id();
-    const uint32_t team = lane / kTeam;
-    const bool team_lead = (lane & (kTeam - 1)) == 0;
     uint32_t n = 0;
     for (uint32_t base = 0; base < count; base += 32) {
         const uint32_t i = base + lane;
@@ -83,15 +81,9 @@ __device__ __forceinline__ uint32_t score_candidates(const WarpStrip &s, uint32_
         n += __popc(mask);
     }
     __syncwarp();
-    for (uint32_t g = 0; g < n; g += kTeamsPerWarp) {
-        const uint32_t r = g + team;
-        const bool active = r < n;
-        const uint32_t slot = active ? s.work[r] : 0;
-        const uint32_t id = active ? s.cand_id[slot] : 0;
-        const float part = team_partial(s.query, data + (uint64_t) id * dim, dim, active);
-        const float sum = team_fold(part);
-        if (active && team_lead) s.cand_dist[slot] = finish_metric(sum, metric);
-    }
+    warp_rows(s.query, data, dim, metric, n,
+              [&](uint32_t i) { return s.cand_id[s.work[i]]; },
+              [&](uint32_t i, float d) { s.cand_dist[s.work[i]] = d; });
     __syncwarp();
     return n;
 }

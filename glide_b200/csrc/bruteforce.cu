@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(256, 2) segment_knn_kernel(const float *__rest
                 const u64 a = list[j], b = q[L - 1 - j];
                 keys[i] = a < b ? a : b;
             }
-            phase_u64<NL>(keys, L, true);
+            merge_final_u64<NL>(keys);
 #pragma unroll
             for (int i = 0; i < NL; i++) list[NL * lane + i] = keys[i];
             if (lane == 0) qcount[ql] = 0;

@@ -26,8 +26,8 @@ __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
 
 // ---------------------------------------------------------------------------
 // Distance. The value is the reference's (distance.cuh:9-27): fp32 sum of squared
-// differences, sqrt for Euclidean, raw for Cosine. The summation ORDER is this
-// repository's own: team lane t accumulates 4-float chunks t, t+8, ... with fused
+// differences, sqrt for Euclidean, raw for Cosine. Two summation orders are used. Centroid
+// distances (routing, assignment, k-means) use the TEAM order: team lane t accumulates 4-float chunks t, t+8, ... with fused
 // multiply-adds (scalar elements t, t+8, ... when dim % 4 != 0), then a 4,2,1
 // shuffle tree folds the team. All lanes of the team return the folded value.
 // `q` points to shared memory (16-byte aligned), `row` to global memory.
@@ -80,38 +80,114 @@ __device__ __forceinline__ float team_partial(const float *__restrict__ q, const
     return acc;
 }
 
-// Two rows at once (same arithmetic per row as team_partial): the loads of both rows are
-// issued before either is consumed.
-__device__ __forceinline__ void team_partial2(const float *__restrict__ q, const float *__restrict__ row0,
-                                              const float *__restrict__ row1, uint32_t dim, bool active0,
-                                              bool active1, float &out0, float &out1) {
-    const uint32_t t = threadIdx.x & (kTeam - 1);
-    float acc0 = 0.0f, acc1 = 0.0f;
-    if (active0 && active1 && (dim & 3u) == 0) {
-        const uint32_t chunks = dim >> 2;
-        const float4 *q4 = reinterpret_cast<const float4 *>(q);
-        const float4 *r4 = reinterpret_cast<const float4 *>(row0);
-        const float4 *s4 = reinterpret_cast<const float4 *>(row1);
-        uint32_t c = t;
-        for (; c + kTeam < chunks; c += 2 * kTeam) {
-            const float4 b0 = __ldg(r4 + c), b1 = __ldg(r4 + c + kTeam);
-            const float4 d0 = __ldg(s4 + c), d1 = __ldg(s4 + c + kTeam);
-            const float4 qa = q4[c], qb = q4[c + kTeam];
-            acc0 = sq_acc4(qa, b0, acc0); acc1 = sq_acc4(qa, d0, acc1);
-            acc0 = sq_acc4(qb, b1, acc0); acc1 = sq_acc4(qb, d1, acc1);
+// ---------------------------------------------------------------------------
+// Warp-row distances (candidate scoring and pruning). One data row is read by the whole
+// warp: lane l owns the 16-byte chunks l, l+32, ... of the row (for dim 128 exactly one
+// 128-bit load per lane and row), accumulates its chunks with fused multiply-adds in
+// x,y,z,w order, and the 32 lane sums are folded by a 16,8,4,2,1 xor tree, the reference's
+// tree (distance.cuh:18-20). When dim % 4 != 0 lane l owns the scalar elements l, l+32, ...,
+// which is exactly the reference's order (distance.cuh:15-17). The query stays in
+// registers, R = 8/QR rows are loaded before any is consumed, and the R lane sums are
+// folded together: each xor step that still has several rows halves the values per lane
+// instead of shuffling all of them (9 shuffles for 8 rows instead of 40). The pairing of
+// lanes, hence the rounding, is that of the plain tree.
+// ---------------------------------------------------------------------------
+template<int R>
+__device__ __forceinline__ float fold_rows(float (&p)[R]) {
+    const uint32_t lane = lane_id();
+    int bit = 16;
+#pragma unroll
+    for (int half = R / 2; half >= 1; half >>= 1) {
+        const bool hi = (lane & bit) != 0;
+#pragma unroll
+        for (int i = 0; i < half; i++) {
+            const float send = hi ? p[i] : p[i + half];
+            const float keep = hi ? p[i + half] : p[i];
+            p[i] = keep + __shfl_xor_sync(kFullMask, send, bit);
         }
-        for (; c < chunks; c += kTeam) {
-            const float4 b = __ldg(r4 + c), d = __ldg(s4 + c);
-            const float4 qa = q4[c];
-            acc0 = sq_acc4(qa, b, acc0);
-            acc1 = sq_acc4(qa, d, acc1);
-        }
-    } else {
-        acc0 = team_partial(q, row0, dim, active0);
-        acc1 = team_partial(q, row1, dim, active1);
+        bit >>= 1;
     }
-    out0 = acc0;
-    out1 = acc1;
+#pragma unroll
+    for (; bit >= 1; bit >>= 1) p[0] += __shfl_xor_sync(kFullMask, p[0], bit);
+    return p[0];  // the sum of row (lane >> (5 - log2 R)), replicated over 32/R lanes
+}
+
+template<int R> struct Log2 { static constexpr int v = 1 + Log2<R / 2>::v; };
+template<> struct Log2<1> { static constexpr int v = 0; };
+
+// id_at(i) -> row id of the i-th row to score (i < n); sink(i, distance) consumes it (called
+// by one lane per row). QR = number of 16-byte chunks each lane owns (dim <= 128*QR).
+template<int QR, typename IdAt, typename Sink>
+__device__ __forceinline__ void warp_rows_v4(const float *q_smem, const float *__restrict__ data, uint32_t dim,
+                                             int metric, uint32_t n, IdAt id_at, Sink sink) {
+    constexpr int R = 8 / QR;
+    const uint32_t lane = lane_id();
+    const uint32_t chunks = dim >> 2;
+    float4 q[QR];
+#pragma unroll
+    for (int j = 0; j < QR; j++) {
+        const uint32_t c = lane + 32u * j;
+        q[j] = (c < chunks) ? reinterpret_cast<const float4 *>(q_smem)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (uint32_t g = 0; g < n; g += R) {
+        float4 v[R][QR];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const bool act = g + r < n;
+            const uint32_t id = act ? id_at(g + r) : 0u;
+            const float4 *row4 = reinterpret_cast<const float4 *>(data + (uint64_t) id * dim);
+#pragma unroll
+            for (int j = 0; j < QR; j++) {
+                const uint32_t c = lane + 32u * j;
+                v[r][j] = (act && c < chunks) ? __ldg(row4 + c) : q[j];  // q - q adds exactly nothing
+            }
+        }
+        float p[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < QR; j++) acc = sq_acc4(q[j], v[r][j], acc);
+            p[r] = acc;
+        }
+        const float sum = fold_rows<R>(p);
+        const uint32_t my_row = lane >> (5 - Log2<R>::v);
+        if ((lane & (32 / R - 1)) == 0 && g + my_row < n) sink(g + my_row, metric == kEuclidean ? sqrtf(sum) : sum);
+    }
+}
+
+// Any dim: one row at a time. dim % 4 == 0: the chunk ownership of warp_rows_v4; otherwise
+// scalar elements l, l+32, ... (the reference's order).
+template<typename IdAt, typename Sink>
+__device__ __forceinline__ void warp_rows_generic(const float *q_smem, const float *__restrict__ data, uint32_t dim,
+                                                  int metric, uint32_t n, IdAt id_at, Sink sink) {
+    const uint32_t lane = lane_id();
+    for (uint32_t g = 0; g < n; g++) {
+        const float *row = data + (uint64_t) id_at(g) * dim;
+        float p[1] = {0.0f};
+        if ((dim & 3u) == 0) {
+            const float4 *q4 = reinterpret_cast<const float4 *>(q_smem);
+            const float4 *r4 = reinterpret_cast<const float4 *>(row);
+            for (uint32_t c = lane; c < (dim >> 2); c += 32) p[0] = sq_acc4(q4[c], __ldg(r4 + c), p[0]);
+        } else {
+            for (uint32_t i = lane; i < dim; i += 32) {
+                const float d = q_smem[i] - __ldg(row + i);
+                p[0] = __fmaf_rn(d, d, p[0]);
+            }
+        }
+        const float sum = fold_rows<1>(p);
+        if (lane == 0) sink(g, metric == kEuclidean ? sqrtf(sum) : sum);
+    }
+}
+
+template<typename IdAt, typename Sink>
+__device__ __forceinline__ void warp_rows(const float *q_smem, const float *__restrict__ data, uint32_t dim, int metric,
+                                          uint32_t n, IdAt id_at, Sink sink) {
+    if ((dim & 3u) == 0 && dim <= 128) warp_rows_v4<1>(q_smem, data, dim, metric, n, id_at, sink);
+    else if ((dim & 3u) == 0 && dim <= 256) warp_rows_v4<2>(q_smem, data, dim, metric, n, id_at, sink);
+    else if ((dim & 3u) == 0 && dim <= 512) warp_rows_v4<4>(q_smem, data, dim, metric, n, id_at, sink);
+    else if ((dim & 3u) == 0 && dim <= 1024) warp_rows_v4<8>(q_smem, data, dim, metric, n, id_at, sink);
+    else warp_rows_generic(q_smem, data, dim, metric, n, id_at, sink);
 }
 
 __device__ __forceinline__ float finish_metric(float s, int metric) {
@@ -145,45 +221,52 @@ __device__ __forceinline__ void cx_lanes(float (&k)[N], uint32_t (&v)[N], uint32
     }
 }
 
-// One merge phase producing sorted runs of `run` = size elements (size >= 2N means
-// cross-lane strides). asc decided per element by (e & size) == 0, or always for
-// the final phase.
-template<int N>
-__device__ __forceinline__ void bitonic_phase(float (&k)[N], uint32_t (&v)[N], uint32_t size, bool final_phase) {
+// One merge phase producing sorted runs of SIZE elements (SIZE >= 2N means cross-lane
+// strides). Ascending where (e & SIZE) == 0, or everywhere in the final phase. Every
+// bound is a compile-time constant so the whole network unrolls into straight-line code.
+template<int N, int SIZE, bool FINAL>
+__device__ __forceinline__ void bitonic_phase(float (&k)[N], uint32_t (&v)[N]) {
     const uint32_t lane = lane_id();
-    // cross-lane strides: size/2 ... N  (lane stride = stride / N)
-    for (uint32_t stride = size >> 1; stride >= (uint32_t) N; stride >>= 1) {
+    // cross-lane strides: SIZE/2 ... N  (lane stride = stride / N)
+#pragma unroll
+    for (int stride = SIZE / 2; stride >= N; stride >>= 1) {
         const uint32_t ls = stride / N;
-        const bool asc = final_phase || (((N * lane) & size) == 0);
+        const bool asc = FINAL || (((N * lane) & SIZE) == 0);
         const bool lower = (lane & ls) == 0;
         cx_lanes<N>(k, v, ls, lower == asc);
     }
-    // in-register strides: min(size/2, N/2) ... 1
+    // in-register strides: min(SIZE/2, N/2) ... 1
 #pragma unroll
-    for (int stride = N / 2; stride >= 1; stride >>= 1) {
-        if ((uint32_t) stride > (size >> 1)) continue;
+    for (int stride = (SIZE / 2 < N / 2 ? SIZE / 2 : N / 2); stride >= 1; stride >>= 1) {
 #pragma unroll
         for (int i = 0; i < N; i++) {
             const int j = i ^ stride;
             if (i < j) {
                 const uint32_t e = N * lane + i;
-                const bool asc = final_phase || ((e & size) == 0);
+                const bool asc = FINAL || ((e & SIZE) == 0);
                 cx_regs(k[i], v[i], k[j], v[j], asc);
             }
         }
     }
 }
 
+template<int N, int SIZE>
+struct BitonicSortFrom {
+    static __device__ __forceinline__ void run(float (&k)[N], uint32_t (&v)[N]) {
+        bitonic_phase<N, SIZE, SIZE == 32 * N>(k, v);
+        if constexpr (SIZE < 32 * N) BitonicSortFrom<N, SIZE * 2>::run(k, v);
+    }
+};
+
 template<int N>
 __device__ __forceinline__ void warp_sort(float (&k)[N], uint32_t (&v)[N]) {
-#pragma unroll
-    for (uint32_t size = 2; size <= 32u * N; size <<= 1) bitonic_phase<N>(k, v, size, size == 32u * N);
+    BitonicSortFrom<N, 2>::run(k, v);
 }
 
 // Last phase only: input must be bitonic over e (bitonic.cuh warp_merge, range 32).
 template<int N>
 __device__ __forceinline__ void warp_merge_final(float (&k)[N], uint32_t (&v)[N]) {
-    bitonic_phase<N>(k, v, 32u * N, true);
+    bitonic_phase<N, 32 * N, true>(k, v);
 }
 
 // Same network on a shared-memory array of 32*n pairs, n a runtime power of two.
@@ -230,12 +313,13 @@ __device__ __forceinline__ uint32_t visited_insert(uint32_t *table, uint32_t bit
 typedef unsigned long long u64;
 
 // ---- u64 bitonic network, N keys per lane, position e = N*lane + i -------------
-template<int N>
-__device__ __forceinline__ void phase_u64(u64 (&k)[N], uint32_t size, bool final_phase) {
+template<int N, int SIZE, bool FINAL>
+__device__ __forceinline__ void phase_u64_t(u64 (&k)[N]) {
     const uint32_t lane = lane_id();
-    for (uint32_t stride = size >> 1; stride >= (uint32_t) N; stride >>= 1) {
+#pragma unroll
+    for (int stride = SIZE / 2; stride >= N; stride >>= 1) {
         const uint32_t ls = stride / N;
-        const bool asc = final_phase || (((N * lane) & size) == 0);
+        const bool asc = FINAL || (((N * lane) & SIZE) == 0);
         const bool keep_small = ((lane & ls) == 0) == asc;
 #pragma unroll
         for (int i = 0; i < N; i++) {
@@ -244,24 +328,30 @@ __device__ __forceinline__ void phase_u64(u64 (&k)[N], uint32_t size, bool final
         }
     }
 #pragma unroll
-    for (int stride = N / 2; stride >= 1; stride >>= 1) {
-        if ((uint32_t) stride > (size >> 1)) continue;
+    for (int stride = (SIZE / 2 < N / 2 ? SIZE / 2 : N / 2); stride >= 1; stride >>= 1) {
 #pragma unroll
         for (int i = 0; i < N; i++) {
             const int j = i ^ stride;
             if (i < j) {
-                const bool asc = final_phase || (((N * lane + i) & size) == 0);
+                const bool asc = FINAL || (((N * lane + i) & SIZE) == 0);
                 const u64 a = k[i], b = k[j];
                 if ((a > b) == asc && a != b) { k[i] = b; k[j] = a; }
             }
         }
     }
 }
+template<int N, int SIZE>
+struct SortU64From {
+    static __device__ __forceinline__ void run(u64 (&k)[N]) {
+        phase_u64_t<N, SIZE, SIZE == 32 * N>(k);
+        if constexpr (SIZE < 32 * N) SortU64From<N, SIZE * 2>::run(k);
+    }
+};
 template<int N>
-__device__ __forceinline__ void sort_u64(u64 (&k)[N]) {
-#pragma unroll
-    for (uint32_t size = 2; size <= 32u * N; size <<= 1) phase_u64<N>(k, size, size == 32u * N);
-}
+__device__ __forceinline__ void sort_u64(u64 (&k)[N]) { SortU64From<N, 2>::run(k); }
+// final merge phase of a bitonic sequence of 32*N keys
+template<int N>
+__device__ __forceinline__ void merge_final_u64(u64 (&k)[N]) { phase_u64_t<N, 32 * N, true>(k); }
 
 __host__ __device__ constexpr uint32_t round_up32(uint32_t x) { return (x + 31u) & ~31u; }
 

@@ -88,20 +88,11 @@ __device__ __forceinline__ uint32_t spill_pool(const float (&bk)[NB], const uint
 __device__ __forceinline__ uint32_t occlusion_flags(const PruneStrip &ps, uint32_t from, uint32_t P, float *q,
                                                     const float *__restrict__ data, uint32_t center, uint32_t dim,
                                                     float alpha, int metric) {
-    const uint32_t lane = lane_id(), team = lane / kTeam;
     load_query(q, data + (uint64_t) center * dim, dim);
     uint32_t rows = 0;
-    for (uint32_t i0 = from; i0 < P; i0 += kTeamsPerWarp) {
-        const uint32_t i = i0 + team;
-        const bool active = i < P;
-        const uint32_t id = active ? ps.pool_id[i] : 0;
-        const float part = team_partial(q, data + (uint64_t) id * dim, dim, active);
-        const float sum = team_fold(part);
-        if (active && (lane & (kTeam - 1)) == 0) {
-            const float d = finish_metric(sum, metric);
-            ps.flags[i] = (alpha * d < ps.pool_dist[i]) ? 0u : 1u;
-        }
-    }
+    warp_rows(q, data, dim, metric, P > from ? P - from : 0,
+              [&](uint32_t i) { return ps.pool_id[from + i]; },
+              [&](uint32_t i, float d) { ps.flags[from + i] = (alpha * d < ps.pool_dist[from + i]) ? 0u : 1u; });
     rows += (P > from) ? (P - from) : 0;
     __syncwarp();
     return rows;

@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(256) nnd_merge_kernel(const NndDev d) {
         if (take) keys[i] = cand;
         inserted += __popc(__ballot_sync(kFullMask, take));
     }
-    phase_u64<NK>(keys, K, true);
+    merge_final_u64<NK>(keys);
 #pragma unroll
     for (int i = 0; i < NK; i++) list[NK * lane + i] = keys[i];
     if (lane == 0 && inserted) atomicAdd(d.counter, inserted);

@@ -25,11 +25,13 @@ __global__ void gather_rows_kernel(const float *__restrict__ data, const uint32_
 }
 
 // A warp per point: distances to all centroids, network sort, nearest + boundary flag.
-__global__ void __launch_bounds__(256) assign_kernel(const AssignArgs a, uint32_t max_centroid, uint32_t strip_words) {
+__global__ void __launch_bounds__(256) assign_kernel(const AssignArgs a, uint32_t max_centroid, uint32_t strip_words,
+                                                     bool only_flagged) {
     extern __shared__ __align__(16) uint32_t smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t p = blockIdx.x * (blockDim.x >> 5) + warp;
     if (p >= a.n) return;
+    if (only_flagged && a.nearest[p] != kInvalid) return;  // settled by assign_tiled_kernel
     uint32_t *base = smem + (size_t) warp * strip_words;
     float *query = reinterpret_cast<float *>(base);
     uint32_t *scratch = base + dim_pad4(a.dim);
@@ -42,6 +44,122 @@ __global__ void __launch_bounds__(256) assign_kernel(const AssignArgs a, uint32_
             const float *ck = reinterpret_cast<const float *>(scratch);
             // partition_kernel.cuh:58-60
             a.is_boundary[p] = (a.boundary_factor >= 0.0f && a.C > 1 && ck[1] / ck[0] <= a.boundary_factor) ? 0u : kInvalid;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Tiled assignment: the same distances as assign_kernel, bit for bit, computed as a
+// points x centroids contraction. A CTA owns 32 points and walks the centroids in tiles of
+// 64; both tiles are staged through shared memory 32 dimensions at a time and each thread
+// keeps 2 x 4 (point, centroid) pairs in registers. To reproduce the team summation order
+// (lane t of a team owns 16-byte chunks t, t+8, ...; lanes are folded 4-2-1) every pair
+// keeps EIGHT partial sums, one per team lane, and folds them in the same tree at the end.
+// Each point then needs its smallest and second smallest distance; when the smallest is
+// shared by two centroids the point is left to assign_kernel (flag 0xffffffff), whose
+// network sort reproduces the reference's tie order.
+// ---------------------------------------------------------------------------
+constexpr int kAP = 32;          // points per CTA
+constexpr int kAC = 64;          // centroids per tile
+constexpr int kAK = 32;          // dimensions per stage (8 chunks of 4 = one round of the 8 team lanes)
+constexpr int kAPPad = kAP + 2;  // float2 reads stay 8-byte aligned
+constexpr int kACPad = kAC + 4;  // float4 reads stay 16-byte aligned
+
+struct NearState {
+    float d0, d1;    // smallest and second smallest distance
+    uint32_t id;     // centroid of d0
+    uint32_t ties;   // how many centroids share d0
+};
+
+__device__ __forceinline__ void near_add(NearState &s, float d, uint32_t id) {
+    if (d < s.d0) { s.d1 = s.d0; s.d0 = d; s.id = id; s.ties = 1; }
+    else if (d == s.d0) { s.d1 = d; s.ties++; }
+    else if (d < s.d1) { s.d1 = d; }
+}
+
+__device__ __forceinline__ void near_merge(NearState &a, float d0, float d1, uint32_t id, uint32_t ties) {
+    if (d0 < a.d0) { a.d1 = fminf(a.d0, d1); a.d0 = d0; a.id = id; a.ties = ties; }
+    else if (d0 == a.d0) { a.d1 = d0; a.ties += ties; }
+    else { a.d1 = fminf(a.d1, d0); }
+}
+
+__global__ void __launch_bounds__(256) assign_tiled_kernel(const AssignArgs a) {
+    __shared__ __align__(16) float Ps[kAK * kAPPad];
+    __shared__ __align__(16) float Cs[kAK * kACPad];
+    const uint32_t tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const uint32_t p0 = blockIdx.x * kAP;
+    NearState st[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) { st[i].d0 = FLT_MAX; st[i].d1 = FLT_MAX; st[i].id = kInvalid; st[i].ties = 0; }
+
+    for (uint32_t c0 = 0; c0 < a.C; c0 += kAC) {
+        float acc[2][4][8];
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int t = 0; t < 8; t++) acc[i][j][t] = 0.0f;
+        for (uint32_t k0 = 0; k0 < a.dim; k0 += kAK) {
+            for (uint32_t e = tid; e < kAP * kAK; e += 256) {
+                const uint32_t row = e / kAK, kk = e % kAK;
+                const uint32_t p = p0 + row, d = k0 + kk;
+                Ps[kk * kAPPad + row] = (p < a.n && d < a.dim) ? __ldg(a.data + (uint64_t) p * a.dim + d) : 0.0f;
+            }
+            for (uint32_t e = tid; e < kAC * kAK; e += 256) {
+                const uint32_t row = e / kAK, kk = e % kAK;
+                const uint32_t c = c0 + row, d = k0 + kk;
+                Cs[kk * kACPad + row] = (c < a.C && d < a.dim) ? __ldg(a.centroids + (uint64_t) c * a.dim + d) : 0.0f;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int kk = 4 * t + e;
+                    const float2 pv = *reinterpret_cast<const float2 *>(Ps + kk * kAPPad + 2 * ty);
+                    const float4 cv = *reinterpret_cast<const float4 *>(Cs + kk * kACPad + 4 * tx);
+                    const float pa[2] = {pv.x, pv.y};
+                    const float ca[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                    for (int i = 0; i < 2; i++)
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const float df = pa[i] - ca[j];
+                            acc[i][j][t] = __fmaf_rn(df, df, acc[i][j][t]);
+                        }
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t c = c0 + 4 * tx + j;
+                if (c >= a.C) continue;
+                const float *s = acc[i][j];
+                const float sum = ((s[0] + s[4]) + (s[2] + s[6])) + ((s[1] + s[5]) + (s[3] + s[7]));
+                near_add(st[i], a.metric == kEuclidean ? sqrtf(sum) : sum, c);
+            }
+    }
+    // fold the 16 threads (tx) that share a point: they are 16 consecutive lanes
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+#pragma unroll
+        for (int off = 8; off >= 1; off >>= 1) {
+            const float d0 = __shfl_xor_sync(kFullMask, st[i].d0, off);
+            const float d1 = __shfl_xor_sync(kFullMask, st[i].d1, off);
+            const uint32_t id = __shfl_xor_sync(kFullMask, st[i].id, off);
+            const uint32_t ties = __shfl_xor_sync(kFullMask, st[i].ties, off);
+            near_merge(st[i], d0, d1, id, ties);
+        }
+        const uint32_t p = p0 + 2 * ty + i;
+        if (tx == 0 && p < a.n) {
+            const bool unique = st[i].ties == 1;
+            a.nearest[p] = unique ? st[i].id : kInvalid;
+            if (a.is_boundary && unique)  // partition_kernel.cuh:58-60
+                a.is_boundary[p] = (a.boundary_factor >= 0.0f && a.C > 1 && st[i].d1 / st[i].d0 <= a.boundary_factor) ? 0u : kInvalid;
         }
     }
 }
@@ -276,7 +394,11 @@ cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
         if (e != cudaSuccess) return e;
     }
-    assign_kernel<<<(a.n + warps - 1) / warps, warps * 32, smem_bytes, stream>>>(a, max_centroid, strip_words);
+    // the tiled kernel settles every point whose nearest centroid is unique; the warp-per-point
+    // kernel then handles the rest (ties at the minimum; all points when dim % 4 != 0)
+    const bool tiled = (a.dim & 3u) == 0 && a.C >= 2;
+    if (tiled) assign_tiled_kernel<<<(a.n + kAP - 1) / kAP, 256, 0, stream>>>(a);
+    assign_kernel<<<(a.n + warps - 1) / warps, warps * 32, smem_bytes, stream>>>(a, max_centroid, strip_words, tiled);
     return cudaGetLastError();
 }
 

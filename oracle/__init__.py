@@ -19,7 +19,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libglide_oracle.so")
 
 EUCLIDEAN, COSINE = 0, 1
-ORDER_REF, ORDER_TEAM = 0, 1
+# ORDER_WARP: candidate scoring / pruning order of the CUDA kernels; ORDER_TEAM: their order for
+# centroid distances (routing, assignment, k-means); ORDER_REF: the reference's own.
+ORDER_REF, ORDER_TEAM, ORDER_WARP = 0, 1, 2
 INVALID = 0xFFFFFFFF
 
 
@@ -104,7 +106,9 @@ def sort_with_key_value(max_number: int, vals, keys):
 
 
 def search(data, graph, centroids, start_points, queries, p: SearchParams, metric=EUCLIDEAN,
-           order=ORDER_TEAM, threads=0, want_counters=False):
+           order=ORDER_WARP, threads=0, want_counters=False, route_order=None):
+    if route_order is None:
+        route_order = ORDER_REF if order == ORDER_REF else ORDER_TEAM
     data, queries, centroids = _f32(data), _f32(queries), _f32(centroids)
     graph, start_points = _u32(graph), _u32(start_points)
     Q, dim = queries.shape
@@ -114,15 +118,15 @@ def search(data, graph, centroids, start_points, queries, p: SearchParams, metri
     rc = lib().orc_search(_p(data), u32(dim), _p(graph), u32(graph.shape[1]), _p(centroids),
                           u32(centroids.shape[0]), _p(start_points), _p(queries), u32(Q), u32(p.top_k),
                           u32(p.beam), u32(p.max_iterations), u32(p.min_iterations), u32(p.hash_bit),
-                          u32(p.hash_reset_interval), i32(metric), i32(order), _p(ids), _p(dists),
-                          _p(counters), i32(threads))
+                          u32(p.hash_reset_interval), i32(metric), i32(order), i32(route_order), _p(ids),
+                          _p(dists), _p(counters), i32(threads))
     if rc != 0:
         raise ValueError("orc_search: unsupported shape")
     return (ids, dists, counters) if want_counters else (ids, dists)
 
 
 def build_rows(reorder_data, knn, seg_start, seg_len, start_points_local, mapping, num, graph_degree,
-               p: SearchParams, alpha, metric=EUCLIDEAN, order=ORDER_TEAM, graph=None, first=0, count=None,
+               p: SearchParams, alpha, metric=EUCLIDEAN, order=ORDER_WARP, graph=None, first=0, count=None,
                threads=0, want_counters=False):
     reorder_data, knn = _f32(reorder_data), _u32(knn)
     seg_start, seg_len = _u32(seg_start), _u32(seg_len)
@@ -143,7 +147,7 @@ def build_rows(reorder_data, knn, seg_start, seg_len, start_points_local, mappin
 
 
 def build_boundary(reorder_data, knn, num, start_point_local, mapping, graph, p: SearchParams, alpha,
-                   metric=EUCLIDEAN, order=ORDER_TEAM, threads=0):
+                   metric=EUCLIDEAN, order=ORDER_WARP, threads=0):
     reorder_data, knn, mapping = _f32(reorder_data), _u32(knn), _u32(mapping)
     assert graph.dtype == np.uint32 and graph.flags.c_contiguous
     boundary_num = reorder_data.shape[0] - num
@@ -164,14 +168,17 @@ def reverse_graph(graph):
 
 
 def refine(data, graph_in, centroids, start_points, p: SearchParams, alpha, metric=EUCLIDEAN,
-           order=ORDER_TEAM, threads=0):
+           order=ORDER_WARP, threads=0, route_order=None):
+    if route_order is None:
+        route_order = ORDER_REF if order == ORDER_REF else ORDER_TEAM
     data, centroids = _f32(data), _f32(centroids)
     graph_in, start_points = _u32(graph_in), _u32(start_points)
     out = np.empty_like(graph_in)
     rc = lib().orc_refine(_p(data), u32(data.shape[0]), u32(data.shape[1]), _p(graph_in), _p(out),
                           u32(graph_in.shape[1]), _p(centroids), u32(centroids.shape[0]), _p(start_points),
                           u32(p.beam), u32(p.max_iterations), u32(p.min_iterations), u32(p.hash_bit),
-                          u32(p.hash_reset_interval), f32(alpha), i32(metric), i32(order), i32(threads))
+                          u32(p.hash_reset_interval), f32(alpha), i32(metric), i32(order), i32(route_order),
+                          i32(threads))
     if rc != 0:
         raise ValueError("orc_refine: unsupported shape")
     return out
@@ -210,7 +217,7 @@ def select_segments(queries, centroids, min_segment_num, boundary_factor, metric
 
 
 def search_on_sub(data, graph, mapping, start_point, queries, segment_ids, segment_id, p: SearchParams,
-                  final_ids, final_dists, metric=EUCLIDEAN, order=ORDER_TEAM, threads=0):
+                  final_ids, final_dists, metric=EUCLIDEAN, order=ORDER_WARP, threads=0):
     data, queries = _f32(data), _f32(queries)
     graph, mapping, segment_ids = _u32(graph), _u32(mapping), _u32(segment_ids)
     assert final_ids.dtype == np.uint32 and final_dists.dtype == np.float32

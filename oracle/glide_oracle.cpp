@@ -44,10 +44,13 @@ enum Metric : int { kEuclidean = 0, kCosine = 1 };  // params.cuh:5-8
 
 // Summation orders. kOrderRef is the reference's: lane l of a 32-lane warp adds
 // elements l, l+32, ... and a shuffle-down tree (16,8,4,2,1) folds the lanes
-// (distance.cuh:13-21). kOrderTeam is the order used by this repository's CUDA
-// kernels: a team of 8 lanes, lane t owning 4-float chunks t, t+8, ... (scalar
-// elements t, t+8, ... when dim is not a multiple of 4), folded by a 4,2,1 tree.
-enum Order : int { kOrderRef = 0, kOrderTeam = 1 };
+// (distance.cuh:13-21). The other two are the orders of this repository's CUDA kernels.
+// kOrderTeam (centroid distances: routing, assignment, k-means): a team of 8 lanes, lane t
+// owning 4-float chunks t, t+8, ... (scalar elements t, t+8, ... when dim is not a multiple
+// of 4), folded by a 4,2,1 tree. kOrderWarp (candidate scoring and pruning): the 32 lanes
+// of a warp, lane l owning 4-float chunks l, l+32, ..., folded by the reference's
+// 16,8,4,2,1 tree; when dim is not a multiple of 4 it is exactly kOrderRef.
+enum Order : int { kOrderRef = 0, kOrderTeam = 1, kOrderWarp = 2 };
 
 inline float sq_sum(const float *a, const float *b, uint32_t dim, int order) {
     float lane[32];
@@ -55,6 +58,9 @@ inline float sq_sum(const float *a, const float *b, uint32_t dim, int order) {
     if (order == kOrderRef) {
         T = 32;
         V = 1;
+    } else if (order == kOrderWarp) {
+        T = 32;
+        V = (dim % 4 == 0) ? 4 : 1;
     } else {
         T = 8;
         V = (dim % 4 == 0) ? 4 : 1;
@@ -362,12 +368,12 @@ struct BeamState {
     // adjacency row of that partition's start point.
     void seed_by_centroid(const float *query, const float *data, const uint32_t *graph,
                           const uint32_t *start_points, const float *centroids, uint32_t C,
-                          uint32_t dim, int metric, int order) {
+                          uint32_t dim, int metric, int order, int route_order) {
         std::vector<uint32_t> cid(C);
         std::vector<float> cd(C);
         for (uint32_t i = 0; i < C; i++) {
             cid[i] = i;
-            cd[i] = distance(query, centroids + (uint64_t) i * dim, dim, metric, order);
+            cd[i] = distance(query, centroids + (uint64_t) i * dim, dim, metric, route_order);
         }
         sort_with_key_value(ladder_centroid(C), C, cid.data(), cd.data());
         const uint32_t node = start_points[cid[0]];
@@ -626,13 +632,14 @@ int orc_search(const float *data, uint32_t dim, const uint32_t *graph, uint32_t 
                const float *centroids, uint32_t C, const uint32_t *start_points, const float *queries,
                uint32_t Q, uint32_t top_k, uint32_t beam, uint32_t max_iterations,
                uint32_t min_iterations, uint32_t hash_bit, uint32_t hash_reset_interval, int metric,
-               int order, uint32_t *out_ids, float *out_dists, uint64_t *counters, int threads) {
+               int order, int route_order, uint32_t *out_ids, float *out_dists, uint64_t *counters,
+               int threads) {
     if (beam % 32 || beam == 0 || beam > 512 || degree > 256 || top_k > beam) return -1;
     const SearchCfg cfg{beam, max_iterations, min_iterations, hash_bit, hash_reset_interval};
     parallel_for(Q, threads, [&](int64_t q) {
         BeamState s(cfg, degree);
         const float *query = queries + (uint64_t) q * dim;
-        s.seed_by_centroid(query, data, graph, start_points, centroids, C, dim, metric, order);
+        s.seed_by_centroid(query, data, graph, start_points, centroids, C, dim, metric, order, route_order);
         s.run(cfg, kInvalid, graph, query, data, dim, metric, order);
         for (uint32_t i = 0; i < top_k; i++) {
             out_ids[(uint64_t) q * top_k + i] = s.beam_id[i] & kClean;
@@ -760,7 +767,7 @@ int orc_refine(const float *data, uint32_t num, uint32_t dim, const uint32_t *gr
                uint32_t *graph_out, uint32_t degree, const float *centroids, uint32_t C,
                const uint32_t *start_points, uint32_t beam, uint32_t max_iterations,
                uint32_t min_iterations, uint32_t hash_bit, uint32_t hash_reset_interval, float alpha,
-               int metric, int order, int threads) {
+               int metric, int order, int route_order, int threads) {
     if (beam % 32 || beam == 0 || beam > 512 || degree > 256) return -1;
     const SearchCfg cfg{beam, max_iterations, min_iterations, hash_bit, hash_reset_interval};
     parallel_for(num, threads, [&](int64_t t) {
@@ -775,7 +782,7 @@ int orc_refine(const float *data, uint32_t num, uint32_t dim, const uint32_t *gr
         }
         const float *query = data + (uint64_t) p * dim;
         BeamState st(cfg, degree);
-        st.seed_by_centroid(query, data, graph_in, start_points, centroids, C, dim, metric, order);
+        st.seed_by_centroid(query, data, graph_in, start_points, centroids, C, dim, metric, order, route_order);
         st.run(cfg, p, graph_in, query, data, dim, metric, order);
         std::vector<uint32_t> pid;
         std::vector<float> pdist;

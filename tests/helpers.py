@@ -42,14 +42,14 @@ def exact_partition_knn(reorder_data, seg_start, seg_len, k, metric):
 
 
 def oracle_pipeline(base, centroid_num=4, boundary_factor=1.1, knn_degree=16, graph_degree=16, build_beam=32,
-                    refine_beam=64, alpha=1.05, metric=oracle.EUCLIDEAN, order=oracle.ORDER_TEAM, seed=3,
-                    with_refine=True):
+                    refine_beam=64, alpha=1.05, metric=oracle.EUCLIDEAN, order=oracle.ORDER_WARP, seed=3,
+                    with_refine=True, route_order=oracle.ORDER_TEAM):
     """partition -> exact kNN per partition -> build -> boundary merge -> reverse -> refine, all on the oracle."""
     n, dim = base.shape
     rng = np.random.default_rng(seed)
     sample = base[rng.permutation(n)[:max(centroid_num * 20, 64)]]
-    centroids, _, _ = oracle.kmeans(sample, centroid_num, 10, order=order, metric=metric, init=0)
-    seg_index, seg_start, seg_len = oracle.define_partition(base, centroids, boundary_factor, metric, order)
+    centroids, _, _ = oracle.kmeans(sample, centroid_num, 10, order=route_order, metric=metric, init=0)
+    seg_index, seg_start, seg_len = oracle.define_partition(base, centroids, boundary_factor, metric, route_order)
     reorder_data, mapping = oracle.reorder(base, seg_index, seg_start, int(seg_len[centroid_num]))
     knn = exact_partition_knn(reorder_data, seg_start, seg_len, knn_degree, metric)
     local_sp = np.array([rng.integers(0, max(int(l), 1)) for l in seg_len], np.uint32)
@@ -66,7 +66,7 @@ def oracle_pipeline(base, centroid_num=4, boundary_factor=1.1, knn_degree=16, gr
     after_reverse = graph.copy()
     p_refine = oracle.SearchParams.derive(refine_beam, knn_degree)  # quirk: hash sized from knn_degree
     if with_refine:
-        graph = oracle.refine(base, graph, centroids, orig_sp, p_refine, alpha, metric, order)
+        graph = oracle.refine(base, graph, centroids, orig_sp, p_refine, alpha, metric, order, route_order=route_order)
     return dict(centroids=centroids, seg_index=seg_index, seg_start=seg_start, seg_len=seg_len,
                 reorder_data=reorder_data, mapping=mapping, knn=knn, local_sp=local_sp, orig_sp=orig_sp,
                 p_build=p_build, p_refine=p_refine, after_build=after_build, after_boundary=after_boundary,

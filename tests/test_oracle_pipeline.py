@@ -110,7 +110,7 @@ def test_search_recall_and_exact_distances(pipe):
         assert np.all(np.diff(dists, axis=1) >= 0)
         for q in range(0, 200, 37):
             for j in range(10):
-                want = oracle.distance(queries[q], base[ids[q, j]], oracle.EUCLIDEAN, oracle.ORDER_TEAM)
+                want = oracle.distance(queries[q], base[ids[q, j]], oracle.EUCLIDEAN, oracle.ORDER_WARP)
                 assert dists[q, j] == want
         assert counters[:, 1].max() <= sp.max_iterations
     assert recalls[0] >= 0.9 and recalls[-1] >= recalls[0] - 1e-6 and recalls[-1] >= 0.97

@@ -12,7 +12,7 @@ def test_distance_orders_agree_with_float64():
     for dim in (1, 3, 32, 96, 100, 128, 960):
         a, b = rng.random(dim, dtype=np.float32), rng.random(dim, dtype=np.float32)
         ref = float(np.sqrt(np.sum((a.astype(np.float64) - b.astype(np.float64)) ** 2)))
-        for order in (oracle.ORDER_REF, oracle.ORDER_TEAM):
+        for order in (oracle.ORDER_REF, oracle.ORDER_TEAM, oracle.ORDER_WARP):
             assert oracle.distance(a, b, oracle.EUCLIDEAN, order) == pytest.approx(ref, rel=1e-5)
             assert oracle.distance(a, b, oracle.COSINE, order) == pytest.approx(ref * ref, rel=1e-5)
 
@@ -27,6 +27,7 @@ def test_distance_is_order_independent_on_integer_data():
         assert oracle.distance(a, b, oracle.COSINE, oracle.ORDER_REF) == exact
         assert oracle.distance(a, b, oracle.COSINE, oracle.ORDER_TEAM) == exact
         assert oracle.distance(a, b, oracle.EUCLIDEAN, oracle.ORDER_TEAM) == np.sqrt(np.float32(exact))
+        assert oracle.distance(a, b, oracle.COSINE, oracle.ORDER_WARP) == exact
 
 
 def _textbook_bitonic(keys, vals, n_regs):
@@ -125,3 +126,11 @@ def test_bruteforce_matches_numpy():
     want = np.argsort(d2, axis=1, kind="stable")[:, :10]
     assert np.array_equal(ids, want.astype(np.uint32))
     assert np.allclose(d, np.sqrt(np.take_along_axis(d2, want, 1)), rtol=1e-5)
+
+
+def test_warp_order_equals_reference_order_for_odd_dims():
+    # dim % 4 != 0: the kernels fall back to scalar lane-strided sums, the reference's own order
+    rng = np.random.default_rng(5)
+    for dim in (1, 30, 33, 101):
+        a, b = rng.random(dim, dtype=np.float32), rng.random(dim, dtype=np.float32)
+        assert oracle.distance(a, b, oracle.EUCLIDEAN, oracle.ORDER_WARP) == oracle.distance(a, b, oracle.EUCLIDEAN, oracle.ORDER_REF)
