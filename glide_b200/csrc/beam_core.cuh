@@ -29,13 +29,14 @@ struct WarpStrip {
     float *cand_dist;    // 32*NC
     uint32_t *visited;   // 1 << hash_bit
     uint32_t *work;      // 32*NC: slots of the candidates to score
+    uint32_t *work_id;   // 32*NC: their ids
     uint32_t *extra;     // mode-specific scratch (pool, rows, merge buffers)
 };
 
 __host__ __device__ inline uint32_t dim_pad4(uint32_t dim) { return (dim + 3u) & ~3u; }
 
 __host__ __device__ inline uint32_t strip_words_base(uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
-    return dim_pad4(dim) + 3 * max_cand + (1u << hash_bit);
+    return dim_pad4(dim) + 4 * max_cand + (1u << hash_bit);
 }
 
 __device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
@@ -45,7 +46,8 @@ __device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, ui
     s.cand_dist = reinterpret_cast<float *>(s.cand_id + max_cand);
     s.visited = s.cand_id + 2 * max_cand;
     s.work = s.visited + (1u << hash_bit);
-    s.extra = s.work + max_cand;
+    s.work_id = s.work + max_cand;
+    s.extra = s.work_id + max_cand;
     return s;
 }
 
@@ -77,12 +79,16 @@ __device__ __forceinline__ uint32_t score_candidates(const WarpStrip &s, uint32_
         const bool valid = (id != kInvalid) && (id != skip_id);
         if (i < count && !valid) s.cand_dist[i] = FLT_MAX;
         const uint32_t mask = __ballot_sync(kFullMask, valid);
-        if (valid) s.work[n + __popc(mask & ((1u << lane) - 1))] = i;
+        if (valid) {
+            const uint32_t k = n + __popc(mask & ((1u << lane) - 1));
+            s.work[k] = i;
+            s.work_id[k] = id;
+        }
         n += __popc(mask);
     }
     __syncwarp();
     warp_rows(s.query, data, dim, metric, n,
-              [&](uint32_t i) { return s.cand_id[s.work[i]]; },
+              [&](uint32_t i) { return s.work_id[i]; },
               [&](uint32_t i, float d) { s.cand_dist[s.work[i]] = d; });
     __syncwarp();
     return n;

@@ -168,7 +168,16 @@ __device__ __forceinline__ void warp_rows_generic(const float *q_smem, const flo
         if ((dim & 3u) == 0) {
             const float4 *q4 = reinterpret_cast<const float4 *>(q_smem);
             const float4 *r4 = reinterpret_cast<const float4 *>(row);
-            for (uint32_t c = lane; c < (dim >> 2); c += 32) p[0] = sq_acc4(q4[c], __ldg(r4 + c), p[0]);
+            const uint32_t chunks = dim >> 2;
+            uint32_t c = lane;
+            for (; c + 96 < chunks; c += 128) {  // four loads in flight per lane
+                const float4 b0 = __ldg(r4 + c), b1 = __ldg(r4 + c + 32), b2 = __ldg(r4 + c + 64), b3 = __ldg(r4 + c + 96);
+                p[0] = sq_acc4(q4[c], b0, p[0]);
+                p[0] = sq_acc4(q4[c + 32], b1, p[0]);
+                p[0] = sq_acc4(q4[c + 64], b2, p[0]);
+                p[0] = sq_acc4(q4[c + 96], b3, p[0]);
+            }
+            for (; c < chunks; c += 32) p[0] = sq_acc4(q4[c], __ldg(r4 + c), p[0]);
         } else {
             for (uint32_t i = lane; i < dim; i += 32) {
                 const float d = q_smem[i] - __ldg(row + i);
@@ -183,10 +192,10 @@ __device__ __forceinline__ void warp_rows_generic(const float *q_smem, const flo
 template<typename IdAt, typename Sink>
 __device__ __forceinline__ void warp_rows(const float *q_smem, const float *__restrict__ data, uint32_t dim, int metric,
                                           uint32_t n, IdAt id_at, Sink sink) {
+    // register budget (a third variant pushes the search kernels from 64 to 100 registers):
+    // the query-in-registers path serves dim <= 128, wider rows stream chunk by chunk against
+    // the query in shared memory
     if ((dim & 3u) == 0 && dim <= 128) warp_rows_v4<1>(q_smem, data, dim, metric, n, id_at, sink);
-    else if ((dim & 3u) == 0 && dim <= 256) warp_rows_v4<2>(q_smem, data, dim, metric, n, id_at, sink);
-    else if ((dim & 3u) == 0 && dim <= 512) warp_rows_v4<4>(q_smem, data, dim, metric, n, id_at, sink);
-    else if ((dim & 3u) == 0 && dim <= 1024) warp_rows_v4<8>(q_smem, data, dim, metric, n, id_at, sink);
     else warp_rows_generic(q_smem, data, dim, metric, n, id_at, sink);
 }
 

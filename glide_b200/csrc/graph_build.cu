@@ -243,7 +243,7 @@ __device__ __forceinline__ void boundary_merge(const PruneStrip &ps, const uint3
 }
 
 template<int NB, int NC>
-__global__ void __launch_bounds__(256) build_kernel(const BuildDev d) {
+__global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
     extern __shared__ __align__(16) uint32_t smem[];
     const BuildArgs &a = d.a;
     const uint32_t warps_per_cta = blockDim.x >> 5;
