@@ -417,3 +417,39 @@ def test_sharded_build_on_two_gpus_equals_plain_build(tmp_path):
     port = 29400 + os.getpid() % 500
     mp.spawn(_sharded_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert open(tmp_path / "rank0.txt").read() == "ok" and open(tmp_path / "rank1.txt").read() == "ok"
+
+
+def test_large_path_end_to_end(gpu_ctx):
+    """preprocess_for_large -> build_knn_for_large -> GLIDE_large.build -> search, checked against
+    the oracle replaying the same stages on the same graphs, and against exact kNN for recall."""
+    from glide_b200 import large
+    from glide_b200.params import IndexParameter
+    base, queries = helpers.small_dataset("uniform", 6000, 32, 150, seed=13)
+    pre = large.preprocess_for_large(gpu_ctx, base, 4, 0.1, batch_num=3, seed=2)
+    assert pre["h_segment_length"].sum() == 6000 and sorted(pre["h_map"].tolist()) == list(range(6000))
+    want_seg = oracle.define_partition(base, pre["h_centroids"], -1.0)[0][:, 0]
+    for s, (lo, ln) in enumerate(zip(pre["h_segment_start"], pre["h_segment_length"])):
+        members = pre["h_map"][int(lo):int(lo) + int(ln)]
+        assert np.all(want_seg[members] == s) and np.all(np.diff(members.astype(np.int64)) > 0)
+    knn, _ = large.build_knn_for_large(gpu_ctx, NNDescentParameter(16), pre["h_reorder_data"], pre["h_segment_start"],
+                                       pre["h_segment_length"])
+    index = large.GLIDE_large(gpu_ctx, 24, Metric.Euclidean, pre["h_reorder_data"], pre["h_map"], pre["h_centroids"],
+                              pre["h_segment_start"], pre["h_segment_length"])
+    pk = SearchParameter(beam=64).derive(16)
+    pr = SearchParameter(beam=128).derive(16)
+    index.build(IndexParameter(24, 16, 1.05), pk, pr, knn, seed=5)
+    assert (index.graph_view() != INVALID).any(axis=1).all()
+    sp = SearchParameter(top_k=10, beam=64).derive(24)
+    ids, dists, _ = index.search(sp, 2, 1.2, dev(gpu_ctx, queries))
+    # oracle replay of the search over the GPU-built subgraphs
+    o = oracle.SearchParams(sp.beam, sp.max_iterations, 0, sp.hash_bit, sp.hash_reset_interval, 10)
+    routes = oracle.select_segments(queries, pre["h_centroids"], 2, 1.2)
+    want_ids = np.full((150, 10), INVALID, np.uint32)
+    want_d = np.full((150, 10), np.finfo(np.float32).max, np.float32)
+    for s, (lo, ln) in enumerate(zip(pre["h_segment_start"], pre["h_segment_length"])):
+        lo, ln = int(lo), int(ln)
+        oracle.search_on_sub(pre["h_reorder_data"][lo:lo + ln], index.graph_view()[lo:lo + ln], pre["h_map"][lo:lo + ln],
+                             int(index.start_point_view()[s]), queries, routes, s, o, want_ids, want_d)
+    assert np.array_equal(ids, want_ids) and np.array_equal(dists, want_d)
+    gt = oracle.bruteforce_knn(base, queries, 10, want_dists=False)
+    assert api.calculate_recall(ids, gt, 10) > 0.9
