@@ -211,10 +211,16 @@ __device__ __forceinline__ float finish_metric(float s, int metric) {
 // keys end up in the same slots as there.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void cx_regs(float &k0, uint32_t &v0, float &k1, uint32_t &v1, bool asc) {
-    if ((k0 != k1) && ((k0 < k1) != asc)) {
-        const float tk = k0; k0 = k1; k1 = tk;
-        const uint32_t tv = v0; v0 = v1; v1 = tv;
-    }
+    // min/max keep equal keys where they are (no exchange on a tie), like the reference's
+    // swap_if_needed (bitonic.cuh:24-33); the values follow their keys.
+    const float lo = fminf(k0, k1), hi = fmaxf(k0, k1);
+    const float n0 = asc ? lo : hi;
+    const bool moved = (n0 != k0);
+    const uint32_t t0 = moved ? v1 : v0, t1 = moved ? v0 : v1;
+    k1 = asc ? hi : lo;
+    k0 = n0;
+    v0 = t0;
+    v1 = t1;
 }
 
 template<int N>
@@ -223,10 +229,10 @@ __device__ __forceinline__ void cx_lanes(float (&k)[N], uint32_t (&v)[N], uint32
     for (int i = 0; i < N; i++) {
         const float ok = __shfl_xor_sync(kFullMask, k[i], lane_xor);
         const uint32_t ov = __shfl_xor_sync(kFullMask, v[i], lane_xor);
-        if ((k[i] != ok) && ((k[i] < ok) != keep_small)) {
-            k[i] = ok;
-            v[i] = ov;
-        }
+        // keep the smaller (or larger) key; on a tie the own pair stays (bitonic.cuh:35-44)
+        const float nk = keep_small ? fminf(k[i], ok) : fmaxf(k[i], ok);
+        v[i] = (nk != k[i]) ? ov : v[i];
+        k[i] = nk;
     }
 }
 
