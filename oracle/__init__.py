@@ -134,7 +134,7 @@ def build_rows(reorder_data, knn, seg_start, seg_len, start_points_local, mappin
     if graph is None:
         graph = np.full((num, graph_degree), INVALID, np.uint32)
     count = num - first if count is None else count
-    counters = np.zeros((count, 3), np.uint64) if want_counters else None
+    counters = np.zeros((count, 4), np.uint64) if want_counters else None
     rc = lib().orc_build_rows(_p(reorder_data), u32(reorder_data.shape[1]), _p(knn), u32(knn.shape[1]),
                               _p(seg_start), _p(seg_len), u32(seg_start.size), _p(start_points_local),
                               _p(mapping), u32(first), u32(count), u32(graph_degree), u32(p.beam),
@@ -147,7 +147,7 @@ def build_rows(reorder_data, knn, seg_start, seg_len, start_points_local, mappin
 
 
 def build_boundary(reorder_data, knn, num, start_point_local, mapping, graph, p: SearchParams, alpha,
-                   metric=EUCLIDEAN, order=ORDER_WARP, threads=0):
+                   metric=EUCLIDEAN, order=ORDER_WARP, threads=0, pool_sizes=None):
     reorder_data, knn, mapping = _f32(reorder_data), _u32(knn), _u32(mapping)
     assert graph.dtype == np.uint32 and graph.flags.c_contiguous
     boundary_num = reorder_data.shape[0] - num
@@ -155,7 +155,7 @@ def build_boundary(reorder_data, knn, num, start_point_local, mapping, graph, p:
                                   u32(num), u32(boundary_num), u32(start_point_local), _p(mapping),
                                   u32(graph.shape[1]), u32(p.beam), u32(p.max_iterations),
                                   u32(p.min_iterations), u32(p.hash_bit), u32(p.hash_reset_interval),
-                                  f32(alpha), i32(metric), i32(order), _p(graph), i32(threads))
+                                  f32(alpha), i32(metric), i32(order), _p(graph), _p(pool_sizes), i32(threads))
     if rc != 0:
         raise ValueError("orc_build_boundary: unsupported shape")
     return graph
@@ -168,7 +168,7 @@ def reverse_graph(graph):
 
 
 def refine(data, graph_in, centroids, start_points, p: SearchParams, alpha, metric=EUCLIDEAN,
-           order=ORDER_WARP, threads=0, route_order=None):
+           order=ORDER_WARP, threads=0, route_order=None, pool_sizes=None):
     if route_order is None:
         route_order = ORDER_REF if order == ORDER_REF else ORDER_TEAM
     data, centroids = _f32(data), _f32(centroids)
@@ -178,7 +178,7 @@ def refine(data, graph_in, centroids, start_points, p: SearchParams, alpha, metr
                           u32(graph_in.shape[1]), _p(centroids), u32(centroids.shape[0]), _p(start_points),
                           u32(p.beam), u32(p.max_iterations), u32(p.min_iterations), u32(p.hash_bit),
                           u32(p.hash_reset_interval), f32(alpha), i32(metric), i32(order), i32(route_order),
-                          i32(threads))
+                          _p(pool_sizes), i32(threads))
     if rc != 0:
         raise ValueError("orc_refine: unsupported shape")
     return out

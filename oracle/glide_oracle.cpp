@@ -681,6 +681,7 @@ int orc_build_rows(const float *reorder_data, uint32_t dim, const uint32_t *knn,
         std::vector<uint32_t> pid;
         std::vector<float> pdist;
         st.finish_pool(pid, pdist);
+        const uint64_t pool_size = pid.size();
         std::vector<uint32_t> out(graph_degree);
         uint64_t pairs = 0;
         sync_prune(pdata, dim, pid, pdist, graph_degree, alpha, metric, order, out.data(), &pairs);
@@ -688,9 +689,10 @@ int orc_build_rows(const float *reorder_data, uint32_t dim, const uint32_t *knn,
         for (uint32_t i = 0; i < graph_degree; i++)  // graph_kernel.cuh:152-158 (+segment_start :92)
             row[i] = (out[i] == kInvalid) ? kInvalid : map[out[i] + seg_start[s]];
         if (counters) {
-            counters[3 * t] = st.n_dist;
-            counters[3 * t + 1] = st.n_iter;
-            counters[3 * t + 2] = pairs;
+            counters[4 * t] = st.n_dist;
+            counters[4 * t + 1] = st.n_iter;
+            counters[4 * t + 2] = pairs;
+            counters[4 * t + 3] = pool_size;  // == beam when no beam slot stayed unfilled
         }
     });
     return 0;
@@ -703,7 +705,7 @@ int orc_build_boundary(const float *reorder_data, uint32_t dim, const uint32_t *
                        uint32_t start_point_local, const uint32_t *map, uint32_t graph_degree,
                        uint32_t beam, uint32_t max_iterations, uint32_t min_iterations,
                        uint32_t hash_bit, uint32_t hash_reset_interval, float alpha, int metric,
-                       int order, uint32_t *graph, int threads) {
+                       int order, uint32_t *graph, uint64_t *pool_sizes, int threads) {
     if (beam % 32 || beam == 0 || beam > 512 || knn_degree > 256) return -1;
     const SearchCfg cfg{beam, max_iterations, min_iterations, hash_bit, hash_reset_interval};
     const float *pdata = reorder_data + (uint64_t) num * dim;
@@ -717,6 +719,7 @@ int orc_build_boundary(const float *reorder_data, uint32_t dim, const uint32_t *
         std::vector<uint32_t> pid;
         std::vector<float> pdist;
         st.finish_pool(pid, pdist);
+        if (pool_sizes) pool_sizes[t] = pid.size();
         std::vector<uint32_t> out(graph_degree);
         sync_prune(pdata, dim, pid, pdist, graph_degree, alpha, metric, order, out.data(), nullptr);
         for (uint32_t i = 0; i < graph_degree; i++)
@@ -767,7 +770,7 @@ int orc_refine(const float *data, uint32_t num, uint32_t dim, const uint32_t *gr
                uint32_t *graph_out, uint32_t degree, const float *centroids, uint32_t C,
                const uint32_t *start_points, uint32_t beam, uint32_t max_iterations,
                uint32_t min_iterations, uint32_t hash_bit, uint32_t hash_reset_interval, float alpha,
-               int metric, int order, int route_order, int threads) {
+               int metric, int order, int route_order, uint64_t *pool_sizes, int threads) {
     if (beam % 32 || beam == 0 || beam > 512 || degree > 256) return -1;
     const SearchCfg cfg{beam, max_iterations, min_iterations, hash_bit, hash_reset_interval};
     parallel_for(num, threads, [&](int64_t t) {
@@ -776,6 +779,7 @@ int orc_refine(const float *data, uint32_t num, uint32_t dim, const uint32_t *gr
         uint32_t *out = graph_out + (uint64_t) p * degree;
         uint32_t need = 0;
         for (uint32_t i = 0; i < degree; i++) need += (row[i] == kInvalid);
+        if (pool_sizes) pool_sizes[p] = beam;  // rows without holes are not searched
         if (need == 0) {
             for (uint32_t i = 0; i < degree; i++) out[i] = row[i];
             return;
@@ -787,6 +791,7 @@ int orc_refine(const float *data, uint32_t num, uint32_t dim, const uint32_t *gr
         std::vector<uint32_t> pid;
         std::vector<float> pdist;
         st.finish_pool(pid, pdist);
+        if (pool_sizes) pool_sizes[p] = pid.size();
         prune_refine(data, dim, p, pid, pdist, row, degree, alpha, metric, order, out, nullptr);
     });
     return 0;
