@@ -112,15 +112,24 @@ __device__ __forceinline__ uint32_t expand_parent(const WarpStrip &s, uint32_t p
 
 // search_kernel.cuh:336-360: seed from a start point's row. exclude_id keeps its
 // slot but gets distance FLT_MAX.
+// *excluded_kept is set when the excluded id occurs: that slot then holds a valid id with distance
+// FLT_MAX, the one input the narrow candidate sort of beam_loop cannot take.
 __device__ __forceinline__ uint32_t seed_from_row(const WarpStrip &s, uint32_t start_point, uint32_t exclude_id,
                                                   const uint32_t *__restrict__ graph, uint32_t degree,
                                                   uint32_t hash_bit, const float *__restrict__ data,
-                                                  uint32_t dim, int metric) {
-    for (uint32_t i = lane_id(); i < degree; i += 32) {
-        const uint32_t index = __ldg(graph + (uint64_t) start_point * degree + i);
-        const uint32_t flag = (index != kInvalid) ? visited_insert(s.visited, hash_bit, index) : 0;
-        s.cand_id[i] = flag ? index : kInvalid;
+                                                  uint32_t dim, int metric, bool *excluded_kept = nullptr) {
+    bool kept = false;
+    for (uint32_t base = 0; base < degree; base += 32) {
+        const uint32_t i = base + lane_id();
+        uint32_t index = kInvalid, flag = 0;
+        if (i < degree) {
+            index = __ldg(graph + (uint64_t) start_point * degree + i);
+            flag = (index != kInvalid) ? visited_insert(s.visited, hash_bit, index) : 0;
+            s.cand_id[i] = flag ? index : kInvalid;
+        }
+        kept = kept || (__ballot_sync(kFullMask, flag && index == exclude_id) != 0);
     }
+    if (excluded_kept) *excluded_kept = kept;
     __syncwarp();
     return score_candidates(s, degree, exclude_id, data, dim, metric);
 }
@@ -197,12 +206,12 @@ __device__ __forceinline__ uint32_t nearest_centroid(const float *q_smem, const 
 // The search loop proper. On return bk/bv hold the beam (ascending, position
 // j = NB*lane + i, ids still carrying the explored flag). Returns the number of
 // expansions; *rows_read accumulates data rows fetched.
-template<int NB, int NC>
+template<int NB, int NC, bool NARROW_SORT = false>
 __device__ __forceinline__ uint32_t beam_loop(float (&bk)[NB], uint32_t (&bv)[NB], const WarpStrip &s,
                                               const BeamParams &p, uint32_t own_id,
                                               const uint32_t *__restrict__ graph, uint32_t degree,
                                               const float *__restrict__ data, uint32_t dim, int metric,
-                                              uint32_t *rows_read) {
+                                              uint32_t *rows_read, bool wide_first_sort = false) {
     const uint32_t lane = lane_id();
     constexpr uint32_t MAXB = 32u * NB;
     uint32_t iter = 0;
@@ -210,7 +219,25 @@ __device__ __forceinline__ uint32_t beam_loop(float (&bk)[NB], uint32_t (&bv)[NB
     uint32_t rows = 0;
     while (true) {
         // -- sort the candidates (search_kernel.cuh:9-37) --
-        {
+        // The reference sorts MAX_CANDIDATE = 64 slots even for degree <= 32, the upper half being
+        // padding (FLT_MAX, 0xffffffff). As long as every FLT_MAX slot carries the padding id, the
+        // first `degree` outputs of that network equal those of the 32-slot network on the real
+        // slots alone, ties included (checked exhaustively-at-random in
+        // tests/test_oracle_primitives.py); the only input that breaks this is the seed row's
+        // excluded id (valid id, FLT_MAX), flagged by wide_first_sort. Used by the build kernels
+        // (instruction bound); the query search kernel is bound by row gathers and measured
+        // slower with it.
+        if (NARROW_SORT && NC == 2 && degree <= 32 && !(wide_first_sort && iter == 0)) {
+            float ck[1] = {lane < degree ? s.cand_dist[lane] : FLT_MAX};
+            uint32_t cv[1] = {lane < degree ? s.cand_id[lane] : kInvalid};
+            warp_sort<1>(ck, cv);
+            __syncwarp();
+            if (lane < degree && lane < p.beam) {
+                s.cand_dist[lane] = ck[0];
+                s.cand_id[lane] = cv[0];
+            }
+            __syncwarp();
+        } else {
             float ck[NC];
             uint32_t cv[NC];
 #pragma unroll

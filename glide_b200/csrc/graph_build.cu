@@ -275,8 +275,9 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
         __syncwarp();
         // The seed step compares the row's partition-local ids with the point's reorder
         // id, as the reference does (graph_kernel.cuh:295-298).
-        rows += seed_from_row(s, a.start_points[seg], point, pknn, a.in_degree, p.hash_bit, pdata, a.dim, a.metric);
-        iters = beam_loop<NB, NC>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows);
+        bool wide = false;
+        rows += seed_from_row(s, a.start_points[seg], point, pknn, a.in_degree, p.hash_bit, pdata, a.dim, a.metric, &wide);
+        iters = beam_loop<NB, NC, true>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows, wide);
         const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
         prune_rows = sync_prune(ps, P, s.query, pdata, a.dim, degree, d.max_degree, a.alpha, a.metric);
         const uint32_t orig = a.map ? a.map[point] : point;
@@ -316,15 +317,16 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
         load_query(s.query, a.data + (uint64_t) point * a.dim, a.dim);
         visited_clear(s.visited, p.hash_bit);
         __syncwarp();
+        bool wide = false;
         if (a.mode == kModeRefine) {
             // routed by the pre-pass (search_kernel.cuh:258-269 via graph_kernel.cuh:638-642)
             rows += seed_from_row(s, a.start_points[a.route[point - a.route_first]], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
                                   a.metric);
         } else {
             rows += seed_from_row(s, a.start_points[0], point, a.graph_in, degree, p.hash_bit, a.data, a.dim,
-                                  a.metric);
+                                  a.metric, &wide);
         }
-        iters = beam_loop<NB, NC>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows);
+        iters = beam_loop<NB, NC, true>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows, wide);
         const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
         prune_rows = sync_prune_refine(ps, P, s.query, a.data, a.dim, point, degree, d.max_degree, need, a.alpha,
                                        a.metric);

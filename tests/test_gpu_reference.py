@@ -135,22 +135,30 @@ def test_reference_reverse_is_one_of_the_orders_the_oracle_allows(gpu_ctx, name)
 
 @pytest.mark.parametrize("name", ["uniform32", "int128"])
 def test_reference_refine_matches_oracle_up_to_its_in_place_race(gpu_ctx, name):
+    """The reference refines rows in place while other CTAs traverse them (graph_kernel.cuh:648); the
+    oracle reads the graph as it was before. To keep that race rare, holes are punched into a sparse
+    subset of the rows of a finished graph: a search then seldom crosses a row that was just refined."""
     base, _, P = case(name)
     n = base.shape[0]
+    rng = np.random.default_rng(3)
+    start = P["graph"].copy()
+    full_rows = np.nonzero((start != INVALID).all(axis=1))[0]
+    chosen = rng.choice(full_rows, size=min(120, full_rows.size), replace=False)
+    start[chosen, 12:] = INVALID
+    start[(start == INVALID).any(axis=1) & ~np.isin(np.arange(n), chosen)] = start[full_rows[0]]  # no other holes
     sizes = np.zeros(n, np.uint64)
-    want = oracle.refine(base, P["after_reverse"], P["centroids"], P["orig_sp"], P["p_refine"], P["alpha"], P["metric"],
+    want = oracle.refine(base, start, P["centroids"], P["orig_sp"], P["p_refine"], P["alpha"], P["metric"],
                          oracle.ORDER_REF, route_order=oracle.ORDER_REF, pool_sizes=sizes)
     if not (sizes == P["p_refine"].beam).all():
         pytest.skip("a beam stayed unfilled: the reference kernel would read out of bounds")
-    g = dev(gpu_ctx, P["after_reverse"])
+    g = dev(gpu_ctx, start)
     t = [dev(gpu_ctx, x) for x in (base, P["centroids"], P["orig_sp"])]
     torch.cuda.synchronize()
     assert ref.refine(t[0].data_ptr(), n, base.shape[1], g.data_ptr(), 16, t[1].data_ptr(), P["centroids"].shape[0],
                       t[2].data_ptr(), P["p_refine"], P["alpha"], P["metric"]) == 0
     got = api.to_u32(g)
-    kept = P["after_reverse"] != INVALID
-    assert np.array_equal(got[kept], P["after_reverse"][kept])
-    # the reference refines rows in place while other CTAs traverse them (graph_kernel.cuh:648), the
-    # oracle reads the graph as it was before; rows agree except where a search crossed a row that
-    # had just been refined
-    assert (got == want).all(axis=1).mean() > 0.97
+    kept = start != INVALID
+    assert np.array_equal(got[kept], start[kept])                  # existing edges are never touched
+    untouched = ~np.isin(np.arange(n), chosen)
+    assert np.array_equal(got[untouched], start[untouched])        # rows without holes stay as they were
+    assert (got[chosen] == want[chosen]).all(axis=1).mean() > 0.9  # refined rows agree up to the race

@@ -134,3 +134,38 @@ def test_warp_order_equals_reference_order_for_odd_dims():
     for dim in (1, 30, 33, 101):
         a, b = rng.random(dim, dtype=np.float32), rng.random(dim, dtype=np.float32)
         assert oracle.distance(a, b, oracle.EUCLIDEAN, oracle.ORDER_WARP) == oracle.distance(a, b, oracle.EUCLIDEAN, oracle.ORDER_REF)
+
+
+def test_narrow_candidate_sort_equals_the_64_slot_network():
+    """The kernels sort degree <= 32 candidates with a 32-slot network although the reference uses 64
+    slots (upper half padding): the first `degree` outputs agree, ties included, as long as every
+    FLT_MAX slot carries the padding id; a FLT_MAX key with a valid id breaks it (the kernels then
+    use the 64-slot network)."""
+    rng = np.random.default_rng(1)
+    fmax = np.finfo(np.float32).max
+
+    def trial(deg, irregular):
+        nvalid = int(rng.integers(0, deg + 1))
+        keys = np.full(deg, fmax, np.float32)
+        vals = np.full(deg, 0xFFFFFFFF, np.uint32)
+        idx = rng.permutation(deg)[:nvalid]
+        keys[idx] = rng.integers(0, 5, nvalid).astype(np.float32)
+        vals[idx] = rng.integers(0, 1000000, nvalid)
+        if irregular and nvalid < deg:
+            free = sorted(set(range(deg)) - set(idx.tolist()))
+            vals[rng.choice(free)] = 777
+        k64 = np.full(64, fmax, np.float32)
+        v64 = np.full(64, 0xFFFFFFFF, np.uint32)
+        for j in range(deg):  # element j in lane j % 32, register j // 32 (search_kernel.cuh:22-27)
+            k64[(j % 32) * 2 + j // 32] = keys[j]
+            v64[(j % 32) * 2 + j // 32] = vals[j]
+        sk, sv = oracle.warp_sort(k64, v64, 2)
+        k32 = np.full(32, fmax, np.float32)
+        v32 = np.full(32, 0xFFFFFFFF, np.uint32)
+        k32[:deg], v32[:deg] = keys, vals
+        a, b = oracle.warp_sort(k32, v32, 1)
+        return np.array_equal(sk[:deg], a[:deg]) and np.array_equal(sv[:deg], b[:deg])
+
+    for deg in (5, 16, 24, 32):
+        assert all(trial(deg, False) for _ in range(3000))
+    assert not all(trial(32, True) for _ in range(200))
