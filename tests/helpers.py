@@ -15,6 +15,8 @@ def small_dataset(kind: str, n: int, dim: int, n_queries: int, seed: int = 7):
         spec = datasets.DatasetSpec("t", n, dim, n_queries, "uniform", 0, "Euclidean", 32, seed)
     elif kind == "int":
         spec = datasets.DatasetSpec("t", n, dim, n_queries, "int_mixture", 16, "Euclidean", 32, seed)
+    elif kind == "scaled":   # the 960-dim config's distribution: N(0,1) centres, sigma 0.3, row scale U[0.5,1.5]
+        spec = datasets.DatasetSpec("t", n, dim, n_queries, "scaled_mixture", 12, "Euclidean", 64, seed)
     elif kind == "unit":
         spec = datasets.DatasetSpec("t", n, dim, n_queries, "unit_mixture", 16, "Cosine", 32, seed)
     else:

@@ -33,6 +33,8 @@ CASES = {
     "int128": dict(kind="int", n=3000, dim=128, nq=200, metric=oracle.EUCLIDEAN),     # exact ties occur
     "unit96": dict(kind="unit", n=2500, dim=96, nq=150, metric=oracle.COSINE),
     "uniform30": dict(kind="uniform", n=1500, dim=30, nq=100, metric=oracle.EUCLIDEAN),  # dim % 4 != 0
+    "scaled960": dict(kind="scaled", n=1200, dim=960, nq=60, metric=oracle.EUCLIDEAN),   # wide rows (generic row path)
+    "uniform200": dict(kind="uniform", n=1500, dim=200, nq=80, metric=oracle.EUCLIDEAN),  # 50 chunks: partial second round
 }
 _cache = {}
 
@@ -78,7 +80,7 @@ def test_search_host_entry_point(gpu_ctx):
     assert np.array_equal(ids2, want_ids) and np.array_equal(d2, want_d) and seconds > 0
 
 
-@pytest.mark.parametrize("name", ["uniform16", "int128", "unit96", "uniform30"])
+@pytest.mark.parametrize("name", ["uniform16", "int128", "unit96", "uniform30", "scaled960", "uniform200"])
 def test_define_partition_and_reorder_match_oracle(gpu_ctx, name):
     base, _, P = case(name)
     metric = Metric(P["metric"])
@@ -123,7 +125,7 @@ def test_get_centroids_uses_seeded_sample(gpu_ctx):
     assert np.array_equal(d_c.cpu().numpy(), want_c)
 
 
-@pytest.mark.parametrize("name", ["uniform16", "int128", "unit96", "uniform30"])
+@pytest.mark.parametrize("name", ["uniform16", "int128", "unit96", "uniform30", "scaled960", "uniform200"])
 def test_build_boundary_reverse_refine_match_oracle(gpu_ctx, name):
     base, _, P = case(name)
     metric = Metric(P["metric"])
@@ -453,3 +455,44 @@ def test_large_path_end_to_end(gpu_ctx):
     assert np.array_equal(ids, want_ids) and np.array_equal(dists, want_d)
     gt = oracle.bruteforce_knn(base, queries, 10, want_dists=False)
     assert api.calculate_recall(ids, gt, 10) > 0.9
+
+
+def test_full_size_cfg1_properties(gpu_ctx):
+    """The benchmark's own workload (1,000,000 x 128, 10,000 queries) through size-independent
+    properties: results sorted, ids valid and distinct, distances equal to a recomputation, recall
+    against exact kNN, exact kNN equal to the host's on a sample, graph rows free of duplicates and
+    self loops, search idempotent, and a sample of queries bit-equal to the oracle."""
+    from glide_b200 import datasets, pipeline
+    spec = datasets.CONFIGS["cfg1"]
+    base, queries = datasets.make(spec)
+    d_base, d_q = dev(gpu_ctx, base), dev(gpu_ctx, queries)
+    cfg = pipeline.BuildConfig(centroid_num=1024, sample_factor=0.1, seed=spec.seed)
+    res = pipeline.build_small(gpu_ctx, d_base, cfg)
+    graph = api.to_u32(res.index.graph_view())
+    n = base.shape[0]
+    valid = graph != INVALID
+    assert (graph[valid] < n).all()
+    assert not (graph == np.arange(n, dtype=np.uint32)[:, None]).any()          # no self loops
+    for r in graph[::997]:                                                        # no duplicate neighbours
+        r = r[r != INVALID]
+        assert len(set(r.tolist())) == r.size
+    assert valid.mean() > 0.98
+    gt_ids, _ = api.bruteforce_knn(gpu_ctx, d_base, d_q, 10)
+    gt = api.to_u32(gt_ids)
+    host_gt = oracle.bruteforce_knn(base, queries[:32], 10, want_dists=False)
+    assert np.array_equal(gt[:32], host_gt)
+    sp = pipeline.derive_search_params(40, 32)
+    ids, dists, _ = res.index.search(sp, d_q)
+    ids2, dists2, _ = res.index.search(sp, d_q)
+    assert np.array_equal(ids, ids2) and np.array_equal(dists, dists2)              # idempotent
+    assert (np.diff(dists, axis=1) >= 0).all()
+    assert (ids < n).all()
+    assert all(len(set(r.tolist())) == 10 for r in ids[::101])
+    for q in range(0, 10000, 503):   # distances are what they claim to be (integer data: exact)
+        want = np.sqrt(((base[ids[q]].astype(np.float64) - queries[q].astype(np.float64)) ** 2).sum(axis=1))
+        assert np.array_equal(dists[q], want.astype(np.float32))
+    assert api.calculate_recall(ids, gt, 10) >= 0.95
+    o = oracle.SearchParams(sp.beam, sp.max_iterations, 0, sp.hash_bit, sp.hash_reset_interval, 10)
+    want_ids, want_d = oracle.search(base, graph, res.index.centroid_view().cpu().numpy(),
+                                     api.to_u32(res.index.start_point_view()), queries[:200], o)
+    assert np.array_equal(ids[:200], want_ids) and np.array_equal(dists[:200], want_d)
