@@ -260,7 +260,7 @@ def run_ours(args):
     # ---- traffic counters of one search pass (untimed) ----
     ctx.enable_counters(True)
     index.search(sp, d_queries)
-    rows_read, expansions, _ = ctx.read_counters()
+    rows_read, expansions, _, _ = ctx.read_counters()
     ctx.enable_counters(False)
     C = index.centroid_num()
     # algorithmic bytes of the search kernel: every data row it scores, one adjacency row per

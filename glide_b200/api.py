@@ -95,10 +95,12 @@ class Context:
     def enable_counters(self, on: bool):
         self.lib.glide_enable_counters(self.handle, 1 if on else 0)
 
-    def read_counters(self) -> tuple[int, int, int]:
-        out = (C.c_uint64 * 3)()
+    def read_counters(self) -> tuple[int, int, int, int]:
+        """(rows read while searching, expansions, rows read while pruning, points whose beam
+        ended unfilled) of the last search / build / refine call."""
+        out = (C.c_uint64 * 4)()
         self.check(self.lib.glide_read_counters(self.handle, out))
-        return int(out[0]), int(out[1]), int(out[2])
+        return int(out[0]), int(out[1]), int(out[2]), int(out[3])
 
 
 # torch has no uint32 arithmetic, but plain storage works; ids live in int32 tensors

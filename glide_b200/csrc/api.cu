@@ -24,7 +24,7 @@ struct glide_ctx {
     float last_ms = 0.0f;
     void *ws = nullptr;  // scratch, grown on demand
     size_t ws_bytes = 0;
-    unsigned long long *counters = nullptr;  // 3 x u64 on the device
+    unsigned long long *counters = nullptr;  // 4 x u64 on the device
     bool counters_on = false;
 };
 
@@ -109,7 +109,7 @@ struct Timed {
 
 unsigned long long *counters_or_null(glide_ctx *ctx) {
     if (!ctx->counters_on) return nullptr;
-    cudaMemsetAsync(ctx->counters, 0, 3 * sizeof(unsigned long long), ctx->stream);
+    cudaMemsetAsync(ctx->counters, 0, 4 * sizeof(unsigned long long), ctx->stream);
     return ctx->counters;
 }
 
@@ -141,7 +141,7 @@ int glide_ctx_create(int device, glide_ctx **out) {
     if (cudaSetDevice(device) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_start) != cudaSuccess || cudaEventCreate(&ctx->ev_stop) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_mid) != cudaSuccess ||
-        cudaMalloc(&ctx->counters, 3 * sizeof(unsigned long long)) != cudaSuccess) {
+        cudaMalloc(&ctx->counters, 4 * sizeof(unsigned long long)) != cudaSuccess) {
         delete ctx;
         return GLIDE_ERR_CUDA;
     }
@@ -174,10 +174,10 @@ void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]) {
 
 void glide_enable_counters(glide_ctx *ctx, int on) { if (ctx) ctx->counters_on = on != 0; }
 
-int glide_read_counters(glide_ctx *ctx, uint64_t out[3]) {
+int glide_read_counters(glide_ctx *ctx, uint64_t out[4]) {
     if (!ctx || !out) return GLIDE_ERR_BAD_ARG;
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
-    GL_CUDA(ctx, cudaMemcpyAsync(out, ctx->counters, 3 * sizeof(uint64_t), cudaMemcpyDeviceToHost, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(out, ctx->counters, 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost, ctx->stream));
     GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return GLIDE_OK;
 }

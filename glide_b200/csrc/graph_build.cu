@@ -257,6 +257,7 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
     const uint32_t degree = a.out_degree;
 
     uint32_t rows = 0, prune_rows = 0, iters = 0;
+    bool short_pool = false;
     float bk[NB];
     uint32_t bv[NB];
 
@@ -279,6 +280,7 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
         rows += seed_from_row(s, a.start_points[seg], point, pknn, a.in_degree, p.hash_bit, pdata, a.dim, a.metric, &wide);
         iters = beam_loop<NB, NC, true>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows, wide);
         const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
+        short_pool = P < p.beam;
         prune_rows = sync_prune(ps, P, s.query, pdata, a.dim, degree, d.max_degree, a.alpha, a.metric);
         const uint32_t orig = a.map ? a.map[point] : point;
         uint32_t *out = a.graph_out + (uint64_t) orig * degree;
@@ -328,6 +330,7 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
         }
         iters = beam_loop<NB, NC, true>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows, wide);
         const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
+        short_pool = P < p.beam;
         prune_rows = sync_prune_refine(ps, P, s.query, a.data, a.dim, point, degree, d.max_degree, need, a.alpha,
                                        a.metric);
         uint32_t pos_num = 0;  // :660-671: holes, front to back
@@ -343,6 +346,7 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
         atomicAdd(a.counters + 0, (unsigned long long) rows);
         atomicAdd(a.counters + 1, (unsigned long long) iters);
         atomicAdd(a.counters + 2, (unsigned long long) prune_rows);
+        if (short_pool) atomicAdd(a.counters + 3, 1ull);
     }
 }
 

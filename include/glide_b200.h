@@ -190,10 +190,11 @@ int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t nu
 /* Device milliseconds of the two kernels of the last glide_search on this context:
  * out[0] the routing pre-pass (nearest centroid per query), out[1] the search kernel. */
 void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]);
-/* Traffic counters of the last search/build/refine call when enabled: rows read during
- * search, expansions, rows read during pruning. */
+/* Counters of the last search/build/refine call when enabled: rows read during search,
+ * expansions, rows read during pruning, and (build/refine only) points whose beam ended with
+ * fewer than `beam` entries. */
 void glide_enable_counters(glide_ctx *ctx, int on);
-int glide_read_counters(glide_ctx *ctx, uint64_t out[3]);
+int glide_read_counters(glide_ctx *ctx, uint64_t out[4]);
 
 /* ---- large path (glide_large_impl.cuh) -------------------------------------------------- */
 /* select_segment_kernel, search_kernel.cuh:546-607; d_out: q x centroid_num. */

@@ -52,3 +52,10 @@ def refine(d_data, num, dim, d_graph, degree, d_centroids, c, d_sp, p, alpha, me
 def define_partition(d_data, num, dim, d_centroids, c, boundary_factor, metric, d_seg_len, d_seg_index) -> int:
     return lib().ref_define_partition(vp(d_data), u32(num), u32(dim), vp(d_centroids), u32(c), f32(boundary_factor),
                                       i32(metric), vp(d_seg_len), vp(d_seg_index))
+
+
+def last_seconds() -> float:
+    """Device time of the kernels of the last harness call (CUDA events)."""
+    f = lib().ref_last_ms
+    f.restype = C.c_float
+    return float(f()) / 1000.0

@@ -38,6 +38,15 @@ inline uint32_t round_up32(uint32_t x) { return (x + 31u) & ~31u; }
         }                                                                               \
     } while (0)
 
+// Device time of the kernels of the last call, taken with events on the default stream.
+float g_last_ms = 0.0f;
+struct EventTimer {
+    cudaEvent_t a = nullptr, b = nullptr;
+    EventTimer() { cudaEventCreate(&a); cudaEventCreate(&b); cudaEventRecord(a, 0); }
+    void stop() { cudaEventRecord(b, 0); cudaEventSynchronize(b); cudaEventElapsedTime(&g_last_ms, a, b); }
+    ~EventTimer() { cudaEventDestroy(a); cudaEventDestroy(b); }
+};
+
 // the beam ladder of kernel_config.cuh:40-48 for MAX_CANDIDATE = 64, MAX_CENTROID = 32
 template<typename F64, typename F128, typename F256>
 int by_beam(uint32_t beam, F64 f64, F128 f128, F256 f256) {
@@ -51,6 +60,8 @@ int by_beam(uint32_t beam, F64 f64, F128 f128, F256 f256) {
 
 extern "C" {
 
+float ref_last_ms() { return g_last_ms; }
+
 // GLIDE::search launch, glide_impl.cuh:389-437, block size 64 (kernel_config.cuh:11).
 int ref_search(const float *d_data, uint32_t dim, const uint32_t *d_graph, uint32_t degree, const float *d_centroids,
                uint32_t C, const uint32_t *d_start_points, const float *d_queries, uint32_t Q, uint32_t top_k,
@@ -61,6 +72,7 @@ int ref_search(const float *d_data, uint32_t dim, const uint32_t *d_graph, uint3
     const uint32_t smem = dim * sizeof(float) + rbs * (sizeof(uint32_t) + sizeof(float)) +
                           hashmap::get_size(hash_bit) * sizeof(uint32_t) + 5 * sizeof(uint32_t);
     const Metric m = metric == 0 ? Metric::Euclidean : Metric::Cosine;
+    EventTimer timer;
     auto launch = [&](auto kernel) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) return -3;
         kernel<<<Q, 64, smem>>>(d_ids, d_dists, top_k, d_data, d_queries, d_graph, degree, beam, max_iterations,
@@ -72,6 +84,7 @@ int ref_search(const float *d_data, uint32_t dim, const uint32_t *d_graph, uint3
                      [&] { return launch(search_kernel<64, 256, 32, float, uint32_t>); });
     if (rc) return rc;
     REF_CHECK(cudaGetLastError());
+    timer.stop();
     REF_CHECK(cudaDeviceSynchronize());
     return 0;
 }
@@ -89,6 +102,7 @@ int ref_build(const float *d_reorder, uint32_t reorder_num, uint32_t dim, const 
     uint32_t smem = dim * sizeof(float) + rbs * (sizeof(uint32_t) + sizeof(float)) + max_graph_degree * sizeof(uint32_t) +
                     hashmap::get_size(hash_bit) * sizeof(uint32_t) + 7 * sizeof(uint32_t) + bitmap_size * sizeof(uint32_t);
     const Metric m = metric == 0 ? Metric::Euclidean : Metric::Cosine;
+    EventTimer timer;
     auto launch1 = [&](auto kernel) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) return -3;
         kernel<<<num, 64, smem>>>(d_reorder, d_graph, d_start_points_local, d_seg_start, d_seg_len, knn_degree, graph_degree,
@@ -120,6 +134,7 @@ int ref_build(const float *d_reorder, uint32_t reorder_num, uint32_t dim, const 
         REF_CHECK(cudaGetLastError());
         REF_CHECK(cudaDeviceSynchronize());
     }
+    timer.stop();
     return 0;
 }
 
@@ -132,11 +147,13 @@ int ref_reverse(uint32_t *d_graph, uint32_t num, uint32_t degree) {
     REF_CHECK(cudaMalloc(&dst, (size_t) num * 4));
     REF_CHECK(cudaMemset(rev, 0xff, (size_t) num * degree * 4));
     REF_CHECK(cudaMemset(cnt, 0, (size_t) num * 4));
+    EventTimer timer;
     for (uint32_t k = 0; k < degree; k++)
         reverse_graph_kernel<uint32_t><<<(num + 511) / 512, 512>>>(dst, rev, cnt, d_graph, num, degree, k);
     const uint32_t max_graph_degree = round_up32(degree);
     insert_reverse_kernel<uint32_t><<<num, 32, max_graph_degree * 4>>>(d_graph, rev, cnt, num, degree, max_graph_degree);
     REF_CHECK(cudaGetLastError());
+    timer.stop();
     REF_CHECK(cudaDeviceSynchronize());
     cudaFree(rev); cudaFree(cnt); cudaFree(dst);
     return 0;
@@ -154,6 +171,7 @@ int ref_refine(const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_grap
     const uint32_t smem = dim * sizeof(float) + rbs * (sizeof(uint32_t) + sizeof(float)) + 2 * max_graph_degree * sizeof(uint32_t) +
                           hashmap::get_size(hash_bit) * sizeof(uint32_t) + 9 * sizeof(uint32_t) + bitmap_size * sizeof(uint32_t);
     const Metric m = metric == 0 ? Metric::Euclidean : Metric::Cosine;
+    EventTimer timer;
     auto launch = [&](auto kernel) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) return -3;
         kernel<<<num, 64, smem>>>(d_data, d_graph, d_start_points, d_centroids, degree, max_graph_degree, dim, beam, hash_bit,
@@ -165,6 +183,7 @@ int ref_refine(const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_grap
                      [&] { return launch(refine_kernel<64, 256, 32, float, uint32_t>); });
     if (rc) return rc;
     REF_CHECK(cudaGetLastError());
+    timer.stop();
     REF_CHECK(cudaDeviceSynchronize());
     return 0;
 }
@@ -175,10 +194,12 @@ int ref_define_partition(const float *d_data, uint32_t num, uint32_t dim, float 
     if (C > 32) return -2;
     REF_CHECK(cudaMemset(d_segment_lengths, 0, (size_t) (C + 1) * 4));
     const uint32_t smem = dim * sizeof(float) + C * (sizeof(float) + sizeof(uint32_t));
+    EventTimer timer;
     define_partition_kernel<32, float, uint32_t><<<num, 256, smem>>>(d_data, d_centroids, num, dim, C, d_segment_lengths,
                                                                      d_segment_indexes, boundary_factor,
                                                                      metric == 0 ? Metric::Euclidean : Metric::Cosine);
     REF_CHECK(cudaGetLastError());
+    timer.stop();
     REF_CHECK(cudaDeviceSynchronize());
     return 0;
 }
