@@ -100,11 +100,12 @@ __device__ __forceinline__ uint32_t expand_parent(const WarpStrip &s, uint32_t p
                                                   const uint32_t *__restrict__ graph, uint32_t degree,
                                                   uint32_t hash_bit, const float *__restrict__ data,
                                                   uint32_t dim, int metric) {
-    for (uint32_t i = lane_id(); i < degree; i += 32) {
+    for (uint32_t base = 0; base < degree; base += 32) {
+        const uint32_t i = base + lane_id();
         uint32_t nb = kInvalid;
-        if (parent != kInvalid) nb = __ldg(graph + (uint64_t) parent * degree + i);
-        const uint32_t flag = (nb != kInvalid && nb != own_id) ? visited_insert(s.visited, hash_bit, nb) : 0;
-        s.cand_id[i] = flag ? nb : kInvalid;
+        if (i < degree && parent != kInvalid) nb = __ldg(graph + (uint64_t) parent * degree + i);
+        const uint32_t flag = visited_insert(s.visited, hash_bit, nb, nb != kInvalid && nb != own_id);
+        if (i < degree) s.cand_id[i] = flag ? nb : kInvalid;
     }
     __syncwarp();
     return score_candidates(s, degree, kInvalid, data, dim, metric);
@@ -121,12 +122,10 @@ __device__ __forceinline__ uint32_t seed_from_row(const WarpStrip &s, uint32_t s
     bool kept = false;
     for (uint32_t base = 0; base < degree; base += 32) {
         const uint32_t i = base + lane_id();
-        uint32_t index = kInvalid, flag = 0;
-        if (i < degree) {
-            index = __ldg(graph + (uint64_t) start_point * degree + i);
-            flag = (index != kInvalid) ? visited_insert(s.visited, hash_bit, index) : 0;
-            s.cand_id[i] = flag ? index : kInvalid;
-        }
+        uint32_t index = kInvalid;
+        if (i < degree) index = __ldg(graph + (uint64_t) start_point * degree + i);
+        const uint32_t flag = visited_insert(s.visited, hash_bit, index, index != kInvalid);
+        if (i < degree) s.cand_id[i] = flag ? index : kInvalid;
         kept = kept || (__ballot_sync(kFullMask, flag && index == exclude_id) != 0);
     }
     if (excluded_kept) *excluded_kept = kept;
@@ -325,12 +324,181 @@ __device__ __forceinline__ uint32_t beam_loop(float (&bk)[NB], uint32_t (&bv)[NB
 #pragma unroll
             for (int i = 0; i < NB; i++) {
                 const uint32_t j = NB * lane + i;
-                if (j < p.beam) visited_insert(s.visited, p.hash_bit, bv[i] & kClean);
+                visited_insert(s.visited, p.hash_bit, bv[i] & kClean, j < p.beam);
             }
             __syncwarp();
         }
         if (terminate && iter >= p.min_iterations) break;
         rows += expand_parent(s, parent, own_id, graph, degree, p.hash_bit, data, dim, metric);
+        iter++;
+    }
+    if (rows_read) *rows_read += rows;
+    return iter;
+}
+
+// ---------------------------------------------------------------------------
+// Lane-resident variant for adjacency rows of at most 32 entries: candidate slot l lives in
+// lane l's registers from the adjacency read to the merge, so the loop touches shared memory
+// only for the visited set. Same networks, same tie order:
+//  * the reference sorts MAX_CANDIDATE = 64 slots, the upper 32 being padding (FLT_MAX,
+//    0xffffffff); the first 32 outputs of that network equal those of the 32-slot network on the
+//    real slots alone as long as every FLT_MAX slot carries the padding id (checked at random in
+//    tests/test_oracle_primitives.py). The one input that breaks this is the seed row's excluded
+//    id (a valid id with FLT_MAX), which takes the 64-slot network once (wide_first_sort);
+//  * for beam <= 32 the 64-position merge network splits, after its first stride-32 step, into
+//    two independent halves of which only the lower one is kept, so NB = 1 gives the same beam.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t seed_lanes(const WarpStrip &s, uint32_t start_point, uint32_t exclude_id,
+                                               const uint32_t *__restrict__ graph, uint32_t degree, uint32_t hash_bit,
+                                               const float *__restrict__ data, uint32_t dim, int metric, float &ck,
+                                               uint32_t &cv, bool *excluded_kept = nullptr) {
+    const uint32_t lane = lane_id();
+    uint32_t index = kInvalid;
+    if (lane < degree) index = __ldg(graph + (uint64_t) start_point * degree + lane);
+    const uint32_t flag = visited_insert(s.visited, hash_bit, index, index != kInvalid);
+    cv = flag ? index : kInvalid;
+    if (excluded_kept) *excluded_kept = __ballot_sync(kFullMask, flag && index == exclude_id) != 0;
+    const uint32_t mask = __ballot_sync(kFullMask, cv != kInvalid && cv != exclude_id);
+    __syncwarp();
+    ck = score_lanes(s.query, data, dim, metric, mask, cv);
+    return __popc(mask);
+}
+
+__device__ __forceinline__ uint32_t expand_lanes(const WarpStrip &s, uint32_t parent, uint32_t own_id,
+                                                 const uint32_t *__restrict__ graph, uint32_t degree, uint32_t hash_bit,
+                                                 const float *__restrict__ data, uint32_t dim, int metric, float &ck,
+                                                 uint32_t &cv) {
+    const uint32_t lane = lane_id();
+    uint32_t nb = kInvalid;
+    if (lane < degree && parent != kInvalid) nb = __ldg(graph + (uint64_t) parent * degree + lane);
+    const uint32_t flag = visited_insert(s.visited, hash_bit, nb, nb != kInvalid && nb != own_id);
+    cv = flag ? nb : kInvalid;
+    const uint32_t mask = __ballot_sync(kFullMask, flag != 0);
+    __syncwarp();
+#ifdef GLIDE_EXP_H2
+    if (flag) {
+        const uint32_t k = __popc(mask & ((1u << lane) - 1));
+        s.work[k] = lane;
+        s.work_id[k] = nb;
+    }
+    s.cand_dist[lane] = FLT_MAX;
+    __syncwarp();
+    warp_rows(s.query, data, dim, metric, __popc(mask),
+              [&](uint32_t i) { return s.work_id[i]; },
+              [&](uint32_t i, float d) { s.cand_dist[s.work[i]] = d; });
+    __syncwarp();
+    ck = s.cand_dist[lane];
+    __syncwarp();
+#else
+    ck = score_lanes(s.query, data, dim, metric, mask, cv);
+#endif
+    return __popc(mask);
+}
+
+// (ck, cv): the seed step's candidates, slot = lane. Otherwise as beam_loop.
+template<int NB>
+__device__ __forceinline__ uint32_t beam_loop_lanes(float (&bk)[NB], uint32_t (&bv)[NB], const WarpStrip &s,
+                                                    const BeamParams &p, uint32_t own_id,
+                                                    const uint32_t *__restrict__ graph, uint32_t degree,
+                                                    const float *__restrict__ data, uint32_t dim, int metric,
+                                                    uint32_t *rows_read, float ck, uint32_t cv,
+                                                    bool wide_first_sort = false) {
+    const uint32_t lane = lane_id();
+    constexpr uint32_t MAXB = 32u * NB;
+    uint32_t iter = 0;
+    bool terminate = false;
+    uint32_t rows = 0;
+    while (true) {
+        // -- sort the candidates (search_kernel.cuh:9-37): afterwards lane j holds the j-th --
+        if (wide_first_sort && iter == 0) {
+            float k2[2] = {ck, FLT_MAX};          // slot j = lane + 32*i
+            uint32_t v2[2] = {cv, kInvalid};
+            warp_sort<2>(k2, v2);                 // sorted position e = 2*lane + i
+            const float a = __shfl_sync(kFullMask, k2[0], lane >> 1), b = __shfl_sync(kFullMask, k2[1], lane >> 1);
+            const uint32_t c = __shfl_sync(kFullMask, v2[0], lane >> 1), d = __shfl_sync(kFullMask, v2[1], lane >> 1);
+            ck = (lane & 1u) ? b : a;
+            cv = (lane & 1u) ? d : c;
+        } else {
+            float k1[1] = {ck};
+            uint32_t v1[1] = {cv};
+            warp_sort<1>(k1, v1);
+            ck = k1[0];
+            cv = v1[0];
+        }
+        // -- merge into the beam (search_kernel.cuh:97-147) --
+        if (iter == 0) {
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                const float c = __shfl_sync(kFullMask, ck, j & 31u);
+                const uint32_t id = __shfl_sync(kFullMask, cv, j & 31u);
+                const bool take = (j < p.beam) && (j < degree);
+                bk[i] = take ? c : FLT_MAX;
+                bv[i] = take ? id : kInvalid;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                const uint32_t k = MAXB - 1 - j;
+                const float c = __shfl_sync(kFullMask, ck, k & 31u);
+                const uint32_t id = __shfl_sync(kFullMask, cv, k & 31u);
+                if (k < p.beam && k < degree && bk[i] > c) {
+                    bk[i] = c;
+                    bv[i] = id;
+                }
+            }
+            warp_merge_final<NB>(bk, bv);
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                if (j >= p.beam) {  // the reference keeps only `beam` slots between iterations
+                    bk[i] = FLT_MAX;
+                    bv[i] = kInvalid;
+                }
+            }
+        }
+        const bool reset = ((iter + 1) % p.hash_reset_interval) == 0;
+        if (reset) {
+            __syncwarp();
+            visited_clear(s.visited, p.hash_bit);
+            __syncwarp();
+        }
+        if (iter + 1 == p.max_iterations) break;
+        // -- first beam slot not yet expanded (search_kernel.cuh:292-325) --
+        uint32_t parent = kInvalid;
+        {
+            int first = -1;
+#pragma unroll
+            for (int i = NB - 1; i >= 0; i--)
+                if ((bv[i] & kExplored) == 0) first = i;
+            const uint32_t has = __ballot_sync(kFullMask, first >= 0);
+            if (has == 0) {
+                terminate = true;
+            } else {
+                const uint32_t src = __ffs(has) - 1;
+                uint32_t mine = kInvalid;
+                if (lane == src) {
+#pragma unroll
+                    for (int i = 0; i < NB; i++)
+                        if (i == first) {
+                            mine = bv[i];
+                            bv[i] |= kExplored;
+                        }
+                }
+                parent = __shfl_sync(kFullMask, mine, src);
+            }
+        }
+        if (reset) {  // search_kernel.cuh:327-334
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const uint32_t j = NB * lane + i;
+                visited_insert(s.visited, p.hash_bit, bv[i] & kClean, j < p.beam);
+            }
+            __syncwarp();
+        }
+        if (terminate && iter >= p.min_iterations) break;
+        rows += expand_lanes(s, parent, own_id, graph, degree, p.hash_bit, data, dim, metric, ck, cv);
         iter++;
     }
     if (rows_read) *rows_read += rows;

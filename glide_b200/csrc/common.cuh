@@ -156,34 +156,40 @@ __device__ __forceinline__ void warp_rows_v4(const float *q_smem, const float *_
     }
 }
 
-// Any dim: one row at a time. dim % 4 == 0: the chunk ownership of warp_rows_v4; otherwise
-// scalar elements l, l+32, ... (the reference's order).
+// Lane partial sum of one row for any dim. dim % 4 == 0: the chunk ownership of warp_rows_v4;
+// otherwise scalar elements l, l+32, ... (the reference's order).
+__device__ __forceinline__ float lane_row_partial(const float *q_smem, const float *__restrict__ row, uint32_t dim) {
+    const uint32_t lane = lane_id();
+    float acc = 0.0f;
+    if ((dim & 3u) == 0) {
+        const float4 *q4 = reinterpret_cast<const float4 *>(q_smem);
+        const float4 *r4 = reinterpret_cast<const float4 *>(row);
+        const uint32_t chunks = dim >> 2;
+        uint32_t c = lane;
+        for (; c + 96 < chunks; c += 128) {  // four loads in flight per lane
+            const float4 b0 = __ldg(r4 + c), b1 = __ldg(r4 + c + 32), b2 = __ldg(r4 + c + 64), b3 = __ldg(r4 + c + 96);
+            acc = sq_acc4(q4[c], b0, acc);
+            acc = sq_acc4(q4[c + 32], b1, acc);
+            acc = sq_acc4(q4[c + 64], b2, acc);
+            acc = sq_acc4(q4[c + 96], b3, acc);
+        }
+        for (; c < chunks; c += 32) acc = sq_acc4(q4[c], __ldg(r4 + c), acc);
+    } else {
+        for (uint32_t i = lane; i < dim; i += 32) {
+            const float d = q_smem[i] - __ldg(row + i);
+            acc = __fmaf_rn(d, d, acc);
+        }
+    }
+    return acc;
+}
+
+// Any dim: one row at a time.
 template<typename IdAt, typename Sink>
 __device__ __forceinline__ void warp_rows_generic(const float *q_smem, const float *__restrict__ data, uint32_t dim,
                                                   int metric, uint32_t n, IdAt id_at, Sink sink) {
     const uint32_t lane = lane_id();
     for (uint32_t g = 0; g < n; g++) {
-        const float *row = data + (uint64_t) id_at(g) * dim;
-        float p[1] = {0.0f};
-        if ((dim & 3u) == 0) {
-            const float4 *q4 = reinterpret_cast<const float4 *>(q_smem);
-            const float4 *r4 = reinterpret_cast<const float4 *>(row);
-            const uint32_t chunks = dim >> 2;
-            uint32_t c = lane;
-            for (; c + 96 < chunks; c += 128) {  // four loads in flight per lane
-                const float4 b0 = __ldg(r4 + c), b1 = __ldg(r4 + c + 32), b2 = __ldg(r4 + c + 64), b3 = __ldg(r4 + c + 96);
-                p[0] = sq_acc4(q4[c], b0, p[0]);
-                p[0] = sq_acc4(q4[c + 32], b1, p[0]);
-                p[0] = sq_acc4(q4[c + 64], b2, p[0]);
-                p[0] = sq_acc4(q4[c + 96], b3, p[0]);
-            }
-            for (; c < chunks; c += 32) p[0] = sq_acc4(q4[c], __ldg(r4 + c), p[0]);
-        } else {
-            for (uint32_t i = lane; i < dim; i += 32) {
-                const float d = q_smem[i] - __ldg(row + i);
-                p[0] = __fmaf_rn(d, d, p[0]);
-            }
-        }
+        float p[1] = {lane_row_partial(q_smem, data + (uint64_t) id_at(g) * dim, dim)};
         const float sum = fold_rows<1>(p);
         if (lane == 0) sink(g, metric == kEuclidean ? sqrtf(sum) : sum);
     }
@@ -197,6 +203,51 @@ __device__ __forceinline__ void warp_rows(const float *q_smem, const float *__re
     // the query in shared memory
     if ((dim & 3u) == 0 && dim <= 128) warp_rows_v4<1>(q_smem, data, dim, metric, n, id_at, sink);
     else warp_rows_generic(q_smem, data, dim, metric, n, id_at, sink);
+}
+
+// Lane-resident scoring: lane l holds candidate id `cv` (scored when bit l of `mask` is set) and
+// receives its distance; other lanes get FLT_MAX. The ids travel by shuffle, the rows are read by
+// the whole warp exactly as in warp_rows (same chunk ownership, same fold), so the distances are
+// bit-identical to the shared-memory path; nothing is staged in shared memory.
+__device__ __forceinline__ float score_lanes(const float *q_smem, const float *__restrict__ data, uint32_t dim,
+                                             int metric, uint32_t mask, uint32_t cv) {
+    const uint32_t lane = lane_id();
+    float mine = FLT_MAX;
+    uint32_t m = mask;
+    if ((dim & 3u) == 0 && dim <= 128) {
+        const bool own = lane < (dim >> 2);
+        const float4 q = own ? reinterpret_cast<const float4 *>(q_smem)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t my_rank = __popc(mask & ((1u << lane) - 1));
+        const bool valid = ((mask >> lane) & 1u) != 0;
+        for (uint32_t g = 0; m != 0; g++) {
+            float4 v[8];
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                const bool act = m != 0;
+                const uint32_t src = act ? (uint32_t) __ffs(m) - 1u : 0u;
+                m &= m - 1u;
+                const uint32_t id = __shfl_sync(kFullMask, cv, src);
+                v[r] = (act && own) ? __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * dim) + lane) : q;
+            }
+            float p[8];
+#pragma unroll
+            for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
+            const float sum = fold_rows<8>(p);  // row r of the batch sits in lanes 4r .. 4r+3
+            const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
+            mine = (valid && (my_rank >> 3) == g) ? got : mine;
+        }
+        if (metric == kEuclidean) mine = valid ? sqrtf(mine) : mine;  // once per lane, no branch per batch
+    } else {
+        while (m != 0) {
+            const uint32_t src = (uint32_t) __ffs(m) - 1u;
+            m &= m - 1u;
+            const uint32_t id = __shfl_sync(kFullMask, cv, src);
+            float p[1] = {lane_row_partial(q_smem, data + (uint64_t) id * dim, dim)};
+            const float sum = fold_rows<1>(p);
+            if (lane == src) mine = metric == kEuclidean ? sqrtf(sum) : sum;
+        }
+    }
+    return mine;
 }
 
 __device__ __forceinline__ float finish_metric(float s, int metric) {
@@ -313,16 +364,25 @@ __device__ __forceinline__ void visited_clear(uint32_t *table, uint32_t bits) {
     for (uint32_t i = lane_id(); i < (1u << bits); i += 32) table[i] = kInvalid;
 }
 
-__device__ __forceinline__ uint32_t visited_insert(uint32_t *table, uint32_t bits, uint32_t key) {
+// Called by the whole warp; lanes with want == false only keep the others company. The probe
+// loop runs in lockstep (its trip count is the longest probe chain among the lanes), so the warp
+// leaves it converged: a per-lane loop with early exits left the lanes split for the code that
+// follows, which doubled the row-load instructions of the scoring step.
+__device__ __forceinline__ uint32_t visited_insert(uint32_t *table, uint32_t bits, uint32_t key, bool want) {
     const uint32_t size = 1u << bits, mask = size - 1;
     uint32_t index = (key ^ (key >> bits)) & mask;
-    for (uint32_t i = 0; i < size; i++) {
-        const uint32_t old = atomicCAS(&table[index], kInvalid, key);
-        if (old == kInvalid) return 1;
-        if (old == key) return 0;
-        index = (index + 1) & mask;
+    uint32_t result = 0, left = size;
+    bool pending = want;
+    while (__any_sync(kFullMask, pending)) {
+        if (pending) {
+            const uint32_t old = atomicCAS(&table[index], kInvalid, key);
+            result = (old == kInvalid) ? 1u : 0u;
+            left--;
+            pending = !(old == kInvalid || old == key || left == 0);
+            index = (index + 1) & mask;
+        }
     }
-    return 0;
+    return result;
 }
 
 typedef unsigned long long u64;

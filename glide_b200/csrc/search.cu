@@ -9,6 +9,12 @@ namespace glide {
 
 namespace {
 
+#ifdef GLIDE_EXP_H2
+constexpr uint32_t kLanesCand = 32;
+#else
+constexpr uint32_t kLanesCand = 0;
+#endif
+
 struct SearchDev {
     SearchArgs a;
     uint32_t max_centroid;
@@ -33,7 +39,9 @@ __device__ inline void warp_merge_final_smem(float *k, uint32_t *v, uint32_t n_p
     }
 }
 
-template<int NB, int NC>
+// LANES: adjacency rows of at most 32 entries, candidates stay in registers (beam_loop_lanes);
+// the strip then holds only the query and the visited set.
+template<int NB, int NC, bool LANES>
 __global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
     extern __shared__ __align__(16) uint32_t smem[];
     const SearchArgs &a = d.a;
@@ -42,7 +50,7 @@ __global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
     const uint32_t q = blockIdx.x * warps_per_cta + warp;
     if (q >= a.Q) return;
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
-    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, 32u * NC, p.hash_bit);
+    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLanesCand : 32u * NC, p.hash_bit);
 
     const bool sub = (a.segment_ids != nullptr);
     if (sub) {  // search_kernel.cuh:676-692: skip queries not routed to this partition
@@ -70,11 +78,18 @@ __global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
     } else {
         start_node = a.start_point;
     }
-    rows += seed_from_row(s, start_node, kInvalid, a.graph, a.degree, p.hash_bit, a.data, a.dim, a.metric);
-
     float bk[NB];
     uint32_t bv[NB];
-    const uint32_t iters = beam_loop<NB, NC>(bk, bv, s, p, kInvalid, a.graph, a.degree, a.data, a.dim, a.metric, &rows);
+    uint32_t iters;
+    if constexpr (LANES) {
+        float ck;
+        uint32_t cv;
+        rows += seed_lanes(s, start_node, kInvalid, a.graph, a.degree, p.hash_bit, a.data, a.dim, a.metric, ck, cv);
+        iters = beam_loop_lanes<NB>(bk, bv, s, p, kInvalid, a.graph, a.degree, a.data, a.dim, a.metric, &rows, ck, cv);
+    } else {
+        rows += seed_from_row(s, start_node, kInvalid, a.graph, a.degree, p.hash_bit, a.data, a.dim, a.metric);
+        iters = beam_loop<NB, NC>(bk, bv, s, p, kInvalid, a.graph, a.degree, a.data, a.dim, a.metric, &rows);
+    }
 
     if (!sub) {
 #pragma unroll
@@ -166,9 +181,9 @@ uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
     return m;
 }
 
-template<int NB, int NC>
+template<int NB, int NC, bool LANES = false>
 cudaError_t launch_search_t(const SearchDev &d, uint32_t warps_per_cta, size_t smem_bytes, cudaStream_t stream) {
-    auto kernel = search_kernel<NB, NC>;
+    auto kernel = search_kernel<NB, NC, LANES>;
     if (smem_bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
         if (e != cudaSuccess) return e;
@@ -190,12 +205,25 @@ cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
     const uint32_t max_beam = a.p.beam <= 64 ? 64 : (a.p.beam <= 128 ? 128 : (a.p.beam <= 256 ? 256 : 512));
     const uint32_t max_cand = a.degree <= 64 ? 64 : (a.degree <= 128 ? 128 : 256);
     const uint32_t extra = a.segment_ids ? 4 * d.max_topk : 0;
-    d.strip_words = (strip_words_base(a.dim, max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
+#ifdef GLIDE_EXP_NO_LANES
+    const bool lanes = false;
+#else
+    const bool lanes = a.degree <= 32;
+#endif
+    d.strip_words = (strip_words_base(a.dim, lanes ? kLanesCand : max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;
     while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;
     if (strip_bytes * warps > 200 * 1024) return cudaErrorInvalidValue;
     const int nb = max_beam / 32, nc = max_cand / 32;
+    if (lanes) {
+        const size_t bytes = strip_bytes * warps;
+        if (a.p.beam <= 32) return launch_search_t<1, 2, true>(d, warps, bytes, stream);
+        if (nb == 2) return launch_search_t<2, 2, true>(d, warps, bytes, stream);
+        if (nb == 4) return launch_search_t<4, 2, true>(d, warps, bytes, stream);
+        if (nb == 8) return launch_search_t<8, 2, true>(d, warps, bytes, stream);
+        return launch_search_t<16, 2, true>(d, warps, bytes, stream);
+    }
     GLIDE_DISPATCH_NB_NC(launch_search_t, nb, nc, d, warps, strip_bytes * warps, stream);
 }
 

