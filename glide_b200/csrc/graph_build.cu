@@ -242,7 +242,9 @@ __device__ __forceinline__ void boundary_merge(const PruneStrip &ps, const uint3
     }
 }
 
-template<int NB, int NC>
+// LANES: adjacency rows searched have at most 32 entries; candidates stay in registers
+// (beam_loop_lanes) and the strip holds no candidate arrays.
+template<int NB, int NC, bool LANES>
 __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
     extern __shared__ __align__(16) uint32_t smem[];
     const BuildArgs &a = d.a;
@@ -252,7 +254,7 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
     if (t >= a.count) return;
     const uint32_t point = a.first + t;
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
-    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, 32u * NC, p.hash_bit);
+    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? 0u : 32u * NC, p.hash_bit);
     PruneStrip ps = make_prune_strip(s.extra, d.max_beam, d.max_degree);
     const uint32_t degree = a.out_degree;
 
@@ -277,8 +279,18 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
         // The seed step compares the row's partition-local ids with the point's reorder
         // id, as the reference does (graph_kernel.cuh:295-298).
         bool wide = false;
-        rows += seed_from_row(s, a.start_points[seg], point, pknn, a.in_degree, p.hash_bit, pdata, a.dim, a.metric, &wide);
-        iters = beam_loop<NB, NC, true>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows, wide);
+        if constexpr (LANES) {
+            float ck;
+            uint32_t cv;
+            rows += seed_lanes(s, a.start_points[seg], point, pknn, a.in_degree, p.hash_bit, pdata, a.dim, a.metric, ck, cv,
+                               &wide);
+            iters = beam_loop_lanes<NB>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows,
+                                        ck, cv, wide);
+        } else {
+            rows += seed_from_row(s, a.start_points[seg], point, pknn, a.in_degree, p.hash_bit, pdata, a.dim, a.metric, &wide);
+            iters = beam_loop<NB, NC, true>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows,
+                                            wide);
+        }
         const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
         short_pool = P < p.beam;
         prune_rows = sync_prune(ps, P, s.query, pdata, a.dim, degree, d.max_degree, a.alpha, a.metric);
@@ -320,15 +332,18 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
         visited_clear(s.visited, p.hash_bit);
         __syncwarp();
         bool wide = false;
-        if (a.mode == kModeRefine) {
-            // routed by the pre-pass (search_kernel.cuh:258-269 via graph_kernel.cuh:638-642)
-            rows += seed_from_row(s, a.start_points[a.route[point - a.route_first]], kInvalid, a.graph_in, degree, p.hash_bit, a.data, a.dim,
-                                  a.metric);
+        // kModeRefine: routed by the pre-pass (search_kernel.cuh:258-269 via graph_kernel.cuh:638-642)
+        const uint32_t start = a.mode == kModeRefine ? a.start_points[a.route[point - a.route_first]] : a.start_points[0];
+        const uint32_t exclude = a.mode == kModeRefine ? kInvalid : point;
+        if constexpr (LANES) {
+            float ck;
+            uint32_t cv;
+            rows += seed_lanes(s, start, exclude, a.graph_in, degree, p.hash_bit, a.data, a.dim, a.metric, ck, cv, &wide);
+            iters = beam_loop_lanes<NB>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows, ck, cv, wide);
         } else {
-            rows += seed_from_row(s, a.start_points[0], point, a.graph_in, degree, p.hash_bit, a.data, a.dim,
-                                  a.metric, &wide);
+            rows += seed_from_row(s, start, exclude, a.graph_in, degree, p.hash_bit, a.data, a.dim, a.metric, &wide);
+            iters = beam_loop<NB, NC, true>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows, wide);
         }
-        iters = beam_loop<NB, NC, true>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows, wide);
         const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
         short_pool = P < p.beam;
         prune_rows = sync_prune_refine(ps, P, s.query, a.data, a.dim, point, degree, d.max_degree, need, a.alpha,
@@ -356,9 +371,9 @@ uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
     return m;
 }
 
-template<int NB, int NC>
+template<int NB, int NC, bool LANES = false>
 cudaError_t launch_build_t(const BuildDev &d, uint32_t warps_per_cta, size_t smem_bytes, cudaStream_t stream) {
-    auto kernel = build_kernel<NB, NC>;
+    auto kernel = build_kernel<NB, NC, LANES>;
     if (smem_bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
         if (e != cudaSuccess) return e;
@@ -508,12 +523,20 @@ cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
     d.max_beam = max_beam;
     d.max_degree = round_up32(a.out_degree);
     uint32_t extra = prune_strip_words(max_beam, d.max_degree);
-    d.strip_words = (strip_words_base(a.dim, max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
+    const bool lanes = a.in_degree <= 32;
+    d.strip_words = (strip_words_base(a.dim, lanes ? 0 : max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;
     while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;
     if (strip_bytes * warps > 200 * 1024) return cudaErrorInvalidValue;
     const int nb = max_beam / 32, nc = max_cand / 32;
+    if (lanes) {
+        const size_t bytes = strip_bytes * warps;
+        if (nb == 2) return launch_build_t<2, 2, true>(d, warps, bytes, stream);
+        if (nb == 4) return launch_build_t<4, 2, true>(d, warps, bytes, stream);
+        if (nb == 8) return launch_build_t<8, 2, true>(d, warps, bytes, stream);
+        return launch_build_t<16, 2, true>(d, warps, bytes, stream);
+    }
     GLIDE_DISPATCH_NB_NC(launch_build_t, nb, nc, d, warps, strip_bytes * warps, stream);
 }
 
