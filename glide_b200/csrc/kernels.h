@@ -99,8 +99,13 @@ struct AssignArgs {
     int metric;
     uint32_t *nearest;      // n
     uint32_t *is_boundary;  // n: 0 for a boundary point, 0xffffffff otherwise (a slot key); may be nullptr
+    float *tc_norms;        // C + 1 floats of scratch for the tensor-core prefilter; nullptr: exact kernels only
 };
 cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream);
+// Tensor-core prefilter + exact re-rank (assign_tc.cu); settles every point whose nearest centroid
+// is unique, flags the rest with 0xffffffff in `nearest`. Eligible: tc_norms given, dim % 8 == 0, dim <= 128, C >= 2.
+bool assign_tc_eligible(const AssignArgs &a);
+cudaError_t launch_assign_tc(const AssignArgs &a, cudaStream_t stream);
 
 // Deterministic slots: slot[p] = number of q < p with key[q] == key[p] (keys < K,
 // key == 0xffffffff means "none" and yields slot 0xffffffff); totals[K] = counts.

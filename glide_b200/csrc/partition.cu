@@ -3,6 +3,7 @@
 // (define_partition_kernel, :22-66), order-independent slot assignment replacing the
 // reference's atomics (:57-60), the permuted copy (reorder_kernel, :68-100) and the
 // Lloyd centroid update used in place of cuVS kmeans::fit (partition.cuh:48-54).
+#include <cstdlib>
 #include "beam_core.cuh"
 #include "kernels.h"
 
@@ -396,8 +397,15 @@ cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream) {
     }
     // the tiled kernel settles every point whose nearest centroid is unique; the warp-per-point
     // kernel then handles the rest (ties at the minimum; all points when dim % 4 != 0)
+    // GLIDE_B200_EXACT_ASSIGN=1 keeps the tensor cores out of it (the tests compare both ways)
+    static const bool exact_only = [] { const char *e = std::getenv("GLIDE_B200_EXACT_ASSIGN"); return e && e[0] == '1'; }();
     const bool tiled = (a.dim & 3u) == 0 && a.C >= 2;
-    if (tiled) assign_tiled_kernel<<<(a.n + kAP - 1) / kAP, 256, 0, stream>>>(a);
+    if (!exact_only && assign_tc_eligible(a)) {
+        cudaError_t e = launch_assign_tc(a, stream);
+        if (e != cudaSuccess) return e;
+    } else if (tiled) {
+        assign_tiled_kernel<<<(a.n + kAP - 1) / kAP, 256, 0, stream>>>(a);
+    }
     assign_kernel<<<(a.n + warps - 1) / warps, warps * 32, smem_bytes, stream>>>(a, max_centroid, strip_words, tiled);
     return cudaGetLastError();
 }

@@ -499,3 +499,50 @@ def test_full_size_cfg1_properties(gpu_ctx):
     want_ids, want_d = oracle.search(base, graph, res.index.centroid_view().cpu().numpy(),
                                      api.to_u32(res.index.start_point_view()), queries[:200], o)
     assert np.array_equal(ids[:200], want_ids) and np.array_equal(dists[:200], want_d)
+
+
+def _stress_partition_inputs(kind, rng):
+    """Inputs chosen to strain the tensor-core prefilter of the assignment: many centroids, large
+    common offsets (norms far above the distances), duplicated and nearly duplicated centroids."""
+    n, dim, C = 6000, 128, 300
+    if kind == "mixture_1024":
+        C = 1024
+        cent = rng.uniform(0, 120, (C, dim)).astype(np.float32)
+        base = np.clip(np.rint(cent[rng.integers(0, C, n)] + rng.normal(0, 20, (n, dim))), 0, 218).astype(np.float32)
+        centroids = (cent + rng.normal(0, 2, (C, dim))).astype(np.float32)
+    elif kind == "offset":          # |p|, |c| ~ 1e4 while distances ~ 10: the margin swallows everything
+        base = (1000.0 + rng.normal(0, 1, (n, dim))).astype(np.float32)
+        centroids = (1000.0 + rng.normal(0, 1, (C, dim))).astype(np.float32)
+    elif kind == "duplicates":      # exact ties between centroids -> the network's tie order decides
+        centroids = rng.normal(0, 1, (C, dim)).astype(np.float32)
+        centroids[1::2] = centroids[0::2]
+        base = (centroids[rng.integers(0, C, n)] + rng.normal(0, 0.3, (n, dim))).astype(np.float32)
+    elif kind == "near_duplicates":  # centroids one ulp-scale step apart
+        centroids = rng.normal(0, 1, (C, dim)).astype(np.float32)
+        centroids[1::2] = centroids[0::2] * np.float32(1.0 + 3e-7)
+        base = (centroids[rng.integers(0, C, n)] + rng.normal(0, 0.3, (n, dim))).astype(np.float32)
+    elif kind == "unit96":
+        dim = 96
+        centroids = rng.normal(0, 1, (C, dim)).astype(np.float32)
+        centroids /= np.linalg.norm(centroids, axis=1, keepdims=True)
+        base = (centroids[rng.integers(0, C, n)] + rng.normal(0, 0.05, (n, dim))).astype(np.float32)
+        base /= np.linalg.norm(base, axis=1, keepdims=True)
+    elif kind == "int_ties":        # small integers: equal distances to different centroids are common
+        C = 64
+        centroids = rng.integers(0, 3, (C, dim)).astype(np.float32)
+        base = rng.integers(0, 3, (n, dim)).astype(np.float32)
+    return base, centroids
+
+
+@pytest.mark.parametrize("kind", ["mixture_1024", "offset", "duplicates", "near_duplicates", "unit96", "int_ties"])
+def test_assignment_with_tensor_core_prefilter_is_exact(gpu_ctx, kind):
+    """The assignment's tensor-core prefilter only proposes candidates; the exact re-rank and the
+    tie fallback must give the oracle's nearest centroid, slot and boundary flag for every point."""
+    base, centroids = _stress_partition_inputs(kind, np.random.default_rng(11))
+    metric = oracle.COSINE if kind == "unit96" else oracle.EUCLIDEAN
+    for factor in (1.1, -1.0):
+        want_index, want_start, want_len = oracle.define_partition(base, centroids, factor, metric)
+        d_seg, seg_start, seg_len = api.define_partition(gpu_ctx, dev(gpu_ctx, base), dev(gpu_ctx, centroids), factor,
+                                                         Metric(metric))
+        assert np.array_equal(seg_len, want_len) and np.array_equal(seg_start, want_start)
+        assert np.array_equal(api.to_u32(d_seg), want_index)
