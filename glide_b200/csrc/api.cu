@@ -286,7 +286,7 @@ int glide_kmeans_fit(glide_ctx *ctx, const float *d_sample, uint32_t n, uint32_t
     uint32_t rounds = 0;
     uint32_t *cur = labels_a, *prev = labels_b;
     for (uint32_t it = 0; it < max_iter; it++) {
-        AssignArgs a{d_sample, n, dim, d_centroids, C, -1.0f, metric, cur, nullptr, C <= 4096 ? ctx->tc_norms : nullptr};
+        AssignArgs a{d_sample, n, dim, d_centroids, C, -1.0f, metric, cur, nullptr, C <= 4096 ? ctx->tc_norms : nullptr, nullptr};
         GL_CUDA(ctx, launch_assign(a, st));
         GL_CUDA(ctx, launch_count_changed(cur, prev, n, changed, st));
         uint32_t h_changed = 0;
@@ -370,7 +370,8 @@ int glide_define_partition(glide_ctx *ctx, const float *d_data, uint32_t n, uint
     uint32_t *totals = b.take<uint32_t>(C + 1);
     cudaStream_t st = ctx->stream;
     Timed timer(ctx);
-    AssignArgs a{d_data, n, dim, d_centroids, C, boundary_factor, metric, nearest, bkey, ctx->tc_norms};
+    unsigned long long *cnt = counters_or_null(ctx);
+    AssignArgs a{d_data, n, dim, d_centroids, C, boundary_factor, metric, nearest, bkey, ctx->tc_norms, cnt ? cnt + 3 : nullptr};
     GL_CUDA(ctx, launch_assign(a, st));
     GL_CUDA(ctx, launch_slots(nearest, n, C, slot, totals, hist, st));
     GL_CUDA(ctx, launch_slots(bkey, n, 1, bslot, totals + C, hist, st));
@@ -644,7 +645,7 @@ static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t
     Timed timer(ctx);
     GL_CUDA(ctx, cudaMemcpyAsync(snapshot, d_graph, graph_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     if (mode == kModeRefine) {
-        AssignArgs r{d_data, num, dim, d_centroids, C, -1.0f, metric, route, nullptr, C <= 4096 ? ctx->tc_norms : nullptr};
+        AssignArgs r{d_data, num, dim, d_centroids, C, -1.0f, metric, route, nullptr, C <= 4096 ? ctx->tc_norms : nullptr, nullptr};
         GL_CUDA(ctx, launch_assign(r, ctx->stream));
     }
     BuildArgs a{};
@@ -675,7 +676,7 @@ int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32
     if (rc) return rc;
     uint32_t *route = static_cast<uint32_t *>(ctx->ws);
     Timed timer(ctx);
-    AssignArgs r{d_data + (size_t) first * dim, count, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms};
+    AssignArgs r{d_data + (size_t) first * dim, count, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms, nullptr};
     GL_CUDA(ctx, launch_assign(r, ctx->stream));
     BuildArgs a{};
     a.mode = kModeRefine;
@@ -723,7 +724,7 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
     a.out_ids = d_out_ids; a.out_dists = d_out_dists;
     a.counters = counters_or_null(ctx);
     Timed timer(ctx);
-    AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms};
+    AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms, a.counters ? a.counters + 3 : nullptr};
     GL_CUDA(ctx, launch_assign(r, ctx->stream));
     GL_CUDA(ctx, cudaEventRecord(ctx->ev_mid, ctx->stream));
     GL_CUDA(ctx, launch_search(a, ctx->stream));
@@ -811,7 +812,7 @@ int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t nu
     a.counters = counters_or_null(ctx);
     Timed timer(ctx);
     // no scratch for the tensor-core prefilter here: this entry point keeps to the exact kernels
-    AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, nullptr};
+    AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, nullptr, nullptr};
     GL_CUDA(ctx, launch_assign(r, ctx->stream));
     GL_CUDA(ctx, launch_search(a, ctx->stream));
     return timer.finish();

@@ -12,16 +12,17 @@
 //   re-rank the exact fp32 distance of every candidate in the reference's summation order (the
 //           8-lane team order of common.cuh), then nearest / second nearest / boundary flag.
 //
-// The margin bounds |approx - exact|: TF32 operands carry a relative rounding error of 2^-11
-// each, so the dot product is off by at most ~2^-10 |p||c| (Cauchy-Schwarz), the distance by
-// twice that; the margin is twice THAT again plus the rounding of the norms and of the
-// reference's own sum. A point with more candidates than fit, or whose two best exact distances
-// are equal, is left with the flag 0xffffffff for the warp-per-point kernel, whose full network
-// sort reproduces the reference's tie order. The results are therefore those of the exact path,
-// bit for bit.
+// The margin bounds |approx - exact|: kind::tf32 keeps 10 explicit mantissa bits of each fp32
+// operand (relative error below 2^-10), so the dot product is off by at most ~2^-9 |p||c|
+// (Cauchy-Schwarz) and the distance by twice that, 2^-8 |p||c|; the kernel allows 2^-7 |p||c| plus
+// the rounding of the norms and of the reference's own sum, and compares against the minimum plus
+// twice that. A point with more candidates than fit, or whose two best exact distances are equal,
+// is left with the flag 0xffffffff for the warp-per-point kernel, whose full network sort
+// reproduces the reference's tie order. The results are therefore those of the exact path, bit for
+// bit.
 //
-// The contraction is issued as mma.sync m16n8k8 TF32: at 2 x Q x C x dim flops (2.6 GFLOP for
-// 10,000 queries x 1,024 centroids x 128) it is latency bound, not tensor-throughput bound.
+// The contraction runs on the 5th-generation tensor cores: tcgen05.mma kind::tf32, 128 x 128 x 8
+// per instruction, operands in shared memory, accumulator in tensor memory.
 #include "beam_core.cuh"
 #include "kernels.h"
 
@@ -29,31 +30,12 @@ namespace glide {
 
 namespace {
 
-constexpr int kCand = 8;        // candidates kept per point
-constexpr int kTile = 64;       // centroids per tile
-constexpr int kMaxKSteps = 16;  // dim <= 128
-
-__device__ __forceinline__ uint32_t to_tf32(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return u;
-}
-
-__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
+constexpr int kCand = 16;       // candidates kept per point
+constexpr uint32_t kMaxDim = 128;
 
 __device__ __forceinline__ void min2_add(float &m1, float &m2, float d) {
     m2 = fminf(m2, fmaxf(m1, d));
     m1 = fminf(m1, d);
-}
-
-__device__ __forceinline__ void min2_merge(float &m1, float &m2, float o1, float o2) {
-    m2 = fminf(fminf(m2, o2), fmaxf(m1, o1));
-    m1 = fminf(m1, o1);
 }
 
 struct ExactNear {
@@ -100,177 +82,225 @@ __global__ void centroid_norms_kernel(const float *__restrict__ centroids, uint3
     }
 }
 
-// PT points per CTA (32 or 64), PT/16 m-tiles, two warps per m-tile (each takes four of the
-// eight n8 tiles of a 64-centroid tile): PT/8 warps. Centroid tiles arrive through a two-stage
-// cp.async pipeline (exact fp32 in shared memory, rounded to TF32 as the fragments are read).
-template<int PT>
-__global__ void __launch_bounds__(PT * 4) assign_tc_kernel(const AssignArgs a) {
-    extern __shared__ __align__(16) float smem_f[];
-    constexpr int MT = PT / 16;
-    constexpr int WARPS = MT * 2;
-    constexpr int THREADS = WARPS * 32;
-    const uint32_t dim = a.dim, dimp = dim + 4, ksteps = dim >> 3, chunks = dim >> 2;
-    float *Praw = smem_f;                              // PT x dimp, exact fp32 rows of the points
-    float *Cs = Praw + PT * dimp;                      // 2 x kTile x dimp, exact fp32 centroid tiles
-    float *pn = Cs + 2 * kTile * dimp;                 // PT norms
-    float *thr = pn + PT;                              // PT thresholds
-    float *rowmin = thr + PT;                          // 2 x PT x 2 (n-half, row, min1/min2)
-    uint32_t *cnt = reinterpret_cast<uint32_t *>(rowmin + 4 * PT);   // PT
-    uint32_t *cand = cnt + PT;                         // PT x kCand
+// ---------------------------------------------------------------------------
+// One CTA owns 128 points
+// (the M of a 128 x 128 x 8 TF32 MMA), walks the centroids in tiles of 128 and keeps the
+// 128 x 128 fp32 accumulator of a tile in tensor memory, double buffered (256 columns), so the
+// MMAs of tile t+1 run while the threads read tile t out with tcgen05.ld. Row i of the
+// accumulator lives in tensor-memory lane i and is read by thread i alone: the running minimum,
+// the threshold and the candidate list of a point never leave its thread.
+//
+// Operands are staged by cp.async straight into the K-major "no swizzle" canonical layout the
+// MMA's shared-memory descriptor names: 8 rows x 16 bytes form a contiguous 128-byte core
+// matrix; the next 16-byte K chunk follows at +128 bytes (leading byte offset), the next 8-row
+// group at +chunks*128 bytes (stride byte offset). kind::tf32 reads fp32 words and drops the low
+// 13 mantissa bits, a relative error of 2^-10 per operand; the margin below allows twice the
+// resulting bound. Every wait on an mbarrier is bounded; a CTA whose wait runs out flags all of
+// its points for the exact kernel instead of trusting the accumulator.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kUmmaRows = 128;   // points per CTA = centroids per tile
+constexpr uint32_t kTmemCols = 256;   // two accumulator buffers of 128 columns
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    // start address, leading byte offset, stride byte offset (all without their 4 LSBs), descriptor
+    // version 1, no swizzle
+    return (uint64_t) ((smem_addr >> 4) & 0x3fffu) | ((uint64_t) ((lbo_bytes >> 4) & 0x3fffu) << 16) |
+           ((uint64_t) ((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(128) assign_umma_kernel(const AssignArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_u[];
+    const uint32_t dim = a.dim, chunks = dim >> 2, ksteps = dim >> 3;
+    const uint32_t tile_bytes = kUmmaRows * dim * 4;
+    const uint32_t sbo = chunks * 128u, lbo = 128u;
+    uint8_t *As = smem_u;
+    uint8_t *Bs = As + tile_bytes;                                          // two tiles
+    float *cn_s = reinterpret_cast<float *>(Bs + 2 * tile_bytes);           // 2 x 128 centroid norms
+    uint32_t *cand = reinterpret_cast<uint32_t *>(cn_s + 2 * kUmmaRows);    // 128 x kCand
+    uint64_t *mbar = reinterpret_cast<uint64_t *>(cand + kUmmaRows * kCand);  // 2
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(mbar + 2);
     const float *norms = a.tc_norms;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t gid = lane >> 2, tig = lane & 3;
-    const uint32_t mt = warp % MT, nh = warp / MT;
-    const uint32_t p0 = blockIdx.x * PT;
-    const uint32_t tiles = (a.C + kTile - 1) / kTile;
+    const uint32_t p0 = blockIdx.x * kUmmaRows;
+    const uint32_t tiles = (a.C + kUmmaRows - 1) / kUmmaRows, total = 2 * tiles;
 
-    auto issue_tile = [&](uint32_t t) {  // t counts tiles over both passes
-        const uint32_t c0 = (t % tiles) * kTile;
-        float *buf = Cs + (t & 1u) * kTile * dimp;
-        for (uint32_t e = tid; e < kTile * chunks; e += THREADS) {
-            const uint32_t row = e / chunks, c = e % chunks;
-            const uint32_t cid = c0 + row;
-            const bool valid = cid < a.C;
-            cp_async16(buf + row * dimp + 4 * c, a.centroids + (uint64_t) (valid ? cid : 0) * dim + 4 * c, valid);
+    // 128 rows x chunks 16-byte pieces; a warp instruction moves 8 rows x 4 chunks: 64 contiguous
+    // bytes per row on the global side, 512 contiguous bytes on the shared side
+    auto stage_rows = [&](uint8_t *dst, const float *src, uint32_t first_row, uint32_t row_limit) {
+        const uint32_t cgroups = chunks >> 2;
+        for (uint32_t g = warp; g < 16 * cgroups; g += 4) {
+            const uint32_t r = (g / cgroups) * 8 + (lane & 7), c = (g % cgroups) * 4 + (lane >> 3);
+            const bool valid = first_row + r < row_limit;
+            cp_async16(dst + (r >> 3) * sbo + c * lbo + (r & 7) * 16,
+                       src + (uint64_t) (valid ? first_row + r : 0) * dim + 4 * c, valid);
         }
+    };
+    auto stage_tile = [&](uint32_t t) {  // t counts tiles over both passes
+        const uint32_t c0 = (t % tiles) * kUmmaRows;
+        stage_rows(Bs + (t & 1u) * tile_bytes, a.centroids, c0, a.C);
+        cn_s[(t & 1u) * kUmmaRows + tid] = c0 + tid < a.C ? __ldg(norms + c0 + tid) : 0.0f;
         cp_async_commit();
     };
-    issue_tile(0);
 
-    // ---- stage the points (exact), their norms, and this warp's A fragments ----
-    for (uint32_t e = tid; e < PT * 32; e += THREADS) {
-        const uint32_t row = e >> 5, c = e & 31;
-        const uint32_t p = p0 + row;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p < a.n && c < chunks) v = __ldg(reinterpret_cast<const float4 *>(a.data + (uint64_t) p * dim) + c);
-        float s = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(kFullMask, s, off);
-        if (c < chunks) *reinterpret_cast<float4 *>(Praw + row * dimp + 4 * c) = v;
-        if (c == 0) pn[row] = s;
+    if (tid == 0) {
+        const uint32_t b0 = smem_u32(mbar), b1 = smem_u32(mbar + 1);
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b0) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b1) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < PT) cnt[tid] = 0;
+    __syncwarp();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    stage_rows(As, a.data, p0, a.n);
+    stage_tile(0);
+    cp_async_wait<0>();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    uint32_t af[kMaxKSteps][4];
-#pragma unroll
-    for (int ks = 0; ks < kMaxKSteps; ks++) {
-        if ((uint32_t) ks < ksteps) {
-            const float *r0 = Praw + (mt * 16 + gid) * dimp + ks * 8, *r1 = r0 + 8 * dimp;
-            af[ks][0] = to_tf32(r0[tig]);
-            af[ks][1] = to_tf32(r1[tig]);
-            af[ks][2] = to_tf32(r0[tig + 4]);
-            af[ks][3] = to_tf32(r1[tig + 4]);
-        } else {
-            af[ks][0] = af[ks][1] = af[ks][2] = af[ks][3] = 0u;
-        }
-    }
-    const uint32_t row0 = mt * 16 + gid, row1 = row0 + 8;
-    const float pn0 = pn[row0], pn1 = pn[row1];
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
 
-    float m1[2] = {FLT_MAX, FLT_MAX}, m2[2] = {FLT_MAX, FLT_MAX};
-    float t0 = 0.f, t1 = 0.f;
-    for (uint32_t t = 0; t < 2 * tiles; t++) {
-        const int pass = t >= tiles;
-        const uint32_t c0 = (t % tiles) * kTile;
-        if (t + 1 < 2 * tiles) {
-            issue_tile(t + 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+    // squared norm of this thread's point, from the staged copy
+    float pnr = 0.0f;
+    for (uint32_t c = 0; c < chunks; c++) {
+        const float4 v = *reinterpret_cast<const float4 *>(As + (tid >> 3) * sbo + c * lbo + (tid & 7) * 16);
+        pnr += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float cm = __ldg(norms + a.C);
+    const float err = 0.0078125f * sqrtf(pnr) * sqrtf(cm) + 1.52587890625e-5f * (pnr + cm);
+
+    // instruction descriptor: D fp32, A and B TF32, both K-major, N = 128, M = 128
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kUmmaRows >> 3) << 17) | ((kUmmaRows >> 4) << 24);
+    const uint32_t a_addr = smem_u32(As), b_addr = smem_u32(Bs);
+    const uint32_t lane_base = (warp & 3u) * 32u;
+
+    float m1 = FLT_MAX, m2 = FLT_MAX, thr = 0.0f;
+    uint32_t n_c = 0;
+    bool ok = true, need_second = false;
+    for (uint32_t t = 0; t < total; t++) {
+        const uint32_t buf = t & 1u;
+        if (tid == 0) {
+            for (uint32_t ks = 0; ks < ksteps; ks++)
+                umma_tf32(tmem_base + buf * kUmmaRows, umma_desc(a_addr + ks * 2 * lbo, lbo, sbo),
+                          umma_desc(b_addr + buf * tile_bytes + ks * 2 * lbo, lbo, sbo), idesc, ks > 0 ? 1u : 0u);
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar + buf))
+                         : "memory");
         }
-        __syncthreads();  // tile t has landed for every thread
-        const float *buf = Cs + (t & 1u) * kTile * dimp;
-        float2 cn2[4];
-#pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-            const uint32_t cid = c0 + (nh * 4 + nt) * 8 + 2 * tig;   // even, so cid + 1 <= C when cid < C and C is even
-            cn2[nt].x = cid < a.C ? __ldg(norms + cid) : 0.0f;
-            cn2[nt].y = cid + 1 < a.C ? __ldg(norms + cid + 1) : 0.0f;
-        }
-        float acc[4][4];
-#pragma unroll
-        for (int nt = 0; nt < 4; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
-#pragma unroll
-        for (int ks = 0; ks < kMaxKSteps; ks++) {
-            if ((uint32_t) ks < ksteps) {
-#pragma unroll
-                for (int nt = 0; nt < 4; nt++) {
-                    const float *b = buf + ((nh * 4 + nt) * 8 + gid) * dimp + ks * 8 + tig;
-                    mma_tf32(acc[nt], af[ks], to_tf32(b[0]), to_tf32(b[4]));
-                }
+        if (t + 1 < total) stage_tile(t + 1);   // overlaps the MMAs of tile t
+        {   // wait for the MMAs of tile t: phase parity of this buffer's barrier
+            const uint32_t bar = smem_u32(mbar + buf), parity = (t >> 1) & 1u;
+            uint32_t done = 0;
+            for (uint32_t spin = 0; spin < kSpinLimit && !done; spin++) {
+                asm volatile(
+                    "{\n\t"
+                    ".reg .pred p;\n\t"
+                    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                    "selp.u32 %0, 1, 0, p;\n\t"
+                    "}\n"
+                    : "=r"(done)
+                    : "r"(bar), "r"(parity)
+                    : "memory");
             }
+            // every thread takes the same branch below (tcgen05.ld is a warp-wide instruction)
+            ok = __syncthreads_and(done != 0) != 0;
         }
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t c0 = (t % tiles) * kUmmaRows;
+        const float *cn = cn_s + buf * kUmmaRows;
+        const bool second = t >= tiles;
+        for (uint32_t cb = 0; cb < kUmmaRows; cb += 32) {
+            uint32_t r[32];
+            tmem_load32(tmem_base + (lane_base << 16) + buf * kUmmaRows + cb, r);
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t cid = c0 + (nh * 4 + nt) * 8 + 2 * tig + (i & 1);
-                if (cid >= a.C) continue;
-                const int r = i >> 1;
-                const float d = (r ? pn1 : pn0) + ((i & 1) ? cn2[nt].y : cn2[nt].x) - 2.0f * acc[nt][i];
-                if (pass == 0) {
-                    min2_add(m1[r], m2[r], d);
-                } else if (d <= (r ? t1 : t0)) {
-                    const uint32_t row = r ? row1 : row0;
-                    const uint32_t k = atomicAdd(&cnt[row], 1u);
-                    if (k < (uint32_t) kCand) cand[row * kCand + k] = cid;
+            for (int j = 0; j < 32; j++) {
+                const uint32_t cid = c0 + cb + j;
+                const float d = (cid < a.C) ? (pnr + cn[cb + j]) - 2.0f * __uint_as_float(r[j]) : FLT_MAX;
+                if (!second) {
+                    min2_add(m1, m2, d);
+                } else if (d <= thr) {
+                    if (n_c < (uint32_t) kCand) cand[tid * kCand + n_c] = cid;
+                    n_c++;
                 }
             }
         }
         if (t + 1 == tiles) {
-            // smallest / second smallest per row: over the quad, then over the two n-halves
-#pragma unroll
-            for (int r = 0; r < 2; r++) {
-#pragma unroll
-                for (int off = 1; off <= 2; off <<= 1) {
-                    const float o1 = __shfl_xor_sync(kFullMask, m1[r], off), o2 = __shfl_xor_sync(kFullMask, m2[r], off);
-                    min2_merge(m1[r], m2[r], o1, o2);
-                }
+            // Routing and k-means need the nearest centroid only. The boundary test d1 / d0 <= factor
+            // (partition_kernel.cuh:58-60) needs the exact second nearest distance only when the ratio
+            // can come near the factor at all: if even the most favourable reading of the two
+            // approximate minima leaves it clearly above, the point is not a boundary point and the
+            // dense crowd of centroids around the second minimum never has to be re-ranked.
+            const bool boundary_test = a.is_boundary && a.boundary_factor >= 0.0f && a.C > 1;
+            if (boundary_test) {
+                const float lo2 = fmaxf(m2 - err, 0.0f), hi1 = m1 + err;
+                const float f = a.metric == kEuclidean ? a.boundary_factor * a.boundary_factor : a.boundary_factor;
+                need_second = !(lo2 > f * hi1 * 1.001f);
             }
-            if (tig == 0) {
-                rowmin[(nh * PT + row0) * 2 + 0] = m1[0];
-                rowmin[(nh * PT + row0) * 2 + 1] = m2[0];
-                rowmin[(nh * PT + row1) * 2 + 0] = m1[1];
-                rowmin[(nh * PT + row1) * 2 + 1] = m2[1];
-            }
-            __syncthreads();
-            if (tid < PT) {
-                float a1 = rowmin[tid * 2], a2 = rowmin[tid * 2 + 1];
-                min2_merge(a1, a2, rowmin[(PT + tid) * 2], rowmin[(PT + tid) * 2 + 1]);
-                // the boundary test needs the second nearest too; routing and k-means only the nearest
-                const float base = (a.is_boundary && a.C > 1) ? a2 : a1;
-                const float pnr = pn[tid], cm = __ldg(norms + a.C);
-                const float err = 0.00390625f * sqrtf(pnr) * sqrtf(cm) + 1.52587890625e-5f * (pnr + cm);
-                thr[tid] = base + 2.0f * err + 6.103515625e-5f * fabsf(base);
-            }
-            __syncthreads();
-            t0 = thr[row0];
-            t1 = thr[row1];
+            const float base = need_second ? m2 : m1;
+            thr = base + 2.0f * err + 6.103515625e-5f * fabsf(base);
         }
-        __syncthreads();  // buffer t & 1 is free for tile t + 2
+        cp_async_wait<0>();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
+    cp_async_wait<0>();
+    __shared__ uint32_t cnt_s[kUmmaRows];
+    // a CTA whose wait ran out leaves every point to the exact kernel; bit 31: second nearest not needed
+    cnt_s[tid] = (ok ? n_c : (uint32_t) kCand + 1) | (need_second ? 0u : 0x80000000u);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 
-    // ---- exact re-rank in the reference's team order ----
+    // ---- exact re-rank in the reference's team order (point rows re-read from global memory) ----
     const uint32_t team = lane >> 3;
-    for (uint32_t row = warp; row < (uint32_t) PT; row += WARPS) {
+    for (uint32_t row = warp; row < kUmmaRows; row += 4) {
         const uint32_t p = p0 + row;
         if (p >= a.n) continue;
-        const uint32_t n_c = cnt[row];
+        const uint32_t cnt = cnt_s[row] & 0x7fffffffu;
+        const bool far_second = (cnt_s[row] >> 31) != 0;
         ExactNear st{FLT_MAX, FLT_MAX, kInvalid, 0u};
-        const bool overflow = n_c > (uint32_t) kCand;
+        const bool overflow = cnt > (uint32_t) kCand;
         if (!overflow) {
-            for (uint32_t g = 0; g < n_c; g += 4) {
+            for (uint32_t g = 0; g < cnt; g += 4) {
                 const uint32_t j = g + team;
-                const bool active = j < n_c;
+                const bool active = j < cnt;
                 const uint32_t cid = active ? cand[row * kCand + j] : 0u;
-                const float part = team_partial(Praw + row * dimp, a.centroids + (uint64_t) cid * dim, dim, active);
+                const float part = team_partial(a.data + (uint64_t) p * dim, a.centroids + (uint64_t) cid * dim, dim, active);
                 const float sum = team_fold(part);
-                if (active) exact_add(st, finish_metric(sum, a.metric), cid);  // every lane of the team holds the same state
+                if (active) exact_add(st, finish_metric(sum, a.metric), cid);
             }
-            // fold the four teams (lanes 0, 8, 16, 24 are representative)
 #pragma unroll
             for (int off = 16; off >= 8; off >>= 1) {
                 const float d0 = __shfl_xor_sync(kFullMask, st.d0, off), d1 = __shfl_xor_sync(kFullMask, st.d1, off);
@@ -282,37 +312,30 @@ __global__ void __launch_bounds__(PT * 4) assign_tc_kernel(const AssignArgs a) {
             const bool unique = !overflow && st.ties == 1;
             a.nearest[p] = unique ? st.id : kInvalid;
             if (a.is_boundary && unique)  // partition_kernel.cuh:58-60
-                a.is_boundary[p] = (a.boundary_factor >= 0.0f && a.C > 1 && st.d1 / st.d0 <= a.boundary_factor) ? 0u : kInvalid;
+                a.is_boundary[p] = (!far_second && a.boundary_factor >= 0.0f && a.C > 1 && st.d1 / st.d0 <= a.boundary_factor) ? 0u : kInvalid;
         }
     }
 }
 
-template<int PT>
-cudaError_t launch_tc(const AssignArgs &a, cudaStream_t stream) {
-    const uint32_t dimp = a.dim + 4;
-    const size_t smem_bytes = ((size_t) (PT + 2 * kTile) * dimp + PT + PT + 4 * PT + PT + PT * kCand) * 4;
-    auto kernel = assign_tc_kernel<PT>;
-    if (smem_bytes > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
-        if (e != cudaSuccess) return e;
-    }
-    kernel<<<(a.n + PT - 1) / PT, PT * 4, smem_bytes, stream>>>(a);
+cudaError_t launch_umma(const AssignArgs &a, cudaStream_t stream) {
+    const size_t smem_bytes = (size_t) 3 * kUmmaRows * a.dim * 4 + 2 * kUmmaRows * 4 + kUmmaRows * kCand * 4 + 2 * 8 + 16;
+    cudaError_t e = cudaFuncSetAttribute(assign_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+    if (e != cudaSuccess) return e;
+    assign_umma_kernel<<<(a.n + kUmmaRows - 1) / kUmmaRows, 128, smem_bytes, stream>>>(a);
     return cudaGetLastError();
 }
 
 }  // namespace
 
 bool assign_tc_eligible(const AssignArgs &a) {
-    return a.tc_norms != nullptr && (a.dim & 7u) == 0 && a.dim <= 8 * kMaxKSteps && a.C >= 2;
+    return a.tc_norms != nullptr && (a.dim & 15u) == 0 && a.dim <= kMaxDim && a.C >= 2;
 }
 
 cudaError_t launch_assign_tc(const AssignArgs &a, cudaStream_t stream) {
     cudaError_t e = cudaMemsetAsync(a.tc_norms + a.C, 0, sizeof(float), stream);
     if (e != cudaSuccess) return e;
     centroid_norms_kernel<<<(a.C + 7) / 8, 256, 0, stream>>>(a.centroids, a.C, a.dim, a.tc_norms);
-    // small batches: more, smaller CTAs
-    if (a.n <= 65536) return launch_tc<32>(a, stream);
-    return launch_tc<64>(a, stream);
+    return launch_umma(a, stream);
 }
 
 }  // namespace glide

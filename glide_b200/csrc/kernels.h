@@ -100,6 +100,7 @@ struct AssignArgs {
     uint32_t *nearest;      // n
     uint32_t *is_boundary;  // n: 0 for a boundary point, 0xffffffff otherwise (a slot key); may be nullptr
     float *tc_norms;        // C + 1 floats of scratch for the tensor-core prefilter; nullptr: exact kernels only
+    unsigned long long *fallback_counter;  // += points settled by the warp-per-point kernel; may be nullptr
 };
 cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream);
 // Tensor-core prefilter + exact re-rank (assign_tc.cu); settles every point whose nearest centroid

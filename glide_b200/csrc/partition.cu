@@ -32,7 +32,8 @@ __global__ void __launch_bounds__(256) assign_kernel(const AssignArgs a, uint32_
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t p = blockIdx.x * (blockDim.x >> 5) + warp;
     if (p >= a.n) return;
-    if (only_flagged && a.nearest[p] != kInvalid) return;  // settled by assign_tiled_kernel
+    if (only_flagged && a.nearest[p] != kInvalid) return;  // settled by the tiled or tensor-core kernel
+    if (only_flagged && a.fallback_counter && lane == 0) atomicAdd(a.fallback_counter, 1ull);
     uint32_t *base = smem + (size_t) warp * strip_words;
     float *query = reinterpret_cast<float *>(base);
     uint32_t *scratch = base + dim_pad4(a.dim);

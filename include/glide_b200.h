@@ -190,9 +190,11 @@ int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t nu
 /* Device milliseconds of the two kernels of the last glide_search on this context:
  * out[0] the routing pre-pass (nearest centroid per query), out[1] the search kernel. */
 void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]);
-/* Counters of the last search/build/refine call when enabled: rows read during search,
- * expansions, rows read during pruning, and (build/refine only) points whose beam ended with
- * fewer than `beam` entries. */
+/* Counters of the last search/build/refine/define_partition call when enabled: rows read during
+ * search, expansions, rows read during pruning, and a fourth that depends on the call: build and
+ * refine count the points whose beam ended with fewer than `beam` entries; search and
+ * define_partition count the points whose nearest centroid was settled by the exact
+ * warp-per-point kernel (a tie, or too many candidates after the tensor-core prefilter). */
 void glide_enable_counters(glide_ctx *ctx, int on);
 int glide_read_counters(glide_ctx *ctx, uint64_t out[4]);
 

@@ -542,7 +542,14 @@ def test_assignment_with_tensor_core_prefilter_is_exact(gpu_ctx, kind):
     metric = oracle.COSINE if kind == "unit96" else oracle.EUCLIDEAN
     for factor in (1.1, -1.0):
         want_index, want_start, want_len = oracle.define_partition(base, centroids, factor, metric)
+        gpu_ctx.enable_counters(True)
         d_seg, seg_start, seg_len = api.define_partition(gpu_ctx, dev(gpu_ctx, base), dev(gpu_ctx, centroids), factor,
                                                          Metric(metric))
+        by_fallback = gpu_ctx.read_counters()[3]
+        gpu_ctx.enable_counters(False)
         assert np.array_equal(seg_len, want_len) and np.array_equal(seg_start, want_start)
         assert np.array_equal(api.to_u32(d_seg), want_index)
+        if kind in ("mixture_1024", "unit96"):      # the prefilter, not the fallback, does the work on ordinary data
+            assert by_fallback < 0.02 * base.shape[0]
+        if kind == "duplicates":                    # every nearest centroid has a twin: all points tie
+            assert by_fallback == base.shape[0]
