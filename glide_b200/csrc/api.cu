@@ -25,6 +25,7 @@ struct glide_ctx {
     void *ws = nullptr;  // scratch, grown on demand
     size_t ws_bytes = 0;
     unsigned long long *counters = nullptr;  // 4 x u64 on the device
+    uint32_t *ticket = nullptr;              // one word: the search kernel's query counter
     float *tc_norms = nullptr;               // 4096 + 1 floats: centroid norms for the assignment's tensor-core prefilter
     bool counters_on = false;
 };
@@ -143,7 +144,8 @@ int glide_ctx_create(int device, glide_ctx **out) {
         cudaEventCreate(&ctx->ev_start) != cudaSuccess || cudaEventCreate(&ctx->ev_stop) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_mid) != cudaSuccess ||
         cudaMalloc(&ctx->counters, 4 * sizeof(unsigned long long)) != cudaSuccess ||
-        cudaMalloc(&ctx->tc_norms, (4096 + 1) * sizeof(float)) != cudaSuccess) {
+        cudaMalloc(&ctx->tc_norms, (4096 + 1) * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&ctx->ticket, sizeof(uint32_t)) != cudaSuccess) {
         delete ctx;
         return GLIDE_ERR_CUDA;
     }
@@ -158,6 +160,7 @@ void glide_ctx_destroy(glide_ctx *ctx) {
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->tc_norms) cudaFree(ctx->tc_norms);
+    if (ctx->ticket) cudaFree(ctx->ticket);
     if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
     if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
     if (ctx->ev_mid) cudaEventDestroy(ctx->ev_mid);
@@ -723,6 +726,7 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
     a.centroids = d_centroids; a.C = C; a.start_points = d_start_points; a.route = route;
     a.out_ids = d_out_ids; a.out_dists = d_out_dists;
     a.counters = counters_or_null(ctx);
+    a.ticket = ctx->ticket;
     Timed timer(ctx);
     AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms, a.counters ? a.counters + 3 : nullptr};
     GL_CUDA(ctx, launch_assign(r, ctx->stream));
@@ -849,6 +853,7 @@ int glide_search_on_sub(glide_ctx *ctx, const float *d_data, uint32_t dim, const
     a.segment_ids = d_segment_ids; a.segment_num = segment_num; a.segment_id = segment_id;
     a.start_point = start_point; a.map = d_map;
     a.counters = counters_or_null(ctx);
+    a.ticket = ctx->ticket;
     Timed timer(ctx);
     GL_CUDA(ctx, launch_search(a, ctx->stream));
     return timer.finish();

@@ -33,6 +33,8 @@ struct SearchArgs {
     uint32_t segment_num, segment_id, start_point;
     const uint32_t *map;         // local id -> global id (large path)
     unsigned long long *counters;  // [0] data rows read, [1] expansions; may be nullptr
+    uint32_t *ticket;            // one word, zeroed by launch_search: warps draw their next query from it;
+                                 // nullptr: query q runs on warp q of the grid
 };
 cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream);
 
@@ -104,7 +106,7 @@ struct AssignArgs {
 };
 cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream);
 // Tensor-core prefilter + exact re-rank (assign_tc.cu); settles every point whose nearest centroid
-// is unique, flags the rest with 0xffffffff in `nearest`. Eligible: tc_norms given, dim % 8 == 0, dim <= 128, C >= 2.
+// is unique, flags the rest with 0xffffffff in `nearest`. Eligible: tc_norms given, dim % 16 == 0, dim <= 128, C >= 2.
 bool assign_tc_eligible(const AssignArgs &a);
 cudaError_t launch_assign_tc(const AssignArgs &a, cudaStream_t stream);
 

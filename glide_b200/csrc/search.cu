@@ -42,15 +42,9 @@ __device__ inline void warp_merge_final_smem(float *k, uint32_t *v, uint32_t n_p
 // LANES: adjacency rows of at most 32 entries, candidates stay in registers (beam_loop_lanes);
 // the strip then holds only the query and the visited set.
 template<int NB, int NC, bool LANES>
-__global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
-    extern __shared__ __align__(16) uint32_t smem[];
+__device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &s, const BeamParams &p, uint32_t q) {
     const SearchArgs &a = d.a;
-    const uint32_t warps_per_cta = blockDim.x >> 5;
-    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
-    const uint32_t q = blockIdx.x * warps_per_cta + warp;
-    if (q >= a.Q) return;
-    const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
-    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLanesCand : 32u * NC, p.hash_bit);
+    const uint32_t lane = lane_id();
 
     const bool sub = (a.segment_ids != nullptr);
     if (sub) {  // search_kernel.cuh:676-692: skip queries not routed to this partition
@@ -144,6 +138,44 @@ __global__ void __launch_bounds__(256) search_kernel(const SearchDev d) {
     }
 }
 
+// A warp per query. With a ticket counter the grid is sized to what the device holds at once and
+// every warp draws its next query as soon as it finishes one, so a slow query delays neither the
+// other warps of its CTA nor a whole wave of CTAs.
+template<int NB, int NC, bool LANES>
+__device__ __forceinline__ void search_body(const SearchDev &d) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    const SearchArgs &a = d.a;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
+    const WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLanesCand : 32u * NC, p.hash_bit);
+    if (a.ticket == nullptr) {
+        const uint32_t q = blockIdx.x * warps_per_cta + warp;
+        if (q < a.Q) search_one<NB, NC, LANES>(d, s, p, q);
+        return;
+    }
+    while (true) {
+        uint32_t q = 0;
+        if (lane == 0) q = atomicAdd(a.ticket, 1u);
+        q = __shfl_sync(kFullMask, q, 0);
+        if (q >= a.Q) break;
+        search_one<NB, NC, LANES>(d, s, p, q);
+        __syncwarp();
+    }
+}
+
+// Register targets per beam class (measured): 64 registers for beams up to 64 slots (4 CTAs per
+// SM), 80 up to 128, 128 beyond. The 32-slot instance does best with the compiler's own choice.
+template<int NB, int NC, bool LANES>
+__global__ void __launch_bounds__(256, NB == 2 ? 4 : (NB == 4 ? 3 : 2)) search_kernel(const SearchDev d) {
+    search_body<NB, NC, LANES>(d);
+}
+
+template<int NC, bool LANES>
+__global__ void __launch_bounds__(256) search_kernel_32(const SearchDev d) {
+    search_body<1, NC, LANES>(d);
+}
+
 // select_segment_kernel (search_kernel.cuh:546-607): a warp per query.
 __global__ void __launch_bounds__(128) select_segment_kernel(const SelectSegmentArgs a, uint32_t max_centroid,
                                                              uint32_t strip_words) {
@@ -183,12 +215,23 @@ uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
 
 template<int NB, int NC, bool LANES = false>
 cudaError_t launch_search_t(const SearchDev &d, uint32_t warps_per_cta, size_t smem_bytes, cudaStream_t stream) {
-    auto kernel = search_kernel<NB, NC, LANES>;
+    void (*kernel)(const SearchDev) = search_kernel<NB, NC, LANES>;
+    if constexpr (NB == 1) kernel = search_kernel_32<NC, LANES>;
     if (smem_bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
         if (e != cudaSuccess) return e;
     }
-    const uint32_t grid = (d.a.Q + warps_per_cta - 1) / warps_per_cta;
+    uint32_t grid = (d.a.Q + warps_per_cta - 1) / warps_per_cta;
+    if (d.a.ticket) {
+        int per_sm = 0, dev = 0, sms = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int) (warps_per_cta * 32), smem_bytes);
+        if (e != cudaSuccess) return e;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+        const uint32_t resident = (uint32_t) (per_sm > 0 ? per_sm : 1) * (uint32_t) sms;
+        if (grid > resident) grid = resident;
+        if ((e = cudaMemsetAsync(d.a.ticket, 0, sizeof(uint32_t), stream)) != cudaSuccess) return e;
+    }
     kernel<<<grid, warps_per_cta * 32, smem_bytes, stream>>>(d);
     return cudaGetLastError();
 }
