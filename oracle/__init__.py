@@ -3,8 +3,10 @@
 TEST INFRASTRUCTURE: only tests, the smoke check and the benchmark's CPU-baseline
 leg may import this package. The product package never does.
 
-PARITY UNPINNED: the reference has no golden vectors or CPU path to pin against;
-see the header of ``glide_oracle.cpp``.
+Pinned on the GPU against the reference's own kernels (``ref_harness.cu``,
+``tests/test_gpu_reference.py``) for search, build, boundary merge, reverse edges, refine and
+assignment; PARITY UNPINNED for k-means and NN-descent (cuVS arithmetic, not in the reference
+tree). See the header of ``glide_oracle.cpp``.
 """
 from __future__ import annotations
 

@@ -6,11 +6,16 @@
 // or call it; only tests, the smoke check and the CPU-baseline leg of the benchmark
 // do.
 //
-// PARITY UNPINNED: the reference ships no golden vectors, known-answer tests or
-// fixtures for any stage, has no CPU code path, and cannot be built without
-// RAFT/cuVS (fetched at configure time, absent here). The restatement below was
-// therefore checked only by reading, by its own invariants (exact brute force,
-// sortedness, set semantics) and against the CUDA path of this repository.
+// PINNING. The reference ships no golden vectors, known-answer tests or fixtures for any
+// stage, has no CPU code path, and its programs cannot be built without RAFT/cuVS (fetched
+// at configure time, absent here). Its kernel headers, however, compile on their own:
+// ref_harness.cu launches the reference's search, build, boundary, reverse, refine and
+// partition kernels, and the GPU tests (tests/test_gpu_reference.py) compare them with this
+// restatement in the reference's summation order: search, build, boundary merge and
+// assignment bit for bit; reverse edges as one of the arrival orders allowed here; refine up
+// to the reference's in-place race. PARITY UNPINNED for what has no reference arithmetic in
+// the tree: k-means and NN-descent (cuVS calls), which restate this repository's own
+// algorithms, and for the CPU-only view (without a GPU the harness cannot run).
 //
 // Each function cites the reference file:line it follows (paths relative to the
 // reference's src/ directory).
