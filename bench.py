@@ -4,7 +4,7 @@
     python bench.py --gpus N --steps K --warmup W [--config cfg1] [--impl reference]
 
 A step is one pass of the search kernel over one batch of Q queries (10,000 for cfg1)
-at the smallest beam of a fixed ladder that reaches recall@10 >= 0.95 against exact
+at the smallest beam (a fixed ladder, then bisection between its steps) that reaches recall@10 >= 0.95 against exact
 kNN; the index is built once before the timed region and its stage times are reported
 under "build". `value` is queries/s with queries resident in HBM (sum over ranks / max
 time over ranks); `e2e` is the same through the host-buffer entry point with the H2D
@@ -252,6 +252,20 @@ def run_ours(args):
         if rec >= TARGET_RECALL:
             chosen = (beam, sp, rec)
             break
+    if chosen is not None and len(curve) >= 2:
+        # recall grows with the beam: bisect between the last ladder step below the target and the first above it
+        lo, hi = curve[-2]["beam"], chosen[0]
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            sp_mid = pipeline.derive_search_params(mid, spec.graph_degree, TOP_K)
+            ids, _, sec = index.search(sp_mid, d_queries)
+            rec = api.calculate_recall(ids, gt, TOP_K)
+            curve.append({"beam": mid, "recall": round(rec, 4), "qps": round(Q / sec, 1)})
+            if rec >= TARGET_RECALL:
+                hi, chosen = mid, (mid, sp_mid, rec)
+            else:
+                lo = mid
+        curve.sort(key=lambda c: c["beam"])
     if chosen is None:
         beam = BEAM_LADDER[-1]
         chosen = (beam, pipeline.derive_search_params(beam, spec.graph_degree, TOP_K), curve[-1]["recall"])

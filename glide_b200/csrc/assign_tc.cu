@@ -23,6 +23,8 @@
 //
 // The contraction runs on the 5th-generation tensor cores: tcgen05.mma kind::tf32, 128 x 128 x 8
 // per instruction, operands in shared memory, accumulator in tensor memory.
+#include <cstdlib>
+#include <cuda.h>
 #include "beam_core.cuh"
 #include "kernels.h"
 
@@ -325,6 +327,297 @@ cudaError_t launch_umma(const AssignArgs &a, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Warp-specialised variant for dim % 32 == 0: operand tiles arrive by TMA (2-D tensor maps over
+// the row-major matrices, boxes of 32 floats x 128 rows, 128-byte swizzle), one producer thread
+// issues the copies and the MMAs, eight epilogue warps read the accumulators (warp w: tensor-memory
+// lanes 32*(w%4).., columns 64*(w/4)..). A tile then costs max(copy, MMA, epilogue), not their sum.
+//
+// Barriers (mbarriers in shared memory; every wait is bounded and a wait that runs out raises
+// `failed`, after which nobody waits any more and every point of the CTA is flagged):
+//   a_full        the point tile has landed              (TMA complete_tx)
+//   b_full[s]     centroid tile in stage s has landed    (TMA complete_tx)
+//   mma_done[s]   MMAs of the tile in stage s / TMEM buffer s have completed (tcgen05.commit);
+//                 frees stage s for the next copy and hands buffer s to the epilogue
+//   tmem_free[s]  all eight epilogue warps have read buffer s (8 arrivals)
+// ---------------------------------------------------------------------------
+constexpr uint32_t kEpilogueWarps = 8;
+constexpr uint32_t kTmaThreads = (kEpilogueWarps + 1) * 32;
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait; gives up early when another thread of the CTA already failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *failed) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kSpinLimit; spin++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spin & 1023u) == 1023u && *failed) return false;
+    }
+    *failed = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const void *tmap, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+// K-major operand with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    return (uint64_t) ((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t) (1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const AssignArgs a, const __grid_constant__ CUtensorMap tm_points,
+                                                                       const __grid_constant__ CUtensorMap tm_centroids) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    const uint32_t dim = a.dim, kblocks = dim >> 5, ksteps = dim >> 3;
+    const uint32_t sub_bytes = kUmmaRows * 128u;              // one 32-float column block of a tile
+    const uint32_t tile_bytes = kblocks * sub_bytes;
+    uint8_t *As = base;
+    uint8_t *Bs = As + tile_bytes;                            // two stages
+    float *rowmin = reinterpret_cast<float *>(Bs + 2 * tile_bytes);       // 2 halves x 128 rows x 2
+    uint32_t *cand = reinterpret_cast<uint32_t *>(rowmin + 4 * kUmmaRows);  // 128 x kCand
+    uint32_t *cnt = cand + kUmmaRows * kCand;                 // 128 counters; later bit 31: far second
+    uint64_t *bars = reinterpret_cast<uint64_t *>(cnt + kUmmaRows);       // a_full, b_full[2], mma_done[2], tmem_free[2]
+    uint64_t *a_full = bars, *b_full = bars + 1, *mma_done = bars + 3, *tmem_free = bars + 5;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
+    volatile uint32_t *failed = tmem_slot + 1;
+    const float *norms = a.tc_norms;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t p0 = blockIdx.x * kUmmaRows;
+    const uint32_t tiles = (a.C + kUmmaRows - 1) / kUmmaRows, total = 2 * tiles;
+
+    if (tid == 0) {
+        mbar_init(a_full, 1);
+        for (int s = 0; s < 2; s++) { mbar_init(b_full + s, 1); mbar_init(mma_done + s, 1); mbar_init(tmem_free + s, kEpilogueWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *failed = 0;
+    }
+    if (tid < kUmmaRows) cnt[tid] = 0;
+    if (warp == kEpilogueWarps) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == kEpilogueWarps) {
+        // ================= producer: TMA copies and MMA issue, one thread =================
+        if (lane == 0) {
+            auto load_tile = [&](uint8_t *dst, const CUtensorMap *tm, uint32_t row0, uint64_t *bar) {
+                mbar_expect_tx(bar, tile_bytes);
+                for (uint32_t kb = 0; kb < kblocks; kb++) tma_load_2d(dst + kb * sub_bytes, tm, kb * 32u, row0, bar);
+            };
+            load_tile(As, &tm_points, p0, a_full);
+            load_tile(Bs, &tm_centroids, 0, b_full + 0);
+            if (total > 1) load_tile(Bs + tile_bytes, &tm_centroids, (1u % tiles) * kUmmaRows, b_full + 1);
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kUmmaRows >> 3) << 17) | ((kUmmaRows >> 4) << 24);
+            const uint32_t a_addr = smem_u32(As), b_addr = smem_u32(Bs);
+            bool ok = mbar_wait(a_full, 0, failed);
+            for (uint32_t t = 0; t < total && ok; t++) {
+                const uint32_t s = t & 1u, use = t >> 1;
+                ok = mbar_wait(b_full + s, use & 1u, failed);
+                if (ok && t >= 2) ok = mbar_wait(tmem_free + s, (use - 1) & 1u, failed);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (uint32_t ks = 0; ks < ksteps; ks++) {
+                    const uint32_t off = (ks >> 2) * sub_bytes + (ks & 3u) * 32u;
+                    umma_tf32(tmem_base + s * kUmmaRows, umma_desc_sw128(a_addr + off),
+                              umma_desc_sw128(b_addr + s * tile_bytes + off), idesc, ks > 0 ? 1u : 0u);
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mma_done + s))
+                             : "memory");
+                if (t + 2 < total) {   // stage s is free once these MMAs have read it
+                    ok = mbar_wait(mma_done + s, use & 1u, failed);
+                    if (ok) load_tile(Bs + s * tile_bytes, &tm_centroids, ((t + 2) % tiles) * kUmmaRows, b_full + s);
+                }
+            }
+        }
+    } else {
+        // ================= epilogue warps =================
+        const uint32_t quad = warp & 3u, half = warp >> 2;
+        const uint32_t row = quad * 32u + lane;
+        const uint32_t p = p0 + row;
+        float pnr = 0.0f;
+        if (p < a.n) {
+            const float4 *src = reinterpret_cast<const float4 *>(a.data + (uint64_t) p * dim);
+            for (uint32_t c = 0; c < (dim >> 2); c++) {
+                const float4 v = __ldg(src + c);
+                pnr += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+        const float cm = __ldg(norms + a.C);
+        const float err = 0.0078125f * sqrtf(pnr) * sqrtf(cm) + 1.52587890625e-5f * (pnr + cm);
+        float m1 = FLT_MAX, m2 = FLT_MAX, thr = 0.0f;
+        bool need_second = false;
+        for (uint32_t t = 0; t < total; t++) {
+            const uint32_t s = t & 1u, use = t >> 1;
+            bool ok = !*failed && mbar_wait(mma_done + s, use & 1u, failed);
+            ok = __all_sync(kFullMask, ok);   // tcgen05.ld is a warp-wide instruction
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t c0 = (t % tiles) * kUmmaRows + half * 64u;
+                const bool second = t >= tiles;
+                for (uint32_t cb = 0; cb < 64; cb += 32) {
+                    uint32_t r[32];
+                    tmem_load32(tmem_base + ((quad * 32u) << 16) + s * kUmmaRows + half * 64u + cb, r);
+#pragma unroll
+                    for (int j4 = 0; j4 < 32; j4 += 4) {
+                        const uint32_t cid = c0 + cb + j4;
+                        float4 cn4 = make_float4(0.f, 0.f, 0.f, 0.f);   // norms[] has C + 1 entries; guard the tail
+                        if (cid + 3 < a.C) cn4 = __ldg(reinterpret_cast<const float4 *>(norms + cid));
+                        else {
+                            if (cid < a.C) cn4.x = __ldg(norms + cid);
+                            if (cid + 1 < a.C) cn4.y = __ldg(norms + cid + 1);
+                            if (cid + 2 < a.C) cn4.z = __ldg(norms + cid + 2);
+                        }
+                        const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const float d = (cid + j < a.C) ? (pnr + cn[j]) - 2.0f * __uint_as_float(r[j4 + j]) : FLT_MAX;
+                            if (!second) {
+                                min2_add(m1, m2, d);
+                            } else if (d <= thr) {
+                                const uint32_t k = atomicAdd(&cnt[row], 1u);
+                                if (k < (uint32_t) kCand) cand[row * kCand + k] = cid + j;
+                            }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_free + s);
+            }
+            if (t + 1 == tiles) {
+                // both column halves of a row meet here
+                rowmin[(half * kUmmaRows + row) * 2] = m1;
+                rowmin[(half * kUmmaRows + row) * 2 + 1] = m2;
+                named_barrier_sync(1, kEpilogueWarps * 32);
+                const float o1 = rowmin[((half ^ 1u) * kUmmaRows + row) * 2], o2 = rowmin[((half ^ 1u) * kUmmaRows + row) * 2 + 1];
+                m2 = fminf(fminf(m2, o2), fmaxf(m1, o1));
+                m1 = fminf(m1, o1);
+                const bool boundary_test = a.is_boundary && a.boundary_factor >= 0.0f && a.C > 1;
+                if (boundary_test) {
+                    const float lo2 = fmaxf(m2 - err, 0.0f), hi1 = m1 + err;
+                    const float f = a.metric == kEuclidean ? a.boundary_factor * a.boundary_factor : a.boundary_factor;
+                    need_second = !(lo2 > f * hi1 * 1.001f);
+                }
+                const float basev = need_second ? m2 : m1;
+                thr = basev + 2.0f * err + 6.103515625e-5f * fabsf(basev);
+            }
+        }
+        named_barrier_sync(1, kEpilogueWarps * 32);
+        if (half == 0) {
+            const uint32_t n_c = *failed ? (uint32_t) kCand + 1 : cnt[row];
+            cnt[row] = (n_c > (uint32_t) kCand ? (uint32_t) kCand + 1 : n_c) | (need_second ? 0u : 0x80000000u);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == kEpilogueWarps) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        return;
+    }
+
+    // ---- exact re-rank in the reference's team order (point rows re-read from global memory) ----
+    const uint32_t team = lane >> 3;
+    for (uint32_t row = warp; row < kUmmaRows; row += kEpilogueWarps) {
+        const uint32_t p = p0 + row;
+        if (p >= a.n) continue;
+        const uint32_t n_c = cnt[row] & 0x7fffffffu;
+        const bool far_second = (cnt[row] >> 31) != 0;
+        ExactNear st{FLT_MAX, FLT_MAX, kInvalid, 0u};
+        const bool overflow = n_c > (uint32_t) kCand;
+        if (!overflow) {
+            for (uint32_t g = 0; g < n_c; g += 4) {
+                const uint32_t j = g + team;
+                const bool active = j < n_c;
+                const uint32_t cid = active ? cand[row * kCand + j] : 0u;
+                const float part = team_partial(a.data + (uint64_t) p * dim, a.centroids + (uint64_t) cid * dim, dim, active);
+                const float sum = team_fold(part);
+                if (active) exact_add(st, finish_metric(sum, a.metric), cid);
+            }
+#pragma unroll
+            for (int off = 16; off >= 8; off >>= 1) {
+                const float d0 = __shfl_xor_sync(kFullMask, st.d0, off), d1 = __shfl_xor_sync(kFullMask, st.d1, off);
+                const uint32_t id = __shfl_xor_sync(kFullMask, st.id, off), ties = __shfl_xor_sync(kFullMask, st.ties, off);
+                exact_merge(st, d0, d1, id, ties);
+            }
+        }
+        if (lane == 0) {
+            const bool unique = !overflow && st.ties == 1;
+            a.nearest[p] = unique ? st.id : kInvalid;
+            if (a.is_boundary && unique)  // partition_kernel.cuh:58-60
+                a.is_boundary[p] = (!far_second && a.boundary_factor >= 0.0f && a.C > 1 && st.d1 / st.d0 <= a.boundary_factor) ? 0u : kInvalid;
+        }
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// rows x dim fp32 row-major; boxes of 32 floats x 128 rows, 128-byte swizzle, zero fill past the last row
+bool make_row_map(CUtensorMap *tm, const float *ptr, uint32_t rows, uint32_t dim) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {dim, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t) dim * 4};
+    const cuuint32_t box[2] = {32, kUmmaRows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Returns cudaErrorNotSupported when the tensor maps cannot be made (the caller then takes the cp.async kernel).
+cudaError_t launch_umma_tma(const AssignArgs &a, cudaStream_t stream) {
+    if ((reinterpret_cast<uintptr_t>(a.data) & 15u) || (reinterpret_cast<uintptr_t>(a.centroids) & 15u)) return cudaErrorNotSupported;
+    CUtensorMap tm_points, tm_centroids;
+    if (!make_row_map(&tm_points, a.data, a.n, a.dim) || !make_row_map(&tm_centroids, a.centroids, a.C, a.dim)) return cudaErrorNotSupported;
+    const size_t smem_bytes = 1024 + (size_t) 3 * kUmmaRows * a.dim * 4 + 4 * kUmmaRows * 4 + kUmmaRows * kCand * 4 + kUmmaRows * 4 + 7 * 8 + 16;
+    cudaError_t e = cudaFuncSetAttribute(assign_umma_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
+    if (e != cudaSuccess) return e;
+    assign_umma_tma_kernel<<<(a.n + kUmmaRows - 1) / kUmmaRows, kTmaThreads, smem_bytes, stream>>>(a, tm_points, tm_centroids);
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 bool assign_tc_eligible(const AssignArgs &a) {
@@ -335,6 +628,11 @@ cudaError_t launch_assign_tc(const AssignArgs &a, cudaStream_t stream) {
     cudaError_t e = cudaMemsetAsync(a.tc_norms + a.C, 0, sizeof(float), stream);
     if (e != cudaSuccess) return e;
     centroid_norms_kernel<<<(a.C + 7) / 8, 256, 0, stream>>>(a.centroids, a.C, a.dim, a.tc_norms);
+    static const bool no_tma = [] { const char *v = std::getenv("GLIDE_B200_NO_TMA"); return v && v[0] == '1'; }();
+    if ((a.dim & 31u) == 0 && !no_tma) {
+        e = launch_umma_tma(a, stream);
+        if (e != cudaErrorNotSupported) return e;
+    }
     return launch_umma(a, stream);
 }
 
