@@ -26,7 +26,7 @@ struct glide_ctx {
     size_t ws_bytes = 0;
     unsigned long long *counters = nullptr;  // 4 x u64 on the device
     uint32_t *ticket = nullptr;              // one word: the search kernel's query counter
-    float *tc_norms = nullptr;               // 4096 + 1 floats: centroid norms for the assignment's tensor-core prefilter
+    float *tc_norms = nullptr;               // centroid norms for the assignment's tensor-core prefilter (up to 4096 centroids)
     bool counters_on = false;
 };
 
@@ -144,7 +144,7 @@ int glide_ctx_create(int device, glide_ctx **out) {
         cudaEventCreate(&ctx->ev_start) != cudaSuccess || cudaEventCreate(&ctx->ev_stop) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_mid) != cudaSuccess ||
         cudaMalloc(&ctx->counters, 4 * sizeof(unsigned long long)) != cudaSuccess ||
-        cudaMalloc(&ctx->tc_norms, (4096 + 1) * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&ctx->tc_norms, (4096 + 128 + 1) * sizeof(float)) != cudaSuccess ||
         cudaMalloc(&ctx->ticket, sizeof(uint32_t)) != cudaSuccess) {
         delete ctx;
         return GLIDE_ERR_CUDA;

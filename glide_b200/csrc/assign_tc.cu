@@ -396,7 +396,11 @@ __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const Assi
     const uint32_t tile_bytes = kblocks * sub_bytes;
     uint8_t *As = base;
     uint8_t *Bs = As + tile_bytes;                            // two stages
-    float *rowmin = reinterpret_cast<float *>(Bs + 2 * tile_bytes);       // 2 halves x 128 rows x 2
+    // Norms of the centroid tiles, FOUR buffers (tile t uses t & 3): the copy for tile t+2 is issued as
+    // soon as the MMAs of tile t are done, while the epilogue may still be reading tile t's norms; the
+    // copy for tile t+4 is only issued after the MMAs of tile t+2, which waited for that epilogue.
+    float *cn_s = reinterpret_cast<float *>(Bs + 2 * tile_bytes);
+    float *rowmin = cn_s + 4 * kUmmaRows;                                 // 2 halves x 128 rows x 2
     uint32_t *cand = reinterpret_cast<uint32_t *>(rowmin + 4 * kUmmaRows);  // 128 x kCand
     uint32_t *cnt = cand + kUmmaRows * kCand;                 // 128 counters; later bit 31: far second
     uint64_t *bars = reinterpret_cast<uint64_t *>(cnt + kUmmaRows);       // a_full, b_full[2], mma_done[2], tmem_free[2]
@@ -429,13 +433,20 @@ __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const Assi
     if (warp == kEpilogueWarps) {
         // ================= producer: TMA copies and MMA issue, one thread =================
         if (lane == 0) {
-            auto load_tile = [&](uint8_t *dst, const CUtensorMap *tm, uint32_t row0, uint64_t *bar) {
-                mbar_expect_tx(bar, tile_bytes);
+            // a centroid tile travels with the 128 norms of its rows (a plain bulk copy; the norms
+            // array is padded to a whole tile)
+            auto load_tile = [&](uint8_t *dst, const CUtensorMap *tm, uint32_t row0, uint64_t *bar, float *norm_dst) {
+                mbar_expect_tx(bar, tile_bytes + (norm_dst ? kUmmaRows * 4u : 0u));
                 for (uint32_t kb = 0; kb < kblocks; kb++) tma_load_2d(dst + kb * sub_bytes, tm, kb * 32u, row0, bar);
+                if (norm_dst)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     smem_u32(norm_dst)),
+                                 "l"(reinterpret_cast<uint64_t>(norms + row0)), "r"(kUmmaRows * 4u), "r"(smem_u32(bar))
+                                 : "memory");
             };
-            load_tile(As, &tm_points, p0, a_full);
-            load_tile(Bs, &tm_centroids, 0, b_full + 0);
-            if (total > 1) load_tile(Bs + tile_bytes, &tm_centroids, (1u % tiles) * kUmmaRows, b_full + 1);
+            load_tile(As, &tm_points, p0, a_full, nullptr);
+            load_tile(Bs, &tm_centroids, 0, b_full + 0, cn_s);
+            if (total > 1) load_tile(Bs + tile_bytes, &tm_centroids, (1u % tiles) * kUmmaRows, b_full + 1, cn_s + kUmmaRows);
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kUmmaRows >> 3) << 17) | ((kUmmaRows >> 4) << 24);
             const uint32_t a_addr = smem_u32(As), b_addr = smem_u32(Bs);
             bool ok = mbar_wait(a_full, 0, failed);
@@ -454,7 +465,7 @@ __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const Assi
                              : "memory");
                 if (t + 2 < total) {   // stage s is free once these MMAs have read it
                     ok = mbar_wait(mma_done + s, use & 1u, failed);
-                    if (ok) load_tile(Bs + s * tile_bytes, &tm_centroids, ((t + 2) % tiles) * kUmmaRows, b_full + s);
+                    if (ok) load_tile(Bs + s * tile_bytes, &tm_centroids, ((t + 2) % tiles) * kUmmaRows, b_full + s, cn_s + ((t + 2) & 3u) * kUmmaRows);
                 }
             }
         }
@@ -489,13 +500,7 @@ __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const Assi
 #pragma unroll
                     for (int j4 = 0; j4 < 32; j4 += 4) {
                         const uint32_t cid = c0 + cb + j4;
-                        float4 cn4 = make_float4(0.f, 0.f, 0.f, 0.f);   // norms[] has C + 1 entries; guard the tail
-                        if (cid + 3 < a.C) cn4 = __ldg(reinterpret_cast<const float4 *>(norms + cid));
-                        else {
-                            if (cid < a.C) cn4.x = __ldg(norms + cid);
-                            if (cid + 1 < a.C) cn4.y = __ldg(norms + cid + 1);
-                            if (cid + 2 < a.C) cn4.z = __ldg(norms + cid + 2);
-                        }
+                        const float4 cn4 = *reinterpret_cast<const float4 *>(cn_s + (t & 3u) * kUmmaRows + half * 64u + cb + j4);  // broadcast
                         const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
@@ -611,7 +616,7 @@ cudaError_t launch_umma_tma(const AssignArgs &a, cudaStream_t stream) {
     if ((reinterpret_cast<uintptr_t>(a.data) & 15u) || (reinterpret_cast<uintptr_t>(a.centroids) & 15u)) return cudaErrorNotSupported;
     CUtensorMap tm_points, tm_centroids;
     if (!make_row_map(&tm_points, a.data, a.n, a.dim) || !make_row_map(&tm_centroids, a.centroids, a.C, a.dim)) return cudaErrorNotSupported;
-    const size_t smem_bytes = 1024 + (size_t) 3 * kUmmaRows * a.dim * 4 + 4 * kUmmaRows * 4 + kUmmaRows * kCand * 4 + kUmmaRows * 4 + 7 * 8 + 16;
+    const size_t smem_bytes = 1024 + (size_t) 3 * kUmmaRows * a.dim * 4 + 8 * kUmmaRows * 4 + kUmmaRows * kCand * 4 + kUmmaRows * 4 + 7 * 8 + 16;
     cudaError_t e = cudaFuncSetAttribute(assign_umma_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
     if (e != cudaSuccess) return e;
     assign_umma_tma_kernel<<<(a.n + kUmmaRows - 1) / kUmmaRows, kTmaThreads, smem_bytes, stream>>>(a, tm_points, tm_centroids);

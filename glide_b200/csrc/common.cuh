@@ -209,43 +209,55 @@ __device__ __forceinline__ void warp_rows(const float *q_smem, const float *__re
 // receives its distance; other lanes get FLT_MAX. The ids travel by shuffle, the rows are read by
 // the whole warp exactly as in warp_rows (same chunk ownership, same fold), so the distances are
 // bit-identical to the shared-memory path; nothing is staged in shared memory.
-__device__ __forceinline__ float score_lanes(const float *q_smem, const float *__restrict__ data, uint32_t dim,
-                                             int metric, uint32_t mask, uint32_t cv) {
+// Fast path of score_lanes: dim % 4 == 0 and dim <= 128, the query chunk of this lane in `q`
+// (zero when the lane owns no chunk).
+__device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const float *__restrict__ data, uint32_t dim,
+                                                int metric, uint32_t mask, uint32_t cv) {
     const uint32_t lane = lane_id();
     float mine = FLT_MAX;
     uint32_t m = mask;
-    if ((dim & 3u) == 0 && dim <= 128) {
-        const bool own = lane < (dim >> 2);
-        const float4 q = own ? reinterpret_cast<const float4 *>(q_smem)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
-        const uint32_t my_rank = __popc(mask & ((1u << lane) - 1));
-        const bool valid = ((mask >> lane) & 1u) != 0;
-        for (uint32_t g = 0; m != 0; g++) {
-            float4 v[8];
+    const uint32_t my_rank = __popc(mask & ((1u << lane) - 1));
+    const bool valid = ((mask >> lane) & 1u) != 0;
+    for (uint32_t g = 0; m != 0; g++) {
+        float4 v[8];
 #pragma unroll
-            for (int r = 0; r < 8; r++) {
-                const bool act = m != 0;
-                const uint32_t src = act ? (uint32_t) __ffs(m) - 1u : 0u;
-                m &= m - 1u;
-                const uint32_t id = __shfl_sync(kFullMask, cv, src);
-                v[r] = (act && own) ? __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * dim) + lane) : q;
-            }
-            float p[8];
-#pragma unroll
-            for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
-            const float sum = fold_rows<8>(p);  // row r of the batch sits in lanes 4r .. 4r+3
-            const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
-            mine = (valid && (my_rank >> 3) == g) ? got : mine;
-        }
-        if (metric == kEuclidean) mine = valid ? sqrtf(mine) : mine;  // once per lane, no branch per batch
-    } else {
-        while (m != 0) {
-            const uint32_t src = (uint32_t) __ffs(m) - 1u;
+        for (int r = 0; r < 8; r++) {
+            const bool act = m != 0;
+            const uint32_t src = act ? (uint32_t) __ffs(m) - 1u : 0u;
             m &= m - 1u;
             const uint32_t id = __shfl_sync(kFullMask, cv, src);
-            float p[1] = {lane_row_partial(q_smem, data + (uint64_t) id * dim, dim)};
-            const float sum = fold_rows<1>(p);
-            if (lane == src) mine = metric == kEuclidean ? sqrtf(sum) : sum;
+            v[r] = (act && own) ? __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * dim) + lane) : q;
         }
+        float p[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
+        const float sum = fold_rows<8>(p);  // row r of the batch sits in lanes 4r .. 4r+3
+        const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
+        mine = (valid && (my_rank >> 3) == g) ? got : mine;
+    }
+    if (metric == kEuclidean) mine = valid ? sqrtf(mine) : mine;  // once per lane, no branch per batch
+    return mine;
+}
+
+__device__ __forceinline__ bool rows_fit_lanes(uint32_t dim) { return (dim & 3u) == 0 && dim <= 128; }
+
+__device__ __forceinline__ float score_lanes(const float *q_smem, const float *__restrict__ data, uint32_t dim,
+                                             int metric, uint32_t mask, uint32_t cv) {
+    const uint32_t lane = lane_id();
+    if (rows_fit_lanes(dim)) {
+        const bool own = lane < (dim >> 2);
+        const float4 q = own ? reinterpret_cast<const float4 *>(q_smem)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+        return score_lanes_q4(q, own, data, dim, metric, mask, cv);
+    }
+    float mine = FLT_MAX;
+    uint32_t m = mask;
+    while (m != 0) {
+        const uint32_t src = (uint32_t) __ffs(m) - 1u;
+        m &= m - 1u;
+        const uint32_t id = __shfl_sync(kFullMask, cv, src);
+        float p[1] = {lane_row_partial(q_smem, data + (uint64_t) id * dim, dim)};
+        const float sum = fold_rows<1>(p);
+        if (lane == src) mine = metric == kEuclidean ? sqrtf(sum) : sum;
     }
     return mine;
 }

@@ -22,159 +22,105 @@ struct BuildDev {
     uint32_t max_degree;  // round_up32(out_degree)
 };
 
-// Extra strip layout (words): pool_id[max_beam] pool_dist[max_beam] flags[max_beam]
-// picks[max_degree] row[max_degree] bits[max_degree/32].
+// Extra strip layout (words): picks[max_degree] row[max_degree] bits[max_degree/32].
 struct PruneStrip {
-    uint32_t *pool_id;
-    float *pool_dist;
-    uint32_t *flags;
     uint32_t *picks;
     uint32_t *row;
     uint32_t *bits;
 };
 
-__host__ __device__ inline uint32_t prune_strip_words(uint32_t max_beam, uint32_t max_degree) {
-    return 3 * max_beam + 2 * max_degree + max_degree / 32;
-}
+__host__ __device__ inline uint32_t prune_strip_words(uint32_t max_degree) { return 2 * max_degree + max_degree / 32; }
 
-__device__ __forceinline__ PruneStrip make_prune_strip(uint32_t *extra, uint32_t max_beam, uint32_t max_degree) {
+__device__ __forceinline__ PruneStrip make_prune_strip(uint32_t *extra, uint32_t max_degree) {
     PruneStrip ps;
-    ps.pool_id = extra;
-    ps.pool_dist = reinterpret_cast<float *>(extra + max_beam);
-    ps.flags = extra + 2 * max_beam;
-    ps.picks = extra + 3 * max_beam;
+    ps.picks = extra;
     ps.row = ps.picks + max_degree;
     ps.bits = ps.row + max_degree;
     return ps;
 }
 
-// Spill the beam into the pool, flags cleared (graph_kernel.cuh:65-67), dropping
-// unfilled slots: the reference would dereference them as data rows
-// (graph_kernel.cuh:92,104); with a full beam this is the identity. Returns pool size.
+// ---------------------------------------------------------------------------
+// Register-resident pruning: sync_prune (graph_kernel.cuh:70-143) and its refine variant
+// (:455-578) on the beam as it sits in registers (entry j = NB*lane + i), without a pool in
+// shared memory. The reference compacts the pool after every pick; here an entry is a bit in
+// alive[i] (bit l = lane l, register i), "first pool entry" is the alive entry with the smallest
+// j, and dropping an entry clears its bit, which visits the same centres in the same order and
+// tests the same pairs. build: the centre is pool[0], every other entry e is dropped when
+// alpha * d(centre, e) < d(point, e). refine: the centre is the first entry that is neither the
+// point nor already in its row, entries before it are dropped, and the centre itself goes through
+// the test with the others (d = 0, so it stays only at distance 0 from the point).
+// picks[0..limit) receives pool-relative ids, unused slots kInvalid. Returns rows read;
+// *pool_size = entries that were filled.
+// ---------------------------------------------------------------------------
 template<int NB>
-__device__ __forceinline__ uint32_t spill_pool(const float (&bk)[NB], const uint32_t (&bv)[NB], uint32_t beam,
-                                               const PruneStrip &ps) {
+__device__ __forceinline__ uint32_t prune_lanes(const float (&bk)[NB], const uint32_t (&bv)[NB], uint32_t beam,
+                                                const PruneStrip &ps, float *q_smem, const float *__restrict__ data,
+                                                uint32_t dim, uint32_t degree, uint32_t max_degree, uint32_t limit,
+                                                float alpha, int metric, bool refine, uint32_t point_id,
+                                                uint32_t *pool_size) {
     const uint32_t lane = lane_id();
+    for (uint32_t i = lane; i < max_degree; i += 32) ps.picks[i] = kInvalid;
+    uint32_t id[NB], alive[NB], eligible[NB];
+    uint32_t P = 0;
 #pragma unroll
     for (int i = 0; i < NB; i++) {
         const uint32_t j = NB * lane + i;
-        if (j < beam) {
-            ps.pool_id[j] = bv[i] & kClean;
-            ps.pool_dist[j] = bk[i];
+        id[i] = bv[i] & kClean;
+        const bool filled = (j < beam) && (id[i] != kPadClean);
+        alive[i] = __ballot_sync(kFullMask, filled);
+        P += __popc(alive[i]);
+        bool ok = filled;
+        if (refine && filled) {  // select_point (:455-492): not the point, not in its row
+            ok = id[i] != point_id;
+            for (uint32_t r = 0; r < degree && ok; r++) ok = ps.row[r] != id[i];
         }
+        eligible[i] = __ballot_sync(kFullMask, ok);
     }
+    *pool_size = P;
     __syncwarp();
-    uint32_t next = 0;
-    for (uint32_t base = 0; base < beam; base += 32) {
-        const uint32_t i = base + lane;
-        const uint32_t id = (i < beam) ? ps.pool_id[i] : kPadClean;
-        const float dist = (i < beam) ? ps.pool_dist[i] : FLT_MAX;
-        const bool keep = (id != kPadClean);
-        const uint32_t mask = __ballot_sync(kFullMask, keep);
-        __syncwarp();
-        if (keep) {
-            const uint32_t pos = next + __popc(mask & ((1u << lane) - 1));
-            ps.pool_id[pos] = id;
-            ps.pool_dist[pos] = dist;
-        }
-        next += __popc(mask);
-        __syncwarp();
-    }
-    return next;
-}
-
-// For pool entries [from, P): flags[i] = !(alpha * d(center, pool[i]) < pool_dist[i]),
-// the occlusion test of graph_kernel.cuh:103-114. The centre row is staged in `q`.
-__device__ __forceinline__ uint32_t occlusion_flags(const PruneStrip &ps, uint32_t from, uint32_t P, float *q,
-                                                    const float *__restrict__ data, uint32_t center, uint32_t dim,
-                                                    float alpha, int metric) {
-    load_query(q, data + (uint64_t) center * dim, dim);
-    uint32_t rows = 0;
-    warp_rows(q, data, dim, metric, P > from ? P - from : 0,
-              [&](uint32_t i) { return ps.pool_id[from + i]; },
-              [&](uint32_t i, float d) { ps.flags[from + i] = (alpha * d < ps.pool_dist[from + i]) ? 0u : 1u; });
-    rows += (P > from) ? (P - from) : 0;
-    __syncwarp();
-    return rows;
-}
-
-// Stable compaction of pool entries [from, P) whose flag is set; returns new size.
-__device__ __forceinline__ uint32_t compact_pool(const PruneStrip &ps, uint32_t from, uint32_t P) {
-    const uint32_t lane = lane_id();
-    uint32_t next = 0;
-    for (uint32_t base = from & ~31u; base < P; base += 32) {
-        const uint32_t i = base + lane;
-        const bool keep = (i >= from) && (i < P) && (ps.flags[i] != 0);
-        const uint32_t id = keep ? ps.pool_id[i] : 0;
-        const float dist = keep ? ps.pool_dist[i] : 0.0f;
-        const uint32_t mask = __ballot_sync(kFullMask, keep);
-        __syncwarp();
-        if (keep) {
-            const uint32_t pos = next + __popc(mask & ((1u << lane) - 1));
-            ps.pool_id[pos] = id;
-            ps.pool_dist[pos] = dist;
-        }
-        next += __popc(mask);
-        __syncwarp();
-    }
-    return next;
-}
-
-// graph_kernel.cuh:70-143. picks[0..degree) receives pool-relative ids, unused slots
-// kInvalid. Returns rows read.
-__device__ __forceinline__ uint32_t sync_prune(const PruneStrip &ps, uint32_t P, float *q,
-                                               const float *__restrict__ data, uint32_t dim, uint32_t degree,
-                                               uint32_t max_degree, float alpha, int metric) {
-    const uint32_t lane = lane_id();
-    for (uint32_t i = lane; i < max_degree; i += 32) ps.picks[i] = kInvalid;
-    __syncwarp();
+    const bool fast = rows_fit_lanes(dim);
+    const bool own = lane < (dim >> 2);
     uint32_t nsize = 0, rows = 0;
-    while (nsize < degree && P > 0) {
-        const uint32_t center = ps.pool_id[0];
+    while (nsize < limit) {
+        uint32_t best = kInvalid;
+#pragma unroll
+        for (int i = 0; i < NB; i++) {
+            const uint32_t m = alive[i] & eligible[i];
+            if (m) best = min(best, (uint32_t) NB * ((uint32_t) __ffs(m) - 1u) + (uint32_t) i);
+        }
+        if (best == kInvalid) break;
+        const uint32_t cl = best / NB, ci = best % NB;
+        uint32_t mine = id[0];
+#pragma unroll
+        for (int i = 1; i < NB; i++) mine = ((uint32_t) i == ci) ? id[i] : mine;
+        const uint32_t center = __shfl_sync(kFullMask, mine, cl);
         if (lane == 0) ps.picks[nsize] = center;
         nsize++;
-        if (lane == 0) ps.flags[0] = 0;
-        rows += occlusion_flags(ps, 1, P, q, data, center, dim, alpha, metric);
-        P = compact_pool(ps, 0, P);
-    }
-    __syncwarp();
-    return rows;
-}
-
-// graph_kernel.cuh:455-578: like sync_prune, but the next centre is the first pool
-// entry that is neither the point itself nor already in its row, only entries from
-// that position on are tested, and at most `need` picks are made.
-__device__ __forceinline__ uint32_t sync_prune_refine(const PruneStrip &ps, uint32_t P, float *q,
-                                                      const float *__restrict__ data, uint32_t dim,
-                                                      uint32_t point_id, uint32_t degree, uint32_t max_degree,
-                                                      uint32_t need, float alpha, int metric) {
-    const uint32_t lane = lane_id();
-    for (uint32_t i = lane; i < max_degree; i += 32) ps.picks[i] = kInvalid;
-    __syncwarp();
-    uint32_t nsize = 0, rows = 0;
-    while (nsize < need && P > 0) {
-        // select_point (:455-492)
-        uint32_t pos = kInvalid;
-        for (uint32_t base = 0; base < P && pos == kInvalid; base += 32) {
-            const uint32_t i = base + lane;
-            bool ok = false;
-            if (i < P) {
-                const uint32_t id = ps.pool_id[i];
-                if (id != kInvalid && id != point_id) {
-                    ok = true;
-                    for (uint32_t j = 0; j < degree; j++)
-                        if (ps.row[j] == id) { ok = false; break; }
-                }
+#pragma unroll
+        for (int i = 0; i < NB; i++) {
+            if (refine) {  // entries before the centre leave the pool
+                const uint32_t upto = ((uint32_t) i < ci) ? cl + 1 : cl;   // lanes 0 .. upto-1
+                alive[i] &= ~(upto >= 32 ? 0xffffffffu : ((1u << upto) - 1u));
+            } else if ((uint32_t) i == ci) {
+                alive[i] &= ~(1u << cl);
             }
-            const uint32_t mask = __ballot_sync(kFullMask, ok);
-            if (mask) pos = base + __ffs(mask) - 1;
         }
-        if (pos == kInvalid) break;
-        const uint32_t center = ps.pool_id[pos];
-        if (lane == 0) ps.picks[nsize] = center;
-        nsize++;
-        rows += occlusion_flags(ps, pos, P, q, data, center, dim, alpha, metric);
-        P = compact_pool(ps, pos, P);
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (fast) {
+            if (own) q = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) center * dim) + lane);
+        } else {
+            __syncwarp();
+            load_query(q_smem, data + (uint64_t) center * dim, dim);
+        }
+#pragma unroll
+        for (int i = 0; i < NB; i++) {
+            if (alive[i] == 0) continue;
+            rows += __popc(alive[i]);
+            const float d = fast ? score_lanes_q4(q, own, data, dim, metric, alive[i], id[i])
+                                 : score_lanes(q_smem, data, dim, metric, alive[i], id[i]);
+            const bool occluded = ((alive[i] >> lane) & 1u) && (alpha * d < bk[i]);   // graph_kernel.cuh:103-114
+            alive[i] &= ~__ballot_sync(kFullMask, occluded);
+        }
     }
     __syncwarp();
     return rows;
@@ -255,7 +201,7 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
     const uint32_t point = a.first + t;
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
     WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? 0u : 32u * NC, p.hash_bit);
-    PruneStrip ps = make_prune_strip(s.extra, d.max_beam, d.max_degree);
+    PruneStrip ps = make_prune_strip(s.extra, d.max_degree);
     const uint32_t degree = a.out_degree;
 
     uint32_t rows = 0, prune_rows = 0, iters = 0;
@@ -291,9 +237,10 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
             iters = beam_loop<NB, NC, true>(bk, bv, s, p, point - seg_start, pknn, a.in_degree, pdata, a.dim, a.metric, &rows,
                                             wide);
         }
-        const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
+        uint32_t P;
+        prune_rows = prune_lanes<NB>(bk, bv, p.beam, ps, s.query, pdata, a.dim, degree, d.max_degree, degree, a.alpha, a.metric,
+                                     false, kInvalid, &P);
         short_pool = P < p.beam;
-        prune_rows = sync_prune(ps, P, s.query, pdata, a.dim, degree, d.max_degree, a.alpha, a.metric);
         const uint32_t orig = a.map ? a.map[point] : point;
         uint32_t *out = a.graph_out + (uint64_t) orig * degree;
         if (a.mode == kModeBuild) {  // map_to_graph_sub / map_to_graph (:145-158)
@@ -344,10 +291,10 @@ __global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
             rows += seed_from_row(s, start, exclude, a.graph_in, degree, p.hash_bit, a.data, a.dim, a.metric, &wide);
             iters = beam_loop<NB, NC, true>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows, wide);
         }
-        const uint32_t P = spill_pool<NB>(bk, bv, p.beam, ps);
+        uint32_t P;
+        prune_rows = prune_lanes<NB>(bk, bv, p.beam, ps, s.query, a.data, a.dim, degree, d.max_degree, need, a.alpha, a.metric,
+                                     true, point, &P);
         short_pool = P < p.beam;
-        prune_rows = sync_prune_refine(ps, P, s.query, a.data, a.dim, point, degree, d.max_degree, need, a.alpha,
-                                       a.metric);
         uint32_t pos_num = 0;  // :660-671: holes, front to back
         for (uint32_t base = 0; base < d.max_degree; base += 32) {
             const uint32_t i = base + lane;
@@ -522,7 +469,7 @@ cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
     const uint32_t max_cand = a.in_degree <= 64 ? 64 : (a.in_degree <= 128 ? 128 : 256);
     d.max_beam = max_beam;
     d.max_degree = round_up32(a.out_degree);
-    uint32_t extra = prune_strip_words(max_beam, d.max_degree);
+    uint32_t extra = prune_strip_words(d.max_degree);
     const bool lanes = a.in_degree <= 32;
     d.strip_words = (strip_words_base(a.dim, lanes ? 0 : max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;

@@ -101,7 +101,8 @@ struct AssignArgs {
     int metric;
     uint32_t *nearest;      // n
     uint32_t *is_boundary;  // n: 0 for a boundary point, 0xffffffff otherwise (a slot key); may be nullptr
-    float *tc_norms;        // C + 1 floats of scratch for the tensor-core prefilter; nullptr: exact kernels only
+    float *tc_norms;        // scratch for the tensor-core prefilter: C rounded up to a multiple of 128, plus 1,
+                            // floats (norms, padding, their maximum at [C]); nullptr: exact kernels only
     unsigned long long *fallback_counter;  // += points settled by the warp-per-point kernel; may be nullptr
 };
 cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream);

@@ -553,3 +553,37 @@ def test_assignment_with_tensor_core_prefilter_is_exact(gpu_ctx, kind):
             assert by_fallback < 0.02 * base.shape[0]
         if kind == "duplicates":                    # every nearest centroid has a twin: all points tie
             assert by_fallback == base.shape[0]
+
+
+_ASSIGN_CHILD = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+import oracle
+from glide_b200 import api
+from glide_b200.params import Metric
+import test_gpu_parity as t
+ctx = api.Context(0)
+for kind in ("mixture_1024", "unit96", "int_ties"):
+    base, centroids = t._stress_partition_inputs(kind, np.random.default_rng(5))
+    metric = oracle.COSINE if kind == "unit96" else oracle.EUCLIDEAN
+    want = oracle.define_partition(base, centroids, 1.1, metric)
+    d_seg, seg_start, seg_len = api.define_partition(ctx, torch.from_numpy(base).cuda(), torch.from_numpy(centroids).cuda(),
+                                                     1.1, Metric(metric))
+    assert np.array_equal(api.to_u32(d_seg), want[0]) and np.array_equal(seg_len, want[2]), kind
+print("ok")
+"""
+
+
+@pytest.mark.parametrize("env", ["GLIDE_B200_NO_TMA", "GLIDE_B200_EXACT_ASSIGN"])
+def test_assignment_variants_behind_switches_are_exact_too(env):
+    """The cp.async-staged tensor-core kernel (taken when a tensor map cannot be made or dim % 32 != 0)
+    and the exact fp32 kernels (other dims, no scratch) give the same partitioning; each is selected by
+    an environment switch read when the library first assigns, hence the child process."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = _ASSIGN_CHILD.format(root=root, tests=os.path.join(root, "tests"))
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, **{env: "1"}), capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout + out.stderr
