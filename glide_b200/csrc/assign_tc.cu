@@ -33,6 +33,7 @@ namespace glide {
 namespace {
 
 constexpr int kCand = 16;       // candidates kept per point
+constexpr uint32_t kUmmaRows = 128;   // points per CTA = centroids per tile
 constexpr uint32_t kMaxDim = 128;
 
 __device__ __forceinline__ void min2_add(float &m1, float &m2, float d) {
@@ -51,10 +52,39 @@ __device__ __forceinline__ void exact_add(ExactNear &s, float d, uint32_t id) {
     else if (d < s.d1) { s.d1 = d; }
 }
 
-__device__ __forceinline__ void exact_merge(ExactNear &a, float d0, float d1, uint32_t id, uint32_t ties) {
-    if (d0 < a.d0) { a.d1 = fminf(a.d0, d1); a.d0 = d0; a.id = id; a.ties = ties; }
-    else if (d0 == a.d0) { a.d1 = d0; a.ties += ties; }
-    else { a.d1 = fminf(a.d1, d0); }
+// Exact re-rank of one CTA's 128 points in the reference's team order: an 8-lane team per point
+// (four points per warp at a time), the team walks the point's candidates. count[row]: number of
+// candidates (> kCand: overflow), bit 31: the second nearest is known to be too far for the
+// boundary test. Point rows are re-read from global memory.
+__device__ __forceinline__ void rerank_rows(const AssignArgs &a, uint32_t p0, const uint32_t *count, const uint32_t *cand,
+                                            uint32_t warp, uint32_t warps) {
+    const uint32_t lane = lane_id(), team = lane >> 3;
+    for (uint32_t row0 = warp * 4; row0 < kUmmaRows; row0 += warps * 4) {
+        const uint32_t row = row0 + team;
+        const uint32_t p = p0 + row;
+        const bool live = p < a.n;
+        const uint32_t n_c = live ? (count[row] & 0x7fffffffu) : 0u;
+        const bool far_second = (count[row] >> 31) != 0;
+        const bool overflow = n_c > (uint32_t) kCand;
+        const uint32_t mine = overflow ? 0u : n_c;
+        uint32_t longest = mine;
+#pragma unroll
+        for (int off = 16; off >= 8; off >>= 1) longest = max(longest, __shfl_xor_sync(kFullMask, longest, off));
+        ExactNear st{FLT_MAX, FLT_MAX, kInvalid, 0u};
+        for (uint32_t j = 0; j < longest; j++) {
+            const bool active = j < mine;
+            const uint32_t cid = active ? cand[row * kCand + j] : 0u;
+            const float part = team_partial(a.data + (uint64_t) (live ? p : 0) * a.dim, a.centroids + (uint64_t) cid * a.dim, a.dim, active);
+            const float sum = team_fold(part);
+            if (active) exact_add(st, finish_metric(sum, a.metric), cid);  // every lane of the team holds the same state
+        }
+        if (live && (lane & 7u) == 0) {
+            const bool unique = !overflow && st.ties == 1;
+            a.nearest[p] = unique ? st.id : kInvalid;
+            if (a.is_boundary && unique)  // partition_kernel.cuh:58-60
+                a.is_boundary[p] = (!far_second && a.boundary_factor >= 0.0f && a.C > 1 && st.d1 / st.d0 <= a.boundary_factor) ? 0u : kInvalid;
+        }
+    }
 }
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src, bool valid) {
@@ -100,7 +130,6 @@ __global__ void centroid_norms_kernel(const float *__restrict__ centroids, uint3
 // resulting bound. Every wait on an mbarrier is bounded; a CTA whose wait runs out flags all of
 // its points for the exact kernel instead of trusting the accumulator.
 // ---------------------------------------------------------------------------
-constexpr uint32_t kUmmaRows = 128;   // points per CTA = centroids per tile
 constexpr uint32_t kTmemCols = 256;   // two accumulator buffers of 128 columns
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -285,38 +314,7 @@ __global__ void __launch_bounds__(128) assign_umma_kernel(const AssignArgs a) {
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 
-    // ---- exact re-rank in the reference's team order (point rows re-read from global memory) ----
-    const uint32_t team = lane >> 3;
-    for (uint32_t row = warp; row < kUmmaRows; row += 4) {
-        const uint32_t p = p0 + row;
-        if (p >= a.n) continue;
-        const uint32_t cnt = cnt_s[row] & 0x7fffffffu;
-        const bool far_second = (cnt_s[row] >> 31) != 0;
-        ExactNear st{FLT_MAX, FLT_MAX, kInvalid, 0u};
-        const bool overflow = cnt > (uint32_t) kCand;
-        if (!overflow) {
-            for (uint32_t g = 0; g < cnt; g += 4) {
-                const uint32_t j = g + team;
-                const bool active = j < cnt;
-                const uint32_t cid = active ? cand[row * kCand + j] : 0u;
-                const float part = team_partial(a.data + (uint64_t) p * dim, a.centroids + (uint64_t) cid * dim, dim, active);
-                const float sum = team_fold(part);
-                if (active) exact_add(st, finish_metric(sum, a.metric), cid);
-            }
-#pragma unroll
-            for (int off = 16; off >= 8; off >>= 1) {
-                const float d0 = __shfl_xor_sync(kFullMask, st.d0, off), d1 = __shfl_xor_sync(kFullMask, st.d1, off);
-                const uint32_t id = __shfl_xor_sync(kFullMask, st.id, off), ties = __shfl_xor_sync(kFullMask, st.ties, off);
-                exact_merge(st, d0, d1, id, ties);
-            }
-        }
-        if (lane == 0) {
-            const bool unique = !overflow && st.ties == 1;
-            a.nearest[p] = unique ? st.id : kInvalid;
-            if (a.is_boundary && unique)  // partition_kernel.cuh:58-60
-                a.is_boundary[p] = (!far_second && a.boundary_factor >= 0.0f && a.C > 1 && st.d1 / st.d0 <= a.boundary_factor) ? 0u : kInvalid;
-        }
-    }
+    rerank_rows(a, p0, cnt_s, cand, warp, 4);
 }
 
 cudaError_t launch_umma(const AssignArgs &a, cudaStream_t stream) {
@@ -549,38 +547,7 @@ __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const Assi
         return;
     }
 
-    // ---- exact re-rank in the reference's team order (point rows re-read from global memory) ----
-    const uint32_t team = lane >> 3;
-    for (uint32_t row = warp; row < kUmmaRows; row += kEpilogueWarps) {
-        const uint32_t p = p0 + row;
-        if (p >= a.n) continue;
-        const uint32_t n_c = cnt[row] & 0x7fffffffu;
-        const bool far_second = (cnt[row] >> 31) != 0;
-        ExactNear st{FLT_MAX, FLT_MAX, kInvalid, 0u};
-        const bool overflow = n_c > (uint32_t) kCand;
-        if (!overflow) {
-            for (uint32_t g = 0; g < n_c; g += 4) {
-                const uint32_t j = g + team;
-                const bool active = j < n_c;
-                const uint32_t cid = active ? cand[row * kCand + j] : 0u;
-                const float part = team_partial(a.data + (uint64_t) p * dim, a.centroids + (uint64_t) cid * dim, dim, active);
-                const float sum = team_fold(part);
-                if (active) exact_add(st, finish_metric(sum, a.metric), cid);
-            }
-#pragma unroll
-            for (int off = 16; off >= 8; off >>= 1) {
-                const float d0 = __shfl_xor_sync(kFullMask, st.d0, off), d1 = __shfl_xor_sync(kFullMask, st.d1, off);
-                const uint32_t id = __shfl_xor_sync(kFullMask, st.id, off), ties = __shfl_xor_sync(kFullMask, st.ties, off);
-                exact_merge(st, d0, d1, id, ties);
-            }
-        }
-        if (lane == 0) {
-            const bool unique = !overflow && st.ties == 1;
-            a.nearest[p] = unique ? st.id : kInvalid;
-            if (a.is_boundary && unique)  // partition_kernel.cuh:58-60
-                a.is_boundary[p] = (!far_second && a.boundary_factor >= 0.0f && a.C > 1 && st.d1 / st.d0 <= a.boundary_factor) ? 0u : kInvalid;
-        }
-    }
+    rerank_rows(a, p0, cnt, cand, warp, kEpilogueWarps);
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
