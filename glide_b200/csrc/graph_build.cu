@@ -191,7 +191,7 @@ __device__ __forceinline__ void boundary_merge(const PruneStrip &ps, const uint3
 // LANES: adjacency rows searched have at most 32 entries; candidates stay in registers
 // (beam_loop_lanes) and the strip holds no candidate arrays.
 template<int NB, int NC, bool LANES>
-__global__ void __launch_bounds__(256, 3) build_kernel(const BuildDev d) {
+__global__ void __launch_bounds__(256, NB == 2 ? 4 : (NB == 4 ? 3 : 2)) build_kernel(const BuildDev d) {
     extern __shared__ __align__(16) uint32_t smem[];
     const BuildArgs &a = d.a;
     const uint32_t warps_per_cta = blockDim.x >> 5;
@@ -485,6 +485,18 @@ cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
         return launch_build_t<16, 2, true>(d, warps, bytes, stream);
     }
     GLIDE_DISPATCH_NB_NC(launch_build_t, nb, nc, d, warps, strip_bytes * warps, stream);
+}
+
+// First launches pay for loading the kernel and for growing the device's local-memory
+// reservation (tens of milliseconds); a context pays them once, at creation, with launches that
+// find no work (count = 0: every warp returns at once).
+cudaError_t preload_build_kernels(cudaStream_t stream) {
+    BuildDev d{};
+    build_kernel<2, 2, true><<<1, 32, 0, stream>>>(d);
+    build_kernel<4, 2, true><<<1, 32, 0, stream>>>(d);
+    build_kernel<2, 2, false><<<1, 32, 0, stream>>>(d);
+    build_kernel<4, 2, false><<<1, 32, 0, stream>>>(d);
+    return cudaGetLastError();
 }
 
 }  // namespace glide

@@ -37,6 +37,7 @@ struct SearchArgs {
                                  // nullptr: query q runs on warp q of the grid
 };
 cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream);
+cudaError_t preload_search_kernels(cudaStream_t stream);
 
 struct SelectSegmentArgs {
     const float *queries;
@@ -76,6 +77,7 @@ struct BuildArgs {
     unsigned long long *counters;  // [0] rows read in search, [1] expansions, [2] rows read in pruning
 };
 cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream);
+cudaError_t preload_build_kernels(cudaStream_t stream);
 
 struct ReverseArgs {
     uint32_t *graph;   // num x degree, updated in place

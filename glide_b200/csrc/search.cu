@@ -238,6 +238,16 @@ cudaError_t launch_search_t(const SearchDev &d, uint32_t warps_per_cta, size_t s
 
 }  // namespace
 
+// See preload_build_kernels: launches without work (Q = 0, no ticket) that load the common instances.
+cudaError_t preload_search_kernels(cudaStream_t stream) {
+    SearchDev d{};
+    search_kernel_32<2, true><<<1, 32, 0, stream>>>(d);
+    search_kernel<2, 2, true><<<1, 32, 0, stream>>>(d);
+    search_kernel<4, 2, true><<<1, 32, 0, stream>>>(d);
+    search_kernel<2, 2, false><<<1, 32, 0, stream>>>(d);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
     if (a.Q == 0) return cudaSuccess;
     SearchDev d;
