@@ -147,6 +147,12 @@ def cpu_bruteforce_qps(base, queries, seconds_target, metric):
     t0 = time.perf_counter()
     oracle.bruteforce_knn(base, queries[:sample], TOP_K, metric, threads=cores, want_dists=False)
     dt = time.perf_counter() - t0
+    if dt < 0.66 * seconds_target and sample < len(queries):
+        # the small probe underestimates a large batch's throughput: size the sample once more from this run
+        sample = int(min(len(queries), sample * seconds_target / dt))
+        t0 = time.perf_counter()
+        oracle.bruteforce_knn(base, queries[:sample], TOP_K, metric, threads=cores, want_dists=False)
+        dt = time.perf_counter() - t0
     return sample / dt, cores, sample, dt
 
 
