@@ -218,15 +218,30 @@ __device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const 
     uint32_t m = mask;
     const uint32_t my_rank = __popc(mask & ((1u << lane) - 1));
     const bool valid = ((mask >> lane) & 1u) != 0;
+    const bool all_own = dim == 128;   // every lane owns a chunk: loads need no predicate
     for (uint32_t g = 0; m != 0; g++) {
         float4 v[8];
+        if (all_own) {
+            // slots past the last row of a ragged batch re-read row 0 (their sums are never delivered):
+            // cheaper than predicating eight 128-bit loads and pre-setting their registers
 #pragma unroll
-        for (int r = 0; r < 8; r++) {
-            const bool act = m != 0;
-            const uint32_t src = act ? (uint32_t) __ffs(m) - 1u : 0u;
-            m &= m - 1u;
-            const uint32_t id = __shfl_sync(kFullMask, cv, src);
-            v[r] = (act && own) ? __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * dim) + lane) : q;
+            for (int r = 0; r < 8; r++) {
+                const bool act = m != 0;
+                const uint32_t src = act ? (uint32_t) __ffs(m) - 1u : 0u;
+                m &= m - 1u;
+                const uint32_t got_id = __shfl_sync(kFullMask, cv, src);
+                const uint32_t id = act ? got_id : 0u;
+                v[r] = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * 128u) + lane);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                const bool act = m != 0;
+                const uint32_t src = act ? (uint32_t) __ffs(m) - 1u : 0u;
+                m &= m - 1u;
+                const uint32_t id = __shfl_sync(kFullMask, cv, src);
+                v[r] = (act && own) ? __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * dim) + lane) : q;
+            }
         }
         float p[8];
 #pragma unroll

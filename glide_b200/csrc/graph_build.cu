@@ -191,7 +191,7 @@ __device__ __forceinline__ void boundary_merge(const PruneStrip &ps, const uint3
 // LANES: adjacency rows searched have at most 32 entries; candidates stay in registers
 // (beam_loop_lanes) and the strip holds no candidate arrays.
 template<int NB, int NC, bool LANES>
-__global__ void __launch_bounds__(256, NB == 2 ? 4 : (NB == 4 ? 3 : 2)) build_kernel(const BuildDev d) {
+__global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const BuildDev d) {
     extern __shared__ __align__(16) uint32_t smem[];
     const BuildArgs &a = d.a;
     const uint32_t warps_per_cta = blockDim.x >> 5;
