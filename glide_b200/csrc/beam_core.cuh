@@ -375,23 +375,7 @@ __device__ __forceinline__ uint32_t expand_lanes(const WarpStrip &s, uint32_t pa
     cv = flag ? nb : kInvalid;
     const uint32_t mask = __ballot_sync(kFullMask, flag != 0);
     __syncwarp();
-#ifdef GLIDE_EXP_H2
-    if (flag) {
-        const uint32_t k = __popc(mask & ((1u << lane) - 1));
-        s.work[k] = lane;
-        s.work_id[k] = nb;
-    }
-    s.cand_dist[lane] = FLT_MAX;
-    __syncwarp();
-    warp_rows(s.query, data, dim, metric, __popc(mask),
-              [&](uint32_t i) { return s.work_id[i]; },
-              [&](uint32_t i, float d) { s.cand_dist[s.work[i]] = d; });
-    __syncwarp();
-    ck = s.cand_dist[lane];
-    __syncwarp();
-#else
     ck = score_lanes(s.query, data, dim, metric, mask, cv);
-#endif
     return __popc(mask);
 }
 

@@ -234,18 +234,26 @@ __device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const 
                 v[r] = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * 128u) + lane);
             }
         } else {
+            // lanes without a chunk of their own re-read chunk 0 and contribute nothing
+            const uint32_t my_chunk = own ? lane : 0u;
 #pragma unroll
             for (int r = 0; r < 8; r++) {
                 const bool act = m != 0;
                 const uint32_t src = act ? (uint32_t) __ffs(m) - 1u : 0u;
                 m &= m - 1u;
-                const uint32_t id = __shfl_sync(kFullMask, cv, src);
-                v[r] = (act && own) ? __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * dim) + lane) : q;
+                const uint32_t got_id = __shfl_sync(kFullMask, cv, src);
+                const uint32_t id = act ? got_id : 0u;
+                v[r] = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) id * dim) + my_chunk);
             }
         }
         float p[8];
+        if (all_own) {
 #pragma unroll
-        for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
+            for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
+        } else {
+#pragma unroll
+            for (int r = 0; r < 8; r++) p[r] = own ? sq_acc4(q, v[r], 0.0f) : 0.0f;
+        }
         const float sum = fold_rows<8>(p);  // row r of the batch sits in lanes 4r .. 4r+3
         const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
         mine = (valid && (my_rank >> 3) == g) ? got : mine;
