@@ -131,7 +131,7 @@ def partition_count(spec) -> int:
     clusters, their kNN graphs have one connected component per cluster, and a beam search that
     enters at a partition's start point only reaches that component. (The reference's default of
     10 partitions suits data whose kNN graph is connected.)"""
-    return 1 if spec.n <= 20000 else max(1, min(spec.centres, spec.n // 256))
+    return 1 if spec.n <= 20000 else max(1, min(spec.centres, spec.n // 64))
 
 
 def cpu_bruteforce_qps(base, queries, seconds_target, metric):
@@ -232,7 +232,7 @@ def run_ours(args):
 
     # ---- build (untimed region of the step loop, reported on its own) ----
     centroid_num = partition_count(spec)
-    cfg = pipeline.BuildConfig(metric=metric, graph_degree=spec.graph_degree, knn_degree=32,
+    cfg = pipeline.BuildConfig(metric=metric, graph_degree=spec.graph_degree, knn_degree=max(32, spec.graph_degree),
                                centroid_num=centroid_num, sample_factor=0.1 if centroid_num > 32 else 0.01,
                                seed=spec.seed)
     t0 = time.perf_counter()
