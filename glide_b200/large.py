@@ -36,7 +36,7 @@ def preprocess_for_large(ctx: api.Context, h_data: np.ndarray, centroid_num: int
     (no boundary test, partition_kernel.cuh:122-162), then the rows grouped by partition in ascending
     row order. Returns dict(h_reorder_data, h_map, h_segment_start, h_segment_length, h_centroids, seconds)."""
     n, dim = h_data.shape
-    sample_num = int(n * sample_factor)
+    sample_num = max(centroid_num, int(n * sample_factor))
     ids = api.sample_ids(n, sample_num, seed)
     d_sample = torch.from_numpy(np.ascontiguousarray(h_data[ids])).to(ctx.torch_device)
     d_centroids, _, _ = api.kmeans_fit(ctx, d_sample, centroid_num, 0, metric, 1)

@@ -1,5 +1,5 @@
-"""The four small-path command line tools run as the reference's test.sh runs its binaries
-(test.sh:27-33): stage files in the reference's formats, one CSV line per pipeline run."""
+"""The command line tools run as the reference's test.sh runs its binaries (test.sh:27-33): stage
+files in the reference's formats, one CSV line per pipeline run; small path and large path."""
 import os
 import subprocess
 
@@ -71,3 +71,48 @@ def test_cli_usage_and_bad_file(tmp_path):
     r = subprocess.run([os.path.join(BIN, "small_knn"), str(tmp_path / "nope"), str(tmp_path / "k"), str(tmp_path / "r.csv"), "32"],
                        capture_output=True, text=True)
     assert r.returncode == 1 and "Cannot open file" in r.stderr
+
+
+def test_large_pipeline_cli(tmp_path, gpu_ctx):
+    """The four large-path tools (argv contracts of large_*.cu) against the Python mirror of the same
+    path: same partition files, and the same search results for the index the tools built."""
+    from glide_b200 import large
+    from glide_b200.params import IndexParameter, Metric
+    if not os.path.exists(os.path.join(BIN, "large_search")):
+        subprocess.run(["make", "-C", os.path.join(ROOT, "glide_b200", "apps")], check=True)
+    base, queries = helpers.small_dataset("uniform", 9000, 32, 200, seed=23)
+    gt = oracle.bruteforce_knn(base, queries, 100, want_dists=False)
+    io.save_matrix_data(tmp_path / "base.fbin", base)
+    io.save_matrix_data(tmp_path / "query.fbin", queries)
+    io.save_matrix_data(tmp_path / "gt", gt)
+    pre, knn, graph, csv = tmp_path / "pre", tmp_path / "knn", tmp_path / "graph", tmp_path / "result.csv"
+    run(os.path.join(BIN, "large_preprocess"), tmp_path / "base.fbin", pre, csv, 5, 0.1, "Euclidean", 3)
+    run(os.path.join(BIN, "large_knn"), pre, knn, csv, 32)
+    run(os.path.join(BIN, "large_build"), pre, knn, graph, csv, "Euclidean", 32, 32, 1.05, 64, 128, 3)
+    out = run(os.path.join(BIN, "large_search"), pre, tmp_path / "query.fbin", tmp_path / "gt", graph, csv, "Euclidean", 10, 64,
+              2, 1.2)
+    assert "total_recall" in out
+    seg_start, seg_len = io.load_segment(str(pre) + ".segment")
+    mapping = io.load_vector_data(str(pre) + ".map")
+    reorder = io.load_matrix_data(str(pre) + ".reorder")
+    cent = io.load_matrix_data(str(pre) + ".centroid")
+    assert seg_start.size == 5 and seg_len.sum() == 9000 and sorted(mapping.tolist()) == list(range(9000))
+    assert np.array_equal(reorder, base[mapping])
+    for s, l in zip(seg_start, seg_len):                 # ascending original id inside a partition
+        assert (np.diff(mapping[s:s + l].astype(np.int64)) > 0).all()
+    # the Python mirror partitions the same way (same seeded sample, same k-means, same assignment)
+    P = large.preprocess_for_large(gpu_ctx, base, 5, 0.1, 10, Metric.Euclidean, seed=3)
+    assert np.array_equal(P["h_map"], mapping) and np.array_equal(P["h_segment_length"], seg_len)
+    assert np.array_equal(P["h_centroids"], cent)
+    g = io.load_matrix_data(str(graph) + ".graph", np.uint32)
+    sp = io.load_vector_data(str(graph) + ".sp")
+    assert g.shape == (9000, 32) and sp.size == 5
+    fields = open(csv).read().strip().splitlines()[-1].split(",")
+    recall = float(fields[-1])
+    assert recall >= 0.95
+    # the index the tools wrote, searched through the Python mirror: identical recall
+    index = large.GLIDE_large(gpu_ctx, 32, Metric.Euclidean, reorder, mapping, cent, seg_start, seg_len)
+    index.load(g, sp)
+    import torch
+    ids, _, _ = index.search(SearchParameter(top_k=10, beam=64).derive(32), 2, 1.2, torch.from_numpy(queries).to(gpu_ctx.torch_device))
+    assert abs(api.calculate_recall(ids, gt, 10) - recall) < 1e-6
