@@ -381,7 +381,7 @@ def run_ours(args):
             "recall_curve": curve,
             "e2e": {"value": e2e_qps, "unit": "queries/s", "h2d_bytes_per_step": Q * spec.dim * 4,
                     "d2h_bytes_per_step": Q * TOP_K * 8, "recall_at_10": round(e2e_recall, 4)},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": int(ctx.lib.glide_last_search_launches(ctx.handle)) * args.steps,
             "kernels_ms_per_step": {"route(assign_kernel)": round(route_ms / args.steps, 4),
                                     "search_kernel": round(search_ms / args.steps, 4)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

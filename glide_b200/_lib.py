@@ -52,6 +52,7 @@ SIGNATURES = {
     "glide_search_host": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_search_static_scratch": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_last_search_split_ms": (None, [vp, P(f32)]),
+    "glide_last_search_launches": (u32, [vp]),
     "glide_enable_counters": (None, [vp, i32]),
     "glide_read_counters": (i32, [vp, P(u64)]),
     "glide_select_segments": (i32, [vp, vp, u32, u32, vp, u32, u32, f32, i32, vp]),

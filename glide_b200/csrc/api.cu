@@ -26,6 +26,7 @@ struct glide_ctx {
     size_t ws_bytes = 0;
     unsigned long long *counters = nullptr;  // 4 x u64 on the device
     uint32_t *ticket = nullptr;              // one word: the search kernel's query counter
+    uint32_t last_launches = 0;              // kernels enqueued by the last glide_search
     float *tc_norms = nullptr;               // centroid norms for the assignment's tensor-core prefilter (up to 4096 centroids)
     bool counters_on = false;
 };
@@ -184,6 +185,8 @@ void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]) {
     out[0] = ctx->split_ms[0];
     out[1] = ctx->split_ms[1];
 }
+
+uint32_t glide_last_search_launches(const glide_ctx *ctx) { return ctx ? ctx->last_launches : 0; }
 
 void glide_enable_counters(glide_ctx *ctx, int on) { if (ctx) ctx->counters_on = on != 0; }
 
@@ -736,9 +739,11 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
     a.ticket = ctx->ticket;
     Timed timer(ctx);
     AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms, a.counters ? a.counters + 3 : nullptr};
-    GL_CUDA(ctx, launch_assign(r, ctx->stream));
+    uint32_t launched = 0;
+    GL_CUDA(ctx, launch_assign(r, ctx->stream, &launched));
     GL_CUDA(ctx, cudaEventRecord(ctx->ev_mid, ctx->stream));
     GL_CUDA(ctx, launch_search(a, ctx->stream));
+    ctx->last_launches = launched + 1;
     rc = timer.finish();
     if (rc) return rc;
     cudaEventElapsedTime(&ctx->split_ms[0], ctx->ev_start, ctx->ev_mid);

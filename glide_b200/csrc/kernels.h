@@ -107,11 +107,12 @@ struct AssignArgs {
                             // floats (norms, padding, their maximum at [C]); nullptr: exact kernels only
     unsigned long long *fallback_counter;  // += points settled by the warp-per-point kernel; may be nullptr
 };
-cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream);
+// *launched (optional) receives the number of kernels this call enqueued
+cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream, uint32_t *launched = nullptr);
 // Tensor-core prefilter + exact re-rank (assign_tc.cu); settles every point whose nearest centroid
 // is unique, flags the rest with 0xffffffff in `nearest`. Eligible: tc_norms given, dim % 16 == 0, dim <= 128, C >= 2.
 bool assign_tc_eligible(const AssignArgs &a);
-cudaError_t launch_assign_tc(const AssignArgs &a, cudaStream_t stream);
+cudaError_t launch_assign_tc(const AssignArgs &a, cudaStream_t stream);   // two kernels: norms, prefilter + re-rank
 
 // Deterministic slots: slot[p] = number of q < p with key[q] == key[p] (keys < K,
 // key == 0xffffffff means "none" and yields slot 0xffffffff); totals[K] = counts.

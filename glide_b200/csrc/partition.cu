@@ -385,7 +385,8 @@ cudaError_t launch_gather_rows(const float *data, const uint32_t *ids, uint32_t 
     return cudaGetLastError();
 }
 
-cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream) {
+cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream, uint32_t *launched) {
+    if (launched) *launched = 0;
     if (a.n == 0) return cudaSuccess;
     const uint32_t max_centroid = pow2_at_least(a.C, 32);
     const uint32_t strip_words = (dim_pad4(a.dim) + 2 * max_centroid + 3u) & ~3u;
@@ -404,9 +405,12 @@ cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream) {
     if (!exact_only && assign_tc_eligible(a)) {
         cudaError_t e = launch_assign_tc(a, stream);
         if (e != cudaSuccess) return e;
+        if (launched) *launched += 2;
     } else if (tiled) {
         assign_tiled_kernel<<<(a.n + kAP - 1) / kAP, 256, 0, stream>>>(a);
+        if (launched) *launched += 1;
     }
+    if (launched) *launched += 1;
     assign_kernel<<<(a.n + warps - 1) / warps, warps * 32, smem_bytes, stream>>>(a, max_centroid, strip_words, tiled);
     return cudaGetLastError();
 }

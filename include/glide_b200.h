@@ -190,6 +190,8 @@ int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t nu
 /* Device milliseconds of the two kernels of the last glide_search on this context:
  * out[0] the routing pre-pass (nearest centroid per query), out[1] the search kernel. */
 void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]);
+/* Number of kernels the last glide_search enqueued (routing kernels + the search kernel). */
+uint32_t glide_last_search_launches(const glide_ctx *ctx);
 /* Counters of the last search/build/refine/define_partition call when enabled: rows read during
  * search, expansions, rows read during pruning, and a fourth that depends on the call: build and
  * refine count the points whose beam ended with fewer than `beam` entries; search and
