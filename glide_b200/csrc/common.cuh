@@ -165,15 +165,20 @@ __device__ __forceinline__ float lane_row_partial(const float *q_smem, const flo
         const float4 *q4 = reinterpret_cast<const float4 *>(q_smem);
         const float4 *r4 = reinterpret_cast<const float4 *>(row);
         const uint32_t chunks = dim >> 2;
-        uint32_t c = lane;
-        for (; c + 96 < chunks; c += 128) {  // four loads in flight per lane
-            const float4 b0 = __ldg(r4 + c), b1 = __ldg(r4 + c + 32), b2 = __ldg(r4 + c + 64), b3 = __ldg(r4 + c + 96);
-            acc = sq_acc4(q4[c], b0, acc);
-            acc = sq_acc4(q4[c + 32], b1, acc);
-            acc = sq_acc4(q4[c + 64], b2, acc);
-            acc = sq_acc4(q4[c + 96], b3, acc);
+        // eight 16-byte loads in flight per lane (a 960-dim row is 7.5 of them), accumulated in chunk order
+        for (uint32_t c = lane; c < chunks; c += 256) {
+            float4 b[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const uint32_t ck = c + 32u * k;
+                b[k] = ck < chunks ? __ldg(r4 + ck) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const uint32_t ck = c + 32u * k;
+                if (ck < chunks) acc = sq_acc4(q4[ck], b[k], acc);
+            }
         }
-        for (; c < chunks; c += 32) acc = sq_acc4(q4[c], __ldg(r4 + c), acc);
     } else {
         for (uint32_t i = lane; i < dim; i += 32) {
             const float d = q_smem[i] - __ldg(row + i);

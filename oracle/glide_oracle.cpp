@@ -13,9 +13,11 @@
 // partition kernels, and the GPU tests (tests/test_gpu_reference.py) compare them with this
 // restatement in the reference's summation order: search, build, boundary merge and
 // assignment bit for bit; reverse edges as one of the arrival orders allowed here; refine up
-// to the reference's in-place race. PARITY UNPINNED for what has no reference arithmetic in
+// to the reference's in-place race. Outputs of those reference kernels on small seeded inputs are
+// stored under tests/golden/ (made by tests/golden/make_reference_goldens.py) and compared
+// with this restatement by the CPU-only tests. PARITY UNPINNED for what has no reference arithmetic in
 // the tree: k-means and NN-descent (cuVS calls), which restate this repository's own
-// algorithms, and for the CPU-only view (without a GPU the harness cannot run).
+// algorithms.
 //
 // Each function cites the reference file:line it follows (paths relative to the
 // reference's src/ directory).
