@@ -643,6 +643,36 @@ int glide_reverse_graph(glide_ctx *ctx, uint32_t *d_graph, uint32_t num, uint32_
     return timer.finish();
 }
 
+// Points of a refine launch in partition order: order[] lists 0..count-1 grouped by route[] (ascending
+// index inside a group). The kernel results do not depend on the order in which points are
+// processed (every point reads the snapshot and writes its own row); grouping makes the warps that
+// run together walk the same part of the graph and of the data, which is what keeps the subgraph
+// build in L2. Scratch: slot[count], totals[C+1], offsets[C+1], hist[slot_scratch_words], scan tmp.
+struct OrderScratch {
+    uint32_t *slot, *totals, *offsets, *hist, *order;
+    void *scan_tmp;
+};
+size_t order_scratch_bytes(uint32_t count, uint32_t C) {
+    return 2 * align256((size_t) count * 4) + 2 * align256((size_t) (C + 2) * 4) + align256(slot_scratch_words(count, C) * 4) +
+           align256(scan_tmp_bytes(C + 1)) + 256;
+}
+OrderScratch carve_order_scratch(char *base, uint32_t count, uint32_t C) {
+    OrderScratch o;
+    o.slot = reinterpret_cast<uint32_t *>(base); base += align256((size_t) count * 4);
+    o.order = reinterpret_cast<uint32_t *>(base); base += align256((size_t) count * 4);
+    o.totals = reinterpret_cast<uint32_t *>(base); base += align256((size_t) (C + 2) * 4);
+    o.offsets = reinterpret_cast<uint32_t *>(base); base += align256((size_t) (C + 2) * 4);
+    o.hist = reinterpret_cast<uint32_t *>(base); base += align256(slot_scratch_words(count, C) * 4);
+    o.scan_tmp = base;
+    return o;
+}
+cudaError_t make_partition_order(const uint32_t *route, uint32_t count, uint32_t C, const OrderScratch &o, cudaStream_t st) {
+    cudaError_t e = launch_slots(route, count, C, o.slot, o.totals, o.hist, st);
+    if (e != cudaSuccess) return e;
+    if ((e = exclusive_scan_u32(o.totals, C, o.offsets, o.scan_tmp, st)) != cudaSuccess) return e;
+    return launch_scatter_members(route, o.slot, o.offsets, count, o.order, st);
+}
+
 static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
                          uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
                          const glide_search_params *p, float relaxant_factor, int metric) {
@@ -651,21 +681,26 @@ static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t
     if (rc) return rc;
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t graph_bytes = (size_t) num * graph_degree * 4;
-    rc = ensure_ws(ctx, align256(graph_bytes) + align256((size_t) num * 4));
+    const bool routed = mode == kModeRefine;
+    rc = ensure_ws(ctx, align256(graph_bytes) + align256((size_t) num * 4) + (routed ? order_scratch_bytes(num, C) : 0));
     if (rc) return rc;
     uint32_t *snapshot = static_cast<uint32_t *>(ctx->ws);
     uint32_t *route = reinterpret_cast<uint32_t *>(static_cast<char *>(ctx->ws) + align256(graph_bytes));
+    const uint32_t *order = nullptr;
     Timed timer(ctx);
     GL_CUDA(ctx, cudaMemcpyAsync(snapshot, d_graph, graph_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
-    if (mode == kModeRefine) {
+    if (routed) {
         AssignArgs r{d_data, num, dim, d_centroids, C, -1.0f, metric, route, nullptr, C <= 4096 ? ctx->tc_norms : nullptr, nullptr};
         GL_CUDA(ctx, launch_assign(r, ctx->stream));
+        const OrderScratch o = carve_order_scratch(reinterpret_cast<char *>(route) + align256((size_t) num * 4), num, C);
+        GL_CUDA(ctx, make_partition_order(route, num, C, o, ctx->stream));
+        order = o.order;
     }
     BuildArgs a{};
     a.mode = mode;
     a.data = d_data; a.dim = dim; a.graph_in = snapshot; a.in_degree = graph_degree;
     a.graph_out = d_graph; a.out_degree = graph_degree;
-    a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route;
+    a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route; a.order = order;
     a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
     a.counters = counters_or_null(ctx);
     GL_CUDA(ctx, launch_build(a, ctx->stream));
@@ -685,13 +720,16 @@ int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32
     if (rc) return rc;
     if (count == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
-    rc = ensure_ws(ctx, align256((size_t) count * 4));
+    rc = ensure_ws(ctx, align256((size_t) count * 4) + order_scratch_bytes(count, C));
     if (rc) return rc;
     uint32_t *route = static_cast<uint32_t *>(ctx->ws);
     Timed timer(ctx);
     AssignArgs r{d_data + (size_t) first * dim, count, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms, nullptr};
     GL_CUDA(ctx, launch_assign(r, ctx->stream));
+    const OrderScratch o = carve_order_scratch(reinterpret_cast<char *>(route) + align256((size_t) count * 4), count, C);
+    GL_CUDA(ctx, make_partition_order(route, count, C, o, ctx->stream));
     BuildArgs a{};
+    a.order = o.order;
     a.mode = kModeRefine;
     a.data = d_data; a.dim = dim; a.graph_in = d_graph_in; a.in_degree = graph_degree;
     a.graph_out = d_graph_out; a.out_degree = graph_degree;

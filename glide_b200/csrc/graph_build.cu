@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t t = blockIdx.x * warps_per_cta + warp;
     if (t >= a.count) return;
-    const uint32_t point = a.first + t;
+    const uint32_t point = a.first + (a.order ? a.order[t] : t);
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
     WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? 0u : 32u * NC, p.hash_bit);
     PruneStrip ps = make_prune_strip(s.extra, d.max_degree);

@@ -69,6 +69,8 @@ struct BuildArgs {
     uint32_t C;
     const uint32_t *route;         // refine: nearest centroid of points route_first, route_first+1, ... (launch_assign)
     uint32_t route_first;
+    const uint32_t *order;         // refine: warp t handles point first + order[t] (points grouped by partition so that
+                                   // warps running together share L2 lines); nullptr: first + t
     uint32_t first, count;         // point range handled by this launch
     uint32_t fixed_segment;        // boundary: the segment every point belongs to
     float alpha;
