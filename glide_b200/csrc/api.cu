@@ -765,7 +765,9 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
     if (rc) return rc;
     GL_REQUIRE(ctx, p->top_k >= 1 && p->top_k <= p->beam, GLIDE_ERR_BAD_ARG, "search: top_k must be in [1, beam]");
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
-    rc = ensure_ws(ctx, align256((size_t) q * 4));
+    // queries are handed out grouped by partition when the batch is large enough for that to matter
+    const bool grouped = C > 1 && q >= 1024 && q <= 262144;
+    rc = ensure_ws(ctx, 2 * align256((size_t) q * 4));
     if (rc) return rc;
     uint32_t *route = static_cast<uint32_t *>(ctx->ws);
     SearchArgs a{};
@@ -779,6 +781,12 @@ int glide_search(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim
     AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms, a.counters ? a.counters + 3 : nullptr};
     uint32_t launched = 0;
     GL_CUDA(ctx, launch_assign(r, ctx->stream, &launched));
+    if (grouped) {
+        uint32_t *order = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(route) + align256((size_t) q * 4));
+        GL_CUDA(ctx, launch_group_by_key(route, q, C, order, ctx->stream));
+        a.order = order;
+        launched += 1;
+    }
     GL_CUDA(ctx, cudaEventRecord(ctx->ev_mid, ctx->stream));
     GL_CUDA(ctx, launch_search(a, ctx->stream));
     ctx->last_launches = launched + 1;
@@ -797,8 +805,8 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
     if (q == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
     GL_REQUIRE(ctx, h_queries && h_out_ids && h_out_dists && p, GLIDE_ERR_BAD_ARG, "search_host: null pointer");
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
-    // layout: [route (used by glide_search)] [queries] [ids] [dists]
-    const size_t route_b = align256((size_t) q * 4);
+    // layout: [route and query order (used by glide_search)] [queries] [ids] [dists]
+    const size_t route_b = 2 * align256((size_t) q * 4);
     const size_t qb = align256((size_t) q * dim * 4), rb = align256((size_t) q * p->top_k * 4);
     int rc = ensure_ws(ctx, route_b + qb + 2 * rb);
     if (rc) return rc;

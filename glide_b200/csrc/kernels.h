@@ -33,6 +33,8 @@ struct SearchArgs {
     uint32_t segment_num, segment_id, start_point;
     const uint32_t *map;         // local id -> global id (large path)
     unsigned long long *counters;  // [0] data rows read, [1] expansions; may be nullptr
+    const uint32_t *order;       // ticket t is query order[t] (queries grouped by partition: warps that run together
+                                 // share L2 lines); nullptr: query t
     uint32_t *ticket;            // one word, zeroed by launch_search: warps draw their next query from it;
                                  // nullptr: query q runs on warp q of the grid
 };
@@ -119,6 +121,8 @@ cudaError_t launch_assign_tc(const AssignArgs &a, cudaStream_t stream);   // two
 // Deterministic slots: slot[p] = number of q < p with key[q] == key[p] (keys < K,
 // key == 0xffffffff means "none" and yields slot 0xffffffff); totals[K] = counts.
 // scratch: block_hist words = slot_scratch_words(n, K).
+// order[] = 0..n-1 grouped by key (keys < K <= 4096; every key must be valid), one CTA; for small n.
+cudaError_t launch_group_by_key(const uint32_t *key, uint32_t n, uint32_t K, uint32_t *order, cudaStream_t stream);
 size_t slot_scratch_words(uint32_t n, uint32_t K);
 cudaError_t launch_slots(const uint32_t *key, uint32_t n, uint32_t K, uint32_t *slot, uint32_t *totals,
                          uint32_t *scratch, cudaStream_t stream);

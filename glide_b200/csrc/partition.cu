@@ -415,6 +415,62 @@ cudaError_t launch_assign(const AssignArgs &a, cudaStream_t stream, uint32_t *la
     return cudaGetLastError();
 }
 
+// Small batches: order[] = the indices 0..n-1 grouped by key, in one CTA (shared-memory histogram, scan,
+// scatter). The order inside a group follows the atomics; callers only use the grouping.
+__global__ void __launch_bounds__(1024) group_by_key_kernel(const uint32_t *__restrict__ key, uint32_t n, uint32_t K,
+                                                            uint32_t *__restrict__ order) {
+    extern __shared__ uint32_t sh[];   // K counters, then K cursors
+    uint32_t *count = sh, *cursor = sh + K;
+    __shared__ uint32_t warp_sums[32];
+    for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) count[k] = 0;
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint32_t k = key[i];
+        if (k < K) atomicAdd(&count[k], 1u);
+    }
+    __syncthreads();
+    // exclusive scan of count[] into cursor[]: K / blockDim consecutive entries per thread
+    const uint32_t per = (K + blockDim.x - 1) / blockDim.x;
+    const uint32_t lo = threadIdx.x * per, hi = min(K, lo + per);
+    uint32_t local = 0;
+    for (uint32_t k = lo; k < hi; k++) local += count[k];
+    uint32_t incl = local;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= (uint32_t) off) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t w = lane < (blockDim.x >> 5) ? warp_sums[lane] : 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, w, off);
+            if (lane >= (uint32_t) off) w += v;
+        }
+        warp_sums[lane] = w;   // inclusive over warps
+    }
+    __syncthreads();
+    uint32_t run = incl - local + (warp ? warp_sums[warp - 1] : 0);
+    for (uint32_t k = lo; k < hi; k++) {
+        cursor[k] = run;
+        run += count[k];
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint32_t k = key[i];
+        if (k < K) order[atomicAdd(&cursor[k], 1u)] = i;
+    }
+}
+
+cudaError_t launch_group_by_key(const uint32_t *key, uint32_t n, uint32_t K, uint32_t *order, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    group_by_key_kernel<<<1, 1024, 2 * (size_t) K * sizeof(uint32_t), stream>>>(key, n, K, order);
+    return cudaGetLastError();
+}
+
 size_t slot_scratch_words(uint32_t n, uint32_t K) { return (size_t) ((n + kSlotBlock - 1) / kSlotBlock) * K; }
 
 cudaError_t launch_slots(const uint32_t *key, uint32_t n, uint32_t K, uint32_t *slot, uint32_t *totals,

@@ -153,6 +153,7 @@ __device__ __forceinline__ void search_body(const SearchDev &d) {
         if (lane == 0) q = atomicAdd(a.ticket, 1u);
         q = __shfl_sync(kFullMask, q, 0);
         if (q >= a.Q) break;
+        if (a.order) q = a.order[q];
         search_one<NB, NC, LANES>(d, s, p, q);
         __syncwarp();
     }
