@@ -183,17 +183,37 @@ __global__ void __launch_bounds__(kSlotBlock) slot_hist_kernel(const uint32_t *_
     for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) block_hist[(uint64_t) blockIdx.x * K + k] = hist[k];
 }
 
-// pass 2: per key, exclusive prefix over blocks (in place); totals[k] = count
-__global__ void slot_prefix_kernel(uint32_t *block_hist, uint32_t blocks, uint32_t K, uint32_t *totals) {
-    const uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
-    if (k >= K) return;
-    uint32_t run = 0;
-    for (uint32_t b = 0; b < blocks; b++) {
-        const uint32_t v = block_hist[(uint64_t) b * K + k];
-        block_hist[(uint64_t) b * K + k] = run;
-        run += v;
+// pass 2: per key, exclusive prefix over blocks (in place); totals[k] = count. A CTA owns 32 keys
+// (threadIdx.x, coalesced) and splits the blocks into 32 contiguous chunks (threadIdx.y): chunk
+// sums, a scan over the chunks in shared memory, then the prefixes.
+__global__ void __launch_bounds__(1024) slot_prefix_kernel(uint32_t *block_hist, uint32_t blocks, uint32_t K, uint32_t *totals) {
+    __shared__ uint32_t chunk_sum[32][33];
+    const uint32_t k = blockIdx.x * 32 + threadIdx.x, y = threadIdx.y;
+    const uint32_t per = (blocks + 31) / 32;
+    const uint32_t lo = y * per, hi = min(blocks, lo + per);
+    uint32_t sum = 0;
+    if (k < K)
+        for (uint32_t b = lo; b < hi; b++) sum += block_hist[(uint64_t) b * K + k];
+    chunk_sum[y][threadIdx.x] = sum;
+    __syncthreads();
+    if (y == 0) {
+        uint32_t run = 0;
+        for (uint32_t c = 0; c < 32; c++) {
+            const uint32_t v = chunk_sum[c][threadIdx.x];
+            chunk_sum[c][threadIdx.x] = run;
+            run += v;
+        }
+        if (k < K) totals[k] = run;
     }
-    totals[k] = run;
+    __syncthreads();
+    if (k < K) {
+        uint32_t run = chunk_sum[y][threadIdx.x];
+        for (uint32_t b = lo; b < hi; b++) {
+            const uint32_t v = block_hist[(uint64_t) b * K + k];
+            block_hist[(uint64_t) b * K + k] = run;
+            run += v;
+        }
+    }
 }
 
 // pass 3: slot = block prefix + rank among earlier points of the block with the same
@@ -478,7 +498,7 @@ cudaError_t launch_slots(const uint32_t *key, uint32_t n, uint32_t K, uint32_t *
     if (n == 0) return cudaMemsetAsync(totals, 0, K * sizeof(uint32_t), stream);
     const uint32_t blocks = (n + kSlotBlock - 1) / kSlotBlock;
     slot_hist_kernel<<<blocks, kSlotBlock, K * sizeof(uint32_t), stream>>>(key, n, K, scratch);
-    slot_prefix_kernel<<<(K + 127) / 128, 128, 0, stream>>>(scratch, blocks, K, totals);
+    slot_prefix_kernel<<<(K + 31) / 32, dim3(32, 32), 0, stream>>>(scratch, blocks, K, totals);
     slot_rank_kernel<<<blocks, kSlotBlock, K * sizeof(uint32_t), stream>>>(key, n, K, scratch, slot);
     return cudaGetLastError();
 }
