@@ -71,6 +71,11 @@ class ClockSampler:
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # nvidia-smi takes a moment to initialise and holds driver locks while it does: wait for its
+            # first sample so that the start-up does not land inside the timed region
+            deadline = time.time() + 5.0
+            while not self.lines and time.time() < deadline and self.proc.poll() is None:
+                time.sleep(0.02)
         except OSError:
             self.proc = None
 
@@ -320,6 +325,7 @@ def run_ours(args):
     barrier()
     if rank == 0:
         sampler.start()
+    barrier()
     kernel_ms = route_ms = search_ms = 0.0
     for _ in range(args.steps):
         flush_l2()
