@@ -13,6 +13,11 @@
 
 namespace glide {
 
+// Lane-resident kernels keep no candidate arrays in the strip, only 2 x this many words at cand_id
+// (the cand_id and cand_dist slots of the layout below) for the ids of a scoring call in rank
+// order: up to 32 ids plus 8 of padding.
+constexpr uint32_t kLaneScratch = 20;
+
 struct BeamParams {
     uint32_t beam;            // multiple of 32, <= 32*NB
     uint32_t max_iterations;
@@ -360,7 +365,7 @@ __device__ __forceinline__ uint32_t seed_lanes(const WarpStrip &s, uint32_t star
     if (excluded_kept) *excluded_kept = __ballot_sync(kFullMask, flag && index == exclude_id) != 0;
     const uint32_t mask = __ballot_sync(kFullMask, cv != kInvalid && cv != exclude_id);
     __syncwarp();
-    ck = score_lanes(s.query, data, dim, metric, mask, cv);
+    ck = score_lanes(s.query, data, dim, metric, mask, cv, s.cand_id);
     return __popc(mask);
 }
 
@@ -375,7 +380,7 @@ __device__ __forceinline__ uint32_t expand_lanes(const WarpStrip &s, uint32_t pa
     cv = flag ? nb : kInvalid;
     const uint32_t mask = __ballot_sync(kFullMask, flag != 0);
     __syncwarp();
-    ck = score_lanes(s.query, data, dim, metric, mask, cv);
+    ck = score_lanes(s.query, data, dim, metric, mask, cv, s.cand_id);
     return __popc(mask);
 }
 

@@ -216,14 +216,54 @@ __device__ __forceinline__ void warp_rows(const float *q_smem, const float *__re
 // bit-identical to the shared-memory path; nothing is staged in shared memory.
 // Fast path of score_lanes: dim % 4 == 0 and dim <= 128, the query chunk of this lane in `q`
 // (zero when the lane owns no chunk).
+// ids_smem: 40 words of per-warp scratch, or nullptr. With scratch the ids are first written in rank
+// order (one store per lane), so that the batch loop reads each id with one broadcast load instead of
+// finding, shuffling and selecting it.
 __device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const float *__restrict__ data, uint32_t dim,
-                                                int metric, uint32_t mask, uint32_t cv) {
+                                                int metric, uint32_t mask, uint32_t cv, uint32_t *ids_smem = nullptr) {
     const uint32_t lane = lane_id();
     float mine = FLT_MAX;
     uint32_t m = mask;
     const uint32_t my_rank = __popc(mask & ((1u << lane) - 1));
     const bool valid = ((mask >> lane) & 1u) != 0;
     const bool all_own = dim == 128;   // every lane owns a chunk: loads need no predicate
+    if (ids_smem != nullptr) {
+        const uint32_t n = __popc(mask);
+        if (valid) ids_smem[my_rank] = cv;
+        if (lane < 8) ids_smem[n + lane] = 0u;   // slots past the last row of a ragged batch re-read row 0
+        __syncwarp();
+        if (all_own) {   // constant row pitch, every lane owns a chunk
+            for (uint32_t g = 0; 8u * g < n; g++) {
+                float4 v[8];
+#pragma unroll
+                for (int r = 0; r < 8; r++)
+                    v[r] = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) ids_smem[8u * g + r] * 128u) + lane);
+                float p[8];
+#pragma unroll
+                for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
+                const float sum = fold_rows<8>(p);  // row r of the batch sits in lanes 4r .. 4r+3
+                const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
+                mine = (valid && (my_rank >> 3) == g) ? got : mine;
+            }
+        } else {
+            const uint32_t my_chunk = own ? lane : 0u;   // lanes without a chunk re-read chunk 0 and contribute nothing
+            for (uint32_t g = 0; 8u * g < n; g++) {
+                float4 v[8];
+#pragma unroll
+                for (int r = 0; r < 8; r++)
+                    v[r] = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) ids_smem[8u * g + r] * dim) + my_chunk);
+                float p[8];
+#pragma unroll
+                for (int r = 0; r < 8; r++) p[r] = own ? sq_acc4(q, v[r], 0.0f) : 0.0f;
+                const float sum = fold_rows<8>(p);
+                const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
+                mine = (valid && (my_rank >> 3) == g) ? got : mine;
+            }
+        }
+        __syncwarp();
+        if (metric == kEuclidean) mine = valid ? sqrtf(mine) : mine;
+        return mine;
+    }
     for (uint32_t g = 0; m != 0; g++) {
         float4 v[8];
         if (all_own) {
@@ -270,12 +310,12 @@ __device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const 
 __device__ __forceinline__ bool rows_fit_lanes(uint32_t dim) { return (dim & 3u) == 0 && dim <= 128; }
 
 __device__ __forceinline__ float score_lanes(const float *q_smem, const float *__restrict__ data, uint32_t dim,
-                                             int metric, uint32_t mask, uint32_t cv) {
+                                             int metric, uint32_t mask, uint32_t cv, uint32_t *ids_smem = nullptr) {
     const uint32_t lane = lane_id();
     if (rows_fit_lanes(dim)) {
         const bool own = lane < (dim >> 2);
         const float4 q = own ? reinterpret_cast<const float4 *>(q_smem)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
-        return score_lanes_q4(q, own, data, dim, metric, mask, cv);
+        return score_lanes_q4(q, own, data, dim, metric, mask, cv, ids_smem);
     }
     float mine = FLT_MAX;
     uint32_t m = mask;

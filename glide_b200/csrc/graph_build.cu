@@ -54,7 +54,8 @@ __device__ __forceinline__ PruneStrip make_prune_strip(uint32_t *extra, uint32_t
 // ---------------------------------------------------------------------------
 template<int NB>
 __device__ __forceinline__ uint32_t prune_lanes(const float (&bk)[NB], const uint32_t (&bv)[NB], uint32_t beam,
-                                                const PruneStrip &ps, float *q_smem, const float *__restrict__ data,
+                                                const PruneStrip &ps, float *q_smem, uint32_t *ids_smem,
+                                                const float *__restrict__ data,
                                                 uint32_t dim, uint32_t degree, uint32_t max_degree, uint32_t limit,
                                                 float alpha, int metric, bool refine, uint32_t point_id,
                                                 uint32_t *pool_size) {
@@ -116,7 +117,7 @@ __device__ __forceinline__ uint32_t prune_lanes(const float (&bk)[NB], const uin
         for (int i = 0; i < NB; i++) {
             if (alive[i] == 0) continue;
             rows += __popc(alive[i]);
-            const float d = fast ? score_lanes_q4(q, own, data, dim, metric, alive[i], id[i])
+            const float d = fast ? score_lanes_q4(q, own, data, dim, metric, alive[i], id[i], ids_smem)
                                  : score_lanes(q_smem, data, dim, metric, alive[i], id[i]);
             const bool occluded = ((alive[i] >> lane) & 1u) && (alpha * d < bk[i]);   // graph_kernel.cuh:103-114
             alive[i] &= ~__ballot_sync(kFullMask, occluded);
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
     if (t >= a.count) return;
     const uint32_t point = a.first + (a.order ? a.order[t] : t);
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
-    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? 0u : 32u * NC, p.hash_bit);
+    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLaneScratch : 32u * NC, p.hash_bit);
     PruneStrip ps = make_prune_strip(s.extra, d.max_degree);
     const uint32_t degree = a.out_degree;
 
@@ -238,7 +239,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
                                             wide);
         }
         uint32_t P;
-        prune_rows = prune_lanes<NB>(bk, bv, p.beam, ps, s.query, pdata, a.dim, degree, d.max_degree, degree, a.alpha, a.metric,
+        prune_rows = prune_lanes<NB>(bk, bv, p.beam, ps, s.query, LANES ? s.cand_id : nullptr, pdata, a.dim, degree, d.max_degree, degree, a.alpha, a.metric,
                                      false, kInvalid, &P);
         short_pool = P < p.beam;
         const uint32_t orig = a.map ? a.map[point] : point;
@@ -292,7 +293,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
             iters = beam_loop<NB, NC, true>(bk, bv, s, p, point, a.graph_in, degree, a.data, a.dim, a.metric, &rows, wide);
         }
         uint32_t P;
-        prune_rows = prune_lanes<NB>(bk, bv, p.beam, ps, s.query, a.data, a.dim, degree, d.max_degree, need, a.alpha, a.metric,
+        prune_rows = prune_lanes<NB>(bk, bv, p.beam, ps, s.query, LANES ? s.cand_id : nullptr, a.data, a.dim, degree, d.max_degree, need, a.alpha, a.metric,
                                      true, point, &P);
         short_pool = P < p.beam;
         uint32_t pos_num = 0;  // :660-671: holes, front to back
@@ -471,7 +472,7 @@ cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
     d.max_degree = round_up32(a.out_degree);
     uint32_t extra = prune_strip_words(d.max_degree);
     const bool lanes = a.in_degree <= 32;
-    d.strip_words = (strip_words_base(a.dim, lanes ? 0 : max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
+    d.strip_words = (strip_words_base(a.dim, lanes ? kLaneScratch : max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;
     while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;
