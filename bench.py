@@ -142,7 +142,8 @@ def partition_count(spec) -> int:
 def cpu_bruteforce_qps(base, queries, seconds_target, metric):
     """Exact kNN on all host cores over a bounded sample of the queries."""
     import oracle
-    cores = oracle.max_threads()
+    # all host threads this process may run on (torchrun sets OMP_NUM_THREADS=1, which would leave one)
+    cores = max(oracle.max_threads(), len(os.sched_getaffinity(0)))
     probe = min(len(queries), max(4 * cores, 32))
     oracle.bruteforce_knn(base, queries[:probe], TOP_K, metric, threads=cores, want_dists=False)  # warm (page faults)
     t0 = time.perf_counter()
@@ -173,7 +174,8 @@ def run_reference(args):
     base = datasets.base_rows(spec, cent=cent)
     queries = datasets.queries(spec, cent=cent)
     metric = oracle.EUCLIDEAN if spec.metric == "Euclidean" else oracle.COSINE
-    cores = oracle.max_threads()
+    # all host threads this process may run on (torchrun sets OMP_NUM_THREADS=1, which would leave one)
+    cores = max(oracle.max_threads(), len(os.sched_getaffinity(0)))
     # size one step at about cpu_seconds / (steps + warmup)
     probe = min(len(queries), max(4 * cores, 32))
     oracle.bruteforce_knn(base, queries[:probe], TOP_K, metric, threads=cores, want_dists=False)  # warm (page faults)
