@@ -28,6 +28,7 @@ SIGNATURES = {
     "glide_last_error": (C.c_char_p, [vp]),
     "glide_ctx_stream": (vp, [vp]),
     "glide_last_kernel_ms": (f32, [vp]),
+    "glide_ctx_workspace_bytes": (C.c_size_t, [vp]),
     "glide_calculate_hash_bitlen": (u32, [u32, u32, f32, u32]),
     "glide_calculate_hash_reset_interval": (u32, [u32, u32, f32, u32]),
     "glide_adjust_search_params": (None, [u32, P(u32), P(u32)]),

@@ -35,11 +35,14 @@ class UnsupportedError(GlideError, ValueError):
 def _ptr(t) -> int:
     if t is None:
         return 0
+    # every buffer of the C ABI holds 4-byte elements (fp32, u32, i32): anything else would be read as garbage
     if isinstance(t, torch.Tensor):
-        assert t.is_contiguous(), "tensor must be contiguous"
+        if not t.is_contiguous() or t.element_size() != 4:
+            raise TypeError(f"tensor must be contiguous with 4-byte elements, got {t.dtype}, contiguous={t.is_contiguous()}")
         return t.data_ptr()
     if isinstance(t, np.ndarray):
-        assert t.flags.c_contiguous, "array must be contiguous"
+        if not t.flags.c_contiguous or t.dtype.itemsize != 4:
+            raise TypeError(f"array must be C-contiguous with 4-byte elements, got {t.dtype}")
         return t.ctypes.data
     raise TypeError(type(t))
 
@@ -436,7 +439,13 @@ class GLIDE:
                     h_dists: np.ndarray | None = None):
         """Host queries in, host results out: the copies are inside the call."""
         ctx = self.ctx
+        h_query = np.ascontiguousarray(h_query, np.float32)
+        if h_query.ndim != 2 or h_query.shape[1] != self.dim():
+            raise ValueError(f"queries must be Q x {self.dim()}")
         q = h_query.shape[0]
+        for name, arr, kinds in (("h_ids", h_ids, (np.uint32, np.int32)), ("h_dists", h_dists, (np.float32,))):
+            if arr is not None and (arr.dtype not in kinds or arr.shape != (q, param.top_k) or not arr.flags.c_contiguous):
+                raise TypeError(f"{name} must be a C-contiguous {q} x {param.top_k} array of {kinds[0].__name__}")
         if h_ids is None:
             h_ids = np.empty((q, param.top_k), np.uint32)
         if h_dists is None:

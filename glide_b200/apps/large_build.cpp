@@ -36,7 +36,7 @@ int main(int argc, char **argv) {
 
         GLIDE_large index(ctx, build_param.graph_degree, build_param.metric, std::move(h_reorder), std::move(h_map),
                           std::move(h_centroids), std::move(seg_start), std::move(seg_len));
-        append_result(result_file, std::to_string(build_param.graph_degree) + ",");
+        append_result(result_file, stream_text(build_param.graph_degree) + ",");
         index.build(build_param, search_param_knn, search_param_refine, h_knn, result_file, seed);
         save_matrix_data(graph_base_file + ".graph", index.graph_view());
         save_vector_data(graph_base_file + ".sp", index.start_point_view());

@@ -30,7 +30,7 @@ int main(int argc, char **argv) {
         auto graph = load_matrix_data<uint32_t>(graph_base_file + ".graph");
         auto start_point = load_vector_data(graph_base_file + ".sp");
 
-        append_result(result_file, std::to_string(search_param.beam) + ",");
+        append_result(result_file, stream_text(search_param.beam) + ",");
         derive_search_params(search_param, graph.cols);   // large_search.cu:98-110
         GLIDE_large index(ctx, graph.cols, metric, std::move(h_reorder), std::move(h_map), std::move(h_centroids),
                           std::move(seg_start), std::move(seg_len));
@@ -39,7 +39,7 @@ int main(int argc, char **argv) {
         HostMatrix<float> result_dists;
         index.search(search_param, min_segment_num, boundary_factor, query, result_ids, result_dists, result_file);
         const float recall = calculate_recall(result_ids, truth, search_param.top_k);
-        append_result(result_file, std::to_string(recall) + "\n");
+        append_result(result_file, stream_text(recall) + "\n");
     } catch (const std::exception &e) {
         std::cerr << "large_search: " << e.what() << std::endl;
         return 1;

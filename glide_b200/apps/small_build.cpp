@@ -38,7 +38,7 @@ int main(int argc, char **argv) {
         DeviceBuffer<uint32_t> d_map(ctx, h_map.data(), h_map.size());
         DeviceBuffer<int> d_knn(ctx, h_knn.data_handle(), h_knn.size());
         GLIDE index(ctx, build_param.graph_degree, h_data, h_centroids, build_param.metric);
-        append_result(result_file, std::to_string(build_param.graph_degree) + ",");
+        append_result(result_file, stream_text(build_param.graph_degree) + ",");
         index.build(build_param, search_param_knn, search_param_refine, d_knn, seg_start, seg_len, d_map, h_map, d_reorder,
                     h_reorder.rows, result_file, seed);
 

@@ -22,7 +22,7 @@ int main(int argc, char **argv) {
         SearchParameter search_param;
         search_param.top_k = (uint32_t) std::stoi(argv[8]);
         search_param.beam = (uint32_t) std::stoi(argv[9]);
-        append_result(result_file, std::to_string(search_param.beam) + ",");
+        append_result(result_file, stream_text(search_param.beam) + ",");
         derive_search_params(search_param, graph.cols);   // small_search.cu:98-107
         GLIDE index(ctx, graph.cols, data, centroids, metric);
         index.load(graph, start_point);
@@ -30,7 +30,7 @@ int main(int argc, char **argv) {
         HostMatrix<float> result_dists;
         index.search(search_param, query, result_ids, result_dists, result_file);
         const float recall = calculate_recall(result_ids, truth, search_param.top_k);
-        append_result(result_file, std::to_string(recall) + "\n");
+        append_result(result_file, stream_text(recall) + "\n");
     } catch (const std::exception &e) {
         std::cerr << "small_search: " << e.what() << std::endl;
         return 1;

@@ -1,6 +1,7 @@
 // C ABI (include/glide_b200.h): argument checks, scratch memory, stream and timing around
 // the kernel launchers. No compute happens on the host; there is no CPU fallback.
 #include <algorithm>
+#include <atomic>
 #include <cfloat>
 #include <cstdarg>
 #include <cstdio>
@@ -179,6 +180,7 @@ void glide_ctx_destroy(glide_ctx *ctx) {
 const char *glide_last_error(const glide_ctx *ctx) { return ctx ? ctx->error.c_str() : "null context"; }
 void *glide_ctx_stream(glide_ctx *ctx) { return ctx ? (void *) ctx->stream : nullptr; }
 float glide_last_kernel_ms(const glide_ctx *ctx) { return ctx ? ctx->last_ms : 0.0f; }
+size_t glide_ctx_workspace_bytes(const glide_ctx *ctx) { return ctx ? ctx->ws_bytes : 0; }
 
 void glide_last_search_split_ms(const glide_ctx *ctx, float out[2]) {
     if (!ctx || !out) return;
@@ -839,7 +841,7 @@ static __device__ __align__(256) uint32_t g_static_route[kStaticRouteCapacity];
 
 namespace {
 constexpr int kMaxDevices = 64;
-uint32_t *g_static_route_ptr[kMaxDevices] = {};  // device address of g_static_route, per device
+std::atomic<uint32_t *> g_static_route_ptr[kMaxDevices];  // device address of g_static_route, per device (zero-initialised)
 }  // namespace
 
 int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim,
@@ -862,12 +864,12 @@ int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t nu
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
     // First call on this device: resolve the array's device address. In host code the symbol is
     // only a handle, never an address a kernel may use.
-    uint32_t *route = g_static_route_ptr[ctx->device];
-    if (!route) {
+    uint32_t *route = g_static_route_ptr[ctx->device].load(std::memory_order_acquire);
+    if (!route) {   // two threads may both resolve it: they store the same address
         void *addr = nullptr;
         GL_CUDA(ctx, cudaGetSymbolAddress(&addr, g_static_route));
         route = static_cast<uint32_t *>(addr);
-        g_static_route_ptr[ctx->device] = route;
+        g_static_route_ptr[ctx->device].store(route, std::memory_order_release);
     }
     SearchArgs a{};
     a.data = d_data; a.graph = d_graph; a.degree = graph_degree; a.dim = dim;
@@ -878,9 +880,16 @@ int glide_search_static_scratch(glide_ctx *ctx, const float *d_data, uint32_t nu
     Timed timer(ctx);
     // no scratch for the tensor-core prefilter here: this entry point keeps to the exact kernels
     AssignArgs r{d_queries, q, dim, d_centroids, C, -1.0f, metric, route, nullptr, nullptr, nullptr};
-    GL_CUDA(ctx, launch_assign(r, ctx->stream));
+    uint32_t launched = 0;
+    GL_CUDA(ctx, launch_assign(r, ctx->stream, &launched));
+    GL_CUDA(ctx, cudaEventRecord(ctx->ev_mid, ctx->stream));
     GL_CUDA(ctx, launch_search(a, ctx->stream));
-    return timer.finish();
+    ctx->last_launches = launched + 1;
+    rc = timer.finish();
+    if (rc) return rc;
+    cudaEventElapsedTime(&ctx->split_ms[0], ctx->ev_start, ctx->ev_mid);
+    cudaEventElapsedTime(&ctx->split_ms[1], ctx->ev_mid, ctx->ev_stop);
+    return GLIDE_OK;
 }
 
 // ---- large path ------------------------------------------------------------------------------

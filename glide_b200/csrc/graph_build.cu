@@ -281,7 +281,12 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
         __syncwarp();
         bool wide = false;
         // kModeRefine: routed by the pre-pass (search_kernel.cuh:258-269 via graph_kernel.cuh:638-642)
-        const uint32_t start = a.mode == kModeRefine ? a.start_points[a.route[point - a.route_first]] : a.start_points[0];
+        uint32_t routed = 0;
+        if (a.mode == kModeRefine) {
+            routed = a.route[point - a.route_first];
+            if (routed >= a.C) routed = 0;   // the routing kernels never write an id beyond C; checked all the same
+        }
+        const uint32_t start = a.start_points[routed];
         const uint32_t exclude = a.mode == kModeRefine ? kInvalid : point;
         if constexpr (LANES) {
             float ck;

@@ -41,7 +41,10 @@ __global__ void __launch_bounds__(256) assign_kernel(const AssignArgs a, uint32_
     const uint32_t c0 = nearest_centroid(query, a.centroids, a.C, max_centroid, a.dim, a.metric, scratch,
                                          a.is_boundary ? kTopTwo : kNearestOnly);
     if (lane == 0) {
-        a.nearest[p] = c0;
+        // A point with a NaN coordinate has NaN distances to every centroid; the network then leaves
+        // a padding slot (id 0xffffffff) in front. Such a point goes to partition 0, so that no
+        // caller ever indexes start points or segment tables with an id beyond C.
+        a.nearest[p] = c0 < a.C ? c0 : 0u;
         if (a.is_boundary) {
             const float *ck = reinterpret_cast<const float *>(scratch);
             // partition_kernel.cuh:58-60

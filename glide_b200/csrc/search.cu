@@ -62,7 +62,8 @@ __device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &
     uint32_t start_node;
     if (!sub) {
         // the nearest centroid was found by the routing pre-pass (search_kernel.cuh:258-269)
-        start_node = a.start_points[a.route[q]];
+        const uint32_t r = a.route[q];
+        start_node = a.start_points[r < a.C ? r : 0u];   // the routing kernels never write an id beyond C; checked all the same
     } else {
         start_node = a.start_point;
     }

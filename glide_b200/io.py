@@ -36,6 +36,10 @@ def save_matrix_data(path: str, matrix: np.ndarray) -> None:
     m = np.ascontiguousarray(matrix)
     if m.ndim != 2:
         raise ValueError("matrix must be 2-D")
+    if m.dtype not in (np.float32, np.uint32, np.int32, np.uint8):
+        # readers take the element type from the caller, not from the file (load.cuh:10-30): writing
+        # float64 or int64 under this header would be read back as twice as many 4-byte values
+        raise TypeError(f"matrix files hold fp32, u32/i32 or uint8 elements, got {m.dtype}")
     with open(path, "wb") as f:
         np.array(m.shape, dtype=np.uint32).tofile(f)
         m.tofile(f)

@@ -54,6 +54,9 @@ void glide_ctx_destroy(glide_ctx *ctx);
 const char *glide_last_error(const glide_ctx *ctx);
 /* cudaStream_t of the context, for callers that enqueue their own work around the calls. */
 void *glide_ctx_stream(glide_ctx *ctx);
+/* Bytes of the context's scratch arena (grown on demand by the calls that need scratch, never
+ * shrunk before glide_ctx_destroy). No counterpart in the reference (RMM pools its memory). */
+size_t glide_ctx_workspace_bytes(const glide_ctx *ctx);
 /* Elapsed device milliseconds of the kernels of the most recent call on this context
  * (the reference's timing convention: cudaEvent pairs around kernels, glide_impl.cuh:144-147). */
 float glide_last_kernel_ms(const glide_ctx *ctx);

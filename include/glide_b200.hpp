@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <fstream>
 #include <stdexcept>
+#include <sstream>
 #include <string>
 #include <vector>
 
@@ -209,6 +210,15 @@ private:
     size_t count_ = 0;
 };
 
+// Numbers go into result files the way the reference streams them (`file << value`, e.g.
+// small_search.cu:121-126): "0.9514", not std::to_string's "0.951400".
+template<typename T>
+inline std::string stream_text(T value) {
+    std::ostringstream out;
+    out << value;
+    return out.str();
+}
+
 inline void append_result(const std::string &file, const std::string &text) {
     std::ofstream out(file, std::ios::app);
     out << text;
@@ -235,7 +245,7 @@ inline void preprocess(const Context &ctx, const PartitionParameter &param, cons
     d_map.adopt(ctx, map, reorder_num);
     const float seconds = ctx.last_kernel_seconds();
     std::printf("preprocessing time: %g s\n", seconds);
-    if (!result_file.empty()) append_result(result_file, std::to_string(seconds) + ",");
+    if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
 }
 
 // ---- build_nnd (nn_descent.cuh:1405-1467) ---------------------------------------------------
@@ -256,7 +266,7 @@ inline HostMatrix<int> build_nnd(const Context &ctx, const NNDescentParameter &p
     HostMatrix<int> out(num, degree);
     d_knn.download(out.data_handle(), out.size());
     std::printf("knn time: %g s\n", seconds);
-    if (!result_file.empty()) append_result(result_file, std::to_string(seconds) + ",");
+    if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
     return out;
 }
 
@@ -319,7 +329,7 @@ public:
             build_time += ctx_.last_kernel_seconds();
         }
         std::printf("index build time: %g s\n", build_time);
-        if (!result_file.empty()) append_result(result_file, std::to_string(build_time) + ",");
+        if (!result_file.empty()) append_result(result_file, stream_text(build_time) + ",");
     }
 
     // GLIDE::search (glide_impl.cuh:370-454): host queries in, host results out
@@ -335,7 +345,7 @@ public:
                                 d_dists.data_handle()));
         const float seconds = ctx_.last_kernel_seconds();
         std::printf("query time: %g s   QPS: %g\n", seconds, h_query.rows / seconds);
-        if (!result_file.empty()) append_result(result_file, std::to_string(seconds) + "," + std::to_string(h_query.rows / seconds) + ",");
+        if (!result_file.empty()) append_result(result_file, stream_text(seconds) + "," + stream_text(h_query.rows / seconds) + ",");
         result_ids = HostMatrix<uint32_t>(h_query.rows, param.top_k);
         result_dists = HostMatrix<float>(h_query.rows, param.top_k);
         d_ids.download(result_ids.data_handle(), result_ids.size());

@@ -72,7 +72,7 @@ inline void preprocess_for_large(const Context &ctx, const PartitionParameter &p
     h_centroids = HostMatrix<float>(C, dim);
     d_centroids.download(h_centroids.data_handle(), h_centroids.size());
     std::printf("preprocessing time: %g s\n", seconds);
-    if (!result_file.empty()) append_result(result_file, std::to_string(seconds) + ",");
+    if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
 }
 
 // kNN graph of every partition, one resident partition at a time; partition-local ids.
@@ -98,7 +98,7 @@ inline HostMatrix<int> build_knn_for_large(const Context &ctx, const NNDescentPa
         d_knn.download(knn.data_handle() + (size_t) start * degree, (size_t) len * degree);
     }
     std::printf("knn time: %g s\n", seconds);
-    if (!result_file.empty()) append_result(result_file, std::to_string(seconds) + ",");
+    if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
     return knn;
 }
 
@@ -172,7 +172,7 @@ public:
             d_graph.download(graph_.data_handle() + (size_t) start * degree_, (size_t) len * degree_);
         }
         std::printf("index build time: %g s\n", seconds);
-        if (!result_file.empty()) append_result(result_file, std::to_string(seconds) + ",");
+        if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
     }
 
     // glide_large_impl.cuh:355-507: route every query to the partitions within boundary_factor of
@@ -204,7 +204,7 @@ public:
             seconds += ctx_.last_kernel_seconds();
         }
         std::printf("query time: %g s   QPS: %g\n", seconds, q / seconds);
-        if (!result_file.empty()) append_result(result_file, std::to_string(seconds) + "," + std::to_string(q / seconds) + ",");
+        if (!result_file.empty()) append_result(result_file, stream_text(seconds) + "," + stream_text(q / seconds) + ",");
         result_ids = HostMatrix<uint32_t>(q, param.top_k);
         result_dists = HostMatrix<float>(q, param.top_k);
         d_ids.download(result_ids.data_handle(), result_ids.size());

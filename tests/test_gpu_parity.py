@@ -68,6 +68,65 @@ def test_search_matches_oracle(gpu_ctx, name, beam):
     assert np.allclose(got_d[same], ref_d[same], rtol=1e-5)
 
 
+# Adjacency rows wider than 32 entries take the shared-memory candidate path (beam_loop) in the
+# search, build and refine kernels; the cases above (degree 16) never reach it. 64 is the 960-dim
+# benchmark configuration's degree (with a kNN degree of 64), 48 a ragged width (one and a half
+# 32-lane rounds).
+WIDE_CASES = {
+    "scaled960_d64": dict(kind="scaled", n=1500, dim=960, nq=60, metric=oracle.EUCLIDEAN, degree=64),
+    "unit96_d48": dict(kind="unit", n=2500, dim=96, nq=100, metric=oracle.COSINE, degree=48),
+    "int128_d64": dict(kind="int", n=3000, dim=128, nq=150, metric=oracle.EUCLIDEAN, degree=64),   # exact ties occur
+}
+
+
+def wide_case(name):
+    key = "wide:" + name
+    if key not in _cache:
+        c = WIDE_CASES[name]
+        base, queries = helpers.small_dataset(c["kind"], c["n"], c["dim"], c["nq"])
+        P = helpers.oracle_pipeline(base, metric=c["metric"], knn_degree=c["degree"], graph_degree=c["degree"],
+                                    build_beam=64, refine_beam=128)
+        _cache[key] = (base, queries, P)
+    return _cache[key]
+
+
+@pytest.mark.parametrize("name", sorted(WIDE_CASES))
+@pytest.mark.parametrize("beam", [32, 64, 100, 256])
+def test_search_on_wide_adjacency_rows_matches_oracle(gpu_ctx, name, beam):
+    base, queries, P = wide_case(name)
+    metric, degree = P["metric"], P["graph"].shape[1]
+    o = oracle.SearchParams.derive(beam, degree, top_k=10)
+    want_ids, want_d = oracle.search(base, P["graph"], P["centroids"], P["orig_sp"], queries, o, metric)
+    d_ids, d_d, _ = api.search(gpu_ctx, dev(gpu_ctx, base), dev(gpu_ctx, P["graph"]), dev(gpu_ctx, P["centroids"]),
+                               dev(gpu_ctx, P["orig_sp"]), dev(gpu_ctx, queries), sp_from(o), Metric(metric))
+    got_ids, got_d = api.to_u32(d_ids), d_d.cpu().numpy()
+    assert np.array_equal(got_ids, want_ids)
+    assert np.array_equal(got_d, want_d)
+    ref_ids, ref_d = oracle.search(base, P["graph"], P["centroids"], P["orig_sp"], queries, o, metric,
+                                   order=oracle.ORDER_REF)
+    same = (ref_ids == got_ids)
+    assert same.mean() > 0.99
+    assert np.allclose(got_d[same], ref_d[same], rtol=1e-5)
+
+
+@pytest.mark.parametrize("name", sorted(WIDE_CASES))
+def test_build_stages_on_wide_rows_match_oracle(gpu_ctx, name):
+    base, _, P = wide_case(name)
+    metric, degree = Metric(P["metric"]), P["graph"].shape[1]
+    n = base.shape[0]
+    d_re, d_knn = dev(gpu_ctx, P["reorder_data"]), dev(gpu_ctx, P["knn"].view(np.uint32))
+    d_map, d_local = dev(gpu_ctx, P["mapping"]), dev(gpu_ctx, P["local_sp"])
+    g = api._u32_tensor(gpu_ctx, (n, degree)); g.fill_(-1)
+    api.subgraph_build_and_merge(gpu_ctx, d_re, d_knn, P["seg_start"], P["seg_len"], d_local, d_map, n, g,
+                                 sp_from(P["p_build"]), P["alpha"], metric)
+    assert np.array_equal(api.to_u32(g), P["after_boundary"])
+    api.reverse_graph(gpu_ctx, g)
+    assert np.array_equal(api.to_u32(g), P["after_reverse"])
+    api.refine(gpu_ctx, dev(gpu_ctx, base), g, dev(gpu_ctx, P["centroids"]), dev(gpu_ctx, P["orig_sp"]),
+               sp_from(P["p_refine"]), P["alpha"], metric)
+    assert np.array_equal(api.to_u32(g), P["graph"])
+
+
 def test_search_host_entry_point(gpu_ctx):
     base, queries, P = case("int128")
     o = oracle.SearchParams.derive(64, 16, top_k=10)

@@ -53,3 +53,46 @@ def test_static_scratch_search_equals_regular_search_twice(gpu_ctx):
     assert rc == -2 and b"65536" in lib.glide_last_error(ctx.handle)
     rc, ids, _ = _search(ctx, lib.glide_search_static_scratch, d_base, d_graph, d_cent, d_sp, dev(queries[:8].copy()), sp)
     assert rc == 0 and ids.shape == (8, 10)
+
+
+def test_static_scratch_search_allocates_nothing():
+    """What the entry point's name promises: on a context that has never grown its scratch arena,
+    a call leaves the arena at zero bytes and the device's free memory where it was."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    base, queries = helpers.small_dataset("int", 2000, 64, 200, seed=22)
+    P = helpers.oracle_pipeline(base)
+    ctx = api.Context(0)     # a fresh context: no earlier call has allocated scratch on it
+    try:
+        dev = lambda a: api.from_u32(ctx, a) if a.dtype == np.uint32 else torch.from_numpy(a).to(ctx.torch_device)
+        d_base, d_graph, d_cent, d_sp = dev(base), dev(P["graph"]), dev(P["centroids"]), dev(P["orig_sp"])
+        d_q = dev(queries)
+        sp = SearchParameter(top_k=10, beam=64).derive(16)
+        lib = ctx.lib
+        assert lib.glide_ctx_workspace_bytes(ctx.handle) == 0
+        # the first call resolves the array's address and loads the kernels; measure around the second
+        rc, ids_0, _ = _search(ctx, lib.glide_search_static_scratch, d_base, d_graph, d_cent, d_sp, d_q, sp)
+        assert rc == 0, lib.glide_last_error(ctx.handle)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(ctx.torch_device)
+        q = d_q.shape[0]
+        d_ids = api._u32_tensor(ctx, (q, sp.top_k))
+        d_d = ctx.empty((q, sp.top_k), torch.float32)
+        pc = api._params_c(sp)
+        torch.cuda.synchronize()
+        free_mid, _ = torch.cuda.mem_get_info(ctx.torch_device)   # the output tensors are the caller's, taken before
+        rc = lib.glide_search_static_scratch(ctx.handle, d_base.data_ptr(), d_base.shape[0], d_base.shape[1],
+                                             d_graph.data_ptr(), d_graph.shape[1], d_cent.data_ptr(), d_cent.shape[0],
+                                             d_sp.data_ptr(), d_q.data_ptr(), q, C.byref(pc), 0, d_ids.data_ptr(),
+                                             d_d.data_ptr())
+        assert rc == 0, lib.glide_last_error(ctx.handle)
+        free_after, _ = torch.cuda.mem_get_info(ctx.torch_device)
+        assert free_after == free_mid <= free_before
+        assert lib.glide_ctx_workspace_bytes(ctx.handle) == 0
+        assert np.array_equal(api.to_u32(d_ids), ids_0)
+        # the regular entry point does grow the arena (that is the difference between the two)
+        rc, ids_1, _ = _search(ctx, lib.glide_search, d_base, d_graph, d_cent, d_sp, d_q, sp)
+        assert rc == 0 and np.array_equal(ids_1, ids_0)
+        assert lib.glide_ctx_workspace_bytes(ctx.handle) > 0
+    finally:
+        ctx.close()
