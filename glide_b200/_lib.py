@@ -49,6 +49,7 @@ SIGNATURES = {
     "glide_reverse_graph": (i32, [vp, vp, u32, u32]),
     "glide_refine_range": (i32, [vp, vp, u32, u32, vp, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32, u32]),
     "glide_refine": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32]),
+    "glide_refine_waves": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32]),
     "glide_search": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_search_host": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_search_static_scratch": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),

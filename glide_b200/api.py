@@ -268,13 +268,18 @@ def reverse_graph(ctx: Context, d_graph):
 
 
 def refine(ctx: Context, d_data, d_graph, d_centroids, d_start_points, p: SearchParameter, relaxant_factor: float,
-           metric: Metric = Metric.Euclidean):
-    """glide_impl.cuh:258-317, in place."""
+           metric: Metric = Metric.Euclidean, wave_rows: int | None = None):
+    """glide_impl.cuh:258-317, in place. wave_rows: points are refined in waves of that many consecutive
+    ids, each wave reading the rows the earlier ones wrote (None: the library's default of 65,536;
+    0: one wave)."""
     pc = _params_c(p)
     ctx.sync_inputs()
-    ctx.check(ctx.lib.glide_refine(ctx.handle, _ptr(d_data), d_data.shape[0], d_data.shape[1], _ptr(d_graph),
-                                   d_graph.shape[1], _ptr(d_centroids), d_centroids.shape[0], _ptr(d_start_points),
-                                   C.byref(pc), relaxant_factor, int(metric)))
+    args = (ctx.handle, _ptr(d_data), d_data.shape[0], d_data.shape[1], _ptr(d_graph), d_graph.shape[1], _ptr(d_centroids),
+            d_centroids.shape[0], _ptr(d_start_points), C.byref(pc), relaxant_factor, int(metric))
+    if wave_rows is None:
+        ctx.check(ctx.lib.glide_refine(*args))
+    else:
+        ctx.check(ctx.lib.glide_refine_waves(*args, wave_rows))
     return ctx.last_kernel_seconds
 
 

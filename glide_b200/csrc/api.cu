@@ -5,6 +5,7 @@
 #include <cfloat>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -27,6 +28,7 @@ struct glide_ctx {
     size_t ws_bytes = 0;
     unsigned long long *counters = nullptr;  // 4 x u64 on the device
     uint32_t *ticket = nullptr;              // one word: the search kernel's query counter
+    uint32_t *start_point_word = nullptr;    // one word: the start point of a per-partition refine
     uint32_t last_launches = 0;              // kernels enqueued by the last glide_search
     float *tc_norms = nullptr;               // centroid norms for the assignment's tensor-core prefilter (up to 4096 centroids)
     bool counters_on = false;
@@ -147,10 +149,11 @@ int glide_ctx_create(int device, glide_ctx **out) {
         cudaEventCreate(&ctx->ev_mid) != cudaSuccess ||
         cudaMalloc(&ctx->counters, 4 * sizeof(unsigned long long)) != cudaSuccess ||
         cudaMalloc(&ctx->tc_norms, (4096 + 128 + 1) * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&ctx->ticket, sizeof(uint32_t)) != cudaSuccess) {
+        cudaMalloc(&ctx->ticket, 2 * sizeof(uint32_t)) != cudaSuccess) {
         delete ctx;
         return GLIDE_ERR_CUDA;
     }
+    ctx->start_point_word = ctx->ticket + 1;
     // load the common kernel instances and let the driver size its local-memory reservation now,
     // not inside the first timed stage
     if (preload_build_kernels(ctx->stream) != cudaSuccess || preload_search_kernels(ctx->stream) != cudaSuccess ||
@@ -675,37 +678,61 @@ cudaError_t make_partition_order(const uint32_t *route, uint32_t count, uint32_t
     return launch_scatter_members(route, o.slot, o.offsets, count, o.order, st);
 }
 
+// Points are refined in waves of wave_rows consecutive ids (0: one wave). Every search of a wave
+// reads the graph as the waves before it left it; the wave's rows go to a staging buffer and are
+// copied into the graph when the wave's kernel is done, so the result does not depend on the order
+// in which warps run. The reference refines in place while other CTAs traverse the rows
+// (graph_kernel.cuh:648, :660-671): a point there sees the rows of (roughly) all points with
+// smaller ids already refined, which is what consecutive waves reproduce up to the wave size.
+constexpr uint32_t kDefaultRefineWaveRows = 65536;
+
+uint32_t default_refine_wave_rows() {
+    static const uint32_t rows = [] {
+        const char *e = std::getenv("GLIDE_B200_REFINE_WAVE");   // experiments: another wave size (0 = one wave)
+        return e ? (uint32_t) std::strtoul(e, nullptr, 10) : kDefaultRefineWaveRows;
+    }();
+    return rows;
+}
+
 static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
                          uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
-                         const glide_search_params *p, float relaxant_factor, int metric) {
+                         const glide_search_params *p, float relaxant_factor, int metric, uint32_t wave_rows) {
     GL_REQUIRE(ctx, d_data && d_graph && d_start_points && num > 0 && dim > 0, GLIDE_ERR_BAD_ARG, "refine: bad argument");
     int rc = check_params(ctx, p, graph_degree);
     if (rc) return rc;
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
-    const size_t graph_bytes = (size_t) num * graph_degree * 4;
+    if (wave_rows == 0 || wave_rows > num) wave_rows = num;
+    const size_t stage_bytes = (size_t) wave_rows * graph_degree * 4;
     const bool routed = mode == kModeRefine;
-    rc = ensure_ws(ctx, align256(graph_bytes) + align256((size_t) num * 4) + (routed ? order_scratch_bytes(num, C) : 0));
+    rc = ensure_ws(ctx, align256(stage_bytes) + align256((size_t) num * 4) + (routed ? order_scratch_bytes(wave_rows, C) : 0));
     if (rc) return rc;
-    uint32_t *snapshot = static_cast<uint32_t *>(ctx->ws);
-    uint32_t *route = reinterpret_cast<uint32_t *>(static_cast<char *>(ctx->ws) + align256(graph_bytes));
-    const uint32_t *order = nullptr;
+    uint32_t *staging = static_cast<uint32_t *>(ctx->ws);
+    uint32_t *route = reinterpret_cast<uint32_t *>(static_cast<char *>(ctx->ws) + align256(stage_bytes));
     Timed timer(ctx);
-    GL_CUDA(ctx, cudaMemcpyAsync(snapshot, d_graph, graph_bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    OrderScratch o{};
     if (routed) {
         AssignArgs r{d_data, num, dim, d_centroids, C, -1.0f, metric, route, nullptr, C <= 4096 ? ctx->tc_norms : nullptr, nullptr};
         GL_CUDA(ctx, launch_assign(r, ctx->stream));
-        const OrderScratch o = carve_order_scratch(reinterpret_cast<char *>(route) + align256((size_t) num * 4), num, C);
-        GL_CUDA(ctx, make_partition_order(route, num, C, o, ctx->stream));
-        order = o.order;
+        o = carve_order_scratch(reinterpret_cast<char *>(route) + align256((size_t) num * 4), wave_rows, C);
     }
-    BuildArgs a{};
-    a.mode = mode;
-    a.data = d_data; a.dim = dim; a.graph_in = snapshot; a.in_degree = graph_degree;
-    a.graph_out = d_graph; a.out_degree = graph_degree;
-    a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route; a.order = order;
-    a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
-    a.counters = counters_or_null(ctx);
-    GL_CUDA(ctx, launch_build(a, ctx->stream));
+    unsigned long long *counters = counters_or_null(ctx);
+    for (uint32_t lo = 0; lo < num; lo += wave_rows) {
+        const uint32_t count = num - lo < wave_rows ? num - lo : wave_rows;
+        BuildArgs a{};
+        if (routed) {   // the wave's points grouped by partition: warps that run together share L2 lines
+            GL_CUDA(ctx, make_partition_order(route + lo, count, C, o, ctx->stream));
+            a.order = o.order;
+        }
+        a.mode = mode;
+        a.data = d_data; a.dim = dim; a.graph_in = d_graph; a.in_degree = graph_degree;
+        a.graph_out = staging; a.out_first = lo; a.out_degree = graph_degree;
+        a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route;
+        a.first = lo; a.count = count; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
+        a.counters = counters;
+        GL_CUDA(ctx, launch_build(a, ctx->stream));
+        GL_CUDA(ctx, cudaMemcpyAsync(d_graph + (size_t) lo * graph_degree, staging, (size_t) count * graph_degree * 4,
+                                     cudaMemcpyDeviceToDevice, ctx->stream));
+    }
     return timer.finish();
 }
 
@@ -742,14 +769,21 @@ int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32
     return timer.finish();
 }
 
-int glide_refine(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
-                 uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
-                 const glide_search_params *p, float relaxant_factor, int metric) {
+int glide_refine_waves(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                       uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
+                       const glide_search_params *p, float relaxant_factor, int metric, uint32_t wave_rows) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
     GL_REQUIRE(ctx, d_centroids && C >= 1, GLIDE_ERR_BAD_ARG, "refine: centroids missing");
     GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
     return refine_common(ctx, kModeRefine, d_data, num, dim, d_graph, graph_degree, d_centroids, C, d_start_points, p,
-                         relaxant_factor, metric);
+                         relaxant_factor, metric, wave_rows);
+}
+
+int glide_refine(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                 uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
+                 const glide_search_params *p, float relaxant_factor, int metric) {
+    return glide_refine_waves(ctx, d_data, num, dim, d_graph, graph_degree, d_centroids, C, d_start_points, p,
+                              relaxant_factor, metric, default_refine_wave_rows());
 }
 
 // ---- search ----------------------------------------------------------------------------------
@@ -963,14 +997,11 @@ int glide_refine_partition(glide_ctx *ctx, const float *d_data, uint32_t num, ui
                            float relaxant_factor, int metric) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
-    uint32_t *d_sp = nullptr;
-    GL_CUDA(ctx, cudaMalloc(&d_sp, 4));
-    cudaError_t e = cudaMemcpy(d_sp, &start_point, 4, cudaMemcpyHostToDevice);
-    int rc = (e == cudaSuccess) ? refine_common(ctx, kModeRefineRow, d_data, num, dim, d_graph, graph_degree, nullptr, 1,
-                                                d_sp, p, relaxant_factor, metric)
-                                : fail(ctx, GLIDE_ERR_CUDA, "cudaMemcpy failed: %s", cudaGetErrorString(e));
-    cudaFree(d_sp);
-    return rc;
+    // the start point travels in the context's own device word (ordered before the kernels on the stream)
+    GL_CUDA(ctx, cudaMemcpyAsync(ctx->start_point_word, &start_point, 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // `start_point` is a stack variable of this call
+    return refine_common(ctx, kModeRefineRow, d_data, num, dim, d_graph, graph_degree, nullptr, 1, ctx->start_point_word,
+                         p, relaxant_factor, metric, default_refine_wave_rows());
 }
 
 }  // extern "C"

@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
         // written to graph_out; the caller passes a snapshot as graph_in so that results
         // do not depend on the order in which points finish.
         const uint32_t *in_row = a.graph_in + (uint64_t) point * degree;
-        uint32_t *out = a.graph_out + (uint64_t) point * degree;
+        uint32_t *out = a.graph_out + (uint64_t) (point - a.out_first) * degree;
         uint32_t need = 0;
         for (uint32_t base = 0; base < d.max_degree; base += 32) {
             const uint32_t i = base + lane;

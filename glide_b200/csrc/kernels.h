@@ -62,6 +62,7 @@ struct BuildArgs {
     const uint32_t *graph_in;  // kNN graph (build/boundary) or the merged graph snapshot (refine)
     uint32_t in_degree;
     uint32_t *graph_out;
+    uint32_t out_first;        // refine: row of point p is written at graph_out + (p - out_first) * out_degree
     uint32_t out_degree;
     const uint32_t *seg_start, *seg_len;  // device, S entries (build/boundary)
     uint32_t S;

@@ -2,6 +2,8 @@
 // search_kernel.cuh:393-490), the large path's query routing (select_segment_kernel,
 // :546-607) and per-partition search with running top-k merge (search_on_sub_kernel +
 // result_merge, :609-765).
+#include <cstdlib>
+
 #include "beam_core.cuh"
 #include "kernels.h"
 
@@ -167,8 +169,11 @@ __global__ void __launch_bounds__(256, NB == 2 ? 4 : (NB == 4 ? 3 : 2)) search_k
     search_body<NB, NC, LANES>(d);
 }
 
+// 32-slot beams: nine warps per CTA and four CTAs per SM (56 registers) hold 36 queries per SM at
+// once, 5,328 on 148 SMs, so that a batch of 10,000 queries is two full rounds; with eight warps
+// (4,736 at once) the same batch is two rounds and a third with a tenth of the warps busy.
 template<int NC, bool LANES>
-__global__ void __launch_bounds__(256) search_kernel_32(const SearchDev d) {
+__global__ void __launch_bounds__(288, 4) search_kernel_32(const SearchDev d) {
     search_body<1, NC, LANES>(d);
 }
 
@@ -262,6 +267,14 @@ cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
     if (strip_bytes * warps > 200 * 1024) return cudaErrorInvalidValue;
     const int nb = max_beam / 32, nc = max_cand / 32;
     if (lanes) {
+        if (a.p.beam <= 32 && warps == 8 && strip_bytes * 9 * 4 <= 200 * 1024) {
+            static const uint32_t w32 = [] {   // experiments: GLIDE_B200_SEARCH_WARPS=8 restores eight warps per CTA
+                const char *e = std::getenv("GLIDE_B200_SEARCH_WARPS");
+                const uint32_t v = e ? (uint32_t) std::strtoul(e, nullptr, 10) : 9u;
+                return (v >= 1 && v <= 9) ? v : 9u;
+            }();
+            warps = w32;
+        }
         const size_t bytes = strip_bytes * warps;
         if (a.p.beam <= 32) return launch_search_t<1, 2, true>(d, warps, bytes, stream);
         if (nb == 2) return launch_search_t<2, 2, true>(d, warps, bytes, stream);

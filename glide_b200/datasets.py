@@ -38,6 +38,12 @@ CONFIGS = {
     "cfg2": DatasetSpec("cfg2", 1_000_000, 960, 1_000, "scaled_mixture", 256, "Euclidean", 64, 2),
     # 10M x 96 cosine: 4,096 centres N(0,1), sigma 0.5, rows normalised
     "cfg3": DatasetSpec("cfg3", 10_000_000, 96, 10_000, "unit_mixture", 4096, "Cosine", 32, 3),
+    # cfg1's generator with 32 mixture components instead of 1,024: with one partition per component
+    # (32 partitions of ~31,000 rows) it lies inside the reference's own size ladders (at most 32
+    # centroids for its 32-entry routing network, kernel_config.cuh:161-171), so the reference's
+    # kernels and this library can be compared at a recall that means something; the partitions are
+    # also large enough for NN-descent to run instead of the all-pairs kernel
+    "cfg1c32": DatasetSpec("cfg1c32", 1_000_000, 128, 10_000, "int_mixture", 32, "Euclidean", 32, 11),
     # 100M x 128: as cfg1 with 16,384 centres
     "cfg4": DatasetSpec("cfg4", 100_000_000, 128, 10_000, "int_mixture", 16384, "Euclidean", 32, 4),
 }

@@ -148,10 +148,19 @@ int glide_subgraph_build_range(glide_ctx *ctx, const float *d_reorder_data, uint
                                int metric, uint32_t first_row, uint32_t row_count, uint32_t *d_graph);
 /* reverse_graph, glide_impl.cuh:194-256. In place. */
 int glide_reverse_graph(glide_ctx *ctx, uint32_t *d_graph, uint32_t num, uint32_t graph_degree);
-/* refine, glide_impl.cuh:258-317. In place (a snapshot is taken internally). */
+/* refine, glide_impl.cuh:258-317. In place. The reference's refine_kernel fills rows while other
+ * CTAs still traverse them (graph_kernel.cuh:648, :660-671), so its result depends on the schedule;
+ * here the points are taken in waves of 65,536 consecutive ids: a wave's searches read the rows the
+ * earlier waves wrote, its own rows are written when the wave is done (same result on every run). */
 int glide_refine(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
                  uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
                  const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor, int metric);
+/* glide_refine with the wave size given (0: one wave, every search reads the graph as it was before
+ * the call). Same reference lines as glide_refine. */
+int glide_refine_waves(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, uint32_t *d_graph,
+                       uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
+                       const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor,
+                       int metric, uint32_t wave_rows);
 
 /* refine for points [first, first + count): searches read d_graph_in (the graph before
  * refinement), the refined rows are written to d_graph_out (a different buffer; rows outside

@@ -170,17 +170,23 @@ def reverse_graph(graph):
 
 
 def refine(data, graph_in, centroids, start_points, p: SearchParams, alpha, metric=EUCLIDEAN,
-           order=ORDER_WARP, threads=0, route_order=None, pool_sizes=None):
+           order=ORDER_WARP, threads=0, route_order=None, pool_sizes=None, wave_rows=0):
+    """wave_rows: points are refined in waves of that many consecutive ids, each wave reading the rows
+    the earlier waves wrote (0: a single wave, i.e. every search reads the graph as it was before).
+    centroids=None: the large path's variant (one partition, seeded from start_points[0]'s row)."""
     if route_order is None:
         route_order = ORDER_REF if order == ORDER_REF else ORDER_TEAM
-    data, centroids = _f32(data), _f32(centroids)
-    graph_in, start_points = _u32(graph_in), _u32(start_points)
+    data = _f32(data)
+    row_mode = centroids is None
+    if not row_mode:
+        centroids = _f32(centroids)
+    graph_in, start_points = _u32(graph_in), _u32(np.atleast_1d(start_points))
     out = np.empty_like(graph_in)
     rc = lib().orc_refine(_p(data), u32(data.shape[0]), u32(data.shape[1]), _p(graph_in), _p(out),
-                          u32(graph_in.shape[1]), _p(centroids), u32(centroids.shape[0]), _p(start_points),
-                          u32(p.beam), u32(p.max_iterations), u32(p.min_iterations), u32(p.hash_bit),
+                          u32(graph_in.shape[1]), _p(centroids), u32(1 if row_mode else centroids.shape[0]),
+                          _p(start_points), u32(p.beam), u32(p.max_iterations), u32(p.min_iterations), u32(p.hash_bit),
                           u32(p.hash_reset_interval), f32(alpha), i32(metric), i32(order), i32(route_order),
-                          _p(pool_sizes), i32(threads))
+                          _p(pool_sizes), i32(threads), u32(wave_rows), i32(1 if row_mode else 0))
     if rc != 0:
         raise ValueError("orc_refine: unsupported shape")
     return out

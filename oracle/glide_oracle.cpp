@@ -769,38 +769,50 @@ int orc_reverse_graph(uint32_t *graph, uint32_t num, uint32_t degree) {
     return 0;
 }
 
-// refine_kernel, graph_kernel.cuh:580-673. The reference updates rows in place
-// while other CTAs traverse them; here every search reads graph_in (the state
-// before refinement) and writes graph_out, which is the outcome of the reference
-// when all reads precede all writes.
+// refine_kernel, graph_kernel.cuh:580-673, and refine_for_large_kernel, :730-821 (row_mode: no
+// centroids, the search is seeded from start_points[0]'s row with the point itself excluded,
+// graph_kernel.cuh:790-792). The reference updates rows in place while other CTAs traverse them,
+// so its result depends on the schedule. Here the points are taken in waves of wave_rows
+// consecutive ids: every search of a wave reads the graph as the waves before it left it, and the
+// wave's rows are written when the whole wave is done. This is the outcome of the reference when
+// its CTAs run wave by wave in id order with all reads of a wave preceding its writes.
+// wave_rows == 0: one wave (every search reads the graph as it was before refinement).
 int orc_refine(const float *data, uint32_t num, uint32_t dim, const uint32_t *graph_in,
                uint32_t *graph_out, uint32_t degree, const float *centroids, uint32_t C,
                const uint32_t *start_points, uint32_t beam, uint32_t max_iterations,
                uint32_t min_iterations, uint32_t hash_bit, uint32_t hash_reset_interval, float alpha,
-               int metric, int order, int route_order, uint64_t *pool_sizes, int threads) {
+               int metric, int order, int route_order, uint64_t *pool_sizes, int threads,
+               uint32_t wave_rows, int row_mode) {
     if (beam % 32 || beam == 0 || beam > 512 || degree > 256) return -1;
     const SearchCfg cfg{beam, max_iterations, min_iterations, hash_bit, hash_reset_interval};
-    parallel_for(num, threads, [&](int64_t t) {
-        const uint32_t p = (uint32_t) t;
-        const uint32_t *row = graph_in + (uint64_t) p * degree;
-        uint32_t *out = graph_out + (uint64_t) p * degree;
-        uint32_t need = 0;
-        for (uint32_t i = 0; i < degree; i++) need += (row[i] == kInvalid);
-        if (pool_sizes) pool_sizes[p] = beam;  // rows without holes are not searched
-        if (need == 0) {
-            for (uint32_t i = 0; i < degree; i++) out[i] = row[i];
-            return;
-        }
-        const float *query = data + (uint64_t) p * dim;
-        BeamState st(cfg, degree);
-        st.seed_by_centroid(query, data, graph_in, start_points, centroids, C, dim, metric, order, route_order);
-        st.run(cfg, p, graph_in, query, data, dim, metric, order);
-        std::vector<uint32_t> pid;
-        std::vector<float> pdist;
-        st.finish_pool(pid, pdist);
-        if (pool_sizes) pool_sizes[p] = pid.size();
-        prune_refine(data, dim, p, pid, pdist, row, degree, alpha, metric, order, out, nullptr);
-    });
+    if (wave_rows == 0 || wave_rows > num) wave_rows = num;
+    std::vector<uint32_t> cur(graph_in, graph_in + (uint64_t) num * degree);   // what searches read
+    for (uint32_t lo = 0; lo < num; lo += wave_rows) {
+        const uint32_t hi = std::min<uint64_t>(num, (uint64_t) lo + wave_rows);
+        parallel_for(hi - lo, threads, [&](int64_t t) {
+            const uint32_t p = lo + (uint32_t) t;
+            const uint32_t *row = cur.data() + (uint64_t) p * degree;
+            uint32_t *out = graph_out + (uint64_t) p * degree;
+            uint32_t need = 0;
+            for (uint32_t i = 0; i < degree; i++) need += (row[i] == kInvalid);
+            if (pool_sizes) pool_sizes[p] = beam;  // rows without holes are not searched
+            if (need == 0) {
+                for (uint32_t i = 0; i < degree; i++) out[i] = row[i];
+                return;
+            }
+            const float *query = data + (uint64_t) p * dim;
+            BeamState st(cfg, degree);
+            if (row_mode) st.seed_by_row(query, p, data, cur.data(), start_points[0], dim, metric, order);
+            else st.seed_by_centroid(query, data, cur.data(), start_points, centroids, C, dim, metric, order, route_order);
+            st.run(cfg, p, cur.data(), query, data, dim, metric, order);
+            std::vector<uint32_t> pid;
+            std::vector<float> pdist;
+            st.finish_pool(pid, pdist);
+            if (pool_sizes) pool_sizes[p] = pid.size();
+            prune_refine(data, dim, p, pid, pdist, row, degree, alpha, metric, order, out, nullptr);
+        });
+        std::memcpy(cur.data() + (uint64_t) lo * degree, graph_out + (uint64_t) lo * degree, (uint64_t) (hi - lo) * degree * 4);
+    }
     return 0;
 }
 

@@ -54,6 +54,41 @@ def define_partition(d_data, num, dim, d_centroids, c, boundary_factor, metric, 
                                       i32(metric), vp(d_seg_len), vp(d_seg_index))
 
 
+def reorder(d_data, d_reorder, d_seg_index, d_map, d_seg_start, num, dim) -> int:
+    return lib().ref_reorder(vp(d_data), vp(d_reorder), vp(d_seg_index), vp(d_map), vp(d_seg_start), u32(num), u32(dim))
+
+
+# ---- large path (uint8 rows and queries, as the reference instantiates it) ----
+def define_partition_for_large(d_data_u8, batch_size, dim, d_centroids, c, metric, d_seg_len, d_seg_index) -> int:
+    return lib().ref_define_partition_for_large(vp(d_data_u8), u32(batch_size), u32(dim), vp(d_centroids), u32(c), i32(metric),
+                                                vp(d_seg_len), vp(d_seg_index))
+
+
+def build_for_large(d_data_u8, length, dim, d_knn, knn_degree, start_point, graph_degree, p, alpha, metric, d_graph) -> int:
+    return lib().ref_build_for_large(vp(d_data_u8), u32(length), u32(dim), vp(d_knn), u32(knn_degree), u32(start_point),
+                                     u32(graph_degree), u32(p.beam), u32(p.max_iterations), u32(p.min_iterations),
+                                     u32(p.hash_bit), u32(p.hash_reset_interval), f32(alpha), i32(metric), vp(d_graph))
+
+
+def refine_for_large(d_data_u8, length, dim, d_graph, graph_degree, start_point, p, alpha, metric) -> int:
+    return lib().ref_refine_for_large(vp(d_data_u8), u32(length), u32(dim), vp(d_graph), u32(graph_degree), u32(start_point),
+                                      u32(p.beam), u32(p.max_iterations), u32(p.min_iterations), u32(p.hash_bit),
+                                      u32(p.hash_reset_interval), f32(alpha), i32(metric))
+
+
+def select_segments(d_queries_u8, q, dim, d_centroids, c, min_segment_num, boundary_factor, metric, d_segment_ids) -> int:
+    return lib().ref_select_segments(vp(d_queries_u8), u32(q), u32(dim), vp(d_centroids), u32(c), u32(min_segment_num),
+                                     f32(boundary_factor), i32(metric), vp(d_segment_ids))
+
+
+def search_on_sub(d_data_u8, dim, d_graph, graph_degree, d_map, start_point, d_queries_u8, q, d_segment_ids, segment_num,
+                  segment_id, p, metric, d_final_ids, d_final_dists) -> int:
+    return lib().ref_search_on_sub(vp(d_data_u8), u32(dim), vp(d_graph), u32(graph_degree), vp(d_map), u32(start_point),
+                                   vp(d_queries_u8), u32(q), vp(d_segment_ids), u32(segment_num), u32(segment_id),
+                                   u32(p.top_k), u32(p.beam), u32(p.max_iterations), u32(p.min_iterations), u32(p.hash_bit),
+                                   u32(p.hash_reset_interval), i32(metric), vp(d_final_ids), vp(d_final_dists))
+
+
 def last_seconds() -> float:
     """Device time of the kernels of the last harness call (CUDA events)."""
     f = lib().ref_last_ms

@@ -207,6 +207,41 @@ def test_build_boundary_reverse_refine_match_oracle(gpu_ctx, name):
     assert np.array_equal(api.to_u32(g), P["graph"])
 
 
+@pytest.mark.parametrize("name", ["int128", "unit96", "uniform30"])
+@pytest.mark.parametrize("wave_rows", [0, 700, 64])
+def test_refine_in_waves_matches_oracle(gpu_ctx, name, wave_rows):
+    """Waves of consecutive ids: a wave's searches read the rows the earlier waves wrote. 0 is one wave;
+    700 leaves a ragged last wave; 64 makes the later waves walk a graph that is mostly refined."""
+    base, _, P = case(name)
+    metric = P["metric"]
+    want = oracle.refine(base, P["after_reverse"], P["centroids"], P["orig_sp"], P["p_refine"], P["alpha"], metric,
+                         wave_rows=wave_rows)
+    g = dev(gpu_ctx, P["after_reverse"])
+    api.refine(gpu_ctx, dev(gpu_ctx, base), g, dev(gpu_ctx, P["centroids"]), dev(gpu_ctx, P["orig_sp"]),
+               sp_from(P["p_refine"]), P["alpha"], Metric(metric), wave_rows=wave_rows)
+    assert np.array_equal(api.to_u32(g), want)
+    if wave_rows:   # the waves matter: the result differs from the single-wave one
+        assert not np.array_equal(want, P["graph"])
+
+
+def test_refine_of_one_partition_matches_oracle(gpu_ctx):
+    """The large path's refine (one resident partition, no centroids, seeded from the partition's start point)."""
+    base, _, P = case("int128")
+    lo, ln = int(P["seg_start"][0]), int(P["seg_len"][0])
+    part = np.ascontiguousarray(P["reorder_data"][lo:lo + ln])
+    knn = np.ascontiguousarray(P["knn"][lo:lo + ln]).view(np.uint32)
+    ob, orf = oracle.SearchParams.derive(64, 16), oracle.SearchParams.derive(128, 16)
+    one = np.array([0], np.uint32)
+    g0 = oracle.build_rows(part, knn, one, np.array([ln], np.uint32), np.array([9], np.uint32),
+                           np.arange(ln, dtype=np.uint32), ln, 24, ob, 1.05)
+    oracle.reverse_graph(g0)
+    want = oracle.refine(part, g0, None, 9, orf, 1.05)
+    assert (want != INVALID).sum() > (g0 != INVALID).sum()
+    d_g = dev(gpu_ctx, g0)
+    api.refine_partition(gpu_ctx, dev(gpu_ctx, part), d_g, 9, sp_from(orf), 1.05)
+    assert np.array_equal(api.to_u32(d_g), want)
+
+
 def test_build_with_wider_graph_than_knn(gpu_ctx):
     # graph_degree 48 > knn_degree 16, beam 64: rows keep holes that reverse edges and refinement fill
     base, _, P = case("uniform16")
