@@ -447,14 +447,15 @@ def run_ours(args):
     cfg = build_config(spec, centroid_num)
     metric = cfg.metric
     if world > 1:
-        # communicator set-up is not part of the build: one tiny collective before the clock starts
-        warm = torch.zeros(1, device=dev)
-        dist.all_reduce(warm)
-        torch.cuda.synchronize(dev)
+        # communicator set-up is not part of the build: the library's own NCCL communicator is created
+        # (and one small collective run on it) before the clock starts
+        from glide_b200 import sharded
+        ctx.init_comm(dist, world, rank)
+        coll = sharded.GlideCollectives(ctx)
         dist.barrier()
     t0 = time.perf_counter()
-    if world > 1:   # partitions assigned to owner ranks, owned rows exchanged over NCCL
-        res = pipeline.build_small_sharded(ctx, d_base, cfg, dist, world, rank)
+    if world > 1:   # kNN by partition owner, build and refine rows split evenly, rows exchanged with all-gathers
+        res = pipeline.build_small_sharded(ctx, d_base, cfg, coll)
     else:
         res = pipeline.build_small(ctx, d_base, cfg)
     torch.cuda.synchronize(dev)
@@ -463,9 +464,9 @@ def run_ours(args):
     sharded_check = None
     if world > 1:
         mine = graph_checksum(torch, index.graph_view())
-        t = torch.tensor([mine, -mine], dtype=torch.int64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        same_on_all = int(t[0]) == mine and int(-t[1]) == mine
+        hi = ctx.all_reduce_u64(torch.tensor([mine], dtype=torch.int64, device=dev), "max")
+        lo = ctx.all_reduce_u64(torch.tensor([mine], dtype=torch.int64, device=dev), "min")
+        same_on_all = int(hi[0]) == mine and int(lo[0]) == mine
         single = None
         if rank == 0:   # rank 0's own single-GPU build of the same seed
             plain = pipeline.build_small(ctx, d_base, cfg)
@@ -611,8 +612,9 @@ def run_ours(args):
             "config": {"workload": workload_string(spec, Q, cfg.centroid_num),
                        "beam": beam, "beam_rounded": sp.beam, "max_iterations": sp.max_iterations, "reduced": reduced,
                        "l2": "512 MB buffer rewritten between timed iterations",
-                       "multi_gpu": ("build sharded by partition owner (owned rows exchanged over NCCL), then one full index "
-                                     "and one query batch per rank") if world > 1 else "single GPU"},
+                       "multi_gpu": ("build sharded: kNN graph by partition owner, subgraph build and refine rows split evenly, "
+                                     "rows exchanged with NCCL all-gathers; then one full index and one query batch per "
+                                     "rank") if world > 1 else "single GPU"},
             "recall_at_10": round(recall, 4),
             "build": {"seconds": round(res.total_seconds, 4), "wall_seconds": round(build_wall, 3),
                       "stages": {k: round(v, 4) for k, v in res.seconds.items()}, "nnd_rounds": res.nnd_rounds,

@@ -47,7 +47,19 @@ SIGNATURES = {
     "glide_subgraph_build_range": (i32, [vp, vp, u32, u32, vp, u32, vp, vp, u32, vp, vp, u32, u32,
                                          P(SearchParamsC), f32, i32, u32, u32, vp]),
     "glide_reverse_graph": (i32, [vp, vp, u32, u32]),
-    "glide_refine_range": (i32, [vp, vp, u32, u32, vp, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32, u32]),
+    "glide_refine_rows": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32, u32, vp]),
+    "glide_subgraph_build_rows": (i32, [vp, vp, u32, u32, vp, u32, vp, vp, u32, vp, vp, u32, u32,
+                                        P(SearchParamsC), f32, i32, u32, u32, vp]),
+    "glide_build_nnd_range": (i32, [vp, vp, u32, u32, vp, vp, u32, u32, u32, f32, u32, u32, u64, i32, u32, vp, P(u32)]),
+    "glide_comm_unique_id": (i32, [vp]),
+    "glide_comm_init": (i32, [vp, vp, u32, u32]),
+    "glide_comm_destroy": (i32, [vp]),
+    "glide_comm_world": (u32, [vp]),
+    "glide_comm_rank": (u32, [vp]),
+    "glide_comm_all_gather_v": (i32, [vp, vp, vp, vp]),
+    "glide_comm_broadcast": (i32, [vp, vp, u64, u32]),
+    "glide_comm_all_reduce_u64": (i32, [vp, vp, u64, i32]),
+    "glide_ctx_synchronize": (i32, [vp]),
     "glide_refine": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32]),
     "glide_refine_waves": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32]),
     "glide_search": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),

@@ -95,6 +95,34 @@ class Context:
     def empty(self, shape, dtype) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype, device=self.torch_device)
 
+    def init_comm(self, dist=None, world: int = 1, rank: int = 0):
+        """Give the context an NCCL communicator over `world` ranks (one process per GPU). The 128-byte
+        rendezvous token is made by rank 0 and carried to the others through torch.distributed's
+        process group `dist` (any backend); from then on torch.distributed plays no part in the data
+        path. One small collective is run so that NCCL's lazy set-up is paid here."""
+        token = np.zeros(128, np.uint8)
+        if rank == 0:
+            rc = self.lib.glide_comm_unique_id(token.ctypes.data)
+            if rc != 0:
+                raise GlideError(rc, "glide_comm_unique_id failed (libnccl.so.2 not found?)")
+        if world > 1:
+            box = [token.tobytes()]
+            dist.broadcast_object_list(box, src=0)
+            token = np.frombuffer(box[0], np.uint8).copy()
+        self.check(self.lib.glide_comm_init(self.handle, token.ctypes.data, world, rank))
+        warm = torch.zeros(2, dtype=torch.int64, device=self.torch_device)
+        self.sync_inputs()
+        self.check(self.lib.glide_comm_all_reduce_u64(self.handle, warm.data_ptr(), 2, 0))
+        self.check(self.lib.glide_ctx_synchronize(self.handle))
+
+    def all_reduce_u64(self, t: torch.Tensor, op: str = "sum"):
+        """In place over the ranks of the context's communicator; t: int64/uint64 tensor on the device."""
+        assert t.element_size() == 8 and t.is_contiguous()
+        self.sync_inputs()
+        self.check(self.lib.glide_comm_all_reduce_u64(self.handle, t.data_ptr(), t.numel(), {"sum": 0, "max": 1, "min": 2}[op]))
+        self.check(self.lib.glide_ctx_synchronize(self.handle))
+        return t
+
     def enable_counters(self, on: bool):
         self.lib.glide_enable_counters(self.handle, 1 if on else 0)
 
@@ -392,7 +420,7 @@ class GLIDE:
 
     def build(self, build_param: IndexParameter, search_param_knn: SearchParameter,
               search_param_refine: SearchParameter, d_knn_graph: torch.Tensor, h_segment_start, h_segment_length,
-              d_map: torch.Tensor, d_reorder_data: torch.Tensor, seed: int = 0):
+              d_map: torch.Tensor, d_reorder_data: torch.Tensor, seed: int = 0, refine_wave_rows: int | None = None):
         """``GLIDE::build`` (glide_impl.cuh:319-368): start points, subgraph build + boundary merge,
         reverse edges, refinement when search_param_refine.beam != 0. Returns kernel seconds."""
         ctx = self.ctx
@@ -416,10 +444,13 @@ class GLIDE:
         times["reverse_graph"] = ctx.last_kernel_seconds
         if search_param_refine.beam != 0:  # glide_impl.cuh:360-362
             pr = _params_c(search_param_refine)
-            ctx.check(ctx.lib.glide_refine(ctx.handle, _ptr(self.d_data), self.num(), self.dim(), _ptr(self.d_graph),
-                                           self.graph_degree(), _ptr(self.d_centroids), self.centroid_num(),
-                                           _ptr(self.d_start_points), C.byref(pr), build_param.relaxant_factor,
-                                           int(self.metric)))
+            args = (ctx.handle, _ptr(self.d_data), self.num(), self.dim(), _ptr(self.d_graph), self.graph_degree(),
+                    _ptr(self.d_centroids), self.centroid_num(), _ptr(self.d_start_points), C.byref(pr),
+                    build_param.relaxant_factor, int(self.metric))
+            if refine_wave_rows is None:    # the library's default wave size
+                ctx.check(ctx.lib.glide_refine(*args))
+            else:
+                ctx.check(ctx.lib.glide_refine_waves(*args, refine_wave_rows))
             times["refine"] = ctx.last_kernel_seconds
         self.stage_seconds = times
         return sum(times.values())

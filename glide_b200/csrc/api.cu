@@ -12,27 +12,11 @@
 #include <vector>
 
 #include "../../include/glide_b200.h"
+#include "ctx.h"
 #include "kernels.h"
 #include "scan.cuh"
 
 using namespace glide;
-
-struct glide_ctx {
-    int device = 0;
-    cudaStream_t stream = nullptr;
-    cudaEvent_t ev_start = nullptr, ev_stop = nullptr, ev_mid = nullptr;
-    float split_ms[2] = {0.0f, 0.0f};  // last glide_search: routing pre-pass, search kernel
-    std::string error;
-    float last_ms = 0.0f;
-    void *ws = nullptr;  // scratch, grown on demand
-    size_t ws_bytes = 0;
-    unsigned long long *counters = nullptr;  // 4 x u64 on the device
-    uint32_t *ticket = nullptr;              // one word: the search kernel's query counter
-    uint32_t *start_point_word = nullptr;    // one word: the start point of a per-partition refine
-    uint32_t last_launches = 0;              // kernels enqueued by the last glide_search
-    float *tc_norms = nullptr;               // centroid norms for the assignment's tensor-core prefilter (up to 4096 centroids)
-    bool counters_on = false;
-};
 
 namespace {
 
@@ -169,6 +153,7 @@ void glide_ctx_destroy(glide_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    glide_comm_release(ctx);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->tc_norms) cudaFree(ctx->tc_norms);
@@ -463,6 +448,16 @@ int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, 
                     const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t S, uint32_t knn_degree,
                     uint32_t max_iterations, float termination_threshold, uint32_t sample, uint32_t exact_max_rows,
                     uint64_t seed, int metric, int32_t *d_knn, uint32_t *iterations_run) {
+    return glide_build_nnd_range(ctx, d_reorder_data, rows, dim, h_segment_start, h_segment_length, S, knn_degree,
+                                 max_iterations, termination_threshold, sample, exact_max_rows, seed, metric, 0, d_knn,
+                                 iterations_run);
+}
+
+int glide_build_nnd_range(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, uint32_t dim,
+                          const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t S,
+                          uint32_t knn_degree, uint32_t max_iterations, float termination_threshold, uint32_t sample,
+                          uint32_t exact_max_rows, uint64_t seed, int metric, uint32_t row_base, int32_t *d_knn,
+                          uint32_t *iterations_run) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
     GL_REQUIRE(ctx, d_reorder_data && h_segment_start && h_segment_length && d_knn, GLIDE_ERR_BAD_ARG, "build_nnd: null pointer");
     GL_REQUIRE(ctx, rows > 0 && dim > 0 && S >= 1, GLIDE_ERR_BAD_ARG, "build_nnd: zero size");
@@ -484,7 +479,7 @@ int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, 
     const uint32_t tile_count = segment_knn_tile_count(h_segment_length, S, exact_max_rows);
     bool need_nnd = false;
     for (uint32_t s = 0; s < S; s++) need_nnd = need_nnd || h_segment_length[s] > exact_max_rows;
-    const size_t nnd_bytes = need_nnd ? nnd_workspace_bytes(rows, K, sample) : 0;
+    const size_t nnd_bytes = need_nnd ? nnd_workspace_bytes(rows, K, sample, S) : 0;
     int rc = ensure_ws(ctx, nnd_bytes + 2 * align256((size_t) S * 4) + align256((size_t) tile_count * 12) + 256);
     if (rc) return rc;
     Bump b(ctx->ws);
@@ -500,14 +495,14 @@ int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, 
     if (iterations_run) *iterations_run = 0;
     if (tile_count) {
         GL_CUDA(ctx, cudaMemcpyAsync(d_tiles, h_tiles.data(), (size_t) tile_count * 12, cudaMemcpyHostToDevice, ctx->stream));
-        GL_CUDA(ctx, launch_segment_knn(d_reorder_data, dim, d_tiles, tile_count, knn_degree, d_knn, ctx->stream));
+        GL_CUDA(ctx, launch_segment_knn(d_reorder_data, dim, d_tiles, tile_count, knn_degree, row_base, d_knn, ctx->stream));
     }
     if (!need_nnd) return timer.finish();
     NndArgs a{};
     a.data = d_reorder_data; a.rows = rows; a.dim = dim;
     a.seg_start = d_start; a.seg_len = d_len; a.S = S; a.min_seg_len = exact_max_rows + 1;
     a.K = K; a.sample = sample; a.max_iterations = max_iterations; a.termination_threshold = termination_threshold;
-    a.seed = seed; a.metric = metric; a.workspace = work; a.workspace_bytes = nnd_bytes;
+    a.seed = seed; a.metric = metric; a.workspace = work; a.workspace_bytes = nnd_bytes; a.row_base = row_base;
     a.out_knn = d_knn; a.out_degree = knn_degree; a.iterations_run = iterations_run; a.stage_ms = nullptr;
     GL_CUDA(ctx, run_nn_descent(a, ctx->stream));
     return timer.finish();
@@ -627,6 +622,42 @@ int glide_subgraph_build_range(glide_ctx *ctx, const float *d_reorder_data, uint
     return timer.finish();
 }
 
+int glide_subgraph_build_rows(glide_ctx *ctx, const float *d_reorder_data, uint32_t reorder_num, uint32_t dim,
+                              const uint32_t *d_knn, uint32_t knn_degree, const uint32_t *h_segment_start,
+                              const uint32_t *h_segment_length, uint32_t S, const uint32_t *d_start_points_local,
+                              const uint32_t *d_map, uint32_t num, uint32_t graph_degree, const glide_search_params *p,
+                              float relaxant_factor, int metric, uint32_t first_row, uint32_t row_count,
+                              uint32_t *d_rows_out) {
+    if (!ctx) return GLIDE_ERR_BAD_ARG;
+    GL_REQUIRE(ctx, d_reorder_data && d_knn && h_segment_start && h_segment_length && d_start_points_local && d_map && d_rows_out,
+               GLIDE_ERR_BAD_ARG, "subgraph_build_rows: null pointer");
+    GL_REQUIRE(ctx, S >= 1 && num <= reorder_num && dim > 0, GLIDE_ERR_BAD_ARG, "subgraph_build_rows: bad sizes");
+    GL_REQUIRE(ctx, (uint64_t) first_row + row_count <= num, GLIDE_ERR_BAD_ARG,
+               "subgraph_build_rows: the range must lie inside the non-boundary rows");
+    int rc = check_params(ctx, p, knn_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, graph_degree >= 1 && graph_degree <= 256, GLIDE_ERR_UNSUPPORTED, "Unsupported graph_degree");
+    if (row_count == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = ensure_ws(ctx, 2 * align256((size_t) S * 4));
+    if (rc) return rc;
+    Bump b(ctx->ws);
+    uint32_t *d_start = b.take<uint32_t>(S), *d_len = b.take<uint32_t>(S);
+    Timed timer(ctx);
+    GL_CUDA(ctx, cudaMemcpyAsync(d_start, h_segment_start, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    GL_CUDA(ctx, cudaMemcpyAsync(d_len, h_segment_length, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    BuildArgs a{};
+    a.mode = kModeBuild;
+    a.data = d_reorder_data; a.dim = dim; a.graph_in = d_knn; a.in_degree = knn_degree;
+    a.graph_out = d_rows_out; a.out_first = first_row; a.rows_by_point = 1; a.out_degree = graph_degree;
+    a.seg_start = d_start; a.seg_len = d_len; a.S = S; a.start_points = d_start_points_local; a.map = d_map;
+    a.first = first_row; a.count = row_count;
+    a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
+    a.counters = counters_or_null(ctx);
+    GL_CUDA(ctx, launch_build(a, ctx->stream));
+    return timer.finish();
+}
+
 int glide_reverse_graph(glide_ctx *ctx, uint32_t *d_graph, uint32_t num, uint32_t graph_degree) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
     GL_REQUIRE(ctx, d_graph && num > 0, GLIDE_ERR_BAD_ARG, "reverse_graph: bad argument");
@@ -736,14 +767,13 @@ static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t
     return timer.finish();
 }
 
-int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph_in,
-                       uint32_t *d_graph_out, uint32_t graph_degree, const float *d_centroids, uint32_t C,
-                       const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor, int metric,
-                       uint32_t first, uint32_t count) {
+int glide_refine_rows(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph,
+                      uint32_t graph_degree, const float *d_centroids, uint32_t C, const uint32_t *d_start_points,
+                      const glide_search_params *p, float relaxant_factor, int metric, uint32_t first, uint32_t count,
+                      uint32_t *d_rows_out) {
     if (!ctx) return GLIDE_ERR_BAD_ARG;
-    GL_REQUIRE(ctx, d_data && d_graph_in && d_graph_out && d_graph_in != d_graph_out && d_centroids && d_start_points,
-               GLIDE_ERR_BAD_ARG, "refine_range: null pointer, or input and output graph are the same buffer");
-    GL_REQUIRE(ctx, num > 0 && dim > 0 && C >= 1 && (uint64_t) first + count <= num, GLIDE_ERR_BAD_ARG, "refine_range: bad sizes");
+    GL_REQUIRE(ctx, d_data && d_graph && d_rows_out && d_centroids && d_start_points, GLIDE_ERR_BAD_ARG, "refine_rows: null pointer");
+    GL_REQUIRE(ctx, num > 0 && dim > 0 && C >= 1 && (uint64_t) first + count <= num, GLIDE_ERR_BAD_ARG, "refine_rows: bad sizes");
     GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
     int rc = check_params(ctx, p, graph_degree);
     if (rc) return rc;
@@ -760,8 +790,8 @@ int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32
     BuildArgs a{};
     a.order = o.order;
     a.mode = kModeRefine;
-    a.data = d_data; a.dim = dim; a.graph_in = d_graph_in; a.in_degree = graph_degree;
-    a.graph_out = d_graph_out; a.out_degree = graph_degree;
+    a.data = d_data; a.dim = dim; a.graph_in = d_graph; a.in_degree = graph_degree;
+    a.graph_out = d_rows_out; a.out_first = first; a.out_degree = graph_degree;
     a.start_points = d_start_points; a.centroids = d_centroids; a.C = C; a.route = route; a.route_first = first;
     a.first = first; a.count = count; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
     a.counters = counters_or_null(ctx);

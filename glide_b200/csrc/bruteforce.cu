@@ -191,7 +191,7 @@ struct SegTile {
 template<int NL>  // list width = 32 * NL
 __global__ void __launch_bounds__(256, 2) segment_knn_kernel(const float *__restrict__ data, uint32_t dim,
                                                              const SegTile *__restrict__ tiles, int32_t *out,
-                                                             uint32_t out_degree) {
+                                                             uint32_t out_degree, uint32_t row_base) {
     extern __shared__ __align__(16) uint32_t smem[];
     constexpr uint32_t L = 32u * NL;
     float *Qs = reinterpret_cast<float *>(smem);                 // [kKT][kQPad]
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(256, 2) segment_knn_kernel(const float *__rest
         const uint32_t ql = i / out_degree, j = i % out_degree;
         const uint32_t id = (uint32_t) lists[ql * L + j];
         const uint64_t flat = (uint64_t) (t.seg_start + t.first + ql) * out_degree + j;
-        uint32_t u = (uint32_t) flat;  // xorshift32, utils.cuh:14-19, as nn_descent.cuh:1384-1391 pads short rows
+        uint32_t u = (uint32_t) (flat + (uint64_t) row_base * out_degree);  // xorshift32, utils.cuh:14-19, as nn_descent.cuh:1384-1391 pads short rows
         u ^= u >> 13; u ^= u << 27; u ^= u >> 5; u *= 0x9E3779B9u;
         out[flat] = (int32_t) (id < t.seg_len ? id : u % t.seg_len);
     }
@@ -368,7 +368,7 @@ void segment_knn_fill_tiles(const uint32_t *h_seg_start, const uint32_t *h_seg_l
 }
 
 cudaError_t launch_segment_knn(const float *data, uint32_t dim, const uint32_t *d_tiles, uint32_t tile_count,
-                               uint32_t out_degree, int32_t *out, cudaStream_t stream) {
+                               uint32_t out_degree, uint32_t row_base, int32_t *out, cudaStream_t stream) {
     if (tile_count == 0) return cudaSuccess;
     if (out_degree == 0 || out_degree > 64) return cudaErrorInvalidValue;
     const uint32_t L = out_degree <= 32 ? 32 : 64;
@@ -377,11 +377,11 @@ cudaError_t launch_segment_knn(const float *data, uint32_t dim, const uint32_t *
     if (L == 32) {
         e = cudaFuncSetAttribute(segment_knn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
         if (e != cudaSuccess) return e;
-        segment_knn_kernel<1><<<tile_count, 256, smem_bytes, stream>>>(data, dim, reinterpret_cast<const SegTile *>(d_tiles), out, out_degree);
+        segment_knn_kernel<1><<<tile_count, 256, smem_bytes, stream>>>(data, dim, reinterpret_cast<const SegTile *>(d_tiles), out, out_degree, row_base);
     } else {
         e = cudaFuncSetAttribute(segment_knn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
         if (e != cudaSuccess) return e;
-        segment_knn_kernel<2><<<tile_count, 256, smem_bytes, stream>>>(data, dim, reinterpret_cast<const SegTile *>(d_tiles), out, out_degree);
+        segment_knn_kernel<2><<<tile_count, 256, smem_bytes, stream>>>(data, dim, reinterpret_cast<const SegTile *>(d_tiles), out, out_degree, row_base);
     }
     return cudaGetLastError();
 }

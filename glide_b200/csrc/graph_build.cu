@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
                                      false, kInvalid, &P);
         short_pool = P < p.beam;
         const uint32_t orig = a.map ? a.map[point] : point;
-        uint32_t *out = a.graph_out + (uint64_t) orig * degree;
+        uint32_t *out = a.graph_out + (uint64_t) (a.rows_by_point ? point - a.out_first : orig) * degree;
         if (a.mode == kModeBuild) {  // map_to_graph_sub / map_to_graph (:145-158)
             for (uint32_t i = lane; i < degree; i += 32) {
                 const uint32_t id = ps.picks[i];

@@ -62,7 +62,8 @@ struct BuildArgs {
     const uint32_t *graph_in;  // kNN graph (build/boundary) or the merged graph snapshot (refine)
     uint32_t in_degree;
     uint32_t *graph_out;
-    uint32_t out_first;        // refine: row of point p is written at graph_out + (p - out_first) * out_degree
+    uint32_t out_first;        // refine (and build with rows_by_point): row of point p is written at graph_out + (p - out_first) * out_degree
+    int rows_by_point;         // build: rows are written by reorder position (see out_first) instead of by original id
     uint32_t out_degree;
     const uint32_t *seg_start, *seg_len;  // device, S entries (build/boundary)
     uint32_t S;
@@ -156,8 +157,9 @@ cudaError_t launch_bruteforce(const float *base, uint32_t n, const float *querie
 uint32_t segment_knn_tile_count(const uint32_t *h_seg_len, uint32_t S, uint32_t max_len);
 void segment_knn_fill_tiles(const uint32_t *h_seg_start, const uint32_t *h_seg_len, uint32_t S, uint32_t max_len,
                             uint32_t *h_tiles);
+// row_base: index of data's row 0 within the whole reordered set (enters the padding hash of short partitions)
 cudaError_t launch_segment_knn(const float *data, uint32_t dim, const uint32_t *d_tiles, uint32_t tile_count,
-                               uint32_t out_degree, int32_t *out, cudaStream_t stream);
+                               uint32_t out_degree, uint32_t row_base, int32_t *out, cudaStream_t stream);
 
 // ---- nn_descent.cu -------------------------------------------------------
 struct NndArgs {
@@ -177,10 +179,12 @@ struct NndArgs {
     size_t workspace_bytes;
     int32_t *out_knn;    // rows x out_degree, partition-local ids
     uint32_t out_degree;
+    uint32_t row_base;         // index of row 0 within the whole reordered set (seeds and padding hash global row numbers,
+                               // so a sharded run gives the rows of the whole run)
     uint32_t *iterations_run;  // host pointer, may be nullptr
     float *stage_ms;           // host pointer [3] (sample, join, merge), may be nullptr
 };
-size_t nnd_workspace_bytes(uint32_t rows, uint32_t K, uint32_t sample);
+size_t nnd_workspace_bytes(uint32_t rows, uint32_t K, uint32_t sample, uint32_t S);
 cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream);
 
 }  // namespace glide

@@ -16,6 +16,8 @@
 // Every step is a pure function of the previous state, so a run is reproducible.
 // Distances inside the lists are squared L2 for both metrics (monotone in the
 // reference's values; only ids leave this stage).
+#include <vector>
+
 #include "beam_core.cuh"
 #include "kernels.h"
 
@@ -48,11 +50,13 @@ struct NndDev {
     uint32_t K, S;
     uint32_t seed;
     uint32_t min_len;  // rows of shorter partitions are skipped by every kernel
+    uint32_t row_base; // index of row 0 within the whole reordered set
     u64 *lists;       // rows x K, ascending
     u64 *props;       // rows x kP
     uint32_t *new_s;  // rows x 2S  (forward | reverse)
     uint32_t *old_s;  // rows x 2S
-    uint32_t *counter;
+    uint32_t *seg_updates;        // S counters: list entries replaced in the current round, per partition
+    const uint32_t *seg_active;   // S flags: 0 once a partition has converged (its rows are skipped from then on)
 };
 
 __device__ __forceinline__ uint32_t gcd_u32(uint32_t a, uint32_t b) {
@@ -81,7 +85,7 @@ __global__ void __launch_bounds__(256) nnd_init_kernel(const NndDev d) {
     load_query(query, d.data + (uint64_t) row * d.dim, d.dim);
     uint32_t stride = 1;
     if (len > 2) {
-        stride = 1 + hash32(row ^ d.seed) % (len - 1);
+        stride = 1 + hash32((row + d.row_base) ^ d.seed) % (len - 1);
         for (int tries = 0; tries < 64 && gcd_u32(stride, len) != 1; tries++) stride = stride % (len - 1) + 1;
         if (gcd_u32(stride, len) != 1) stride = 1;
     }
@@ -119,7 +123,7 @@ __global__ void __launch_bounds__(256) nnd_sample_kernel(const NndDev d) {
     if (row >= d.rows) return;
     const uint32_t K = d.K, S = d.S;
     const uint32_t seg = d.row_segment[row];
-    if (d.seg_len[seg] < d.min_len) return;
+    if (d.seg_len[seg] < d.min_len || !d.seg_active[seg]) return;
     const uint32_t start = d.seg_start[seg], self = row - start;
     u64 *list = d.lists + (uint64_t) row * K;
     uint32_t *fnew = d.new_s + (uint64_t) row * 2 * S;
@@ -177,7 +181,7 @@ __global__ void __launch_bounds__(256) nnd_join_kernel(const NndDev d) {
     const uint32_t tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
     const uint32_t S = d.S, K = d.K;
     const uint32_t seg = d.row_segment[row];
-    if (d.seg_len[seg] < d.min_len) return;
+    if (d.seg_len[seg] < d.min_len || !d.seg_active[seg]) return;
     const uint32_t start = d.seg_start[seg];
 
     // raw ids: [0,2S) new, [2S,4S) old
@@ -307,7 +311,8 @@ __global__ void __launch_bounds__(256) nnd_merge_kernel(const NndDev d) {
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= d.rows) return;
-    if (d.seg_len[d.row_segment[row]] < d.min_len) return;
+    const uint32_t seg = d.row_segment[row];
+    if (d.seg_len[seg] < d.min_len || !d.seg_active[seg]) return;
     constexpr uint32_t K = 32u * NK;
     u64 *list = d.lists + (uint64_t) row * K;
     u64 keys[NK];
@@ -342,7 +347,7 @@ __global__ void __launch_bounds__(256) nnd_merge_kernel(const NndDev d) {
     merge_final_u64<NK>(keys);
 #pragma unroll
     for (int i = 0; i < NK; i++) list[NK * lane + i] = keys[i];
-    if (lane == 0 && inserted) atomicAdd(d.counter, inserted);
+    if (lane == 0 && inserted) atomicAdd(d.seg_updates + seg, inserted);
 }
 
 // Final shrink (nn_descent.cuh:1376-1392): the first out_degree ids per row; an empty
@@ -358,7 +363,7 @@ __global__ void nnd_output_kernel(const NndDev d, int32_t *out, uint32_t out_deg
     const uint32_t len = d.seg_len[d.row_segment[row]];
     if (len < d.min_len) return;
     const uint32_t id = key_id(d.lists[(uint64_t) row * d.K + j]);
-    out[t] = (int32_t) ((id < len) ? id : xorshift32((uint32_t) t) % len);
+    out[t] = (int32_t) ((id < len) ? id : xorshift32((uint32_t) (t + (uint64_t) d.row_base * out_degree)) % len);
 }
 
 __global__ void row_segment_kernel(const uint32_t *seg_start, const uint32_t *seg_len, uint32_t S, uint32_t rows,
@@ -374,29 +379,41 @@ size_t align256(size_t x) { return (x + 255) & ~(size_t) 255; }
 
 }  // namespace
 
-size_t nnd_workspace_bytes(uint32_t rows, uint32_t K, uint32_t sample) {
+size_t nnd_workspace_bytes(uint32_t rows, uint32_t K, uint32_t sample, uint32_t S) {
     return align256((size_t) rows * K * 8) + align256((size_t) rows * kP * 8) +
-           2 * align256((size_t) rows * 2 * sample * 4) + align256((size_t) rows * 4) + 256;
+           2 * align256((size_t) rows * 2 * sample * 4) + align256((size_t) rows * 4) + 2 * align256((size_t) S * 4) + 256;
 }
 
 cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream) {
     if (a.rows == 0) return cudaSuccess;
     if ((a.K != 32 && a.K != 64) || a.sample == 0 || a.sample > kMaxS || a.out_degree > a.K)
         return cudaErrorInvalidValue;
-    if (a.workspace_bytes < nnd_workspace_bytes(a.rows, a.K, a.sample)) return cudaErrorInvalidValue;
+    if (a.workspace_bytes < nnd_workspace_bytes(a.rows, a.K, a.sample, a.S)) return cudaErrorInvalidValue;
     NndDev d;
     d.data = a.data; d.rows = a.rows; d.dim = a.dim;
     d.seg_start = a.seg_start; d.seg_len = a.seg_len;
     d.K = a.K; d.S = a.sample; d.seed = (uint32_t) (a.seed * 0x9E3779B97F4A7C15ull >> 32);
     d.min_len = a.min_seg_len;
+    d.row_base = a.row_base;
     char *w = static_cast<char *>(a.workspace);
     d.lists = reinterpret_cast<u64 *>(w); w += align256((size_t) a.rows * a.K * 8);
     d.props = reinterpret_cast<u64 *>(w); w += align256((size_t) a.rows * kP * 8);
     d.new_s = reinterpret_cast<uint32_t *>(w); w += align256((size_t) a.rows * 2 * a.sample * 4);
     d.old_s = reinterpret_cast<uint32_t *>(w); w += align256((size_t) a.rows * 2 * a.sample * 4);
     uint32_t *row_segment = reinterpret_cast<uint32_t *>(w); w += align256((size_t) a.rows * 4);
-    d.counter = reinterpret_cast<uint32_t *>(w);
+    d.seg_updates = reinterpret_cast<uint32_t *>(w); w += align256((size_t) a.S * 4);
+    uint32_t *seg_active = reinterpret_cast<uint32_t *>(w);
+    d.seg_active = seg_active;
     d.row_segment = row_segment;
+    // Convergence is judged per partition (as the reference does, nn_descent.cuh:1280-1283): which
+    // partitions share a call does not change any partition's result.
+    std::vector<uint32_t> h_len(a.S), h_active(a.S), h_updates(a.S);
+    cudaError_t e0 = cudaMemcpyAsync(h_len.data(), a.seg_len, (size_t) a.S * 4, cudaMemcpyDeviceToHost, stream);
+    if (e0 == cudaSuccess) e0 = cudaStreamSynchronize(stream);
+    if (e0 != cudaSuccess) return e0;
+    uint32_t live = 0;
+    for (uint32_t s2 = 0; s2 < a.S; s2++) { h_active[s2] = h_len[s2] >= a.min_seg_len ? 1u : 0u; live += h_active[s2]; }
+    if ((e0 = cudaMemcpyAsync(seg_active, h_active.data(), (size_t) a.S * 4, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e0;
 
     cudaError_t e;
     row_segment_kernel<<<(a.rows + 255) / 256, 256, 0, stream>>>(a.seg_start, a.seg_len, a.S, a.rows, row_segment);
@@ -424,7 +441,7 @@ cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream) {
         if (timing) cudaEventRecord(ev[0], stream);
         if ((e = cudaMemsetAsync(d.new_s, 0xff, sample_bytes, stream)) != cudaSuccess) return e;
         if ((e = cudaMemsetAsync(d.old_s, 0xff, sample_bytes, stream)) != cudaSuccess) return e;
-        if ((e = cudaMemsetAsync(d.counter, 0, 4, stream)) != cudaSuccess) return e;
+        if ((e = cudaMemsetAsync(d.seg_updates, 0, (size_t) a.S * 4, stream)) != cudaSuccess) return e;
         nnd_sample_kernel<<<wgrid, warps * 32, 0, stream>>>(d);
         if (timing) cudaEventRecord(ev[1], stream);
         nnd_join_kernel<<<a.rows, 256, 0, stream>>>(d);
@@ -433,8 +450,7 @@ cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream) {
         else nnd_merge_kernel<2><<<wgrid, warps * 32, 0, stream>>>(d);
         if (timing) cudaEventRecord(ev[3], stream);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        uint32_t updates = 0;
-        if ((e = cudaMemcpyAsync(&updates, d.counter, 4, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
+        if ((e = cudaMemcpyAsync(h_updates.data(), d.seg_updates, (size_t) a.S * 4, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
         if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return e;
         if (timing) {
             float ms;
@@ -444,8 +460,18 @@ cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream) {
         }
         // the reference stops a partition when a sampled update count falls below
         // threshold * rows * dim / 100 (nn_descent.cuh:1280-1283); here: when fewer than
-        // threshold * rows * K list entries changed in the round.
-        if ((double) updates < (double) a.termination_threshold * a.rows * a.K) { it++; break; }
+        // threshold * rows * K of its list entries changed in the round.
+        bool changed = false;
+        for (uint32_t s2 = 0; s2 < a.S; s2++) {
+            if (!h_active[s2]) continue;
+            if ((double) h_updates[s2] < (double) a.termination_threshold * h_len[s2] * a.K) {
+                h_active[s2] = 0;
+                live--;
+                changed = true;
+            }
+        }
+        if (changed && (e = cudaMemcpyAsync(seg_active, h_active.data(), (size_t) a.S * 4, cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
+        if (live == 0) { it++; break; }
     }
     if (timing) for (auto &x : ev) cudaEventDestroy(x);
     if (a.iterations_run) *a.iterations_run = it;

@@ -31,7 +31,8 @@ typedef enum {
     GLIDE_ERR_UNSUPPORTED = -2,  /* beam > 512, degree > 256, ... (kernel_config.cuh:47-48, :59-60) */
     GLIDE_ERR_CUDA = -3,         /* a CUDA call failed; see glide_last_error */
     GLIDE_ERR_NO_MEMORY = -4,
-    GLIDE_ERR_IO = -5
+    GLIDE_ERR_IO = -5,
+    GLIDE_ERR_NCCL = -6          /* libnccl could not be opened, or an NCCL call failed; see glide_last_error */
 } glide_status;
 
 enum { GLIDE_METRIC_EUCLIDEAN = 0, GLIDE_METRIC_COSINE = 1 }; /* params.cuh:5-8 */
@@ -116,6 +117,16 @@ int glide_build_nnd(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, 
                     const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t segment_num,
                     uint32_t knn_degree, uint32_t max_iterations, float termination_threshold, uint32_t sample,
                     uint32_t exact_max_rows, uint64_t seed, int metric, int32_t *d_knn, uint32_t *iterations_run);
+/* build_nnd for a run of whole partitions cut out of the reordered set (d_rows = the run's first row,
+ * segment starts counted from that row): row_base is the run's first row within the whole set.
+ * Seeds and padding depend on global row numbers, so the runs of a sharded build give exactly the
+ * rows of one glide_build_nnd over everything. The reference runs one thread per partition on one
+ * GPU (nn_descent.cuh:1304-1343); partitions are the unit a multi-GPU build hands to its ranks. */
+int glide_build_nnd_range(glide_ctx *ctx, const float *d_rows, uint32_t rows, uint32_t dim,
+                          const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t segment_num,
+                          uint32_t knn_degree, uint32_t max_iterations, float termination_threshold, uint32_t sample,
+                          uint32_t exact_max_rows, uint64_t seed, int metric, uint32_t row_base, int32_t *d_knn,
+                          uint32_t *iterations_run);
 /* Exact kNN by brute force: the ground truth (the reference reads it from a file,
  * small_search.cu:88). k <= 128. d_out_dists may be null. */
 int glide_bruteforce_knn(glide_ctx *ctx, const float *d_base, uint32_t n, const float *d_queries, uint32_t q,
@@ -162,13 +173,47 @@ int glide_refine_waves(glide_ctx *ctx, const float *d_data, uint32_t num, uint32
                        const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor,
                        int metric, uint32_t wave_rows);
 
-/* refine for points [first, first + count): searches read d_graph_in (the graph before
- * refinement), the refined rows are written to d_graph_out (a different buffer; rows outside
- * the range are not touched). glide_impl.cuh:284-312 launches the whole range. */
-int glide_refine_range(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph_in,
-                       uint32_t *d_graph_out, uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
-                       const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor,
-                       int metric, uint32_t first, uint32_t count);
+/* refine_kernel (glide_impl.cuh:284-312 launches the whole range) for points [first, first + count):
+ * searches read d_graph, the refined rows go to d_rows_out (count x graph_degree, row of point p at
+ * p - first); d_graph itself is not written. A rank of a sharded build refines its slice of a wave
+ * this way and the slices are gathered before the wave is written back. */
+int glide_refine_rows(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_t dim, const uint32_t *d_graph,
+                      uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
+                      const uint32_t *d_start_points, const glide_search_params *p, float relaxant_factor, int metric,
+                      uint32_t first, uint32_t count, uint32_t *d_rows_out);
+/* build_kernel (glide_impl.cuh:114-143) for the non-boundary reorder rows [first_row, first_row +
+ * row_count): the row of reorder id r goes to d_rows_out at r - first_row (neighbours are original
+ * ids, as in the finished graph) instead of to the row of its original id. Rows by reorder position
+ * are contiguous per rank, which is what lets a sharded build exchange them with one all-gather. */
+int glide_subgraph_build_rows(glide_ctx *ctx, const float *d_reorder_data, uint32_t reorder_num, uint32_t dim,
+                              const uint32_t *d_knn, uint32_t knn_degree, const uint32_t *h_segment_start,
+                              const uint32_t *h_segment_length, uint32_t segment_num,
+                              const uint32_t *d_start_points_local, const uint32_t *d_map, uint32_t num,
+                              uint32_t graph_degree, const glide_search_params *p, float relaxant_factor, int metric,
+                              uint32_t first_row, uint32_t row_count, uint32_t *d_rows_out);
+
+/* ---- communicator (multi-GPU builds and searches) -------------------------------------------
+ * One process per GPU; the reference is a single-GPU program (its mains pin device 1,
+ * small_build.cu:33) and has no counterpart for any of these. A context may carry one NCCL
+ * communicator; collectives are enqueued on the context's stream, in order with its kernels.
+ * libnccl.so.2 is opened at run time by the first of these calls. */
+/* 128 opaque bytes made by one rank and carried to the others by the host (a file, a socket, MPI,
+ * torch.distributed's store): the rendezvous token of glide_comm_init. */
+int glide_comm_unique_id(uint8_t out[128]);
+/* Collective: every rank calls it with the same id and world size. */
+int glide_comm_init(glide_ctx *ctx, const uint8_t id[128], uint32_t world, uint32_t rank);
+int glide_comm_destroy(glide_ctx *ctx);
+uint32_t glide_comm_world(const glide_ctx *ctx);   /* 1 without a communicator */
+uint32_t glide_comm_rank(const glide_ctx *ctx);
+/* In-place all-gather of unequal blocks: rank r owns bytes [offsets[r], offsets[r] + counts[r]) of
+ * d_buf (the same offsets and counts on every rank) and every rank ends with all blocks. Returns
+ * after enqueueing. */
+int glide_comm_all_gather_v(glide_ctx *ctx, void *d_buf, const uint64_t *offsets, const uint64_t *counts);
+int glide_comm_broadcast(glide_ctx *ctx, void *d_buf, uint64_t bytes, uint32_t root);
+/* Element-wise over the ranks, in place; op 0 sum, 1 max, 2 min. */
+int glide_comm_all_reduce_u64(glide_ctx *ctx, uint64_t *d_buf, uint64_t count, int op);
+/* Waits for everything enqueued on the context's stream (kernels, copies, collectives). */
+int glide_ctx_synchronize(glide_ctx *ctx);
 
 /* ---- search stage ----------------------------------------------------------------------- */
 /* GLIDE::search, glide_impl.cuh:370-454 (search_kernel, search_kernel.cuh:393-490).

@@ -494,11 +494,19 @@ def _sharded_rank(rank, world, port, out_dir):
     ctx = api.Context(rank)
     base, _ = helpers.small_dataset("int", 4000, 32, 10, seed=9)
     cfg = pipeline.BuildConfig(centroid_num=4, knn_degree=16, graph_degree=16, build_beam=32, refine_beam=64,
-                               sample_factor=0.1, boundary_factor=1.15, seed=3)
+                               sample_factor=0.1, boundary_factor=1.15, seed=3, refine_wave_rows=1000)
     d = torch.from_numpy(base).to(ctx.torch_device)
+    from glide_b200 import sharded
+    ctx.init_comm(dist, world, rank)          # the library's own NCCL communicator; the token travels over torch.distributed
+    shard = pipeline.build_small_sharded(ctx, d, cfg, sharded.GlideCollectives(ctx))
     plain = pipeline.build_small(ctx, d, cfg)
-    shard = pipeline.build_small_sharded(ctx, d, cfg, dist, world, rank)
     ok = torch.equal(plain.index.graph_view(), shard.index.graph_view())
+    # NN-descent partitions (exact kernel off) sharded by owner give the same kNN rows too
+    cfg2 = pipeline.BuildConfig(centroid_num=4, knn_degree=16, graph_degree=16, build_beam=32, refine_beam=64,
+                                sample_factor=0.1, boundary_factor=1.15, seed=3, exact_knn_max_rows=0, refine_wave_rows=1000)
+    a = pipeline.build_small(ctx, d, cfg2)
+    b = pipeline.build_small_sharded(ctx, d, cfg2, sharded.GlideCollectives(ctx))
+    ok = ok and torch.equal(a.index.graph_view(), b.index.graph_view())
     open(os.path.join(out_dir, f"rank{rank}.txt"), "w").write("ok" if ok else "mismatch")
     dist.barrier()
     dist.destroy_process_group()

@@ -1,6 +1,7 @@
-"""World-size-2 (and 3) gloo ranks on CPU: the sharded build's orchestration (row ranges,
-merging rows written by different ranks, boundary-row and range exchanges) over the CPU oracle
-must give the graph the single-process oracle pipeline gives."""
+"""World-size-2 (and 3) gloo ranks on CPU: the sharded build's orchestration (kNN rows by partition
+owner, build rows by reorder position, boundary rows packed and scattered, refine in waves, each
+exchanged with one in-place all-gather) over the CPU oracle must give the graph and the kNN graph
+the single-process oracle pipeline gives."""
 import os
 import sys
 
@@ -27,43 +28,74 @@ def test_split_range_is_a_partition():
             assert max(sizes) - min(sizes) <= 1
 
 
+def test_owner_ranges_cover_all_partitions_in_order():
+    rng = np.random.default_rng(0)
+    for world in (1, 2, 3, 8):
+        for lens in ([5], [10, 10], [100, 200, 300, 50], list(rng.integers(1, 40000, 37)), [977] * 1024 + [300]):
+            r = sharded.owner_ranges(lens, world)
+            assert len(r) == world and r[0][0] == 0 and r[-1][1] == len(lens)
+            assert all(r[i][1] == r[i + 1][0] for i in range(world - 1)) and all(a <= b for a, b in r)
+    # equal partitions split evenly
+    assert [b - a for a, b in sharded.owner_ranges([1000] * 64, 8)] == [8] * 8
+
+
 class OracleBackend:
-    def __init__(self, base, P, graph_i32):
+    """The stage calls of sharded.build_sharded over the CPU restatement of the kernels."""
+
+    def __init__(self, base, P, graph_i32, knn_i32):
         import oracle
-        self.o, self.base, self.P, self.g = oracle, base, P, graph_i32
+        self.o, self.base, self.P = oracle, base, P
+        self.graph, self.knn = graph_i32, knn_i32
 
-    def _view(self):
-        return self.g.numpy().view(np.uint32)
+    def _g(self):
+        return self.graph.numpy().view(np.uint32)
 
-    def build_range(self, first_row, row_count):
+    def knn_segments(self, lo, hi):
+        # the exact per-partition kNN rows the single-process pipeline used (a pure function of the partition)
+        P = self.P
+        first = int(P["seg_start"][lo])
+        end = int(P["seg_start"][hi - 1]) + int(P["seg_len"][hi - 1])
+        self.knn[first:end] = torch.from_numpy(P["knn"][first:end])
+        return 0.0
+
+    def build_rows(self, first, count, out):
         o, P, n = self.o, self.P, self.base.shape[0]
-        g = self._view()
-        end = first_row + row_count
-        if first_row < n and row_count:
-            o.build_rows(P["reorder_data"], P["knn"].view(np.uint32), P["seg_start"], P["seg_len"], P["local_sp"],
-                         P["mapping"], n, g.shape[1], P["p_build"], P["alpha"], P["metric"], P["order"], graph=g,
-                         first=first_row, count=min(end, n) - first_row, threads=1)
-        if end > n and row_count:
-            # boundary copies [max(first,n), end): run the oracle on that sub-range only
-            lo = max(first_row, n)
-            rd, knn, mp_ = P["reorder_data"], P["knn"].view(np.uint32), P["mapping"]
-            full = g.copy()
-            o.build_boundary(rd, knn, n, int(P["local_sp"][-1]), mp_, full, P["p_build"], P["alpha"], P["metric"],
-                             P["order"], threads=1)
-            rows = mp_[lo:end]
-            g[rows] = full[rows]
+        if count == 0:
+            return 0.0
+        knn = self.knn.numpy().view(np.uint32)
+        tmp = np.full((n, self.graph.shape[1]), 0xFFFFFFFF, np.uint32)
+        o.build_rows(P["reorder_data"], knn, P["seg_start"], P["seg_len"], P["local_sp"], P["mapping"], n, tmp.shape[1],
+                     P["p_build"], P["alpha"], P["metric"], P["order"], graph=tmp, first=first, count=count, threads=1)
+        out.copy_(torch.from_numpy(tmp[P["mapping"][first:first + count]].view(np.int32)))
+        return 0.0
+
+    def build_boundary(self, first, count):
+        o, P, n = self.o, self.P, self.base.shape[0]
+        if count == 0:
+            return 0.0
+        g = self._g()
+        full = g.copy()
+        o.build_boundary(P["reorder_data"], self.knn.numpy().view(np.uint32), n, int(P["local_sp"][-1]), P["mapping"], full,
+                         P["p_build"], P["alpha"], P["metric"], P["order"], threads=1)
+        rows = P["mapping"][first:first + count]
+        g[rows] = full[rows]
         return 0.0
 
     def reverse(self):
-        self.o.reverse_graph(self._view())
+        self.o.reverse_graph(self._g())
         return 0.0
 
-    def refine_range(self, snapshot, first, count):
+    def refine_rows(self, first, count, out):
         o, P = self.o, self.P
-        out = o.refine(self.base, snapshot.numpy().view(np.uint32), P["centroids"], P["orig_sp"], P["p_refine"],
-                       P["alpha"], P["metric"], P["order"], threads=1)
-        self._view()[first:first + count] = out[first:first + count]
+        if count == 0:
+            return 0.0
+        res = o.refine(self.base, self._g(), P["centroids"], P["orig_sp"], P["p_refine"], P["alpha"], P["metric"],
+                       P["order"], threads=1)
+        out.copy_(torch.from_numpy(res[first:first + count].view(np.int32)))
         return 0.0
+
+
+WAVE = 500
 
 
 def _worker(rank, world, port, out_dir):
@@ -71,14 +103,19 @@ def _worker(rank, world, port, out_dir):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import helpers
+    import oracle
     base, _ = helpers.small_dataset("int", 1200, 16, 10, seed=4)
-    P = helpers.oracle_pipeline(base, centroid_num=3, boundary_factor=1.15)
+    P = helpers.oracle_pipeline(base, centroid_num=3, boundary_factor=1.15, with_refine=False)
+    want = oracle.refine(base, P["after_reverse"], P["centroids"], P["orig_sp"], P["p_refine"], P["alpha"], P["metric"],
+                         P["order"], wave_rows=WAVE)
     n = base.shape[0]
     graph = torch.full((n, 16), -1, dtype=torch.int32)
-    backend = OracleBackend(base, P, graph)
-    coll = sharded.Collectives(dist, world, rank)
-    sharded.build_sharded(backend, coll, n, int(P["seg_len"][-1]), graph, torch.from_numpy(P["mapping"].astype(np.int64)))
-    ok = np.array_equal(graph.numpy().view(np.uint32), P["graph"])
+    knn = torch.zeros(P["knn"].shape, dtype=torch.int32)
+    backend = OracleBackend(base, P, graph, knn)
+    coll = sharded.TorchCollectives(dist, world, rank)
+    sharded.build_sharded(backend, coll, n, int(P["seg_len"][-1]), P["seg_start"], P["seg_len"],
+                          torch.from_numpy(P["mapping"].astype(np.int64)), wave_rows=WAVE)
+    ok = np.array_equal(graph.numpy().view(np.uint32), want) and np.array_equal(knn.numpy(), P["knn"])
     open(os.path.join(out_dir, f"rank{rank}.txt"), "w").write("ok" if ok else "mismatch")
     dist.destroy_process_group()
 
