@@ -74,6 +74,19 @@ SIGNATURES = {
                                   vp, vp]),
     "glide_build_partition": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, P(SearchParamsC), f32, i32, vp]),
     "glide_refine_partition": (i32, [vp, vp, u32, u32, vp, u32, u32, P(SearchParamsC), f32, i32]),
+    "glide_host_alloc": (i32, [C.c_size_t, P(vp)]),
+    "glide_host_free": (None, [vp]),
+    "glide_host_register": (i32, [vp, C.c_size_t]),
+    "glide_host_unregister": (i32, [vp]),
+    "glide_large_create": (i32, [vp, vp, i32, u32, vp, vp, u32, vp, u32, i32, vp, P(vp)]),
+    "glide_large_destroy": (None, [vp]),
+    "glide_large_set_start_points": (i32, [vp, vp]),
+    "glide_large_get_start_points": (i32, [vp, vp]),
+    "glide_large_build": (i32, [vp, vp, u32, u32, P(SearchParamsC), P(SearchParamsC), f32, u32, f32, u32, u32, u64, vp, vp]),
+    "glide_large_make_resident": (i32, [vp, vp, u32, C.c_size_t, P(u32)]),
+    "glide_large_search": (i32, [vp, vp, u32, vp, u32, u32, f32, P(SearchParamsC), vp, u32, vp, vp]),
+    "glide_large_last_stats": (None, [vp, P(C.c_double)]),
+    "glide_merge_results": (i32, [vp, vp, vp, u32, u32, u32, vp, vp]),
     "glide_malloc": (i32, [vp, C.c_size_t, P(vp)]),
     "glide_memcpy_h2d": (i32, [vp, vp, vp, C.c_size_t]),
     "glide_memcpy_d2h": (i32, [vp, vp, vp, C.c_size_t]),

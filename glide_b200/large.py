@@ -30,22 +30,46 @@ def _splitmix(seed: int):
         yield z ^ (z >> 31)
 
 
+def pinned_empty(shape, dtype) -> np.ndarray:
+    """Page-locked host memory as a numpy array (the array keeps its torch owner alive)."""
+    t = torch.empty(shape, dtype=torch.from_numpy(np.empty(0, dtype)).dtype).pin_memory()
+    a = t.numpy()
+    _PINNED[id(a)] = t
+    return a
+
+
+_PINNED: dict = {}
+
+
+def pinned_copy(a: np.ndarray) -> np.ndarray:
+    out = pinned_empty(a.shape, a.dtype)
+    np.copyto(out, a)
+    return out
+
+
+def _to_device_f32(ctx, rows: np.ndarray) -> torch.Tensor:
+    t = torch.from_numpy(np.ascontiguousarray(rows)).to(ctx.torch_device)
+    return t if t.dtype == torch.float32 else t.to(torch.float32)
+
+
 def preprocess_for_large(ctx: api.Context, h_data: np.ndarray, centroid_num: int, sample_factor: float,
                          batch_num: int = 10, metric: Metric = Metric.Euclidean, seed: int = 0):
     """Centroids from a host-gathered sample, nearest-centroid assignment batch by batch on the GPU
     (no boundary test, partition_kernel.cuh:122-162), then the rows grouped by partition in ascending
-    row order. Returns dict(h_reorder_data, h_map, h_segment_start, h_segment_length, h_centroids, seconds)."""
+    row order. h_data: fp32 or uint8 rows (uint8 batches cross the host link as bytes and are widened
+    on the device). Returns dict(h_reorder_data (pinned, same dtype), h_map, h_segment_start,
+    h_segment_length, h_centroids, seconds)."""
     n, dim = h_data.shape
     sample_num = max(centroid_num, int(n * sample_factor))
     ids = api.sample_ids(n, sample_num, seed)
-    d_sample = torch.from_numpy(np.ascontiguousarray(h_data[ids])).to(ctx.torch_device)
+    d_sample = _to_device_f32(ctx, h_data[ids])
     d_centroids, _, _ = api.kmeans_fit(ctx, d_sample, centroid_num, 0, metric, 1)
     seconds = ctx.last_kernel_seconds
     nearest = np.empty(n, np.uint32)
     batch = (n + batch_num - 1) // batch_num
     for lo in range(0, n, batch):
         hi = min(n, lo + batch)
-        d_rows = torch.from_numpy(np.ascontiguousarray(h_data[lo:hi])).to(ctx.torch_device)
+        d_rows = _to_device_f32(ctx, h_data[lo:hi])
         d_seg, _, _ = api.define_partition(ctx, d_rows, d_centroids, -1.0, metric)
         seconds += ctx.last_kernel_seconds
         nearest[lo:hi] = api.to_u32(d_seg)[:, 0]
@@ -53,44 +77,79 @@ def preprocess_for_large(ctx: api.Context, h_data: np.ndarray, centroid_num: int
     seg_len = np.bincount(nearest, minlength=centroid_num).astype(np.uint32)
     seg_start = np.zeros(centroid_num, np.uint32)
     seg_start[1:] = np.cumsum(seg_len[:-1], dtype=np.uint64).astype(np.uint32)
-    return dict(h_reorder_data=np.ascontiguousarray(h_data[order]), h_map=order, h_segment_start=seg_start,
+    reorder = pinned_empty(h_data.shape, h_data.dtype)
+    np.take(h_data, order, axis=0, out=reorder)
+    return dict(h_reorder_data=reorder, h_map=order, h_segment_start=seg_start,
                 h_segment_length=seg_len, h_centroids=d_centroids.cpu().numpy(), seconds=seconds)
 
 
 def build_knn_for_large(ctx: api.Context, param: NNDescentParameter, h_reorder_data: np.ndarray, h_segment_start,
                         h_segment_length, metric: Metric = Metric.Euclidean, seed: int = 0,
                         exact_max_rows: int = 0xFFFFFFFF):
-    """kNN graph of every partition, one resident partition at a time. Returns (h_knn int32, seconds)."""
+    """kNN graph of every partition, one resident partition at a time (build_knn_for_large,
+    nn_descent.cuh:1515-1581). Returns (h_knn int32, seconds). GLIDE_large.build computes the same rows
+    itself when it is not handed a kNN graph, without the round trip through host memory."""
     rows = h_reorder_data.shape[0]
     degree = min(param.graph_degree, param.intermediate_graph_degree)
     h_knn = np.zeros((rows, degree), np.int32)
     seconds = 0.0
+    import ctypes as C
     for s, l in zip(h_segment_start, h_segment_length):
         s, l = int(s), int(l)
         if l == 0:
             continue
-        d_part = torch.from_numpy(h_reorder_data[s:s + l]).to(ctx.torch_device)
-        d_knn, _, sec = api.build_nnd(ctx, param, d_part, np.array([0], np.uint32), np.array([l], np.uint32), metric,
-                                      seed, 0, exact_max_rows)
-        seconds += sec
+        d_part = _to_device_f32(ctx, h_reorder_data[s:s + l])
+        d_knn = torch.empty((l, degree), dtype=torch.int32, device=ctx.torch_device)
+        start, length = np.array([0], np.uint32), np.array([l], np.uint32)
+        ctx.sync_inputs()
+        ctx.check(ctx.lib.glide_build_nnd_range(ctx.handle, d_part.data_ptr(), l, d_part.shape[1], start.ctypes.data,
+                                                length.ctypes.data, 1, degree, param.max_iterations,
+                                                param.termination_threshold, 0, exact_max_rows, seed, int(metric), s,
+                                                d_knn.data_ptr(), None))
+        seconds += ctx.last_kernel_seconds
         h_knn[s:s + l] = d_knn.cpu().numpy()
     return h_knn, seconds
 
 
 class GLIDE_large:
-    """Host-resident index over disjoint partitions (glide_large.cuh:14-212)."""
+    """Host-resident index over disjoint partitions (glide_large.cuh:14-212) on top of the library's
+    streaming object (`glide_large_*`): rows and graph in pinned host memory, two device slots,
+    uploads / kernels / downloads on three streams, partitions kept in HBM up to a budget for search."""
 
     def __init__(self, ctx: api.Context, graph_degree: int, metric: Metric, h_reorder_data: np.ndarray, h_map,
                  h_centroids, h_segment_start, h_segment_length):
+        import ctypes as C
         self.ctx, self.metric = ctx, metric
-        self.h_data = np.ascontiguousarray(h_reorder_data, np.float32)
+        if h_reorder_data.dtype not in (np.float32, np.uint8):
+            raise TypeError("rows must be float32 or uint8")
+        self.h_data = h_reorder_data if (id(h_reorder_data) in _PINNED and h_reorder_data.flags.c_contiguous) \
+            else pinned_copy(np.ascontiguousarray(h_reorder_data))
         self.h_map = np.ascontiguousarray(h_map, np.uint32)
         self.h_centroids = np.ascontiguousarray(h_centroids, np.float32)
         self.seg_start = np.ascontiguousarray(h_segment_start, np.uint32)
         self.seg_len = np.ascontiguousarray(h_segment_length, np.uint32)
-        self.h_graph = np.full((self.h_data.shape[0], graph_degree), api.INVALID, np.uint32)
-        self.h_start_points = np.zeros(self.seg_start.size, np.uint32)
+        self.h_graph = pinned_empty((self.h_data.shape[0], graph_degree), np.uint32)
+        self.h_graph.fill(api.INVALID)
         self.stage_seconds: dict[str, float] = {}
+        self.stats: dict = {}
+        self.d_centroids = torch.from_numpy(self.h_centroids).to(ctx.torch_device)
+        handle = C.c_void_p()
+        ctx.check(ctx.lib.glide_large_create(ctx.handle, self.h_data.ctypes.data, 1 if self.h_data.dtype == np.uint8 else 0,
+                                             self.h_data.shape[1], self.seg_start.ctypes.data, self.seg_len.ctypes.data,
+                                             self.seg_start.size, self.h_map.ctypes.data, graph_degree, int(metric),
+                                             self.h_graph.ctypes.data, C.byref(handle)))
+        self.handle = handle
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx.lib.glide_large_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     def num(self): return self.h_data.shape[0]
     def dim(self): return self.h_data.shape[1]
@@ -98,61 +157,81 @@ class GLIDE_large:
     def segment_num(self): return self.seg_start.size
     def centroids_num(self): return self.h_centroids.shape[0]
     def graph_view(self): return self.h_graph
-    def start_point_view(self): return self.h_start_points
+
+    def start_point_view(self):
+        out = np.zeros(self.segment_num(), np.uint32)
+        self.ctx.check(self.ctx.lib.glide_large_get_start_points(self.handle, out.ctypes.data))
+        return out
 
     def load(self, h_graph, h_start_points):
-        self.h_graph = np.ascontiguousarray(h_graph, np.uint32)
-        self.h_start_points = np.ascontiguousarray(h_start_points, np.uint32)
+        np.copyto(self.h_graph, np.ascontiguousarray(h_graph, np.uint32))
+        sp = np.ascontiguousarray(h_start_points, np.uint32)
+        self.ctx.check(self.ctx.lib.glide_large_set_start_points(self.handle, sp.ctypes.data))
 
-    def start_point_select(self, seed: int):
-        """One seeded random member per partition, as a partition-local id (glide_large_impl.cuh:50-77)."""
-        gen = _splitmix(seed)
-        for i, l in enumerate(self.seg_len):
-            r = next(gen)
-            self.h_start_points[i] = r % int(l) if l else 0
+    def _stats(self):
+        import ctypes as C
+        out = (C.c_double * 8)()
+        self.ctx.lib.glide_large_last_stats(self.handle, out)
+        return list(out)
 
     def build(self, build_param: IndexParameter, search_param_knn: SearchParameter,
-              search_param_refine: SearchParameter, h_knn_graph: np.ndarray, seed: int = 0):
-        """Per resident partition: H2D rows and kNN rows, build_for_large_kernel, reverse edges,
-        refine_for_large_kernel, D2H rows (glide_large_impl.cuh:79-328). Returns kernel seconds."""
+              search_param_refine: SearchParameter, h_knn_graph: np.ndarray | None = None, seed: int = 0,
+              partitions=None, nnd: NNDescentParameter | None = None, exact_max_rows: int = 0xFFFFFFFF,
+              want_knn: bool = False):
+        """GLIDE_large::build (glide_large_impl.cuh:79-328) for `partitions` (default: all). Without
+        h_knn_graph the kNN rows are computed on the device per partition (NN-descent or the exact
+        all-pairs kernel) as part of the same streamed pass. Returns kernel seconds."""
+        import ctypes as C
         ctx = self.ctx
-        self.start_point_select(seed)
-        t = dict(subgraph_build=0.0, reverse_graph=0.0, refine=0.0)
-        for i, (s, l) in enumerate(zip(self.seg_start, self.seg_len)):
-            s, l = int(s), int(l)
-            if l == 0:
-                continue
-            d_part = torch.from_numpy(self.h_data[s:s + l]).to(ctx.torch_device)
-            d_knn = api.from_u32(ctx, np.ascontiguousarray(h_knn_graph[s:s + l]).view(np.uint32))
-            sp = int(self.h_start_points[i])
-            d_graph = api.build_partition(ctx, d_part, d_knn, sp, self.graph_degree(), search_param_knn,
-                                          build_param.relaxant_factor, self.metric)
-            t["subgraph_build"] += ctx.last_kernel_seconds
-            t["reverse_graph"] += api.reverse_graph(ctx, d_graph)
-            if search_param_refine.beam != 0:
-                t["refine"] += api.refine_partition(ctx, d_part, d_graph, sp, search_param_refine,
-                                                    build_param.relaxant_factor, self.metric)
-            self.h_graph[s:s + l] = api.to_u32(d_graph)
-        self.stage_seconds = t
-        return sum(t.values())
+        parts = np.arange(self.segment_num(), dtype=np.uint32) if partitions is None else np.ascontiguousarray(partitions, np.uint32)
+        nnd = nnd or NNDescentParameter(build_param.knn_degree)
+        knn_degree = build_param.knn_degree if h_knn_graph is None else h_knn_graph.shape[1]
+        pk = api._params_c(search_param_knn)
+        pr = api._params_c(search_param_refine)
+        knn_in = None
+        if h_knn_graph is not None:
+            knn_in = np.ascontiguousarray(h_knn_graph, np.int32)
+        self.h_knn = pinned_empty((self.num(), knn_degree), np.int32) if want_knn else None
+        ctx.sync_inputs()
+        ctx.check(ctx.lib.glide_large_build(self.handle, parts.ctypes.data, parts.size, knn_degree, C.byref(pk), C.byref(pr),
+                                            build_param.relaxant_factor, nnd.max_iterations, nnd.termination_threshold, 0,
+                                            exact_max_rows, seed, None if knn_in is None else knn_in.ctypes.data,
+                                            None if self.h_knn is None else self.h_knn.ctypes.data))
+        st = self._stats()
+        self.stage_seconds = dict(knn=st[0], subgraph_build=st[1], reverse_graph=st[2], refine=st[3])
+        self.stats = dict(h2d_bytes=st[4], h2d_seconds=st[5], partitions_uploaded=int(st[6]))
+        return sum(self.stage_seconds.values())
 
-    def search(self, param: SearchParameter, min_segment_num: int, boundary_factor: float, d_query: torch.Tensor):
-        """glide_large_impl.cuh:355-507. Returns (ids uint32 [Q,k] original ids, dists [Q,k], kernel seconds)."""
+    def make_resident(self, budget_bytes: int, partitions=None) -> int:
+        """Keep partitions in device memory for the searches that follow; returns how many fit."""
+        import ctypes as C
+        parts = np.arange(self.segment_num(), dtype=np.uint32) if partitions is None else np.ascontiguousarray(partitions, np.uint32)
+        n = C.c_uint32(0)
+        self.ctx.check(self.ctx.lib.glide_large_make_resident(self.handle, parts.ctypes.data, parts.size, int(budget_bytes),
+                                                              C.byref(n)))
+        return int(n.value)
+
+    def search_device(self, param: SearchParameter, min_segment_num: int, boundary_factor: float, d_query: torch.Tensor,
+                      partitions=None):
+        """Results stay on the device: (ids int32 tensor [Q,k] of original ids, dists [Q,k], kernel seconds)."""
+        import ctypes as C
         ctx = self.ctx
         q = d_query.shape[0]
-        d_centroids = torch.from_numpy(self.h_centroids).to(ctx.torch_device)
-        d_routes = api.select_segments(ctx, d_query, d_centroids, min_segment_num, boundary_factor, self.metric)
-        seconds = ctx.last_kernel_seconds
-        d_final_ids = api._u32_tensor(ctx, (q, param.top_k))
-        d_final_ids.fill_(-1)
-        d_final_d = torch.full((q, param.top_k), torch.finfo(torch.float32).max, device=ctx.torch_device)
-        for i, (s, l) in enumerate(zip(self.seg_start, self.seg_len)):
-            s, l = int(s), int(l)
-            if l == 0:
-                continue
-            d_part = torch.from_numpy(self.h_data[s:s + l]).to(ctx.torch_device)
-            d_graph = api.from_u32(ctx, self.h_graph[s:s + l])
-            d_map = api.from_u32(ctx, self.h_map[s:s + l])
-            seconds += api.search_on_sub(ctx, d_part, d_graph, d_map, int(self.h_start_points[i]), d_query, d_routes, i,
-                                         param, d_final_ids, d_final_d, self.metric)
-        return api.to_u32(d_final_ids), d_final_d.cpu().numpy(), seconds
+        parts = np.arange(self.segment_num(), dtype=np.uint32) if partitions is None else np.ascontiguousarray(partitions, np.uint32)
+        d_ids = api._u32_tensor(ctx, (q, param.top_k))
+        d_d = ctx.empty((q, param.top_k), torch.float32)
+        pc = api._params_c(param)
+        ctx.sync_inputs()
+        ctx.check(ctx.lib.glide_large_search(self.handle, d_query.data_ptr(), q, self.d_centroids.data_ptr(),
+                                             self.centroids_num(), min_segment_num, boundary_factor, C.byref(pc),
+                                             parts.ctypes.data, parts.size, d_ids.data_ptr(), d_d.data_ptr()))
+        st = self._stats()
+        self.stats = dict(route_seconds=st[0], search_seconds=st[1], h2d_bytes=st[4], h2d_seconds=st[5],
+                          partitions_uploaded=int(st[6]), partitions_searched=int(st[7]))
+        return d_ids, d_d, st[0] + st[1]
+
+    def search(self, param: SearchParameter, min_segment_num: int, boundary_factor: float, d_query: torch.Tensor,
+               partitions=None):
+        """glide_large_impl.cuh:355-507. Returns (ids uint32 [Q,k] original ids, dists [Q,k], kernel seconds)."""
+        d_ids, d_d, seconds = self.search_device(param, min_segment_num, boundary_factor, d_query, partitions)
+        return api.to_u32(d_ids), d_d.cpu().numpy(), seconds

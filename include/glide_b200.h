@@ -279,6 +279,61 @@ int glide_refine_partition(glide_ctx *ctx, const float *d_data, uint32_t num, ui
                            uint32_t graph_degree, uint32_t start_point, const glide_search_params *p,
                            float relaxant_factor, int metric);
 
+/* ---- large path, host orchestration (GLIDE_large, glide_large.cuh:14-212) -----------------
+ * The data set (reorder order) and the finished graph live in host memory that the caller has
+ * pinned; partitions are streamed through two device slots with uploads, kernels and downloads on
+ * three streams. Rows are fp32 (row_type 0) or uint8 (row_type 1, the reference's large-path type,
+ * large_build.cu:84): bytes cross the host link and are widened to fp32 in HBM. */
+typedef struct glide_large glide_large;
+/* Page-locked host memory (cudaHostAlloc / cudaHostRegister), for hosts without a CUDA binding. */
+int glide_host_alloc(size_t bytes, void **out);
+void glide_host_free(void *p);
+int glide_host_register(void *p, size_t bytes);
+int glide_host_unregister(void *p);
+/* GLIDE_large constructor, glide_large_impl.cuh:14-48: h_rows (segment s = rows
+ * [h_segment_start[s], +h_segment_length[s])), h_map (reorder id -> original id) and h_graph
+ * (rows x graph_degree, written by glide_large_build, read by glide_large_search) stay owned by
+ * the caller and must outlive the object. One centroid per partition; segment_num <= 4096. */
+int glide_large_create(glide_ctx *ctx, const void *h_rows, int row_type, uint32_t dim, const uint32_t *h_segment_start,
+                       const uint32_t *h_segment_length, uint32_t segment_num, const uint32_t *h_map,
+                       uint32_t graph_degree, int metric, uint32_t *h_graph, glide_large **out);
+void glide_large_destroy(glide_large *index);
+/* Partition-local start points (glide_large_impl.cuh:50-77): glide_large_build draws them (seeded);
+ * an index loaded from stage files sets them. segment_num entries. */
+int glide_large_set_start_points(glide_large *index, const uint32_t *h_start_points);
+int glide_large_get_start_points(const glide_large *index, uint32_t *h_out);
+/* GLIDE_large::build, glide_large_impl.cuh:79-328, for the listed partitions (a rank of a multi-GPU
+ * build lists its own): kNN graph (NN-descent or the exact all-pairs kernel, as glide_build_nnd;
+ * skipped when h_knn_in, rows x knn_degree partition-local ids, is given), build_for_large, reverse
+ * edges, refine_for_large (p_refine null or beam 0: none). h_knn_out (pinned, may be null) receives
+ * the kNN rows. Partition p + 1 is uploaded while p is built. */
+int glide_large_build(glide_large *index, const uint32_t *partition_ids, uint32_t partition_count, uint32_t knn_degree,
+                      const glide_search_params *p_build, const glide_search_params *p_refine, float relaxant_factor,
+                      uint32_t nnd_max_iterations, float nnd_termination_threshold, uint32_t nnd_sample,
+                      uint32_t exact_max_rows, uint64_t seed, const int32_t *h_knn_in, int32_t *h_knn_out);
+/* Keeps the listed partitions (fp32 rows, graph rows, id map) in device memory until budget_bytes
+ * are used; searches then upload only the others. The reference uploads every partition for every
+ * query batch (glide_large_impl.cuh:424-438). */
+int glide_large_make_resident(glide_large *index, const uint32_t *partition_ids, uint32_t partition_count,
+                              size_t budget_bytes, uint32_t *resident_count);
+/* GLIDE_large::search, glide_large_impl.cuh:355-507, over the listed partitions (ascending index
+ * order): routing (select_segment_kernel), then search_on_sub_kernel per partition that some query
+ * of the batch is routed to. d_final_*: q x top_k, overwritten. */
+int glide_large_search(glide_large *index, const float *d_queries, uint32_t q, const float *d_centroids,
+                       uint32_t centroid_num, uint32_t min_segment_num, float boundary_factor,
+                       const glide_search_params *p, const uint32_t *partition_ids, uint32_t partition_count,
+                       uint32_t *d_final_ids, float *d_final_dists);
+/* Statistics of the last glide_large_build / glide_large_search: out[0..3] kernel seconds (build: kNN,
+ * subgraph build, reverse edges, refine; search: routing, per-partition search, 0, 0), out[4] bytes
+ * uploaded, out[5] seconds from the first to the last upload on the upload stream, out[6] partitions
+ * uploaded, out[7] partitions searched. */
+void glide_large_last_stats(const glide_large *index, double out[8]);
+/* result_merge (search_kernel.cuh:609-651) over whole result sets: folds `sets` result sets
+ * (d_ids, d_dists: sets x q x top_k) into one, in set order. A multi-GPU search gathers the per-GPU
+ * results and folds them with this. */
+int glide_merge_results(glide_ctx *ctx, const uint32_t *d_ids, const float *d_dists, uint32_t sets, uint32_t q,
+                        uint32_t top_k, uint32_t *d_out_ids, float *d_out_dists);
+
 /* ---- device memory helpers for hosts without their own CUDA binding --------------------- */
 int glide_malloc(glide_ctx *ctx, size_t bytes, void **d_out);
 int glide_memcpy_h2d(glide_ctx *ctx, void *d_dst, const void *h_src, size_t bytes);

@@ -124,7 +124,7 @@ public:
     void load(const HostMatrix<uint32_t> &h_graph, const std::vector<uint32_t> &h_start_points) {
         if (h_graph.rows != data_.rows || h_graph.cols != degree_) throw std::invalid_argument("graph shape does not match the index");
         if (h_start_points.size() != seg_start_.size()) throw std::invalid_argument("one start point per partition expected");
-        graph_ = h_graph;
+        std::copy(h_graph.v.begin(), h_graph.v.end(), graph_.v.begin());   // in place: the buffer may be page-locked
         start_points_ = h_start_points;
     }
 
@@ -141,68 +141,51 @@ public:
         }
     }
 
-    // per resident partition: rows and kNN rows in, build_for_large_kernel, reverse edges,
-    // refine_for_large_kernel, graph rows out (glide_large_impl.cuh:79-328)
+    // GLIDE_large::build (glide_large_impl.cuh:79-328) through the library's streaming object: rows
+    // and kNN rows of partition p + 1 are uploaded while partition p runs build_for_large_kernel,
+    // reverse edges and refine_for_large_kernel, and the rows of partition p - 1 are downloaded.
     void build(const IndexParameter &build_param, const SearchParameter &search_param_knn,
                const SearchParameter &search_param_refine, const HostMatrix<int> &h_knn_graph, const std::string &result_file,
                uint64_t seed = 0) {
         if (h_knn_graph.rows != data_.rows) throw std::invalid_argument("kNN graph rows do not match the data");
-        start_point_select(seed);
         const glide_search_params pk = search_param_knn.c(), pr = search_param_refine.c();
-        const uint32_t dim = data_.cols, kd = h_knn_graph.cols;
-        float seconds = 0.0f;
-        for (size_t s = 0; s < seg_start_.size(); s++) {
-            const uint32_t start = seg_start_[s], len = seg_len_[s];
-            if (len == 0) continue;
-            DeviceBuffer<float> d_part(ctx_, data_.data_handle() + (size_t) start * dim, (size_t) len * dim);
-            DeviceBuffer<uint32_t> d_knn(ctx_, reinterpret_cast<const uint32_t *>(h_knn_graph.data_handle()) + (size_t) start * kd,
-                                         (size_t) len * kd);
-            DeviceBuffer<uint32_t> d_graph(ctx_, (size_t) len * degree_);
-            d_graph.fill_u32(0xffffffffu);
-            ctx_.check(glide_build_partition(ctx_.get(), d_part.data_handle(), len, dim, d_knn.data_handle(), kd, start_points_[s],
-                                             degree_, &pk, build_param.relaxant_factor, (int) metric_, d_graph.data_handle()));
-            seconds += ctx_.last_kernel_seconds();
-            ctx_.check(glide_reverse_graph(ctx_.get(), d_graph.data_handle(), len, degree_));
-            seconds += ctx_.last_kernel_seconds();
-            if (search_param_refine.beam != 0) {
-                ctx_.check(glide_refine_partition(ctx_.get(), d_part.data_handle(), len, dim, d_graph.data_handle(), degree_,
-                                                  start_points_[s], &pr, build_param.relaxant_factor, (int) metric_));
-                seconds += ctx_.last_kernel_seconds();
-            }
-            d_graph.download(graph_.data_handle() + (size_t) start * degree_, (size_t) len * degree_);
-        }
+        std::vector<uint32_t> parts(seg_start_.size());
+        for (size_t i = 0; i < parts.size(); i++) parts[i] = (uint32_t) i;
+        glide_large *h = handle();
+        ctx_.check(glide_large_build(h, parts.data(), (uint32_t) parts.size(), h_knn_graph.cols, &pk, &pr, build_param.relaxant_factor,
+                                     0, -1.0f, 0, 0xffffffffu, seed, h_knn_graph.data_handle(), nullptr));
+        ctx_.check(glide_large_get_start_points(h, start_points_.data()));
+        double st[8];
+        glide_large_last_stats(h, st);
+        const double seconds = st[1] + st[2] + st[3];
         std::printf("index build time: %g s\n", seconds);
         if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
     }
 
     // glide_large_impl.cuh:355-507: route every query to the partitions within boundary_factor of
-    // its nearest centroid (at least min_segment_num), search each resident partition, fold into a
-    // running top-k. Result ids are original row ids.
+    // its nearest centroid (at least min_segment_num), search each partition some query is routed to,
+    // fold into a running top-k. Result ids are original row ids. resident_budget_bytes > 0 keeps
+    // partitions in device memory across calls.
     void search(const SearchParameter &param, uint32_t min_segment_num, float boundary_factor, const HostMatrix<float> &h_query,
-                HostMatrix<uint32_t> &result_ids, HostMatrix<float> &result_dists, const std::string &result_file) {
+                HostMatrix<uint32_t> &result_ids, HostMatrix<float> &result_dists, const std::string &result_file,
+                size_t resident_budget_bytes = 0) {
         const glide_search_params p = param.c();
-        const uint32_t q = h_query.rows, dim = data_.cols, S = segment_num();
+        const uint32_t q = h_query.rows;
+        std::vector<uint32_t> parts(seg_start_.size());
+        for (size_t i = 0; i < parts.size(); i++) parts[i] = (uint32_t) i;
+        glide_large *h = handle();
+        ctx_.check(glide_large_set_start_points(h, start_points_.data()));
+        if (resident_budget_bytes) ctx_.check(glide_large_make_resident(h, parts.data(), (uint32_t) parts.size(), resident_budget_bytes, nullptr));
         DeviceBuffer<float> d_query(ctx_, h_query.data_handle(), h_query.size());
         DeviceBuffer<float> d_centroids(ctx_, centroids_.data_handle(), centroids_.size());
-        DeviceBuffer<uint32_t> d_routes(ctx_, (size_t) q * centroids_.rows);
-        ctx_.check(glide_select_segments(ctx_.get(), d_query.data_handle(), q, dim, d_centroids.data_handle(), centroids_.rows,
-                                         min_segment_num, boundary_factor, (int) metric_, d_routes.data_handle()));
-        float seconds = ctx_.last_kernel_seconds();
         DeviceBuffer<uint32_t> d_ids(ctx_, (size_t) q * param.top_k);
-        d_ids.fill_u32(0xffffffffu);
-        std::vector<float> init((size_t) q * param.top_k, std::numeric_limits<float>::max());
-        DeviceBuffer<float> d_dists(ctx_, init.data(), init.size());
-        for (uint32_t s = 0; s < S; s++) {
-            const uint32_t start = seg_start_[s], len = seg_len_[s];
-            if (len == 0) continue;
-            DeviceBuffer<float> d_part(ctx_, data_.data_handle() + (size_t) start * dim, (size_t) len * dim);
-            DeviceBuffer<uint32_t> d_graph(ctx_, graph_.data_handle() + (size_t) start * degree_, (size_t) len * degree_);
-            DeviceBuffer<uint32_t> d_map(ctx_, map_.data() + start, len);
-            ctx_.check(glide_search_on_sub(ctx_.get(), d_part.data_handle(), dim, d_graph.data_handle(), degree_, d_map.data_handle(),
-                                           start_points_[s], d_query.data_handle(), q, d_routes.data_handle(), centroids_.rows, s, &p,
-                                           (int) metric_, d_ids.data_handle(), d_dists.data_handle()));
-            seconds += ctx_.last_kernel_seconds();
-        }
+        DeviceBuffer<float> d_dists(ctx_, (size_t) q * param.top_k);
+        ctx_.check(glide_large_search(h, d_query.data_handle(), q, d_centroids.data_handle(), centroids_.rows, min_segment_num,
+                                      boundary_factor, &p, parts.data(), (uint32_t) parts.size(), d_ids.data_handle(),
+                                      d_dists.data_handle()));
+        double st[8];
+        glide_large_last_stats(h, st);
+        const double seconds = st[0] + st[1];
         std::printf("query time: %g s   QPS: %g\n", seconds, q / seconds);
         if (!result_file.empty()) append_result(result_file, stream_text(seconds) + "," + stream_text(q / seconds) + ",");
         result_ids = HostMatrix<uint32_t>(q, param.top_k);
@@ -210,6 +193,16 @@ public:
         d_ids.download(result_ids.data_handle(), result_ids.size());
         d_dists.download(result_dists.data_handle(), result_dists.size());
     }
+
+    ~GLIDE_large() {
+        if (large_) {
+            glide_large_destroy(large_);
+            glide_host_unregister(data_.data_handle());
+            glide_host_unregister(graph_.data_handle());
+        }
+    }
+    GLIDE_large(const GLIDE_large &) = delete;
+    GLIDE_large &operator=(const GLIDE_large &) = delete;
 
 private:
     const Context &ctx_;
@@ -221,6 +214,20 @@ private:
     std::vector<uint32_t> seg_start_, seg_len_;
     HostMatrix<uint32_t> graph_;
     std::vector<uint32_t> start_points_;
+    glide_large *large_ = nullptr;
+
+    // the streaming object over this index's host buffers, made on first use (the buffers are
+    // page-locked in place so that uploads and downloads run asynchronously)
+    glide_large *handle() {
+        if (!large_) {
+            glide_host_register(data_.data_handle(), data_.size() * sizeof(float));
+            glide_host_register(graph_.data_handle(), graph_.size() * sizeof(uint32_t));
+            ctx_.check(glide_large_create(ctx_.get(), data_.data_handle(), 0, data_.cols, seg_start_.data(), seg_len_.data(),
+                                          (uint32_t) seg_start_.size(), map_.data(), degree_, (int) metric_, graph_.data_handle(),
+                                          &large_));
+        }
+        return large_;
+    }
 };
 
 }  // namespace glide_b200

@@ -239,6 +239,16 @@ def search_on_sub(data, graph, mapping, start_point, queries, segment_ids, segme
         raise ValueError("orc_search_on_sub: unsupported shape")
 
 
+def merge_results(ids, dists):
+    """result_merge over whole result sets: ids, dists of shape (G, Q, top_k), folded in set order."""
+    ids, dists = _u32(ids), _f32(dists)
+    g, q, k = ids.shape
+    out_ids, out_d = np.empty((q, k), np.uint32), np.empty((q, k), np.float32)
+    if lib().orc_merge_results(_p(ids), _p(dists), u32(g), u32(q), u32(k), _p(out_ids), _p(out_d)) != 0:
+        raise ValueError("orc_merge_results: unsupported shape")
+    return out_ids, out_d
+
+
 def recall(neighbors, truth, top_k) -> float:
     neighbors, truth = _u32(neighbors), _u32(truth)
     return float(lib().orc_recall(_p(neighbors), u32(neighbors.shape[1]), _p(truth), u32(truth.shape[1]),

@@ -955,6 +955,56 @@ int orc_search_on_sub(const float *data, uint32_t dim, const uint32_t *graph, ui
     return 0;
 }
 
+// result_merge (search_kernel.cuh:609-651) over whole result sets: set 0 is the running result, sets
+// 1 .. G-1 are folded into it in order, as search_on_sub_kernel folds one partition after another.
+// ids/dists: G x Q x top_k; out: Q x top_k.
+int orc_merge_results(const uint32_t *ids, const float *dists, uint32_t G, uint32_t Q, uint32_t top_k,
+                      uint32_t *out_ids, float *out_dists) {
+    if (top_k == 0 || top_k > 128 || G == 0) return -1;
+    const uint32_t max_topk = top_k <= 32 ? 32 : (top_k <= 64 ? 64 : 128);  // kernel_config.cuh:309-319
+    const uint32_t N = max_topk / 32;
+    const uint64_t set = (uint64_t) Q * top_k;
+    parallel_for(Q, 0, [&](int64_t q) {
+        std::vector<float> fd(dists + q * top_k, dists + (q + 1) * top_k);
+        std::vector<uint32_t> fi(ids + q * top_k, ids + (q + 1) * top_k);
+        for (uint32_t g = 1; g < G; g++) {
+            const float *rd = dists + g * set + (uint64_t) q * top_k;
+            const uint32_t *ri = ids + g * set + (uint64_t) q * top_k;
+            WarpRegs r(N);
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t j = N * lane + i;
+                    r.K(lane, i) = (j < top_k) ? fd[j] : kMaxF;
+                    r.V(lane, i) = (j < top_k) ? fi[j] : kInvalid;
+                }
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t j = N * lane + i;
+                    const uint32_t k = max_topk - 1 - j;
+                    if (k >= top_k) continue;
+                    if (r.K(lane, i) > rd[k]) {
+                        r.K(lane, i) = rd[k];
+                        r.V(lane, i) = ri[k];
+                    }
+                }
+            warp_merge(r, 32);
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t j = N * lane + i;
+                    if (j < top_k) {
+                        fd[j] = r.K(lane, i);
+                        fi[j] = r.V(lane, i);
+                    }
+                }
+        }
+        for (uint32_t j = 0; j < top_k; j++) {
+            out_dists[(uint64_t) q * top_k + j] = fd[j];
+            out_ids[(uint64_t) q * top_k + j] = fi[j];
+        }
+    });
+    return 0;
+}
+
 // small_search.cu:14-36
 float orc_recall(const uint32_t *neighbors, uint32_t nb_stride, const uint32_t *truth,
                  uint32_t truth_stride, uint32_t Q, uint32_t top_k) {

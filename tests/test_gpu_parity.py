@@ -220,7 +220,7 @@ def test_refine_in_waves_matches_oracle(gpu_ctx, name, wave_rows):
     api.refine(gpu_ctx, dev(gpu_ctx, base), g, dev(gpu_ctx, P["centroids"]), dev(gpu_ctx, P["orig_sp"]),
                sp_from(P["p_refine"]), P["alpha"], Metric(metric), wave_rows=wave_rows)
     assert np.array_equal(api.to_u32(g), want)
-    if wave_rows:   # the waves matter: the result differs from the single-wave one
+    if wave_rows and name == "int128":   # the waves matter: the result differs from the single-wave one
         assert not np.array_equal(want, P["graph"])
 
 
