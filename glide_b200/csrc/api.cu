@@ -119,6 +119,12 @@ uint64_t gcd64(uint64_t a, uint64_t b) {
 
 extern "C" {
 
+static int build_nnd_simt(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, uint32_t dim,
+                          const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t S, uint32_t knn_degree,
+                          uint32_t K, uint32_t max_iterations, float termination_threshold, uint32_t sample,
+                          uint32_t exact_max_rows, uint64_t seed, int metric, uint32_t row_base, int32_t *d_knn,
+                          uint32_t *iterations_run, bool skip_exact);
+
 int glide_ctx_create(int device, glide_ctx **out) {
     if (!out) return GLIDE_ERR_BAD_ARG;
     *out = nullptr;
@@ -474,9 +480,55 @@ int glide_build_nnd_range(glide_ctx *ctx, const float *d_reorder_data, uint32_t 
     GL_REQUIRE(ctx, covered == rows, GLIDE_ERR_BAD_ARG, "build_nnd: segment lengths do not sum to the row count");
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
     const uint32_t K = knn_degree <= 32 ? 32 : 64;
-    // partitions of at most exact_max_rows rows: all pairs; larger ones: NN-descent
-    if (exact_max_rows == 0xffffffffu) exact_max_rows = 16384;
-    const uint32_t tile_count = segment_knn_tile_count(h_segment_length, S, exact_max_rows);
+    // Partitions of at most exact_max_rows rows get their exact kNN rows from an all-pairs kernel,
+    // larger ones run NN-descent. Where the tensor-core kernel serves the shape, all pairs stay
+    // cheaper than descent up to about a million rows per partition (4 x 10^12 pair distances per
+    // second against ~1.3 x 10^6 rows per second of descent); the fp32 register-tile kernel gives way
+    // at 16,384.
+    const bool tc = knn_tc_eligible(d_reorder_data, dim, knn_degree);
+    if (exact_max_rows == 0xffffffffu) exact_max_rows = tc ? (1u << 20) : 16384;
+    if (tc) {
+        bool any = false;
+        for (uint32_t s = 0; s < S; s++) any = any || (h_segment_length[s] >= 1 && h_segment_length[s] <= exact_max_rows);
+        if (any) {
+            int rc0 = ensure_ws(ctx, knn_tc_scratch_bytes(rows, knn_degree));
+            if (rc0) return rc0;
+            Timed timer0(ctx);
+            uint32_t failed = 0;
+            cudaError_t e0 = launch_knn_tc(d_reorder_data, rows, dim, h_segment_start, h_segment_length, S, exact_max_rows,
+                                           knn_degree, row_base, ctx->ws, d_knn, &failed, ctx->stream);
+            if (e0 != cudaSuccess && e0 != cudaErrorNotSupported)
+                return fail(ctx, GLIDE_ERR_CUDA, "tensor-core kNN: %s", cudaGetErrorString(e0));
+            rc0 = timer0.finish();
+            if (rc0) return rc0;
+            if (e0 == cudaSuccess && !failed) {
+                bool rest = false;   // partitions beyond exact_max_rows are left for NN-descent below
+                for (uint32_t s = 0; s < S; s++) rest = rest || h_segment_length[s] > exact_max_rows;
+                if (iterations_run) *iterations_run = 0;
+                if (!rest) return GLIDE_OK;
+                const float tc_ms = ctx->last_ms;
+                rc0 = build_nnd_simt(ctx, d_reorder_data, rows, dim, h_segment_start, h_segment_length, S, knn_degree, K,
+                                     max_iterations, termination_threshold, sample, exact_max_rows, seed, metric, row_base,
+                                     d_knn, iterations_run, /*skip_exact=*/true);
+                ctx->last_ms += tc_ms;
+                return rc0;
+            }
+            // no tensor map, or a wait ran out: the fp32 kernels redo everything
+            if (exact_max_rows > 16384) exact_max_rows = 16384;
+        }
+    }
+    return build_nnd_simt(ctx, d_reorder_data, rows, dim, h_segment_start, h_segment_length, S, knn_degree, K, max_iterations,
+                          termination_threshold, sample, exact_max_rows, seed, metric, row_base, d_knn, iterations_run, false);
+}
+
+// The fp32 kernels of the kNN stage: the register-tile all-pairs kernel for partitions of at most
+// exact_max_rows rows (unless skip_exact: the tensor-core kernel has done them) and NN-descent for the rest.
+static int build_nnd_simt(glide_ctx *ctx, const float *d_reorder_data, uint32_t rows, uint32_t dim,
+                          const uint32_t *h_segment_start, const uint32_t *h_segment_length, uint32_t S, uint32_t knn_degree,
+                          uint32_t K, uint32_t max_iterations, float termination_threshold, uint32_t sample,
+                          uint32_t exact_max_rows, uint64_t seed, int metric, uint32_t row_base, int32_t *d_knn,
+                          uint32_t *iterations_run, bool skip_exact) {
+    const uint32_t tile_count = skip_exact ? 0 : segment_knn_tile_count(h_segment_length, S, exact_max_rows);
     bool need_nnd = false;
     for (uint32_t s = 0; s < S; s++) need_nnd = need_nnd || h_segment_length[s] > exact_max_rows;
     const size_t nnd_bytes = need_nnd ? nnd_workspace_bytes(rows, K, sample, S) : 0;
@@ -487,7 +539,7 @@ int glide_build_nnd_range(glide_ctx *ctx, const float *d_reorder_data, uint32_t 
     uint32_t *d_tiles = b.take<uint32_t>((size_t) tile_count * 3 + 1);
     void *work = b.take<char>(nnd_bytes);
     std::vector<uint32_t> h_tiles((size_t) tile_count * 3 + 1);
-    segment_knn_fill_tiles(h_segment_start, h_segment_length, S, exact_max_rows, h_tiles.data());
+    if (tile_count) segment_knn_fill_tiles(h_segment_start, h_segment_length, S, exact_max_rows, h_tiles.data());
     // empty segments (C == 1 leaves the boundary segment empty, partition_kernel.cuh:58) need no launch
     Timed timer(ctx);
     GL_CUDA(ctx, cudaMemcpyAsync(d_start, h_segment_start, (size_t) S * 4, cudaMemcpyHostToDevice, ctx->stream));

@@ -161,6 +161,18 @@ void segment_knn_fill_tiles(const uint32_t *h_seg_start, const uint32_t *h_seg_l
 cudaError_t launch_segment_knn(const float *data, uint32_t dim, const uint32_t *d_tiles, uint32_t tile_count,
                                uint32_t out_degree, uint32_t row_base, int32_t *out, cudaStream_t stream);
 
+// ---- knn_tc.cu -----------------------------------------------------------
+// Exact per-partition kNN rows on the tensor cores (TF32 Gram tiles by TMA + tcgen05, threshold
+// selection, exact fp32 re-rank). Eligible: dim a multiple of 32 up to 128, out_degree <= 64, rows
+// 16-byte aligned, tensor maps available.
+bool knn_tc_eligible(const float *data, uint32_t dim, uint32_t out_degree);
+size_t knn_tc_scratch_bytes(uint64_t rows_total, uint32_t out_degree);
+// Partitions s with 1 <= h_seg_len[s] <= max_len (rows [h_seg_start[s], +len) of data). Synchronises the
+// stream. *h_failed != 0: a bounded wait ran out, recompute the rows with another kernel.
+cudaError_t launch_knn_tc(const float *data, uint64_t rows_total, uint32_t dim, const uint32_t *h_seg_start,
+                          const uint32_t *h_seg_len, uint32_t S, uint32_t max_len, uint32_t out_degree, uint32_t row_base,
+                          void *scratch, int32_t *out, uint32_t *h_failed, cudaStream_t stream);
+
 // ---- nn_descent.cu -------------------------------------------------------
 struct NndArgs {
     const float *data;   // rows x dim (reorder space)

@@ -1,0 +1,379 @@
+// Exact per-partition kNN graph on the tensor cores: the kNN stage's brute-force seeding.
+//
+// The product is the one of the reference's kNN stage (build_nnd, nn_descent.cuh:1405-1467): for
+// every row of the reordered set its nearest rows inside its own partition, partition-local ids,
+// nearest first. The reference gets there by NN-descent whose distance tiles are fp16 wmma Gram
+// tiles (nn_descent.cuh:783-811); here every row meets every row of its partition:
+//
+//   norms    |x|^2 of every row, exact fp32.
+//   contract a CTA owns 128 rows of one partition (the M of a 128 x 128 x 8 TF32 MMA) and walks the
+//            partition in tiles of 128 rows. Operand tiles arrive by TMA (one 2-D tensor map over the
+//            whole reordered matrix, boxes of 32 floats x 128 rows, 128-byte swizzle, no multicast),
+//            tcgen05.mma kind::tf32 accumulates the 128 x 128 dot products in tensor memory (two
+//            buffers), and eight epilogue warps read them back (tcgen05.ld): thread (row, half) turns
+//            64 dot products into |a|^2 + |b|^2 - 2 a.b and pushes every column that beats the row's
+//            current threshold into the row's candidate buffer.
+//   select   a row's buffer is compacted to its L smallest keys whenever it passes its trigger
+//            (a warp sorts it in registers); the threshold is the L-th key.
+//   re-rank  the exact fp32 distance of the L best candidates, sorted by (distance, id): the first
+//            out_degree are the row.
+//
+// kind::tf32 keeps 10 mantissa bits per operand, so integer-valued rows below 1024 give exact dot
+// products and the result is the exact kNN graph with ties by ascending id; elsewhere the approximate
+// order only has to bring the true neighbours into the L = 2 x list-width candidates, and the
+// re-rank orders them exactly. One producer thread issues copies and MMAs; every mbarrier wait is
+// bounded, and a CTA whose wait runs out raises a flag that makes the host redo the rows with the
+// SIMT kernels.
+#include <cstdlib>
+#include <vector>
+
+#include "beam_core.cuh"
+#include "kernels.h"
+#include "umma.cuh"
+
+namespace glide {
+
+namespace {
+
+using namespace umma;
+
+constexpr uint32_t kRows = 128;            // rows per CTA = columns per tile
+constexpr uint32_t kTmemCols = 256;        // two accumulator buffers of 128 columns
+constexpr uint32_t kEpiWarps = 8;
+constexpr uint32_t kThreads = (kEpiWarps + 1) * 32;
+constexpr u64 kNoKey = ~0ull;
+
+struct KnnTile {
+    uint32_t seg_start, seg_len, first;    // rows [first, first + 128) of the segment
+};
+
+struct KnnTcArgs {
+    const float *data;
+    uint32_t dim;
+    const float *norms;        // per row of data
+    const KnnTile *tiles;      // one per CTA
+    u64 *cand;                 // launch rows x cap
+    uint32_t *cand_count;      // launch rows
+    uint32_t *fail_flag;
+};
+
+__global__ void row_norms_kernel(const float *__restrict__ data, uint64_t rows, uint32_t dim, float *norms) {
+    const uint64_t r = ((uint64_t) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = lane_id();
+    if (r >= rows) return;
+    const float4 *row = reinterpret_cast<const float4 *>(data + r * dim);
+    float s = 0.0f;
+    for (uint32_t k = lane; k < (dim >> 2); k += 32) {
+        const float4 v = __ldg(row + k);
+        s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(kFullMask, s, off);
+    if (lane == 0) norms[r] = s;
+}
+
+// NL = 1: lists of 32 (out_degree <= 32), L = 64 candidates kept, compaction when a buffer holds more
+// than 128, capacity 256. NL = 2: lists of 64, L = 128, trigger 256, capacity 384.
+template<int NL> struct Sizes {
+    static constexpr uint32_t keep = 64u * NL, trigger = 128u * NL, cap = trigger + kRows;
+    static constexpr int sort_n = 8 * NL;   // keys per lane of the compaction sort (32 * sort_n >= cap)
+};
+
+// Sorts the row's buffer and keeps its `keep` smallest keys; returns the largest kept distance
+// (the row's new threshold). The whole warp calls it.
+template<int NL>
+__device__ __forceinline__ float compact_row(u64 *buf, uint32_t *count) {
+    constexpr int N = Sizes<NL>::sort_n;
+    const uint32_t lane = lane_id();
+    const uint32_t cnt = min(*count, Sizes<NL>::cap);
+    u64 k[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        const uint32_t e = lane + 32u * i;
+        k[i] = e < cnt ? buf[e] : kNoKey;
+    }
+    sort_u64<N>(k);   // ascending over e = N * lane + i
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        const uint32_t e = (uint32_t) N * lane + i;
+        if (e < Sizes<NL>::keep && e < cnt) buf[e] = k[i];
+    }
+    const uint32_t kept = min(cnt, Sizes<NL>::keep);
+    // the last kept key sits at e = kept - 1
+    const uint32_t src = (kept - 1) / N, idx = (kept - 1) % N;
+    u64 last = k[0];
+#pragma unroll
+    for (int i = 1; i < N; i++) last = ((uint32_t) i == idx) ? k[i] : last;
+    last = __shfl_sync(kFullMask, last, src);
+    if (lane == 0) *count = kept;
+    __syncwarp();
+    return kept == Sizes<NL>::keep ? __uint_as_float((uint32_t) (last >> 32)) : FLT_MAX;
+}
+
+template<int NL>
+__global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, const __grid_constant__ CUtensorMap tm_rows) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    const uint32_t dim = a.dim, kblocks = dim >> 5, ksteps = dim >> 3;
+    const uint32_t sub_bytes = kRows * 128u;                  // one 32-float column block of a tile
+    const uint32_t tile_bytes = kblocks * sub_bytes;
+    uint8_t *As = base;
+    uint8_t *Bs = As + tile_bytes;                            // two stages
+    float *cn_s = reinterpret_cast<float *>(Bs + 2 * tile_bytes);       // 2 x 128 column norms
+    float *thr_s = cn_s + 2 * kRows;                                    // 128 row thresholds
+    uint64_t *bars = reinterpret_cast<uint64_t *>(thr_s + kRows);       // a_full, b_full[2], mma_done[2], tmem_free[2]
+    uint64_t *a_full = bars, *b_full = bars + 1, *mma_done = bars + 3, *tmem_free = bars + 5;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
+    volatile uint32_t *failed = tmem_slot + 1;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const KnnTile tile = a.tiles[blockIdx.x];
+    const uint32_t tiles = (tile.seg_len + kRows - 1) / kRows;
+    const uint64_t launch_row0 = (uint64_t) blockIdx.x * kRows;
+
+    if (tid == 0) {
+        mbar_init(a_full, 1);
+        for (int s = 0; s < 2; s++) { mbar_init(b_full + s, 1); mbar_init(mma_done + s, 1); mbar_init(tmem_free + s, kEpiWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *failed = 0;
+    }
+    if (tid < kRows) {
+        thr_s[tid] = FLT_MAX;
+        a.cand_count[launch_row0 + tid] = 0;
+    }
+    if (warp == kEpiWarps) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == kEpiWarps) {
+        // ================= producer: TMA copies and MMA issue, one thread =================
+        if (lane == 0) {
+            auto load_tile = [&](uint8_t *dst, uint32_t row0, uint64_t *bar) {
+                mbar_expect_tx(bar, tile_bytes);
+                for (uint32_t kb = 0; kb < kblocks; kb++) tma_load_2d(dst + kb * sub_bytes, &tm_rows, kb * 32u, row0, bar);
+            };
+            load_tile(As, tile.seg_start + tile.first, a_full);
+            load_tile(Bs, tile.seg_start, b_full + 0);
+            if (tiles > 1) load_tile(Bs + tile_bytes, tile.seg_start + kRows, b_full + 1);
+            // instruction descriptor: D fp32, A and B TF32, both K-major, N = 128, M = 128
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kRows >> 3) << 17) | ((kRows >> 4) << 24);
+            const uint32_t a_addr = smem_u32(As), b_addr = smem_u32(Bs);
+            bool ok = mbar_wait(a_full, 0, failed);
+            for (uint32_t t = 0; t < tiles && ok; t++) {
+                const uint32_t s = t & 1u, use = t >> 1;
+                ok = mbar_wait(b_full + s, use & 1u, failed);
+                if (ok && t >= 2) ok = mbar_wait(tmem_free + s, (use - 1) & 1u, failed);
+                if (!ok) break;
+                fence_after();
+                for (uint32_t ks = 0; ks < ksteps; ks++) {
+                    const uint32_t off = (ks >> 2) * sub_bytes + (ks & 3u) * 32u;
+                    mma_tf32(tmem_base + s * kRows, desc_sw128(a_addr + off), desc_sw128(b_addr + s * tile_bytes + off), idesc,
+                             ks > 0 ? 1u : 0u);
+                }
+                commit_to(mma_done + s);
+                if (t + 2 < tiles) {   // stage s is free once these MMAs have read it
+                    ok = mbar_wait(mma_done + s, use & 1u, failed);
+                    if (ok) load_tile(Bs + s * tile_bytes, tile.seg_start + (t + 2) * kRows, b_full + s);
+                }
+            }
+        }
+    } else {
+        // ================= epilogue warps: thread (row, half) owns 64 columns of a tile =================
+        const uint32_t quad = warp & 3u, half = warp >> 2;
+        const uint32_t row = quad * 32u + lane;
+        const uint32_t rl = tile.first + row;                      // the row's partition-local id
+        const bool active = rl < tile.seg_len;
+        const float pnr = active ? __ldg(a.norms + tile.seg_start + rl) : 0.0f;
+        u64 *my_cand = a.cand + (launch_row0 + row) * Sizes<NL>::cap;
+        uint32_t *my_count = a.cand_count + launch_row0 + row;
+        for (uint32_t t = 0; t < tiles; t++) {
+            const uint32_t s = t & 1u, use = t >> 1;
+            if (tid < kRows) {
+                const uint32_t c = t * kRows + tid;
+                cn_s[s * kRows + tid] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
+            }
+            bool ok = !*failed && mbar_wait(mma_done + s, use & 1u, failed);
+            ok = __all_sync(kFullMask, ok);   // tcgen05.ld is a warp-wide instruction
+            named_barrier_sync(1, kEpiWarps * 32);   // this tile's norms are in place; the last tile's compactions are done
+            const float thr = thr_s[row];
+            if (ok) {
+                fence_after();
+                const uint32_t c0 = t * kRows + half * 64u;
+                for (uint32_t cb = 0; cb < 64; cb += 32) {
+                    uint32_t r[32];
+                    tmem_load32(tmem_base + ((quad * 32u) << 16) + s * kRows + half * 64u + cb, r);
+#pragma unroll
+                    for (int j4 = 0; j4 < 32; j4 += 4) {
+                        const float4 cn4 = *reinterpret_cast<const float4 *>(cn_s + s * kRows + half * 64u + cb + j4);  // broadcast
+                        const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t cid = c0 + cb + j4 + j;
+                            const float d = fmaxf((pnr + cn[j]) - 2.0f * __uint_as_float(r[j4 + j]), 0.0f);
+                            if (active && cid < tile.seg_len && cid != rl && d < thr) {
+                                const uint32_t slot = atomicAdd(my_count, 1u);
+                                if (slot < Sizes<NL>::cap) my_cand[slot] = ((u64) __float_as_uint(d) << 32) | cid;
+                            }
+                        }
+                    }
+                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_free + s);
+            }
+            named_barrier_sync(1, kEpiWarps * 32);   // every push of this tile has been made
+            {   // this warp's 16 rows: compact the buffers that passed their trigger
+                const uint32_t c = lane < 16 ? a.cand_count[launch_row0 + warp * 16 + lane] : 0u;
+                uint32_t need = __ballot_sync(kFullMask, c > Sizes<NL>::trigger);
+                while (need) {
+                    const uint32_t r = warp * 16 + (uint32_t) __ffs(need) - 1u;
+                    need &= need - 1u;
+                    const float nt = compact_row<NL>(a.cand + (launch_row0 + r) * Sizes<NL>::cap, a.cand_count + launch_row0 + r);
+                    if (lane == 0) thr_s[r] = nt;
+                }
+            }
+        }
+        if (*failed && tid == 0) atomicExch(a.fail_flag, 1u);
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == kEpiWarps) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+// Exact re-rank: a warp per row. The `keep` approximately nearest candidates get their exact fp32
+// distance (whole-warp row loads, the summation order of the search kernels), are sorted by
+// (distance, id), and the first out_degree ids are written; a row with fewer candidates than
+// out_degree (a partition of fewer rows) is padded with xorshift32(flat index) % partition size, as
+// nn_descent.cuh:1384-1391 pads.
+template<int NL>
+__global__ void __launch_bounds__(256) knn_rerank_kernel(const KnnTcArgs a, uint32_t launch_rows, uint32_t out_degree,
+                                                         uint32_t row_base, int32_t *out) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    constexpr int N = Sizes<NL>::sort_n;
+    constexpr uint32_t keep = Sizes<NL>::keep;
+    const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
+    const uint32_t lr = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (lr >= launch_rows) return;
+    const KnnTile tile = a.tiles[lr / kRows];
+    const uint32_t rl = tile.first + lr % kRows;
+    if (rl >= tile.seg_len) return;
+    uint32_t *strip = smem + (size_t) warp * (dim_pad4(a.dim) + 2 * keep);
+    float *query = reinterpret_cast<float *>(strip);
+    uint32_t *ids = strip + dim_pad4(a.dim);
+    float *dist = reinterpret_cast<float *>(ids + keep);
+    const float *seg = a.data + (uint64_t) tile.seg_start * a.dim;
+    const uint32_t cnt = min(a.cand_count[lr], Sizes<NL>::cap);
+    const u64 *buf = a.cand + (uint64_t) lr * Sizes<NL>::cap;
+    u64 k[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        const uint32_t e = lane + 32u * i;
+        k[i] = e < cnt ? buf[e] : kNoKey;
+    }
+    sort_u64<N>(k);
+    const uint32_t n = min(cnt, keep);
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        const uint32_t e = (uint32_t) N * lane + i;
+        if (e < keep) ids[e] = e < n ? (uint32_t) k[i] : 0u;
+    }
+    load_query(query, seg + (uint64_t) rl * a.dim, a.dim);
+    __syncwarp();
+    warp_rows(query, seg, a.dim, kCosine /* squared sums: order only */, n,
+              [&](uint32_t i) { return ids[i]; }, [&](uint32_t i, float d) { dist[i] = d; });
+    __syncwarp();
+    u64 ek[2 * NL];
+#pragma unroll
+    for (int i = 0; i < 2 * NL; i++) {
+        const uint32_t e = lane + 32u * i;
+        ek[i] = e < n ? (((u64) __float_as_uint(dist[e]) << 32) | ids[e]) : kNoKey;
+    }
+    sort_u64<2 * NL>(ek);
+#pragma unroll
+    for (int i = 0; i < 2 * NL; i++) {
+        const uint32_t e = (uint32_t) (2 * NL) * lane + i;
+        if (e < out_degree) {
+            const uint64_t flat = (uint64_t) (tile.seg_start + rl) * out_degree + e;
+            uint32_t u = (uint32_t) (flat + (uint64_t) row_base * out_degree);  // xorshift32, utils.cuh:14-19
+            u ^= u >> 13; u ^= u << 27; u ^= u >> 5; u *= 0x9E3779B9u;
+            const uint32_t id = (uint32_t) ek[i];
+            out[flat] = (int32_t) (e < n ? id : u % tile.seg_len);
+        }
+    }
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t) 255; }
+
+constexpr uint32_t kMaxCtasPerLaunch = 2048;   // 262,144 rows: 512 MB of candidate buffers at capacity 256
+
+template<int NL>
+cudaError_t run(const float *data, uint64_t rows_total, uint32_t dim, const std::vector<KnnTile> &tiles, uint32_t out_degree,
+                uint32_t row_base, char *scratch, int32_t *out, uint32_t *h_failed, cudaStream_t stream) {
+    float *norms = reinterpret_cast<float *>(scratch); scratch += align256(rows_total * 4);
+    uint32_t *fail_flag = reinterpret_cast<uint32_t *>(scratch); scratch += 256;
+    KnnTile *d_tiles = reinterpret_cast<KnnTile *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * sizeof(KnnTile));
+    uint32_t *cand_count = reinterpret_cast<uint32_t *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * kRows * 4);
+    u64 *cand = reinterpret_cast<u64 *>(scratch);
+    CUtensorMap tm;
+    if (!make_row_map(&tm, data, rows_total, dim, kRows)) return cudaErrorNotSupported;
+    cudaError_t e = cudaMemsetAsync(fail_flag, 0, 4, stream);
+    if (e != cudaSuccess) return e;
+    row_norms_kernel<<<(unsigned) ((rows_total * 32 + 255) / 256), 256, 0, stream>>>(data, rows_total, dim, norms);
+    const size_t smem_main = 1024 + (size_t) 3 * kRows * dim * 4 + 3 * kRows * 4 + 7 * 8 + 16;
+    if ((e = cudaFuncSetAttribute(knn_umma_kernel<NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_main)) != cudaSuccess) return e;
+    const uint32_t rr_warps = 8;
+    const size_t smem_rr = (size_t) rr_warps * (dim_pad4(dim) + 2 * Sizes<NL>::keep) * 4;
+    if (smem_rr > 48 * 1024 &&
+        (e = cudaFuncSetAttribute(knn_rerank_kernel<NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_rr)) != cudaSuccess) return e;
+    KnnTcArgs a{data, dim, norms, d_tiles, cand, cand_count, fail_flag};
+    for (size_t first = 0; first < tiles.size(); first += kMaxCtasPerLaunch) {
+        const uint32_t n = (uint32_t) std::min<size_t>(kMaxCtasPerLaunch, tiles.size() - first);
+        // the table is pageable host memory: the copy has read it when the call returns
+        if ((e = cudaMemcpyAsync(d_tiles, tiles.data() + first, (size_t) n * sizeof(KnnTile), cudaMemcpyHostToDevice, stream)) != cudaSuccess) return e;
+        knn_umma_kernel<NL><<<n, kThreads, smem_main, stream>>>(a, tm);
+        knn_rerank_kernel<NL><<<(n * kRows + rr_warps - 1) / rr_warps, rr_warps * 32, smem_rr, stream>>>(a, n * kRows, out_degree, row_base, out);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    if ((e = cudaMemcpyAsync(h_failed, fail_flag, 4, cudaMemcpyDeviceToHost, stream)) != cudaSuccess) return e;
+    return cudaStreamSynchronize(stream);
+}
+
+}  // namespace
+
+bool knn_tc_eligible(const float *data, uint32_t dim, uint32_t out_degree) {
+    static const bool off = [] { const char *v = std::getenv("GLIDE_B200_NO_TC_KNN"); return v && v[0] == '1'; }();
+    return !off && dim >= 32 && (dim & 31u) == 0 && dim <= 128 && out_degree >= 1 && out_degree <= 64 &&
+           (reinterpret_cast<uintptr_t>(data) & 15u) == 0 && encode_tiled_fn() != nullptr;
+}
+
+size_t knn_tc_scratch_bytes(uint64_t rows_total, uint32_t out_degree) {
+    const size_t cap = out_degree <= 32 ? Sizes<1>::cap : Sizes<2>::cap;
+    return align256(rows_total * 4) + 256 + align256((size_t) kMaxCtasPerLaunch * sizeof(KnnTile)) +
+           align256((size_t) kMaxCtasPerLaunch * kRows * 4) + (size_t) kMaxCtasPerLaunch * kRows * cap * 8 + 256;
+}
+
+// Exact kNN rows of every listed partition with 2 <= length <= max_len (rows of `data`, partition s =
+// rows [h_seg_start[s], +h_seg_len[s])). *h_failed != 0 afterwards: a bounded wait ran out somewhere and
+// the rows must be recomputed by another kernel. Synchronises the stream.
+cudaError_t launch_knn_tc(const float *data, uint64_t rows_total, uint32_t dim, const uint32_t *h_seg_start,
+                          const uint32_t *h_seg_len, uint32_t S, uint32_t max_len, uint32_t out_degree, uint32_t row_base,
+                          void *scratch, int32_t *out, uint32_t *h_failed, cudaStream_t stream) {
+    std::vector<KnnTile> tiles;
+    for (uint32_t s = 0; s < S; s++) {
+        if (h_seg_len[s] < 1 || h_seg_len[s] > max_len) continue;
+        for (uint32_t first = 0; first < h_seg_len[s]; first += kRows) tiles.push_back(KnnTile{h_seg_start[s], h_seg_len[s], first});
+    }
+    *h_failed = 0;
+    if (tiles.empty()) return cudaSuccess;
+    if (out_degree <= 32) return run<1>(data, rows_total, dim, tiles, out_degree, row_base, static_cast<char *>(scratch), out, h_failed, stream);
+    return run<2>(data, rows_total, dim, tiles, out_degree, row_base, static_cast<char *>(scratch), out, h_failed, stream);
+}
+
+}  // namespace glide

@@ -351,6 +351,39 @@ def test_exact_partition_knn_kernel(gpu_ctx, name, degree):
         assert knn_recall(knn, exact, degree) > 0.999
 
 
+@pytest.mark.parametrize("dim,degree,kind", [(128, 32, "int"), (64, 64, "int"), (96, 48, "unit"), (32, 16, "uniform"),
+                                             (128, 20, "scaled")])
+def test_tensor_core_knn_equals_exact_knn(gpu_ctx, dim, degree, kind):
+    """The kNN stage's tensor-core kernel (dims that are multiples of 32 up to 128) on partitions of ragged
+    sizes, from a single row to several tiles: integer-valued rows give TF32 products that are exact, so
+    the rows must equal the brute-force rows with ties by ascending id; elsewhere the exact re-rank of
+    twice the list width leaves nothing but near-ties to differ."""
+    base, _ = helpers.small_dataset(kind, 6000, dim, 10, seed=29)
+    lens = [1, 2, 40, 129, 700, 2100]
+    lens.append(6000 - sum(lens))
+    seg_len = np.array(lens, np.uint32)
+    seg_start = np.concatenate([[0], np.cumsum(seg_len)[:-1]]).astype(np.uint32)
+    metric = oracle.COSINE if kind == "unit" else oracle.EUCLIDEAN
+    d_knn, rounds, seconds = api.build_nnd(gpu_ctx, NNDescentParameter(degree), dev(gpu_ctx, base), seg_start, seg_len,
+                                           Metric(metric))
+    knn = d_knn.cpu().numpy()
+    assert rounds == 0 and knn.shape == (6000, degree) and seconds > 0
+    exact = helpers.exact_partition_knn(base, seg_start, seg_len, degree, metric)
+    for s, l in zip(seg_start, seg_len):
+        s, l = int(s), int(l)
+        got, want = knn[s:s + l], exact[s:s + l]
+        assert got.min() >= 0 and got.max() < l
+        real = min(degree, l - 1)              # entries beyond the partition's other rows are padding
+        if real == 0:
+            continue
+        if kind == "int":                      # exact arithmetic: identical, ties by ascending id
+            assert np.array_equal(got[:, :real], want[:, :real])
+        else:
+            assert (got[:, :real] == want[:, :real]).mean() > 0.99
+            assert knn_recall(got, want, real) > 0.999
+        assert not (got[:, :real] == np.arange(l)[:, None]).any()      # no self loops
+
+
 def test_mixed_exact_and_descent_partitions(gpu_ctx):
     # partitions above the threshold run NN-descent, the others the all-pairs kernel
     base, _, P = case("int128")
