@@ -64,6 +64,10 @@ def parse_args():
     ap.add_argument("--rows", type=int, default=0, help="use only the first ROWS base rows (debugging; marks the run reduced)")
     ap.add_argument("--queries", type=int, default=0)
     ap.add_argument("--partitions", type=int, default=0, help="override the partition count")
+    ap.add_argument("--rows-u8", action="store_true", help="large path: keep integer-valued rows as uint8 in host memory")
+    ap.add_argument("--route-min", type=int, default=4, help="large path: partitions every query visits at least")
+    ap.add_argument("--route-factor", type=float, default=1.2, help="large path: visit partitions within this factor of the nearest")
+    ap.add_argument("--max-beam", type=int, default=256, help="large path: last beam of the ladder that is tried")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the host baseline sample")
     ap.add_argument("--clock-seconds", type=float, default=1.5,
@@ -643,9 +647,214 @@ def run_ours(args):
     ctx.close()
 
 
+# --------------------------------------------------------------------------------------------
+# large path (cfg3: 10M x 96 cosine in 64 partitions; cfg4: 100M x 128 in 512 partitions)
+# --------------------------------------------------------------------------------------------
+LARGE = {"cfg3": dict(partitions=64, sample_rows=1 << 18), "cfg4": dict(partitions=512, sample_rows=1 << 19)}
+LARGE_BLOCK = 1 << 22   # rows generated and assigned at a time
+
+
+def run_large(args):
+    """Partitions owned by ranks (consecutive partitions to consecutive ranks, balanced by kNN cost); a
+    rank keeps the rows of its own partitions in pinned host memory and streams them through its GPU
+    (kNN graph, subgraph build, reverse edges, refine per partition). Search: every rank searches its
+    own partitions (kept in HBM) for the whole query batch, the per-rank top-k lists are gathered with
+    one NCCL all-gather and folded with the reference's merge network."""
+    import torch
+    import torch.distributed as dist
+    from glide_b200 import api, datasets, large, pipeline, sharded
+    from glide_b200.params import IndexParameter, Metric, NNDescentParameter
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = api.Context(local_rank)
+    dev = ctx.torch_device
+    if world > 1:
+        ctx.init_comm(dist, world, rank)
+    spec, reduced = make_data(args)
+    metric = Metric.parse(spec.metric)
+    n, dim, S = spec.n, spec.dim, args.partitions or LARGE[args.config]["partitions"]
+    cent = torch.from_numpy(datasets.centres(spec)).to(dev)
+    d_queries = datasets.device_queries(spec, dev, cent)
+    Q = d_queries.shape[0]
+
+    # ---- untimed: centroids, assignment of every row, exact ground truth, this rank's rows to host ----
+    d_sample = datasets.device_rows(spec, 0, min(n, LARGE[args.config]["sample_rows"]), dev, cent)
+    d_centroids, _, _ = api.kmeans_fit(ctx, d_sample, S, 0, metric, 1)
+    del d_sample
+    labels = torch.empty(n, dtype=torch.int32, device=dev)
+    gt_d = torch.full((Q, TOP_K), float("inf"), device=dev)
+    gt_i = torch.full((Q, TOP_K), -1, dtype=torch.int64, device=dev)
+    assign_s = gt_s = 0.0
+    for lo in range(0, n, LARGE_BLOCK):
+        rows = datasets.device_rows(spec, lo, min(LARGE_BLOCK, n - lo), dev, cent)
+        d_seg, _, _ = api.define_partition(ctx, rows, d_centroids, -1.0, metric)
+        assign_s += ctx.last_kernel_seconds
+        labels[lo:lo + rows.shape[0]] = d_seg[:, 0]
+        if rank == 0 or world == 1:
+            ids, dd = api.bruteforce_knn(ctx, rows, d_queries, TOP_K, metric)
+            gt_s += ctx.last_kernel_seconds
+            cat_d = torch.cat([gt_d, dd], dim=1)
+            cat_i = torch.cat([gt_i, ids.to(torch.int64) + lo], dim=1)
+            gt_d, pick = torch.topk(cat_d, TOP_K, dim=1, largest=False)
+            gt_i = torch.gather(cat_i, 1, pick)
+        del rows, d_seg
+    order = torch.sort(labels.to(torch.int64), stable=True)[1]          # reorder id -> original id
+    seg_len = torch.bincount(labels.to(torch.int64), minlength=S).cpu().numpy().astype(np.uint32)
+    seg_start = np.concatenate([[0], np.cumsum(seg_len.astype(np.int64))[:-1]]).astype(np.uint32)
+    owners = sharded.owner_ranges(seg_len, world, 1 << 20)
+    p_lo, p_hi = owners[rank]
+    r_lo = int(seg_start[p_lo]) if p_hi > p_lo else 0
+    r_hi = int(seg_start[p_hi - 1]) + int(seg_len[p_hi - 1]) if p_hi > p_lo else 0
+    mine = r_hi - r_lo
+    pos = torch.empty(n, dtype=torch.int64, device=dev)
+    pos[order] = torch.arange(n, device=dev)
+    h_map = order[r_lo:r_hi].to(torch.int32).cpu().numpy().view(np.uint32)
+    del order, labels
+    d_mine = torch.empty((mine, dim), dtype=torch.float32, device=dev)
+    for lo in range(0, n, LARGE_BLOCK):
+        rows = datasets.device_rows(spec, lo, min(LARGE_BLOCK, n - lo), dev, cent)
+        p = pos[lo:lo + rows.shape[0]]
+        keep = (p >= r_lo) & (p < r_hi)
+        d_mine[p[keep] - r_lo] = rows[keep]
+        del rows
+    del pos
+    use_u8 = args.rows_u8 and spec.kind == "int_mixture"
+    h_rows = large.pinned_empty((mine, dim), np.uint8 if use_u8 else np.float32)
+    t_rows = large._PINNED[id(h_rows)]
+    t_rows.copy_(d_mine.to(torch.uint8) if use_u8 else d_mine)
+    del d_mine
+    torch.cuda.synchronize(dev)
+    torch.cuda.empty_cache()
+
+    # ---- build (timed: wall clock around the streamed pass; kernel seconds per stage beside it) ----
+    degree = spec.graph_degree
+    index = large.GLIDE_large(ctx, degree, metric, h_rows, h_map, d_centroids.cpu().numpy(), seg_start, seg_len, row_offset=r_lo)
+    cfg = pipeline.BuildConfig(metric=metric, graph_degree=degree, knn_degree=32)
+    p_knn, p_refine = pipeline.derive_build_search_params(cfg)
+    my_parts = np.arange(p_lo, p_hi, dtype=np.uint32)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    index.build(IndexParameter(degree, 32, 1.05, metric), p_knn, p_refine, seed=spec.seed, partitions=my_parts)
+    torch.cuda.synchronize(dev)
+    build_wall = time.perf_counter() - t0
+    stage = dict(index.stage_seconds)
+    bstats = dict(index.stats)
+    tb = torch.tensor([build_wall] + [stage[k] for k in ("knn", "subgraph_build", "reverse_graph", "refine")],
+                      dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+    build_wall_max = float(tb[0])
+
+    # ---- search ----
+    resident = index.make_resident(int(150e9), partitions=my_parts)
+    set_ids = torch.empty((world, Q, TOP_K), dtype=torch.int32, device=dev)
+    set_d = torch.empty((world, Q, TOP_K), dtype=torch.float32, device=dev)
+    out_ids = api._u32_tensor(ctx, (Q, TOP_K))
+    out_d = ctx.empty((Q, TOP_K), torch.float32)
+    offs = [r * Q for r in range(world)]
+    cnts = [Q] * world
+    coll = sharded.GlideCollectives(ctx) if world > 1 else None
+
+    def search(sp):
+        """(ids on the host, seconds of this rank's kernels, wall seconds including the gather and the merge)"""
+        torch.cuda.synchronize(dev)
+        t1 = time.perf_counter()
+        d_i, d_dd, ksec = index.search_device(sp, args.route_min, args.route_factor, d_queries, partitions=my_parts)
+        if world == 1:
+            torch.cuda.synchronize(dev)
+            return api.to_u32(d_i), ksec, time.perf_counter() - t1
+        set_ids[rank].copy_(d_i)
+        set_d[rank].copy_(d_dd)
+        coll.all_gather_v(set_ids.view(world * Q, TOP_K), offs, cnts)
+        coll.all_gather_v(set_d.view(world * Q, TOP_K), offs, cnts)
+        coll.sync()
+        ctx.check(ctx.lib.glide_merge_results(ctx.handle, set_ids.data_ptr(), set_d.data_ptr(), world, Q, TOP_K,
+                                              out_ids.data_ptr(), out_d.data_ptr()))
+        torch.cuda.synchronize(dev)
+        return api.to_u32(out_ids), ksec, time.perf_counter() - t1
+
+    gt = gt_i.to(torch.int32).cpu().numpy().view(np.uint32)
+    if world > 1:   # every rank measures recall against rank 0's ground truth
+        g = torch.from_numpy(gt.view(np.int32).copy()).to(dev)
+        dist.broadcast(g, src=0)
+        gt = g.cpu().numpy().view(np.uint32)
+    chosen, curve = None, []
+    for beam in [b for b in BEAM_LADDER if b <= args.max_beam]:
+        sp = pipeline.derive_search_params(beam, degree, TOP_K)
+        ids, ksec, wall = search(sp)
+        rec = api.calculate_recall(ids, gt, TOP_K)
+        curve.append({"beam": beam, "recall": round(rec, 4), "qps_wall": round(Q / wall, 1)})
+        chosen = (beam, sp, rec)
+        if rec >= TARGET_RECALL:
+            break
+    beam, sp, recall = chosen
+    for _ in range(args.warmup):
+        search(sp)
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ksum = wsum = 0.0
+    for _ in range(args.steps):
+        _, ksec, wall = search(sp)
+        ksum += ksec
+        wsum += wall
+    sstats = dict(index.stats)
+    clocks = sampler.stop() if rank == 0 else None
+    ts = torch.tensor([ksum, wsum], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+    kmax, wmax = float(ts[0]), float(ts[1])
+    if rank == 0:
+        line = {
+            "metric": METRIC_NAME, "value": Q * args.steps / kmax, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": kmax / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic (drawn on the device, seeded per block of 2^20 rows)",
+            "config": {"workload": f"{spec.name}: {n}x{dim} {'uint8' if use_u8 else 'fp32'} {spec.metric}, large path, {S} partitions, "
+                                   f"{Q} queries, k={TOP_K}, graph degree {degree}",
+                       "beam": beam, "reduced": reduced, "route_min_partitions": args.route_min, "route_factor": args.route_factor,
+                       "l2": "partitions larger than L2 walked per query batch",
+                       "multi_gpu": "partitions owned by ranks; per-rank top-k gathered (NCCL) and merged" if world > 1 else "single GPU"},
+            "recall_at_10": round(recall, 4), "recall_target_reached": bool(recall >= TARGET_RECALL), "recall_curve": curve,
+            "build": {"wall_seconds": round(build_wall_max, 3),
+                      "kernel_seconds_max_over_ranks": {k: round(float(v), 4) for k, v in
+                                                        zip(("knn", "subgraph_build", "reverse_graph", "refine"), tb[1:].tolist())},
+                      "rank0": {"rows": mine, "partitions": int(p_hi - p_lo), "h2d_gbs": round(bstats["h2d_bytes"] / max(bstats["h2d_seconds"], 1e-9) / 1e9, 2),
+                                "h2d_bytes": bstats["h2d_bytes"], "upload_stream_seconds": round(bstats["h2d_seconds"], 3)},
+                      "untimed": {"assignment_kernel_seconds": round(assign_s, 3), "ground_truth_kernel_seconds": round(gt_s, 3)}},
+            "search": {"resident_partitions_rank0": resident, "partitions_searched_rank0": sstats.get("partitions_searched"),
+                       "partitions_uploaded_rank0": sstats.get("partitions_uploaded"),
+                       "kernel_qps": Q * args.steps / kmax, "wall_qps_with_gather_and_merge": Q * args.steps / wmax},
+            "e2e": {"value": Q * args.steps / wmax, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": Q * TOP_K * 4,
+                    "note": "wall clock of the public call on device-resident queries, result ids read back to the host"},
+            "gpu_launches": None, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    index.close()
+    ctx.close()
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.config in LARGE:
+        if args.impl == "reference":
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference's large path does not compile as shipped "
+                                  "(glide_large.cuh:182 against glide_large_impl.cuh:79) and has no CPU implementation"}), flush=True)
+            return
+        run_large(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

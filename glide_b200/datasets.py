@@ -150,3 +150,47 @@ def queries(spec: DatasetSpec, cent: np.ndarray | None = None) -> np.ndarray:
 def make(spec: DatasetSpec) -> tuple[np.ndarray, np.ndarray]:
     cent = centres(spec)
     return base_rows(spec, cent=cent), queries(spec, cent=cent)
+
+
+# ---------------------------------------------------------------------------------------------
+# Device-side generation for the 10M- and 100M-row configs: the same mixtures drawn with torch's
+# counter-based CUDA generator, one seeded stream per block of 1,048,576 rows, so that any block can
+# be produced on any rank without the others (the numpy generator above would need minutes of host
+# time per 100M rows). The values differ from the numpy stream's; the distribution is the same.
+# ---------------------------------------------------------------------------------------------
+DEVICE_BLOCK = 1 << 20
+
+
+def device_rows(spec: DatasetSpec, first: int, count: int, device, cent=None, stream: int = 1):
+    """Rows [first, first + count) as a float32 tensor on `device` (first must be a multiple of DEVICE_BLOCK
+    unless the range lies inside one block)."""
+    import torch
+    if cent is None:
+        cent = torch.from_numpy(centres(spec)).to(device)
+    out = torch.empty((count, spec.dim), dtype=torch.float32, device=device)
+    done = 0
+    while done < count:
+        row = first + done
+        block, off = divmod(row, DEVICE_BLOCK)
+        take = min(count - done, DEVICE_BLOCK - off)
+        g = torch.Generator(device=device)
+        g.manual_seed(((spec.seed * 7 + stream) << 32) + block)
+        comp = torch.randint(0, spec.centres, (DEVICE_BLOCK,), generator=g, device=device)[off:off + take]
+        noise = torch.randn((DEVICE_BLOCK, spec.dim), generator=g, device=device, dtype=torch.float32)[off:off + take]
+        if spec.kind == "int_mixture":
+            blockv = torch.clamp(torch.round(cent[comp] + 20.0 * noise), 0.0, 218.0)
+        elif spec.kind == "unit_mixture":
+            blockv = cent[comp] + 0.5 * noise
+            blockv = blockv / blockv.norm(dim=1, keepdim=True)
+        elif spec.kind == "scaled_mixture":
+            scale = torch.rand((DEVICE_BLOCK,), generator=g, device=device)[off:off + take] + 0.5
+            blockv = (cent[comp] + 0.3 * noise) * scale[:, None]
+        else:
+            raise ValueError(spec.kind)
+        out[done:done + take] = blockv
+        done += take
+    return out
+
+
+def device_queries(spec: DatasetSpec, device, cent=None):
+    return device_rows(spec, 0, spec.n_queries, device, cent, stream=2)

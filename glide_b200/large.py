@@ -117,7 +117,10 @@ class GLIDE_large:
     uploads / kernels / downloads on three streams, partitions kept in HBM up to a budget for search."""
 
     def __init__(self, ctx: api.Context, graph_degree: int, metric: Metric, h_reorder_data: np.ndarray, h_map,
-                 h_centroids, h_segment_start, h_segment_length):
+                 h_centroids, h_segment_start, h_segment_length, row_offset: int = 0):
+        """row_offset > 0: this process holds only the reorder rows [row_offset, row_offset + len(h_reorder_data))
+        (a rank of a multi-GPU run holds the rows of its own partitions); the segment tables still
+        describe every partition, and only partitions inside that range may be built or searched here."""
         import ctypes as C
         self.ctx, self.metric = ctx, metric
         if h_reorder_data.dtype not in (np.float32, np.uint8):
@@ -128,16 +131,21 @@ class GLIDE_large:
         self.h_centroids = np.ascontiguousarray(h_centroids, np.float32)
         self.seg_start = np.ascontiguousarray(h_segment_start, np.uint32)
         self.seg_len = np.ascontiguousarray(h_segment_length, np.uint32)
+        self.row_offset = int(row_offset)
+        if self.h_map.shape[0] != self.h_data.shape[0]:
+            raise ValueError("one map entry per held row expected")
         self.h_graph = pinned_empty((self.h_data.shape[0], graph_degree), np.uint32)
         self.h_graph.fill(api.INVALID)
         self.stage_seconds: dict[str, float] = {}
         self.stats: dict = {}
         self.d_centroids = torch.from_numpy(self.h_centroids).to(ctx.torch_device)
         handle = C.c_void_p()
-        ctx.check(ctx.lib.glide_large_create(ctx.handle, self.h_data.ctypes.data, 1 if self.h_data.dtype == np.uint8 else 0,
-                                             self.h_data.shape[1], self.seg_start.ctypes.data, self.seg_len.ctypes.data,
-                                             self.seg_start.size, self.h_map.ctypes.data, graph_degree, int(metric),
-                                             self.h_graph.ctypes.data, C.byref(handle)))
+        off = self.row_offset   # the library indexes by global reorder row: hand it where row 0 would lie
+        ctx.check(ctx.lib.glide_large_create(
+            ctx.handle, self.h_data.ctypes.data - off * self.h_data.shape[1] * self.h_data.itemsize,
+            1 if self.h_data.dtype == np.uint8 else 0, self.h_data.shape[1], self.seg_start.ctypes.data,
+            self.seg_len.ctypes.data, self.seg_start.size, self.h_map.ctypes.data - off * 4, graph_degree, int(metric),
+            self.h_graph.ctypes.data - off * graph_degree * 4, C.byref(handle)))
         self.handle = handle
 
     def close(self):
@@ -195,8 +203,9 @@ class GLIDE_large:
         ctx.sync_inputs()
         ctx.check(ctx.lib.glide_large_build(self.handle, parts.ctypes.data, parts.size, knn_degree, C.byref(pk), C.byref(pr),
                                             build_param.relaxant_factor, nnd.max_iterations, nnd.termination_threshold, 0,
-                                            exact_max_rows, seed, None if knn_in is None else knn_in.ctypes.data,
-                                            None if self.h_knn is None else self.h_knn.ctypes.data))
+                                            exact_max_rows, seed,
+                                            None if knn_in is None else knn_in.ctypes.data - self.row_offset * knn_degree * 4,
+                                            None if self.h_knn is None else self.h_knn.ctypes.data - self.row_offset * knn_degree * 4))
         st = self._stats()
         self.stage_seconds = dict(knn=st[0], subgraph_build=st[1], reverse_graph=st[2], refine=st[3])
         self.stats = dict(h2d_bytes=st[4], h2d_seconds=st[5], partitions_uploaded=int(st[6]))

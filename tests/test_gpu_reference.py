@@ -483,10 +483,10 @@ def test_reference_kernels_at_scale_where_recall_is_meaningful(gpu_ctx, capsys):
     component, a configuration inside the reference's own size ladders on which its searches reach a
     useful recall: built-graph fill and search recall at equal beam must agree with the reference
     kernels' (refine is the one stage whose rows cannot be compared bit for bit, the reference's
-    being schedule dependent), and the kNN stage runs NN-descent on partitions of ~31,000 rows."""
+    being schedule dependent), and the kNN stage's rows (partitions of ~31,000 rows) are checked
+    against exact kNN on a sample."""
     import os
     rows = int(os.environ.get("GLIDE_REF_SCALE_ROWS", "1000000"))
     report = _at_scale(gpu_ctx, "cfg1c32", 32, rows, capsys)
-    assert report["knn_stage"]["nn_descent_rounds"] >= 1
-    assert report["knn_stage"]["graph_recall_at_10_on_a_sample"] >= 0.95
+    assert report["knn_stage"]["graph_recall_at_10_on_a_sample"] >= 0.99   # the tensor-core all-pairs kernel: exact rows
     assert report["search"][1]["recall_ours"] > 0.9
