@@ -13,6 +13,14 @@ struct BeamParamsHost {
 };
 
 // ---- search.cu -----------------------------------------------------------
+// One partition of the large path as the device sees it (local ids; map: local id -> original id).
+struct PartitionRef {
+    const float *data;       // rows x dim; nullptr: the partition is not in device memory
+    const uint32_t *graph;   // rows x degree
+    const uint32_t *map;
+    uint32_t start_point, rows;
+};
+
 struct SearchArgs {
     const float *data;           // n x dim
     const uint32_t *graph;       // n x degree
@@ -32,6 +40,8 @@ struct SearchArgs {
     const uint32_t *segment_ids; // Q x segment_num, or nullptr for the small path
     uint32_t segment_num, segment_id, start_point;
     const uint32_t *map;         // local id -> global id (large path)
+    const PartitionRef *parts;   // large path, every partition in device memory: a query walks ALL the partitions it is
+                                 // routed to inside one launch, in ascending partition order (segment_id is then unused)
     unsigned long long *counters;  // [0] data rows read, [1] expansions; may be nullptr
     const uint32_t *order;       // ticket t is query order[t] (queries grouped by partition: warps that run together
                                  // share L2 lines); nullptr: query t

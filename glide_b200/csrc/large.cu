@@ -26,6 +26,7 @@
 
 #include "../../include/glide_b200.h"
 #include "ctx.h"
+#include "kernels.h"
 
 namespace {
 
@@ -142,6 +143,7 @@ struct glide_large {
     bool slot_has_knn = false;
     std::vector<Slot> resident;     // per partition; rows == nullptr when not resident
     size_t resident_bytes = 0;
+    glide::PartitionRef *d_parts = nullptr;   // S entries: where each resident partition lies in device memory
     uint32_t *d_routed = nullptr;   // S counters
     uint32_t *d_routes = nullptr;   // Q x S
     size_t routes_capacity = 0;
@@ -268,7 +270,8 @@ int glide_large_create(glide_ctx *ctx, const void *h_rows, int row_type, uint32_
     L->resident.resize(segment_num);
     if (cudaStreamCreateWithFlags(&L->up, cudaStreamNonBlocking) != cudaSuccess ||
         cudaStreamCreateWithFlags(&L->down, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaMalloc(&L->d_routed, (size_t) segment_num * 4) != cudaSuccess) {
+        cudaMalloc(&L->d_routed, (size_t) segment_num * 4) != cudaSuccess ||
+        cudaMalloc(&L->d_parts, (size_t) segment_num * sizeof(glide::PartitionRef)) != cudaSuccess) {
         glide_large_destroy(L);
         return fail(ctx, GLIDE_ERR_CUDA, "large_create: stream or counter allocation failed");
     }
@@ -285,6 +288,7 @@ void glide_large_destroy(glide_large *L) {
     for (auto &s : L->slot) free_slot(s);
     for (auto &s : L->resident) free_slot(s);
     if (L->d_routed) cudaFree(L->d_routed);
+    if (L->d_parts) cudaFree(L->d_parts);
     if (L->d_routes) cudaFree(L->d_routes);
     if (L->up) cudaStreamDestroy(L->up);
     if (L->down) cudaStreamDestroy(L->down);
@@ -504,6 +508,42 @@ int glide_large_search(glide_large *L, const float *d_queries, uint32_t q, const
         if (!L->resident[s].rows) max_stream_rows = std::max(max_stream_rows, L->seg_len[s]);
     }
     std::sort(todo.begin(), todo.end());
+    if (max_stream_rows == 0 && !todo.empty()) {
+        // Every partition this batch visits lies in device memory: one launch, a warp per query walks
+        // the partitions the query is routed to in ascending order (the order of the reference's
+        // loop over partitions), instead of one launch per partition in which most warps find that
+        // their query is not routed there.
+        std::vector<glide::PartitionRef> refs(S, glide::PartitionRef{nullptr, nullptr, nullptr, 0, 0});
+        for (uint32_t s : todo) {
+            const Slot &r = L->resident[s];
+            refs[s] = glide::PartitionRef{r.rows, r.graph, r.map, L->start_points[s], L->seg_len[s]};
+        }
+        LG_CUDA(ctx, cudaMemcpyAsync(L->d_parts, refs.data(), (size_t) S * sizeof(glide::PartitionRef), cudaMemcpyHostToDevice, ctx->stream));
+        LG_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // refs is a local vector
+        if (p->beam < 32 || p->beam % 32 || p->beam > 512 || p->top_k < 1 || p->top_k > 128 || p->top_k > p->beam)
+            return fail(ctx, GLIDE_ERR_BAD_ARG, "large_search: bad search parameters");
+        glide::SearchArgs a{};
+        a.degree = L->degree; a.dim = L->dim; a.queries = d_queries; a.Q = q; a.top_k = p->top_k; a.metric = L->metric;
+        a.p = glide::BeamParamsHost{p->beam, p->max_iterations, p->min_iterations, p->hash_bit, p->hash_reset_interval};
+        a.C = 1; a.out_ids = d_final_ids; a.out_dists = d_final_dists;
+        a.segment_ids = L->d_routes; a.segment_num = S; a.parts = L->d_parts;
+        a.ticket = ctx->ticket;
+        cudaEvent_t k0, k1;
+        LG_CUDA(ctx, cudaEventCreate(&k0));
+        LG_CUDA(ctx, cudaEventCreate(&k1));
+        LG_CUDA(ctx, cudaEventRecord(k0, ctx->stream));
+        LG_CUDA(ctx, glide::launch_search(a, ctx->stream));
+        LG_CUDA(ctx, cudaEventRecord(k1, ctx->stream));
+        LG_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        float ms = 0;
+        cudaEventElapsedTime(&ms, k0, k1);
+        cudaEventDestroy(k0);
+        cudaEventDestroy(k1);
+        L->last_stage_seconds[1] = ms / 1e3f;
+        L->last_searched_partitions = (uint32_t) todo.size();
+        ctx->last_ms = (L->last_stage_seconds[0] + L->last_stage_seconds[1]) * 1e3f;
+        return GLIDE_OK;
+    }
     if (max_stream_rows) {
         rc = ensure_slots(L, max_stream_rows, L->slot_has_knn, 64);
         if (rc) return rc;

@@ -37,13 +37,23 @@ __device__ inline void warp_merge_final_smem(float *k, uint32_t *v, uint32_t n_p
 
 // LANES: adjacency rows of at most 32 entries, candidates stay in registers (beam_loop_lanes);
 // the strip then holds only the query and the visited set.
-template<int NB, int NC, bool LANES>
-__device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &s, const BeamParams &p, uint32_t q) {
+// The partition a large-path search runs in.
+struct PartView {
+    const float *data;
+    const uint32_t *graph, *map;
+    uint32_t start_point;
+};
+
+template<int NB, int NC, bool LANES, bool PARTS = false>
+__device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &s, const BeamParams &p, uint32_t q,
+                                           const PartView &given, bool check_routed) {
     const SearchArgs &a = d.a;
     const uint32_t lane = lane_id();
+    // outside the multi-partition kernel the partition is the launch's own (kernel parameters, no registers)
+    const PartView view = PARTS ? given : PartView{a.data, a.graph, a.map, a.start_point};
 
     const bool sub = (a.segment_ids != nullptr);
-    if (sub) {  // search_kernel.cuh:676-692: skip queries not routed to this partition
+    if (sub && check_routed) {  // search_kernel.cuh:676-692: skip queries not routed to this partition
         bool routed = false;
         if (lane == 0) {
             for (uint32_t i = 0; i < a.segment_num; i++) {
@@ -67,7 +77,7 @@ __device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &
         const uint32_t r = a.route[q];
         start_node = a.start_points[r < a.C ? r : 0u];   // the routing kernels never write an id beyond C; checked all the same
     } else {
-        start_node = a.start_point;
+        start_node = view.start_point;
     }
     float bk[NB];
     uint32_t bv[NB];
@@ -75,11 +85,11 @@ __device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &
     if constexpr (LANES) {
         float ck;
         uint32_t cv;
-        rows += seed_lanes(s, start_node, kInvalid, a.graph, a.degree, p.hash_bit, a.data, a.dim, a.metric, ck, cv);
-        iters = beam_loop_lanes<NB>(bk, bv, s, p, kInvalid, a.graph, a.degree, a.data, a.dim, a.metric, &rows, ck, cv);
+        rows += seed_lanes(s, start_node, kInvalid, view.graph, a.degree, p.hash_bit, view.data, a.dim, a.metric, ck, cv);
+        iters = beam_loop_lanes<NB>(bk, bv, s, p, kInvalid, view.graph, a.degree, view.data, a.dim, a.metric, &rows, ck, cv);
     } else {
-        rows += seed_from_row(s, start_node, kInvalid, a.graph, a.degree, p.hash_bit, a.data, a.dim, a.metric);
-        iters = beam_loop<NB, NC>(bk, bv, s, p, kInvalid, a.graph, a.degree, a.data, a.dim, a.metric, &rows);
+        rows += seed_from_row(s, start_node, kInvalid, view.graph, a.degree, p.hash_bit, view.data, a.dim, a.metric);
+        iters = beam_loop<NB, NC>(bk, bv, s, p, kInvalid, view.graph, a.degree, view.data, a.dim, a.metric, &rows);
     }
 
     if (!sub) {
@@ -105,7 +115,7 @@ __device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &
             if (j < a.top_k) {
                 rk[j] = bk[i];
                 const uint32_t id = bv[i] & kClean;
-                rv[j] = (id == kPadClean) ? kInvalid : a.map[id];  // an unfilled slot has no global id
+                rv[j] = (id == kPadClean) ? kInvalid : view.map[id];  // an unfilled slot has no global id
             }
         }
         float *fd = a.out_dists + (uint64_t) q * a.top_k;
@@ -138,7 +148,7 @@ __device__ __forceinline__ void search_one(const SearchDev &d, const WarpStrip &
 // A warp per query. With a ticket counter the grid is sized to what the device holds at once and
 // every warp draws its next query as soon as it finishes one, so a slow query delays neither the
 // other warps of its CTA nor a whole wave of CTAs.
-template<int NB, int NC, bool LANES>
+template<int NB, int NC, bool LANES, bool PARTS = false>
 __device__ __forceinline__ void search_body(const SearchDev &d) {
     extern __shared__ __align__(16) uint32_t smem[];
     const SearchArgs &a = d.a;
@@ -146,9 +156,10 @@ __device__ __forceinline__ void search_body(const SearchDev &d) {
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
     const WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLaneScratch : 32u * NC, p.hash_bit);
+    const PartView whole{a.data, a.graph, a.map, a.start_point};
     if (a.ticket == nullptr) {
         const uint32_t q = blockIdx.x * warps_per_cta + warp;
-        if (q < a.Q) search_one<NB, NC, LANES>(d, s, p, q);
+        if (q < a.Q) search_one<NB, NC, LANES>(d, s, p, q, whole, true);
         return;
     }
     while (true) {
@@ -157,7 +168,35 @@ __device__ __forceinline__ void search_body(const SearchDev &d) {
         q = __shfl_sync(kFullMask, q, 0);
         if (q >= a.Q) break;
         if (a.order) q = a.order[q];
-        search_one<NB, NC, LANES>(d, s, p, q);
+        if constexpr (!PARTS) {
+            search_one<NB, NC, LANES>(d, s, p, q, whole, true);
+        } else {
+            // Every partition the query is routed to, in ascending partition order: the order in which
+            // the reference's loop over partitions (glide_large_impl.cuh:424-493) folds them into the
+            // running result. The routed list is a prefix of the query's row of segment_ids.
+            const uint32_t *ids = a.segment_ids + (uint64_t) q * a.segment_num;
+            const uint32_t r0 = lane < a.segment_num ? ids[lane] : kInvalid;
+            const uint32_t r1 = lane + 32u < a.segment_num ? ids[lane + 32u] : kInvalid;
+            const bool longer = a.segment_num > 64u && ids[64] != kInvalid;   // rare: more than 64 partitions routed
+            uint32_t prev = kInvalid;
+            while (true) {
+                uint32_t best = kInvalid;
+                if (r0 != kInvalid && (prev == kInvalid || r0 > prev)) best = r0;
+                if (r1 != kInvalid && (prev == kInvalid || r1 > prev) && r1 < best) best = r1;
+                if (longer)
+                    for (uint32_t i = 64u + lane; i < a.segment_num; i += 32u) {
+                        const uint32_t sid = ids[i];
+                        if (sid != kInvalid && (prev == kInvalid || sid > prev) && sid < best) best = sid;
+                    }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) best = min(best, __shfl_xor_sync(kFullMask, best, off));
+                if (best == kInvalid) break;
+                prev = best;
+                const PartitionRef ref = a.parts[best];
+                if (ref.data != nullptr) search_one<NB, NC, LANES, true>(d, s, p, q, PartView{ref.data, ref.graph, ref.map, ref.start_point}, false);
+                __syncwarp();
+            }
+        }
         __syncwarp();
     }
 }
@@ -214,10 +253,19 @@ uint32_t pow2_at_least(uint32_t x, uint32_t lo) {
     return m;
 }
 
+// Large path with every partition in device memory: a warp walks all the partitions its query is routed to.
+template<int NB, int NC, bool LANES>
+__global__ void __launch_bounds__(256, NB <= 4 ? 3 : 2) search_parts_kernel(const SearchDev d) {
+    search_body<NB, NC, LANES, true>(d);
+}
+
 template<int NB, int NC, bool LANES = false>
 cudaError_t launch_search_t(const SearchDev &d, uint32_t warps_per_cta, size_t smem_bytes, cudaStream_t stream) {
     void (*kernel)(const SearchDev) = search_kernel<NB, NC, LANES>;
     if constexpr (NB == 1) kernel = search_kernel_32<NC, LANES>;
+    if constexpr (NB > 1) {
+        if (d.a.parts != nullptr) kernel = search_parts_kernel<NB, NC, LANES>;
+    }
     if (smem_bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
         if (e != cudaSuccess) return e;
@@ -267,7 +315,7 @@ cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
     if (strip_bytes * warps > 200 * 1024) return cudaErrorInvalidValue;
     const int nb = max_beam / 32, nc = max_cand / 32;
     if (lanes) {
-        if (a.p.beam <= 32 && warps == 8 && strip_bytes * 9 * 4 <= 200 * 1024) {
+        if (a.p.beam <= 32 && warps == 8 && strip_bytes * 9 * 4 <= 200 * 1024 && a.parts == nullptr) {
             static const uint32_t w32 = [] {   // experiments: GLIDE_B200_SEARCH_WARPS=8 restores eight warps per CTA
                 const char *e = std::getenv("GLIDE_B200_SEARCH_WARPS");
                 const uint32_t v = e ? (uint32_t) std::strtoul(e, nullptr, 10) : 9u;
@@ -276,7 +324,7 @@ cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
             warps = w32;
         }
         const size_t bytes = strip_bytes * warps;
-        if (a.p.beam <= 32) return launch_search_t<1, 2, true>(d, warps, bytes, stream);
+        if (a.p.beam <= 32 && a.parts == nullptr) return launch_search_t<1, 2, true>(d, warps, bytes, stream);   // (the 64-slot kernel gives the same beam)
         if (nb == 2) return launch_search_t<2, 2, true>(d, warps, bytes, stream);
         if (nb == 4) return launch_search_t<4, 2, true>(d, warps, bytes, stream);
         if (nb == 8) return launch_search_t<8, 2, true>(d, warps, bytes, stream);
