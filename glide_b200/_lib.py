@@ -64,6 +64,10 @@ SIGNATURES = {
     "glide_refine_waves": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32]),
     "glide_search": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_search_host": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
+    "glide_search_pipe_create": (i32, [vp, u32, u32, u32, u32, P(vp)]),
+    "glide_search_pipe_destroy": (None, [vp]),
+    "glide_search_pipe_submit": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp, P(u32)]),
+    "glide_search_pipe_wait": (i32, [vp, u32]),
     "glide_search_static_scratch": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_last_search_split_ms": (None, [vp, P(f32)]),
     "glide_last_search_launches": (u32, [vp]),

@@ -492,3 +492,55 @@ class GLIDE:
                                             _ptr(self.d_start_points), _ptr(h_query), q, C.byref(pc),
                                             int(self.metric), _ptr(h_ids), _ptr(h_dists)))
         return h_ids, h_dists
+
+    def search_pipe(self, max_queries: int, max_top_k: int, depth: int = 3) -> "SearchPipe":
+        """Host-buffer search with `depth` batches in flight (`glide_search_pipe_*`)."""
+        return SearchPipe(self, max_queries, max_top_k, depth)
+
+
+class SearchPipe:
+    """`glide_search_host` with several batches in flight: `submit` enqueues the upload, the kernels
+    and the download of one batch and returns its slot, `wait(slot)` returns when the batch's
+    results are in the arrays given to `submit`. Pass pinned arrays (`large.pinned_empty`), which
+    must stay alive and untouched until `wait`."""
+
+    def __init__(self, index: "GLIDE", max_queries: int, max_top_k: int, depth: int = 3):
+        self.index, self.ctx = index, index.ctx
+        self._h = C.c_void_p()
+        self.ctx.check(self.ctx.lib.glide_search_pipe_create(self.ctx.handle, int(max_queries), index.dim(), int(max_top_k),
+                                                             int(depth), C.byref(self._h)))
+        self.depth = int(depth)
+
+    def submit(self, param: SearchParameter, h_query: np.ndarray, h_ids: np.ndarray, h_dists: np.ndarray) -> int:
+        ix = self.index
+        q = h_query.shape[0]
+        if h_query.dtype != np.float32 or h_query.ndim != 2 or h_query.shape[1] != ix.dim() or not h_query.flags.c_contiguous:
+            raise TypeError(f"queries must be a C-contiguous Q x {ix.dim()} float32 array")
+        for name, arr, kinds in (("h_ids", h_ids, (np.uint32, np.int32)), ("h_dists", h_dists, (np.float32,))):
+            if arr.dtype not in kinds or arr.shape != (q, param.top_k) or not arr.flags.c_contiguous:
+                raise TypeError(f"{name} must be a C-contiguous {q} x {param.top_k} array of {kinds[0].__name__}")
+        pc = _params_c(param)
+        slot = C.c_uint32()
+        self.ctx.check(self.ctx.lib.glide_search_pipe_submit(
+            self._h, _ptr(ix.d_data), ix.num(), ix.dim(), _ptr(ix.d_graph), ix.graph_degree(), _ptr(ix.d_centroids),
+            ix.centroid_num(), _ptr(ix.d_start_points), _ptr(h_query), q, C.byref(pc), int(ix.metric), _ptr(h_ids),
+            _ptr(h_dists), C.byref(slot)))
+        return slot.value
+
+    def wait(self, slot: int) -> None:
+        self.ctx.check(self.ctx.lib.glide_search_pipe_wait(self._h, int(slot)))
+
+    def drain(self) -> None:
+        for s in range(self.depth):
+            self.wait(s)
+
+    def close(self) -> None:
+        if self._h:
+            self.ctx.lib.glide_search_pipe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -589,6 +589,12 @@ int glide_start_point_select(const uint32_t *h_segment_start, const uint32_t *h_
     return GLIDE_OK;
 }
 
+static uint32_t longest_partition(const uint32_t *h_len, uint32_t lo, uint32_t hi) {
+    uint32_t m = 0;
+    for (uint32_t s = lo; s < hi; s++) m = h_len[s] > m ? h_len[s] : m;
+    return m;
+}
+
 int glide_subgraph_build_and_merge(glide_ctx *ctx, const float *d_reorder_data, uint32_t reorder_num, uint32_t dim,
                                    const uint32_t *d_knn, uint32_t knn_degree, const uint32_t *h_segment_start,
                                    const uint32_t *h_segment_length, uint32_t S, const uint32_t *d_start_points_local,
@@ -617,11 +623,13 @@ int glide_subgraph_build_and_merge(glide_ctx *ctx, const float *d_reorder_data, 
     a.seg_start = d_start; a.seg_len = d_len; a.S = S; a.start_points = d_start_points_local; a.map = d_map;
     a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
     a.counters = counters_or_null(ctx);
+    a.max_seg_rows = longest_partition(h_segment_length, 0, S);
     GL_CUDA(ctx, launch_build(a, ctx->stream));
     const uint32_t boundary_num = reorder_num - num;
     if (!skip_boundary && boundary_num > 0) {  // glide_impl.cuh:149-187
         a.mode = kModeBoundary;
         a.fixed_segment = S - 1;
+        a.max_seg_rows = h_segment_length[S - 1];
         a.first = num;
         a.count = boundary_num;
         GL_CUDA(ctx, launch_build(a, ctx->stream));
@@ -662,6 +670,7 @@ int glide_subgraph_build_range(glide_ctx *ctx, const float *d_reorder_data, uint
         a.mode = kModeBuild;
         a.first = first_row;
         a.count = (end < num ? end : num) - first_row;
+        a.max_seg_rows = longest_partition(h_segment_length, 0, S);
         GL_CUDA(ctx, launch_build(a, ctx->stream));
     }
     if (end > num) {  // boundary copies: build_boundary_kernel
@@ -669,6 +678,7 @@ int glide_subgraph_build_range(glide_ctx *ctx, const float *d_reorder_data, uint
         a.fixed_segment = S - 1;
         a.first = first_row > num ? first_row : num;
         a.count = end - a.first;
+        a.max_seg_rows = h_segment_length[S - 1];
         GL_CUDA(ctx, launch_build(a, ctx->stream));
     }
     return timer.finish();
@@ -706,6 +716,7 @@ int glide_subgraph_build_rows(glide_ctx *ctx, const float *d_reorder_data, uint3
     a.first = first_row; a.count = row_count;
     a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
     a.counters = counters_or_null(ctx);
+    a.max_seg_rows = longest_partition(h_segment_length, 0, S);
     GL_CUDA(ctx, launch_build(a, ctx->stream));
     return timer.finish();
 }
@@ -945,6 +956,134 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
     return GLIDE_OK;
 }
 
+// ---- host-buffer search, several batches in flight ---------------------------------------------
+// glide_search_host blocks until its results are on the host, so the device idles while a batch
+// crosses the host link in either direction. A pipe keeps `depth` batches in flight: uploads on
+// one stream, the kernels of all batches in submission order on the context's stream, downloads
+// on a third, tied together by events. Every batch has its own device buffers and routing scratch.
+struct glide_search_pipe {
+    glide_ctx *ctx = nullptr;
+    uint32_t max_queries = 0, dim = 0, max_top_k = 0, depth = 0, next = 0;
+    cudaStream_t up = nullptr, down = nullptr;
+    struct Slot {
+        float *d_q = nullptr;
+        uint32_t *d_ids = nullptr, *d_route = nullptr;
+        float *d_dists = nullptr;
+        cudaEvent_t uploaded = nullptr, searched = nullptr, done = nullptr;
+        bool busy = false;
+    } slots[8];
+};
+
+int glide_search_pipe_create(glide_ctx *ctx, uint32_t max_queries, uint32_t dim, uint32_t max_top_k, uint32_t depth,
+                             glide_search_pipe **out) {
+    if (!ctx || !out) return GLIDE_ERR_BAD_ARG;
+    *out = nullptr;
+    GL_REQUIRE(ctx, max_queries >= 1 && dim >= 1 && max_top_k >= 1 && depth >= 1 && depth <= 8, GLIDE_ERR_BAD_ARG,
+               "search_pipe_create: sizes must be positive and depth at most 8");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    auto *pipe = new glide_search_pipe;
+    pipe->ctx = ctx; pipe->max_queries = max_queries; pipe->dim = dim; pipe->max_top_k = max_top_k; pipe->depth = depth;
+    cudaError_t e = cudaStreamCreateWithFlags(&pipe->up, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&pipe->down, cudaStreamNonBlocking);
+    for (uint32_t i = 0; i < depth && e == cudaSuccess; i++) {
+        auto &sl = pipe->slots[i];
+        e = cudaMalloc(&sl.d_q, (size_t) max_queries * dim * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&sl.d_ids, (size_t) max_queries * max_top_k * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&sl.d_dists, (size_t) max_queries * max_top_k * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&sl.d_route, 2 * align256((size_t) max_queries * 4));
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.uploaded, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.searched, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) {
+        glide_search_pipe_destroy(pipe);
+        return fail(ctx, e == cudaErrorMemoryAllocation ? GLIDE_ERR_NO_MEMORY : GLIDE_ERR_CUDA, "search_pipe_create: %s",
+                    cudaGetErrorString(e));
+    }
+    *out = pipe;
+    return GLIDE_OK;
+}
+
+void glide_search_pipe_destroy(glide_search_pipe *pipe) {
+    if (!pipe) return;
+    cudaSetDevice(pipe->ctx->device);
+    if (pipe->up) cudaStreamSynchronize(pipe->up);
+    cudaStreamSynchronize(pipe->ctx->stream);
+    if (pipe->down) cudaStreamSynchronize(pipe->down);
+    for (auto &sl : pipe->slots) {
+        cudaFree(sl.d_q); cudaFree(sl.d_ids); cudaFree(sl.d_dists); cudaFree(sl.d_route);
+        if (sl.uploaded) cudaEventDestroy(sl.uploaded);
+        if (sl.searched) cudaEventDestroy(sl.searched);
+        if (sl.done) cudaEventDestroy(sl.done);
+    }
+    if (pipe->up) cudaStreamDestroy(pipe->up);
+    if (pipe->down) cudaStreamDestroy(pipe->down);
+    delete pipe;
+}
+
+int glide_search_pipe_wait(glide_search_pipe *pipe, uint32_t slot) {
+    if (!pipe) return GLIDE_ERR_BAD_ARG;
+    glide_ctx *ctx = pipe->ctx;
+    GL_REQUIRE(ctx, slot < pipe->depth, GLIDE_ERR_BAD_ARG, "search_pipe_wait: no such slot");
+    auto &sl = pipe->slots[slot];
+    if (!sl.busy) return GLIDE_OK;
+    sl.busy = false;
+    GL_CUDA(ctx, cudaEventSynchronize(sl.done));
+    return GLIDE_OK;
+}
+
+int glide_search_pipe_submit(glide_search_pipe *pipe, const float *d_data, uint32_t num, uint32_t dim,
+                             const uint32_t *d_graph, uint32_t graph_degree, const float *d_centroids, uint32_t C,
+                             const uint32_t *d_start_points, const float *h_queries, uint32_t q,
+                             const glide_search_params *p, int metric, uint32_t *h_out_ids, float *h_out_dists,
+                             uint32_t *slot_out) {
+    if (!pipe) return GLIDE_ERR_BAD_ARG;
+    glide_ctx *ctx = pipe->ctx;
+    GL_REQUIRE(ctx, d_data && d_graph && d_centroids && d_start_points && h_queries && h_out_ids && h_out_dists && p && slot_out,
+               GLIDE_ERR_BAD_ARG, "search_pipe_submit: null pointer");
+    GL_REQUIRE(ctx, q >= 1 && q <= pipe->max_queries && dim == pipe->dim && num > 0 && C >= 1, GLIDE_ERR_BAD_ARG,
+               "search_pipe_submit: batch larger than the pipe was made for, or another dim");
+    GL_REQUIRE(ctx, C <= 4096, GLIDE_ERR_UNSUPPORTED, "Unsupported centroids_num");
+    int rc = check_params(ctx, p, graph_degree);
+    if (rc) return rc;
+    GL_REQUIRE(ctx, p->top_k >= 1 && p->top_k <= p->beam && p->top_k <= pipe->max_top_k, GLIDE_ERR_BAD_ARG,
+               "search_pipe_submit: top_k must be in [1, beam] and within the pipe's max_top_k");
+    GL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const uint32_t slot = pipe->next;
+    rc = glide_search_pipe_wait(pipe, slot);   // the slot's last batch has left its buffers
+    if (rc) return rc;
+    auto &sl = pipe->slots[slot];
+    GL_CUDA(ctx, cudaMemcpyAsync(sl.d_q, h_queries, (size_t) q * dim * 4, cudaMemcpyHostToDevice, pipe->up));
+    GL_CUDA(ctx, cudaEventRecord(sl.uploaded, pipe->up));
+    GL_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, sl.uploaded, 0));
+    SearchArgs a{};
+    a.data = d_data; a.graph = d_graph; a.degree = graph_degree; a.dim = dim;
+    a.queries = sl.d_q; a.Q = q; a.top_k = p->top_k; a.metric = metric; a.p = to_host(p);
+    a.centroids = d_centroids; a.C = C; a.start_points = d_start_points; a.route = sl.d_route;
+    a.out_ids = sl.d_ids; a.out_dists = sl.d_dists;
+    a.ticket = ctx->ticket;
+    AssignArgs r{sl.d_q, q, dim, d_centroids, C, -1.0f, metric, sl.d_route, nullptr, ctx->tc_norms, nullptr};
+    uint32_t launched = 0;
+    GL_CUDA(ctx, launch_assign(r, ctx->stream, &launched));
+    if (C > 1 && q >= 1024 && q <= 262144) {
+        uint32_t *order = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(sl.d_route) + align256((size_t) q * 4));
+        GL_CUDA(ctx, launch_group_by_key(sl.d_route, q, C, order, ctx->stream));
+        a.order = order;
+        launched += 1;
+    }
+    GL_CUDA(ctx, launch_search(a, ctx->stream));
+    ctx->last_launches = launched + 1;
+    GL_CUDA(ctx, cudaEventRecord(sl.searched, ctx->stream));
+    GL_CUDA(ctx, cudaStreamWaitEvent(pipe->down, sl.searched, 0));
+    GL_CUDA(ctx, cudaMemcpyAsync(h_out_ids, sl.d_ids, (size_t) q * p->top_k * 4, cudaMemcpyDeviceToHost, pipe->down));
+    GL_CUDA(ctx, cudaMemcpyAsync(h_out_dists, sl.d_dists, (size_t) q * p->top_k * 4, cudaMemcpyDeviceToHost, pipe->down));
+    GL_CUDA(ctx, cudaEventRecord(sl.done, pipe->down));
+    sl.busy = true;
+    pipe->next = (slot + 1) % pipe->depth;
+    *slot_out = slot;
+    return GLIDE_OK;
+}
+
 // ---- search without any allocation -----------------------------------------------------------
 // Some hosts must not allocate device memory at call time: a serving loop whose device memory
 // is handed out once by its own pool and where a cudaMalloc would stall every stream of the
@@ -1070,6 +1209,7 @@ int glide_build_partition(glide_ctx *ctx, const float *d_data, uint32_t num, uin
     a.seg_start = d_start; a.seg_len = d_len; a.S = 1; a.start_points = d_sp; a.map = nullptr;
     a.first = 0; a.count = num; a.alpha = relaxant_factor; a.metric = metric; a.p = to_host(p);
     a.counters = counters_or_null(ctx);
+    a.max_seg_rows = num;
     GL_CUDA(ctx, launch_build(a, ctx->stream));
     return timer.finish();
 }

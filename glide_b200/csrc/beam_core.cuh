@@ -32,7 +32,7 @@ struct WarpStrip {
     float *query;        // dim_pad floats
     uint32_t *cand_id;   // 32*NC
     float *cand_dist;    // 32*NC
-    uint32_t *visited;   // 1 << hash_bit
+    uint32_t *visited;   // visited_words(hash_bit)
     uint32_t *work;      // 32*NC: slots of the candidates to score
     uint32_t *work_id;   // 32*NC: their ids
     uint32_t *extra;     // mode-specific scratch (pool, rows, merge buffers)
@@ -41,7 +41,7 @@ struct WarpStrip {
 __host__ __device__ inline uint32_t dim_pad4(uint32_t dim) { return (dim + 3u) & ~3u; }
 
 __host__ __device__ inline uint32_t strip_words_base(uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
-    return dim_pad4(dim) + 4 * max_cand + (1u << hash_bit);
+    return dim_pad4(dim) + 4 * max_cand + visited_words(hash_bit);
 }
 
 __device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, uint32_t max_cand, uint32_t hash_bit) {
@@ -50,7 +50,7 @@ __device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, ui
     s.cand_id = base + dim_pad4(dim);
     s.cand_dist = reinterpret_cast<float *>(s.cand_id + max_cand);
     s.visited = s.cand_id + 2 * max_cand;
-    s.work = s.visited + (1u << hash_bit);
+    s.work = s.visited + visited_words(hash_bit);
     s.work_id = s.work + max_cand;
     s.extra = s.work_id + max_cand;
     return s;

@@ -437,11 +437,20 @@ __device__ inline void warp_sort_smem(float *k, uint32_t *v, uint32_t n_per_lane
 }
 
 // ---------------------------------------------------------------------------
-// Visited set in shared memory: open addressing, linear probing, one table per
-// warp. Same slot function and "full table reports seen" rule as hashmap.cuh:33-56.
+// Visited set in shared memory, one per warp, in one of two forms chosen by the host:
+//   hash    open addressing, linear probing: same slot function and "full table reports seen"
+//           rule as hashmap.cuh:33-56. `bits` is the table's size exponent.
+//   bitmap  one bit per id, for searches whose ids are partition-local and few enough (the
+//           subgraph build). `bits` carries the number of bitmap words above bit 8. The host
+//           picks it only when the table of the hash form could never fill up between two
+//           resets, so that both forms answer every insert alike; one shared-memory atomic per
+//           lane replaces the probe rounds.
 // ---------------------------------------------------------------------------
+__host__ __device__ inline uint32_t visited_words(uint32_t bits) { return (bits >> 8) ? (bits >> 8) : (1u << bits); }
+
 __device__ __forceinline__ void visited_clear(uint32_t *table, uint32_t bits) {
-    for (uint32_t i = lane_id(); i < (1u << bits); i += 32) table[i] = kInvalid;
+    const uint32_t words = visited_words(bits), fill = (bits >> 8) ? 0u : kInvalid;
+    for (uint32_t i = lane_id(); i < words; i += 32) table[i] = fill;
 }
 
 // Called by the whole warp; lanes with want == false only keep the others company. The probe
@@ -449,6 +458,15 @@ __device__ __forceinline__ void visited_clear(uint32_t *table, uint32_t bits) {
 // leaves it converged: a per-lane loop with early exits left the lanes split for the code that
 // follows, which doubled the row-load instructions of the scoring step.
 __device__ __forceinline__ uint32_t visited_insert(uint32_t *table, uint32_t bits, uint32_t key, bool want) {
+    if (bits >> 8) {   // bitmap; an id beyond the map (a corrupt adjacency row) is reported as seen
+        uint32_t result = 0;
+        if (want && (key >> 5) < (bits >> 8)) {
+            const uint32_t b = 1u << (key & 31u);
+            result = (atomicOr(&table[key >> 5], b) & b) ? 0u : 1u;
+        }
+        __syncwarp();
+        return result;
+    }
     const uint32_t size = 1u << bits, mask = size - 1;
     uint32_t index = (key ^ (key >> bits)) & mask;
     uint32_t result = 0, left = size;

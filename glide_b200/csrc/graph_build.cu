@@ -6,6 +6,8 @@
 //
 // One warp owns one point from search to row write; the beam stays in registers and
 // is spilled to the warp's shared strip only for pruning.
+#include <cstdlib>
+
 #include "beam_core.cuh"
 #include "kernels.h"
 #include "scan.cuh"
@@ -213,8 +215,14 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
     if (a.mode == kModeBuild || a.mode == kModeBoundary) {
         uint32_t seg = a.fixed_segment;
         if (a.mode == kModeBuild) {  // graph_kernel.cuh:276-282
-            for (seg = 0; seg < a.S; seg++)
-                if (point < a.seg_start[seg] + a.seg_len[seg]) break;
+            // first partition that ends beyond the point; partitions lie one after another, so
+            // their ends never decrease and a bisection finds what the reference's scan finds
+            uint32_t lo = 0, hi = a.S;
+            while (lo < hi) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (point < __ldg(a.seg_start + mid) + __ldg(a.seg_len + mid)) hi = mid; else lo = mid + 1;
+            }
+            seg = lo;
             if (seg == a.S) return;
         }
         const uint32_t seg_start = a.seg_start[seg];
@@ -477,7 +485,16 @@ cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
     d.max_degree = round_up32(a.out_degree);
     uint32_t extra = prune_strip_words(d.max_degree);
     const bool lanes = a.in_degree <= 32;
-    d.strip_words = (strip_words_base(a.dim, lanes ? kLaneScratch : max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
+    // Partition-local searches may keep their visited set as a bitmap: when it is no larger than
+    // the hash table (or 4 KB), and when the hash table could not fill up between two resets
+    // (beam entries put back at a reset, one adjacency row per expansion, the seed row), the only
+    // case in which the two forms would answer differently.
+    if ((a.mode == kModeBuild || a.mode == kModeBoundary) && a.max_seg_rows && a.p.hash_bit < 32 && !getenv("GLIDE_B200_NO_BITMAP")) {
+        const uint64_t cap = 1ull << a.p.hash_bit, words = ((uint64_t) a.max_seg_rows + 31) / 32;
+        const uint64_t inserts = (uint64_t) a.p.beam + (uint64_t) a.in_degree * (a.p.hash_reset_interval + 2ull) + 2;
+        if (words <= (cap > 1024 ? cap : 1024) && inserts <= cap) d.a.p.hash_bit = a.p.hash_bit | ((uint32_t) words << 8);
+    }
+    d.strip_words = (strip_words_base(a.dim, lanes ? kLaneScratch : max_cand, d.a.p.hash_bit) + extra + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;
     while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;

@@ -87,6 +87,8 @@ struct BuildArgs {
                                    // warps running together share L2 lines); nullptr: first + t
     uint32_t first, count;         // point range handled by this launch
     uint32_t fixed_segment;        // boundary: the segment every point belongs to
+    uint32_t max_seg_rows;         // build/boundary: rows of the largest partition this launch can touch (0: not known);
+                                   // lets the launcher take the bitmap form of the visited set
     float alpha;
     int metric;
     BeamParamsHost p;

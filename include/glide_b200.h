@@ -229,6 +229,24 @@ int glide_search_host(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
                       uint32_t graph_degree, const float *d_centroids, uint32_t centroid_num,
                       const uint32_t *d_start_points, const float *h_queries, uint32_t q,
                       const glide_search_params *p, int metric, uint32_t *h_out_ids, float *h_out_dists);
+/* glide_search_host with several batches in flight (no counterpart in the reference, whose
+ * small_search main blocks on every batch): uploads, kernels and downloads of consecutive batches
+ * overlap. submit() enqueues one batch of at most max_queries queries from h_queries and returns
+ * the slot it took; wait(slot) returns once that batch's results are in h_out_ids / h_out_dists.
+ * Slots are taken in turn; submit() first waits for the batch that last used its slot. Host
+ * buffers should be pinned (glide_host_alloc / glide_host_register), else the copies block.
+ * Kernels run on the context's stream in submission order, so other calls on the context fall
+ * in line behind them. */
+typedef struct glide_search_pipe glide_search_pipe;
+int glide_search_pipe_create(glide_ctx *ctx, uint32_t max_queries, uint32_t dim, uint32_t max_top_k, uint32_t depth,
+                             glide_search_pipe **out);
+void glide_search_pipe_destroy(glide_search_pipe *pipe);
+int glide_search_pipe_submit(glide_search_pipe *pipe, const float *d_data, uint32_t num, uint32_t dim,
+                             const uint32_t *d_graph, uint32_t graph_degree, const float *d_centroids,
+                             uint32_t centroid_num, const uint32_t *d_start_points, const float *h_queries, uint32_t q,
+                             const glide_search_params *p, int metric, uint32_t *h_out_ids, float *h_out_dists,
+                             uint32_t *slot_out);
+int glide_search_pipe_wait(glide_search_pipe *pipe, uint32_t slot);
 /* glide_search for hosts that must not allocate at call time (a serving loop whose device
  * memory comes from its own pool and where a cudaMalloc would stall the device; a process
  * running near the memory limit). It has no counterpart in the reference. Same arguments and

@@ -139,6 +139,33 @@ def test_search_host_entry_point(gpu_ctx):
     assert np.array_equal(ids2, want_ids) and np.array_equal(d2, want_d) and seconds > 0
 
 
+def test_search_pipe_gives_the_blocking_call_results_for_every_batch(gpu_ctx):
+    """Batches of different sizes through a pipe of depth 3 (more batches than slots, so slots are
+    reused while earlier batches are still in flight): each batch's results equal the oracle's."""
+    from glide_b200 import large
+    base, queries, P = case("int128")
+    o = oracle.SearchParams.derive(64, 16, top_k=10)
+    want_ids, want_d = oracle.search(base, P["graph"], P["centroids"], P["orig_sp"], queries, o)
+    index = api.GLIDE(gpu_ctx, 16, base, P["centroids"])
+    index.load(P["graph"], P["orig_sp"])
+    pipe = index.search_pipe(max_queries=queries.shape[0], max_top_k=10, depth=3)
+    cuts = [(0, 7), (7, 60), (60, 61), (61, queries.shape[0]), (0, queries.shape[0]), (3, 40), (10, 11)]
+    batches = []
+    for lo, hi in cuts:
+        hq = large.pinned_copy(queries[lo:hi])
+        hi_ids, hi_d = large.pinned_empty((hi - lo, 10), np.uint32), large.pinned_empty((hi - lo, 10), np.float32)
+        hi_ids.fill(7)
+        batches.append((lo, hi, hq, hi_ids, hi_d, pipe.submit(sp_from(o), hq, hi_ids, hi_d)))
+    assert [b[5] for b in batches] == [0, 1, 2, 0, 1, 2, 0]
+    pipe.drain()
+    for lo, hi, _, ids, d, _ in batches:
+        assert np.array_equal(ids, want_ids[lo:hi]) and np.array_equal(d, want_d[lo:hi])
+    with pytest.raises(api.GlideError):
+        pipe.submit(sp_from(o), large.pinned_copy(np.zeros((queries.shape[0] + 1, base.shape[1]), np.float32)),
+                    np.empty((queries.shape[0] + 1, 10), np.uint32), np.empty((queries.shape[0] + 1, 10), np.float32))
+    pipe.close()
+
+
 @pytest.mark.parametrize("name", ["uniform16", "int128", "unit96", "uniform30", "scaled960", "uniform200"])
 def test_define_partition_and_reorder_match_oracle(gpu_ctx, name):
     base, _, P = case(name)
