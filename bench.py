@@ -48,7 +48,8 @@ METRIC_NAME = "search QPS @ recall@10>=0.95"
 # (config, rows, queries, partitions, rounded beam, max_iterations); the summaries under
 # profiles/ give the commands. A bench run on another workload reports traffic null.
 NCU_TRAFFIC = {
-    # filled from profiles/search_kernel_cfg1_full_dram.md
+    ("cfg1", 1000000, 10000, 1024, 32, 31): 1_944_421_148,   # profiles/search_kernel_cfg1_full_dram.md (mean of 9 launches)
+    ("cfg1_n400000", 400000, 10000, 1024, 32, 15): 396_663_268,     # same file, the small case captured first
 }
 # issue-slot utilisation of the same kernel from the kept ncu capture (profiles/search_kernel_cfg1_400k.md)
 NCU_ISSUE = {"issue_slots_busy_pct": 60.0, "top_stall": "long_scoreboard", "source": "profiles/search_kernel_cfg1_400k.md"}
