@@ -48,32 +48,6 @@ __device__ __forceinline__ float sq_acc4(const float4 a, const float4 b, float a
     return acc;
 }
 
-// Packed fp32 pairs (sm_100 executes two independent fp32 operations per instruction on a 64-bit
-// register pair: same rounding as the scalar forms, half the issue slots). The warp-row distances
-// below keep TWO running sums per lane: elements x and z of every 4-float chunk go to the first
-// (x before z), y and w to the second; the lane's partial is first + second.
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pk(float lo, float hi) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ float pk_sum(f32x2 v) {
-    float lo, hi;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-    return lo + hi;
-}
-__device__ __forceinline__ f32x2 sq_acc4_pk(const float4 a, const float4 b, f32x2 acc) {
-    f32x2 d01, d23;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d01) : "l"(pk(a.x, a.y)), "l"(pk(b.x, b.y)));
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d23) : "l"(pk(a.z, a.w)), "l"(pk(b.z, b.w)));
-    asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(acc) : "l"(d01), "l"(acc));
-    asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(acc) : "l"(d23), "l"(acc));
-    return acc;
-}
-// one chunk, starting from zero
-__device__ __forceinline__ float sq4_pk(const float4 a, const float4 b) { return pk_sum(sq_acc4_pk(a, b, 0ull)); }
-
 // Partial sum of one team lane. active == false lanes read nothing.
 __device__ __forceinline__ float team_partial(const float *__restrict__ q, const float *__restrict__ row,
                                               uint32_t dim, bool active) {
@@ -109,9 +83,8 @@ __device__ __forceinline__ float team_partial(const float *__restrict__ q, const
 // ---------------------------------------------------------------------------
 // Warp-row distances (candidate scoring and pruning). One data row is read by the whole
 // warp: lane l owns the 16-byte chunks l, l+32, ... of the row (for dim 128 exactly one
-// 128-bit load per lane and row), accumulates its chunks with packed fused multiply-adds into
-// two running sums (x then z, y then w; see sq_acc4_pk), adds the two, and the 32 lane sums are
-// folded by a 16,8,4,2,1 xor tree, the reference's
+// 128-bit load per lane and row), accumulates its chunks with fused multiply-adds in
+// x,y,z,w order, and the 32 lane sums are folded by a 16,8,4,2,1 xor tree, the reference's
 // tree (distance.cuh:18-20). When dim % 4 != 0 lane l owns the scalar elements l, l+32, ...,
 // which is exactly the reference's order (distance.cuh:15-17). The query stays in
 // registers, R = 8/QR rows are loaded before any is consumed, and the R lane sums are
@@ -172,10 +145,10 @@ __device__ __forceinline__ void warp_rows_v4(const float *q_smem, const float *_
         float p[R];
 #pragma unroll
         for (int r = 0; r < R; r++) {
-            f32x2 acc = 0ull;
+            float acc = 0.0f;
 #pragma unroll
-            for (int j = 0; j < QR; j++) acc = sq_acc4_pk(q[j], v[r][j], acc);
-            p[r] = pk_sum(acc);
+            for (int j = 0; j < QR; j++) acc = sq_acc4(q[j], v[r][j], acc);
+            p[r] = acc;
         }
         const float sum = fold_rows<R>(p);
         const uint32_t my_row = lane >> (5 - Log2<R>::v);
@@ -189,7 +162,6 @@ __device__ __forceinline__ float lane_row_partial(const float *q_smem, const flo
     const uint32_t lane = lane_id();
     float acc = 0.0f;
     if ((dim & 3u) == 0) {
-        f32x2 acc2 = 0ull;
         const float4 *q4 = reinterpret_cast<const float4 *>(q_smem);
         const float4 *r4 = reinterpret_cast<const float4 *>(row);
         const uint32_t chunks = dim >> 2;
@@ -204,10 +176,9 @@ __device__ __forceinline__ float lane_row_partial(const float *q_smem, const flo
 #pragma unroll
             for (int k = 0; k < 8; k++) {
                 const uint32_t ck = c + 32u * k;
-                if (ck < chunks) acc2 = sq_acc4_pk(q4[ck], b[k], acc2);
+                if (ck < chunks) acc = sq_acc4(q4[ck], b[k], acc);
             }
         }
-        acc = pk_sum(acc2);
     } else {
         for (uint32_t i = lane; i < dim; i += 32) {
             const float d = q_smem[i] - __ldg(row + i);
@@ -269,7 +240,7 @@ __device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const 
                     v[r] = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) ids_smem[8u * g + r] * 128u) + lane);
                 float p[8];
 #pragma unroll
-                for (int r = 0; r < 8; r++) p[r] = sq4_pk(q, v[r]);
+                for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
                 const float sum = fold_rows<8>(p);  // row r of the batch sits in lanes 4r .. 4r+3
                 const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
                 mine = (valid && (my_rank >> 3) == g) ? got : mine;
@@ -283,7 +254,7 @@ __device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const 
                     v[r] = __ldg(reinterpret_cast<const float4 *>(data + (uint64_t) ids_smem[8u * g + r] * dim) + my_chunk);
                 float p[8];
 #pragma unroll
-                for (int r = 0; r < 8; r++) p[r] = own ? sq4_pk(q, v[r]) : 0.0f;
+                for (int r = 0; r < 8; r++) p[r] = own ? sq_acc4(q, v[r], 0.0f) : 0.0f;
                 const float sum = fold_rows<8>(p);
                 const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);
                 mine = (valid && (my_rank >> 3) == g) ? got : mine;
@@ -323,10 +294,10 @@ __device__ __forceinline__ float score_lanes_q4(const float4 q, bool own, const 
         float p[8];
         if (all_own) {
 #pragma unroll
-            for (int r = 0; r < 8; r++) p[r] = sq4_pk(q, v[r]);
+            for (int r = 0; r < 8; r++) p[r] = sq_acc4(q, v[r], 0.0f);
         } else {
 #pragma unroll
-            for (int r = 0; r < 8; r++) p[r] = own ? sq4_pk(q, v[r]) : 0.0f;
+            for (int r = 0; r < 8; r++) p[r] = own ? sq_acc4(q, v[r], 0.0f) : 0.0f;
         }
         const float sum = fold_rows<8>(p);  // row r of the batch sits in lanes 4r .. 4r+3
         const float got = __shfl_sync(kFullMask, sum, (my_rank & 7u) * 4u);

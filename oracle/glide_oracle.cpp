@@ -55,9 +55,8 @@ enum Metric : int { kEuclidean = 0, kCosine = 1 };  // params.cuh:5-8
 // kOrderTeam (centroid distances: routing, assignment, k-means): a team of 8 lanes, lane t
 // owning 4-float chunks t, t+8, ... (scalar elements t, t+8, ... when dim is not a multiple
 // of 4), folded by a 4,2,1 tree. kOrderWarp (candidate scoring and pruning): the 32 lanes
-// of a warp, lane l owning 4-float chunks l, l+32, ... and keeping two running sums (even and
-// odd elements of its chunks) that it adds at the end, folded by the reference's 16,8,4,2,1
-// tree; when dim is not a multiple of 4 it is exactly kOrderRef.
+// of a warp, lane l owning 4-float chunks l, l+32, ..., folded by the reference's
+// 16,8,4,2,1 tree; when dim is not a multiple of 4 it is exactly kOrderRef.
 enum Order : int { kOrderRef = 0, kOrderTeam = 1, kOrderWarp = 2 };
 
 inline float sq_sum(const float *a, const float *b, uint32_t dim, int order) {
@@ -75,20 +74,6 @@ inline float sq_sum(const float *a, const float *b, uint32_t dim, int order) {
     }
     const uint32_t chunks = dim / V;
     for (uint32_t t = 0; t < T; t++) {
-        if (order == kOrderWarp && V == 4) {
-            // two running sums per lane (the kernels use packed fp32 pairs): elements 0 and 2 of
-            // every chunk go to the first, 1 and 3 to the second; the lane's partial is their sum
-            float even = 0.0f, odd = 0.0f;
-            for (uint32_t c = t; c < chunks; c += T) {
-                for (uint32_t e = 0; e < 4; e++) {
-                    const float diff = a[c * 4 + e] - b[c * 4 + e];
-                    float &acc = (e & 1u) ? odd : even;
-                    acc = fmaf(diff, diff, acc);
-                }
-            }
-            lane[t] = even + odd;
-            continue;
-        }
         float acc = 0.0f;
         for (uint32_t c = t; c < chunks; c += T) {
             for (uint32_t e = 0; e < V; e++) {
