@@ -211,4 +211,8 @@ struct NndArgs {
 size_t nnd_workspace_bytes(uint32_t rows, uint32_t K, uint32_t sample, uint32_t S);
 cudaError_t run_nn_descent(const NndArgs &a, cudaStream_t stream);
 
+// ---- large.cu -------------------------------------------------------------
+// count uint8 values -> fp32 (count % 4 == 0)
+cudaError_t launch_widen_u8(const uint8_t *in, float *out, size_t count, cudaStream_t stream);
+
 }  // namespace glide

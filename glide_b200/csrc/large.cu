@@ -56,6 +56,19 @@ __global__ void widen_u8_kernel(const uint8_t *__restrict__ in, float *__restric
     reinterpret_cast<float4 *>(out)[i] = make_float4((float) b.x, (float) b.y, (float) b.z, (float) b.w);
 }
 
+}  // namespace
+
+namespace glide {
+cudaError_t launch_widen_u8(const uint8_t *in, float *out, size_t count, cudaStream_t stream) {
+    const size_t n4 = count / 4;
+    if (n4 == 0) return cudaSuccess;
+    widen_u8_kernel<<<(unsigned) ((n4 + 255) / 256), 256, 0, stream>>>(in, out, n4);
+    return cudaGetLastError();
+}
+}  // namespace glide
+
+namespace {
+
 // routed[s] += number of queries whose list names partition s (lists end at the first 0xffffffff)
 __global__ void count_routed_kernel(const uint32_t *__restrict__ segment_ids, uint32_t Q, uint32_t C, uint32_t *routed) {
     const uint32_t q = blockIdx.x * blockDim.x + threadIdx.x;

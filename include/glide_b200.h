@@ -215,6 +215,22 @@ int glide_comm_all_reduce_u64(glide_ctx *ctx, uint64_t *d_buf, uint64_t count, i
 /* Waits for everything enqueued on the context's stream (kernels, copies, collectives). */
 int glide_ctx_synchronize(glide_ctx *ctx);
 
+/* ---- matrix files ----------------------------------------------------------------------- */
+/* load_matrix_data, load.cuh:10-30 (u32 rows, u32 dim, then the rows; the reference reads row by
+ * row into pageable memory). elem_bytes 4 (fp32, .fbin) or 1 (uint8). GLIDE_ERR_IO for a missing
+ * file or one shorter than its header says. */
+int glide_matrix_file_info(const char *path, uint32_t elem_bytes, uint32_t *rows, uint32_t *dim);
+/* Reads rows [first_row, first_row + rows) of the file into h_rows (pin it: glide_host_alloc or
+ * glide_host_register) with `threads` reader threads (0: 4) issuing positional reads of chunk_rows
+ * rows (0: 64 MB worth). With d_centroids given, every chunk is uploaded and its rows assigned to
+ * their nearest centroid (define_partition_for_large_kernel, partition_kernel.cuh:122-162) while
+ * later chunks are still being read; h_nearest gets one partition id per row. Without centroids
+ * the call only reads. stats (may be null): [0] seconds until the last chunk was in host memory,
+ * [1] seconds until h_nearest was complete, [2] seconds the device side waited for the file. */
+int glide_load_rows(glide_ctx *ctx, const char *path, uint32_t elem_bytes, uint64_t first_row, uint64_t rows, void *h_rows,
+                    uint32_t chunk_rows, uint32_t threads, const float *d_centroids, uint32_t centroid_num, int metric,
+                    uint32_t *h_nearest, double *stats);
+
 /* ---- search stage ----------------------------------------------------------------------- */
 /* GLIDE::search, glide_impl.cuh:370-454 (search_kernel, search_kernel.cuh:393-490).
  * Device pointers; results Q x top_k. */
