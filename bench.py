@@ -65,6 +65,7 @@ def parse_args():
     ap.add_argument("--rows", type=int, default=0, help="use only the first ROWS base rows (debugging; marks the run reduced)")
     ap.add_argument("--queries", type=int, default=0)
     ap.add_argument("--partitions", type=int, default=0, help="override the partition count")
+    ap.add_argument("--loader-dir", default="/dev/shm", help="--config loader: where the synthetic matrix file is written")
     ap.add_argument("--rows-u8", action="store_true", help="large path: keep integer-valued rows as uint8 in host memory")
     ap.add_argument("--route-min", type=int, default=4, help="large path: partitions every query visits at least")
     ap.add_argument("--route-factor", type=float, default=1.2, help="large path: visit partitions within this factor of the nearest")
@@ -880,8 +881,76 @@ def run_large(args):
     ctx.close()
 
 
+# --------------------------------------------------------------------------------------------
+# loader (row f4: matrix file -> pinned host memory, overlapped with partition assignment)
+# --------------------------------------------------------------------------------------------
+def run_loader(args):
+    """Not a bench line of the contract: one JSON line with the loader's throughput on a synthetic
+    matrix file (cfg4's row shape: 128 uint8 or fp32 values per row, `--rows` of them, written to
+    `--loader-dir`), beside the reference's row-by-row reader timed on the same file."""
+    import tempfile
+    from glide_b200 import api, io as gio, large
+    from glide_b200.params import Metric
+    ctx = api.Context(0)
+    dtype = np.uint8 if args.rows_u8 else np.float32
+    rows, dim, C = args.rows or 8_000_000, 128, args.partitions or 512
+    rng = np.random.default_rng(5)
+    folder = tempfile.mkdtemp(dir=args.loader_dir)
+    path = os.path.join(folder, "rows.bin")
+    block = rng.integers(0, 256, (1 << 20, dim)).astype(dtype)
+    with open(path, "wb") as f:
+        np.array([rows, dim], np.uint32).tofile(f)
+        left = rows
+        while left > 0:
+            block[:min(left, block.shape[0])].tofile(f)
+            left -= block.shape[0]
+    file_gb = (8 + rows * dim * np.dtype(dtype).itemsize) / 1e9
+    d_centroids = torch.from_numpy(rng.integers(0, 256, (C, dim)).astype(np.float32)).to(ctx.torch_device)
+    out = {"loader": "glide_load_rows", "file": f"{rows}x{dim} {np.dtype(dtype).name}, {file_gb:.2f} GB in {args.loader_dir}",
+           "partitions": C, "host_cores": os.cpu_count()}
+    try:
+        for name, kw in (("read_only_4_threads", dict(threads=4)), ("read_only_8_threads", dict(threads=8)),
+                         ("read_and_assign_4_threads", dict(threads=4, d_centroids=d_centroids)),
+                         ("read_and_assign_8_threads", dict(threads=8, d_centroids=d_centroids))):
+            best = None
+            for _ in range(3):
+                h_rows, nearest, st = large.load_rows(ctx, path, dtype, metric=Metric.Euclidean, **kw)
+                if best is None or st["total_seconds"] < best["total_seconds"]:
+                    best = st
+                keep = (h_rows, nearest)
+            out[name] = {"GB/s": round(file_gb / best["total_seconds"], 2), "seconds": round(best["total_seconds"], 4),
+                         "read_seconds": round(best["read_seconds"], 4),
+                         "device_waited_for_file_seconds": round(best["device_waited_seconds"], 4)}
+        # assignment alone on rows already in pinned memory: what the overlap hides
+        t0 = time.perf_counter()
+        pre_rows = keep[0]
+        step = 1 << 19
+        for lo in range(0, rows, step):
+            d_rows = torch.from_numpy(pre_rows[lo:lo + step]).to(ctx.torch_device).to(torch.float32)
+            api.define_partition(ctx, d_rows, d_centroids, -1.0, Metric.Euclidean)
+        torch.cuda.synchronize()
+        out["upload_and_assign_after_the_read"] = {"seconds": round(time.perf_counter() - t0, 4)}
+        if not args.no_cpu_baseline:
+            import oracle
+            t0 = time.perf_counter()
+            ref_rows = oracle.load_matrix_rowwise(path, dtype)
+            dt = time.perf_counter() - t0
+            out["reference_row_by_row_reader"] = {"GB/s": round(file_gb / dt, 2), "seconds": round(dt, 4),
+                                                  "kind": "port of load.cuh:10-30 (one ifstream read per row, pageable memory), 1 thread",
+                                                  "rows_equal": bool(np.array_equal(ref_rows, keep[0]))}
+    finally:
+        os.remove(path)
+        os.rmdir(folder)
+    print(json.dumps(out), flush=True)
+    ctx.close()
+
+
 def main():
     args = parse_args()
+    if args.config == "loader":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_loader(args)
+        return
     if args.config in LARGE:
         if args.impl == "reference":
             if int(os.environ.get("RANK", "0")) == 0:

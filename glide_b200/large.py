@@ -2,9 +2,9 @@
 one at a time (reference ``GLIDE_large``, glide_large.cuh:14-212, glide_large_impl.cuh:14-507;
 ``preprocess_for_large`` partition.cuh:417-447; ``build_knn_for_large`` nn_descent.cuh:1515-1581).
 
-Differences from the reference a caller will notice: data are fp32 (the reference's large
-path is uint8), every random choice is seeded, and no trailing rows are dropped (the reference
-processes floor(N / batch_num) * batch_num rows, partition.cuh:231).
+Differences from the reference a caller will notice: rows may be fp32 or uint8 (the reference's
+large path is uint8 only), every random choice is seeded, and no trailing rows are dropped (the
+reference processes floor(N / batch_num) * batch_num rows, partition.cuh:231).
 Partitions are disjoint (no boundary copies) and every subgraph uses partition-local ids; a
 query visits every partition whose centroid distance is within ``boundary_factor`` of the
 nearest one (at least ``min_segment_num`` partitions) and the per-partition results are folded
@@ -73,14 +73,76 @@ def preprocess_for_large(ctx: api.Context, h_data: np.ndarray, centroid_num: int
         d_seg, _, _ = api.define_partition(ctx, d_rows, d_centroids, -1.0, metric)
         seconds += ctx.last_kernel_seconds
         nearest[lo:hi] = api.to_u32(d_seg)[:, 0]
+    reorder, order, seg_start, seg_len = _group_by_partition(h_data, nearest, centroid_num)
+    return dict(h_reorder_data=reorder, h_map=order, h_segment_start=seg_start,
+                h_segment_length=seg_len, h_centroids=d_centroids.cpu().numpy(), seconds=seconds)
+
+
+def _group_by_partition(h_data: np.ndarray, nearest: np.ndarray, centroid_num: int):
     order = np.argsort(nearest, kind="stable").astype(np.uint32)   # ascending row id inside a partition
     seg_len = np.bincount(nearest, minlength=centroid_num).astype(np.uint32)
     seg_start = np.zeros(centroid_num, np.uint32)
     seg_start[1:] = np.cumsum(seg_len[:-1], dtype=np.uint64).astype(np.uint32)
     reorder = pinned_empty(h_data.shape, h_data.dtype)
     np.take(h_data, order, axis=0, out=reorder)
-    return dict(h_reorder_data=reorder, h_map=order, h_segment_start=seg_start,
-                h_segment_length=seg_len, h_centroids=d_centroids.cpu().numpy(), seconds=seconds)
+    return reorder, order, seg_start, seg_len
+
+
+def matrix_file_info(ctx: api.Context, path: str, dtype) -> tuple[int, int]:
+    """(rows, dim) of a matrix file (load.cuh:16-19); IOError for a missing or truncated file."""
+    import ctypes as C
+    rows, dim = C.c_uint32(), C.c_uint32()
+    rc = ctx.lib.glide_matrix_file_info(str(path).encode(), np.dtype(dtype).itemsize, C.byref(rows), C.byref(dim))
+    if rc != 0:
+        raise IOError(f"{path}: missing, unreadable or shorter than its header says")
+    return rows.value, dim.value
+
+
+def load_rows(ctx: api.Context, path: str, dtype, first_row: int = 0, rows: int | None = None, chunk_rows: int = 0,
+              threads: int = 0, d_centroids: torch.Tensor | None = None, metric: Metric = Metric.Euclidean):
+    """`glide_load_rows`: rows [first_row, first_row + rows) of a matrix file into pinned memory with
+    threaded positional reads; with centroids, every chunk is uploaded and assigned to its nearest
+    centroid while later chunks are still being read. Returns (h_rows, h_nearest or None, stats)."""
+    import ctypes as C
+    dtype = np.dtype(dtype)
+    if dtype not in (np.dtype(np.float32), np.dtype(np.uint8)):
+        raise TypeError("matrix files hold float32 or uint8 rows")
+    n, dim = matrix_file_info(ctx, path, dtype)
+    rows = n - first_row if rows is None else rows
+    h_rows = pinned_empty((rows, dim), dtype)
+    h_nearest = pinned_empty((rows,), np.uint32) if d_centroids is not None else None
+    stats = (C.c_double * 3)()
+    ctx.sync_inputs()
+    rc = ctx.lib.glide_load_rows(ctx.handle, str(path).encode(), dtype.itemsize, int(first_row), int(rows),
+                                 h_rows.ctypes.data, int(chunk_rows), int(threads),
+                                 d_centroids.data_ptr() if d_centroids is not None else None,
+                                 d_centroids.shape[0] if d_centroids is not None else 0, int(metric),
+                                 h_nearest.ctypes.data if h_nearest is not None else None, stats)
+    if rc == -5:
+        raise IOError(ctx.lib.glide_last_error(ctx.handle).decode())
+    ctx.check(rc)
+    return h_rows, h_nearest, dict(read_seconds=stats[0], total_seconds=stats[1], device_waited_seconds=stats[2],
+                                   bytes=rows * dim * dtype.itemsize)
+
+
+def preprocess_file_for_large(ctx: api.Context, path: str, dtype, centroid_num: int, sample_factor: float,
+                              metric: Metric = Metric.Euclidean, seed: int = 0, chunk_rows: int = 0, threads: int = 0):
+    """`preprocess_for_large` from a matrix file: the sample rows are read first (a few positional
+    reads), k-means gives the centroids, then the file streams into pinned memory while the GPU
+    assigns the chunks already read. Same result as `preprocess_for_large` on the loaded array."""
+    dtype = np.dtype(dtype)
+    n, dim = matrix_file_info(ctx, path, dtype)
+    sample_num = max(centroid_num, int(n * sample_factor))
+    ids = api.sample_ids(n, sample_num, seed)
+    on_disk = np.memmap(path, dtype=dtype, mode="r", offset=8, shape=(n, dim))
+    d_sample = _to_device_f32(ctx, np.asarray(on_disk[ids]))
+    del on_disk
+    d_centroids, _, _ = api.kmeans_fit(ctx, d_sample, centroid_num, 0, metric, 1)
+    seconds = ctx.last_kernel_seconds
+    h_rows, nearest, stats = load_rows(ctx, path, dtype, 0, n, chunk_rows, threads, d_centroids, metric)
+    reorder, order, seg_start, seg_len = _group_by_partition(h_rows, nearest, centroid_num)
+    return dict(h_reorder_data=reorder, h_map=order, h_segment_start=seg_start, h_segment_length=seg_len,
+                h_centroids=d_centroids.cpu().numpy(), seconds=seconds, load=stats)
 
 
 def build_knn_for_large(ctx: api.Context, param: NNDescentParameter, h_reorder_data: np.ndarray, h_segment_start,

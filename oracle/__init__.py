@@ -249,6 +249,18 @@ def merge_results(ids, dists):
     return out_ids, out_d
 
 
+def load_matrix_rowwise(path: str, dtype=np.float32) -> np.ndarray:
+    """The reference's loader (load.cuh:10-30): one read per row into pageable memory."""
+    dtype = np.dtype(dtype)
+    rows, dim = C.c_uint32(), C.c_uint32()
+    if lib().orc_load_matrix_rowwise(str(path).encode(), u32(dtype.itemsize), None, C.byref(rows), C.byref(dim)) != 0:
+        raise IOError(f"{path}: cannot read the header")
+    out = np.empty((rows.value, dim.value), dtype)
+    if lib().orc_load_matrix_rowwise(str(path).encode(), u32(dtype.itemsize), _p(out), None, None) != 0:
+        raise IOError(f"{path}: ends before its last row")
+    return out
+
+
 def recall(neighbors, truth, top_k) -> float:
     neighbors, truth = _u32(neighbors), _u32(truth)
     return float(lib().orc_recall(_p(neighbors), u32(neighbors.shape[1]), _p(truth), u32(truth.shape[1]),

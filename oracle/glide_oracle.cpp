@@ -35,6 +35,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <vector>
 #ifdef _OPENMP
 #include <omp.h>
@@ -1002,6 +1003,28 @@ int orc_merge_results(const uint32_t *ids, const float *dists, uint32_t G, uint3
             out_ids[(uint64_t) q * top_k + j] = fi[j];
         }
     });
+    return 0;
+}
+
+// load.cuh:10-30: the matrix file read the reference's way, one ifstream::read per row into
+// pageable memory. `out` holds rows x dim elements of elem_bytes each. Returns 0, or -5 when the
+// file cannot be opened or ends early.
+int orc_load_matrix_rowwise(const char *path, uint32_t elem_bytes, void *out, uint32_t *rows_out, uint32_t *dim_out) {
+    std::ifstream file(path, std::ios::binary);
+    if (!file) return -5;
+    uint32_t num = 0, dim = 0;
+    file.read(reinterpret_cast<char *>(&num), sizeof(uint32_t));
+    file.read(reinterpret_cast<char *>(&dim), sizeof(uint32_t));
+    if (!file) return -5;
+    if (rows_out) *rows_out = num;
+    if (dim_out) *dim_out = dim;
+    if (!out) return 0;
+    char *dst = static_cast<char *>(out);
+    const uint64_t row_bytes = (uint64_t) dim * elem_bytes;
+    for (uint32_t i = 0; i < num; i++) {
+        file.read(dst + (uint64_t) i * row_bytes, (std::streamsize) row_bytes);
+        if (!file) return -5;
+    }
     return 0;
 }
 

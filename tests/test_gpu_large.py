@@ -137,6 +137,30 @@ def test_partition_subsets_fold_into_the_whole_search(gpu_ctx, built):
     assert same.mean() > 0.97                                      # ... and ids, up to ties at equal distance
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.uint8])
+def test_preprocess_from_a_file_equals_preprocess_of_the_loaded_array(gpu_ctx, built, tmp_path, dtype):
+    """The loader reads with several threads in chunks of 700 rows (13 chunks, the last one ragged)
+    while the GPU assigns the chunks already read; partitions, id map and grouped rows equal those of
+    the in-memory path, and the rows land in pinned memory unchanged."""
+    from glide_b200 import io
+    base = built["base"].astype(dtype)
+    path = tmp_path / "base.bin"
+    io.save_matrix_data(str(path), base)
+    assert large.matrix_file_info(gpu_ctx, str(path), dtype) == base.shape
+    want = large.preprocess_for_large(gpu_ctx, base, 6, 0.1, batch_num=4, seed=2)
+    got = large.preprocess_file_for_large(gpu_ctx, str(path), dtype, 6, 0.1, seed=2, chunk_rows=700, threads=3)
+    for key in ("h_map", "h_segment_start", "h_segment_length", "h_centroids", "h_reorder_data"):
+        assert np.array_equal(got[key], want[key]), key
+    assert got["h_reorder_data"].dtype == dtype and got["load"]["bytes"] == base.nbytes
+    # plain read of a row range, no assignment
+    rows, nearest, stats = large.load_rows(gpu_ctx, str(path), dtype, first_row=1234, rows=2000, chunk_rows=300, threads=2)
+    assert nearest is None and np.array_equal(rows, base[1234:3234]) and stats["total_seconds"] > 0
+    with pytest.raises(api.GlideError):
+        large.load_rows(gpu_ctx, str(path), dtype, first_row=8000, rows=2000)
+    with pytest.raises(IOError):
+        large.load_rows(gpu_ctx, str(tmp_path / "missing.bin"), dtype)
+
+
 def test_bad_arguments_are_refused(gpu_ctx, built):
     pre = built["pre"]
     import ctypes as C

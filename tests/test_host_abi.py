@@ -101,6 +101,25 @@ def test_bad_files_raise(tmp_path):
         io.load_segment(p2)
 
 
+def test_matrix_file_info_reads_the_header_and_checks_the_length(tmp_path):
+    """Host-only part of the loader: header fields, and a file shorter than its header says is an error."""
+    lib = _lib.load()
+    m = np.arange(12 * 8, dtype=np.float32).reshape(12, 8)
+    path = tmp_path / "m.fbin"
+    io.save_matrix_data(str(path), m)
+    rows, dim = C.c_uint32(), C.c_uint32()
+    assert lib.glide_matrix_file_info(str(path).encode(), 4, C.byref(rows), C.byref(dim)) == 0
+    assert (rows.value, dim.value) == (12, 8)
+    # the same bytes hold 12 x 8 uint8 rows and then some: accepted; as fp64-sized elements: refused
+    assert lib.glide_matrix_file_info(str(path).encode(), 1, C.byref(rows), C.byref(dim)) == 0
+    assert lib.glide_matrix_file_info(str(path).encode(), 8, C.byref(rows), C.byref(dim)) == -1
+    short = tmp_path / "short.fbin"
+    short.write_bytes(path.read_bytes()[:-4])
+    assert lib.glide_matrix_file_info(str(short).encode(), 4, C.byref(rows), C.byref(dim)) == -5
+    assert lib.glide_matrix_file_info(str(tmp_path / "none.fbin").encode(), 4, C.byref(rows), C.byref(dim)) == -5
+    assert lib.glide_matrix_file_info(None, 4, C.byref(rows), C.byref(dim)) == -1
+
+
 def test_metric_parse():
     assert params.Metric.parse("Euclidean") == params.Metric.Euclidean
     assert params.Metric.parse("Cosine") == params.Metric.Cosine
