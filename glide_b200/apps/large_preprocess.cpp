@@ -18,11 +18,11 @@ int main(int argc, char **argv) {
         param.metric = parse_metric(argv[6]);
         const uint64_t seed = argc > 7 ? std::stoull(argv[7]) : 0;
         Context ctx(argc > 8 ? std::stoi(argv[8]) : 0);
-        auto h_data = load_matrix_data<float>(data_file);
-        HostMatrix<float> h_reorder, h_centroids;
+        // the file is read while the GPU assigns the chunks already in memory (the reference loads it
+        // first, large_preprocess.cu:56, and assigns in 10 batches, :59)
+        HostMatrix<float> h_data, h_reorder, h_centroids;
         std::vector<uint32_t> h_map, seg_start, seg_len;
-        const uint32_t batch_num = 10;   // large_preprocess.cu:59
-        preprocess_for_large(ctx, param, h_data, h_reorder, h_map, seg_start, seg_len, h_centroids, batch_num, result_file, seed);
+        preprocess_for_large(ctx, param, data_file, h_data, h_reorder, h_map, seg_start, seg_len, h_centroids, result_file, seed);
         save_matrix_data(preprocess_file + ".centroid", h_centroids);
         save_segment(preprocess_file + ".segment", seg_start, seg_len);
         save_vector_data(preprocess_file + ".map", h_map);

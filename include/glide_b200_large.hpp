@@ -16,6 +16,27 @@
 
 namespace glide_b200 {
 
+namespace detail {
+// rows grouped by partition, ascending row id inside a partition
+inline void group_by_partition(const HostMatrix<float> &h_data, const uint32_t *nearest, uint32_t C,
+                               HostMatrix<float> &h_reorder_data, std::vector<uint32_t> &h_map,
+                               std::vector<uint32_t> &h_segment_start, std::vector<uint32_t> &h_segment_length) {
+    const uint32_t n = h_data.rows, dim = h_data.cols;
+    h_segment_length.assign(C, 0);
+    for (uint32_t i = 0; i < n; i++) h_segment_length[nearest[i]]++;
+    h_segment_start.assign(C, 0);
+    for (uint32_t c = 1; c < C; c++) h_segment_start[c] = h_segment_start[c - 1] + h_segment_length[c - 1];
+    std::vector<uint32_t> cursor(h_segment_start);
+    h_map.assign(n, 0);
+    h_reorder_data = HostMatrix<float>(n, dim);
+    for (uint32_t i = 0; i < n; i++) {
+        const uint32_t pos = cursor[nearest[i]]++;
+        h_map[pos] = i;
+        std::copy_n(h_data.data_handle() + (size_t) i * dim, dim, h_reorder_data.data_handle() + (size_t) pos * dim);
+    }
+}
+}  // namespace detail
+
 // Centroids from a host-gathered sample (farthest-first + Lloyd on the GPU), nearest-centroid
 // assignment batch by batch (no boundary test, partition_kernel.cuh:122-162), then the rows
 // grouped by partition. h_segment_start / h_segment_length get centroid_num entries.
@@ -56,22 +77,58 @@ inline void preprocess_for_large(const Context &ctx, const PartitionParameter &p
         d_index.download(index.data(), (size_t) cnt * 3);
         for (uint32_t i = 0; i < cnt; i++) nearest[lo + i] = index[(size_t) i * 3];
     }
-    // group by partition, ascending row id inside a partition
-    h_segment_length.assign(C, 0);
-    for (uint32_t i = 0; i < n; i++) h_segment_length[nearest[i]]++;
-    h_segment_start.assign(C, 0);
-    for (uint32_t c = 1; c < C; c++) h_segment_start[c] = h_segment_start[c - 1] + h_segment_length[c - 1];
-    std::vector<uint32_t> cursor(h_segment_start);
-    h_map.assign(n, 0);
-    h_reorder_data = HostMatrix<float>(n, dim);
-    for (uint32_t i = 0; i < n; i++) {
-        const uint32_t pos = cursor[nearest[i]]++;
-        h_map[pos] = i;
-        std::copy_n(h_data.data_handle() + (size_t) i * dim, dim, h_reorder_data.data_handle() + (size_t) pos * dim);
-    }
+    detail::group_by_partition(h_data, nearest.data(), C, h_reorder_data, h_map, h_segment_start, h_segment_length);
     h_centroids = HostMatrix<float>(C, dim);
     d_centroids.download(h_centroids.data_handle(), h_centroids.size());
     std::printf("preprocessing time: %g s\n", seconds);
+    if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
+}
+
+// The same from a matrix file (the reference's main loads the file first, large_preprocess.cu:56,
+// row by row, load.cuh:23-26): the sample rows are read with a few seeks, k-means gives the
+// centroids, then glide_load_rows streams the file into pinned memory with several reader threads
+// while the GPU assigns the chunks already read. Same outputs as loading the file and calling
+// preprocess_for_large; h_data receives the rows in file order.
+inline void preprocess_for_large(const Context &ctx, const PartitionParameter &param, const std::string &data_file,
+                                 HostMatrix<float> &h_data, HostMatrix<float> &h_reorder_data, std::vector<uint32_t> &h_map,
+                                 std::vector<uint32_t> &h_segment_start, std::vector<uint32_t> &h_segment_length,
+                                 HostMatrix<float> &h_centroids, const std::string &result_file, uint64_t seed = 0) {
+    uint32_t n = 0, dim = 0;
+    if (glide_matrix_file_info(data_file.c_str(), 4, &n, &dim) != GLIDE_OK) throw std::runtime_error("Cannot read file " + data_file);
+    const uint32_t C = param.centroid_num;
+    if (n == 0 || dim == 0 || C == 0) throw std::invalid_argument("preprocess_for_large: empty input");
+    float seconds = 0.0f;
+    const uint32_t sample_num = std::max<uint32_t>(C, (uint32_t) ((double) n * param.sample_factor));
+    std::vector<uint32_t> ids(sample_num);
+    if (glide_sample_ids(n, sample_num, seed, ids.data()) != GLIDE_OK) throw std::invalid_argument("sample_ids: bad argument");
+    HostMatrix<float> sample(sample_num, dim);
+    {
+        std::ifstream in(data_file, std::ios::binary);
+        for (uint32_t i = 0; i < sample_num; i++) {
+            in.seekg((std::streamoff) (8 + (uint64_t) ids[i] * dim * 4));
+            in.read(reinterpret_cast<char *>(sample.data_handle() + (size_t) i * dim), (std::streamsize) dim * 4);
+        }
+        if (!in) throw std::runtime_error(data_file + ": truncated");
+    }
+    DeviceBuffer<float> d_sample(ctx, sample.data_handle(), sample.size());
+    DeviceBuffer<float> d_centroids(ctx, (size_t) C * dim);
+    uint32_t rounds = 0;
+    ctx.check(glide_kmeans_fit(ctx.get(), d_sample.data_handle(), sample_num, dim, C, 0, (int) param.metric, 1,
+                               d_centroids.data_handle(), nullptr, &rounds));
+    seconds += ctx.last_kernel_seconds();
+    d_sample.reset();
+    h_data = HostMatrix<float>(n, dim);
+    std::vector<uint32_t> nearest(n);
+    const bool pinned = glide_host_register(h_data.data_handle(), h_data.size() * sizeof(float)) == GLIDE_OK;
+    double stats[3] = {0, 0, 0};
+    const int rc = glide_load_rows(ctx.get(), data_file.c_str(), 4, 0, n, h_data.data_handle(), 0, 0, d_centroids.data_handle(), C,
+                                   (int) param.metric, nearest.data(), stats);
+    if (pinned) glide_host_unregister(h_data.data_handle());
+    ctx.check(rc);
+    detail::group_by_partition(h_data, nearest.data(), C, h_reorder_data, h_map, h_segment_start, h_segment_length);
+    h_centroids = HostMatrix<float>(C, dim);
+    d_centroids.download(h_centroids.data_handle(), h_centroids.size());
+    std::printf("preprocessing time: %g s (file read and assignment, overlapped: %g s)\n", seconds, stats[1]);
     if (!result_file.empty()) append_result(result_file, stream_text(seconds) + ",");
 }
 
