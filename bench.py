@@ -889,7 +889,8 @@ def run_loader(args):
     matrix file (cfg4's row shape: 128 uint8 or fp32 values per row, `--rows` of them, written to
     `--loader-dir`), beside the reference's row-by-row reader timed on the same file."""
     import tempfile
-    from glide_b200 import api, io as gio, large
+    import torch
+    from glide_b200 import api, large
     from glide_b200.params import Metric
     ctx = api.Context(0)
     dtype = np.uint8 if args.rows_u8 else np.float32

@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include "beam_core.cuh"
 #include "kernels.h"
+#include "umma.cuh"
 
 namespace glide {
 
@@ -131,38 +132,13 @@ __global__ void centroid_norms_kernel(const float *__restrict__ centroids, uint3
 // its points for the exact kernel instead of trusting the accumulator.
 // ---------------------------------------------------------------------------
 constexpr uint32_t kTmemCols = 256;   // two accumulator buffers of 128 columns
-constexpr uint32_t kSpinLimit = 1u << 22;
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t) __cvta_generic_to_shared(p); }
+using namespace umma;   // smem_u32, mma_tf32, tmem_load32, mbarriers with bounded waits, TMA loads (umma.cuh)
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     // start address, leading byte offset, stride byte offset (all without their 4 LSBs), descriptor
     // version 1, no swizzle
     return (uint64_t) ((smem_addr >> 4) & 0x3fffu) | ((uint64_t) ((lbo_bytes >> 4) & 0x3fffu) << 16) |
            ((uint64_t) ((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46);
-}
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
-        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 __global__ void __launch_bounds__(128) assign_umma_kernel(const AssignArgs a) {
@@ -242,7 +218,7 @@ __global__ void __launch_bounds__(128) assign_umma_kernel(const AssignArgs a) {
         const uint32_t buf = t & 1u;
         if (tid == 0) {
             for (uint32_t ks = 0; ks < ksteps; ks++)
-                umma_tf32(tmem_base + buf * kUmmaRows, umma_desc(a_addr + ks * 2 * lbo, lbo, sbo),
+                mma_tf32(tmem_base + buf * kUmmaRows, umma_desc(a_addr + ks * 2 * lbo, lbo, sbo),
                           umma_desc(b_addr + buf * tile_bytes + ks * 2 * lbo, lbo, sbo), idesc, ks > 0 ? 1u : 0u);
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar + buf))
                          : "memory");
@@ -342,49 +318,6 @@ cudaError_t launch_umma(const AssignArgs &a, cudaStream_t stream) {
 constexpr uint32_t kEpilogueWarps = 8;
 constexpr uint32_t kTmaThreads = (kEpilogueWarps + 1) * 32;
 
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait; gives up early when another thread of the CTA already failed.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *failed) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < kSpinLimit; spin++) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t"
-            "}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if ((spin & 1023u) == 1023u && *failed) return false;
-    }
-    *failed = 1;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void *dst, const void *tmap, uint32_t x, uint32_t y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
-                 : "memory");
-}
-// K-major operand with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
-    return (uint64_t) ((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t) (1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const AssignArgs a, const __grid_constant__ CUtensorMap tm_points,
                                                                        const __grid_constant__ CUtensorMap tm_centroids) {
     extern __shared__ uint8_t smem_raw[];
@@ -456,8 +389,8 @@ __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const Assi
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (uint32_t ks = 0; ks < ksteps; ks++) {
                     const uint32_t off = (ks >> 2) * sub_bytes + (ks & 3u) * 32u;
-                    umma_tf32(tmem_base + s * kUmmaRows, umma_desc_sw128(a_addr + off),
-                              umma_desc_sw128(b_addr + s * tile_bytes + off), idesc, ks > 0 ? 1u : 0u);
+                    mma_tf32(tmem_base + s * kUmmaRows, desc_sw128(a_addr + off),
+                              desc_sw128(b_addr + s * tile_bytes + off), idesc, ks > 0 ? 1u : 0u);
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mma_done + s))
                              : "memory");
@@ -550,39 +483,11 @@ __global__ void __launch_bounds__(kTmaThreads) assign_umma_tma_kernel(const Assi
     rerank_rows(a, p0, cnt, cand, warp, kEpilogueWarps);
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = [] {
-        void *f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-            f = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(f);
-    }();
-    return fn;
-}
-
-// rows x dim fp32 row-major; boxes of 32 floats x 128 rows, 128-byte swizzle, zero fill past the last row
-bool make_row_map(CUtensorMap *tm, const float *ptr, uint32_t rows, uint32_t dim) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {dim, rows};
-    const cuuint64_t strides[1] = {(cuuint64_t) dim * 4};
-    const cuuint32_t box[2] = {32, kUmmaRows};
-    const cuuint32_t elem[2] = {1, 1};
-    return fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // Returns cudaErrorNotSupported when the tensor maps cannot be made (the caller then takes the cp.async kernel).
 cudaError_t launch_umma_tma(const AssignArgs &a, cudaStream_t stream) {
     if ((reinterpret_cast<uintptr_t>(a.data) & 15u) || (reinterpret_cast<uintptr_t>(a.centroids) & 15u)) return cudaErrorNotSupported;
     CUtensorMap tm_points, tm_centroids;
-    if (!make_row_map(&tm_points, a.data, a.n, a.dim) || !make_row_map(&tm_centroids, a.centroids, a.C, a.dim)) return cudaErrorNotSupported;
+    if (!make_row_map(&tm_points, a.data, a.n, a.dim, kUmmaRows) || !make_row_map(&tm_centroids, a.centroids, a.C, a.dim, kUmmaRows)) return cudaErrorNotSupported;
     const size_t smem_bytes = 1024 + (size_t) 3 * kUmmaRows * a.dim * 4 + 8 * kUmmaRows * 4 + kUmmaRows * kCand * 4 + kUmmaRows * 4 + 7 * 8 + 16;
     cudaError_t e = cudaFuncSetAttribute(assign_umma_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes);
     if (e != cudaSuccess) return e;

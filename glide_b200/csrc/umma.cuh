@@ -1,8 +1,7 @@
 // Thin wrappers over the Blackwell instructions the tensor-core kernels are built from:
 // tcgen05.mma (kind::tf32, operands in shared memory, accumulator in tensor memory), tcgen05.ld,
 // TMA tile loads (cp.async.bulk.tensor, never with cluster multicast) and mbarriers with BOUNDED
-// waits. Used by the exact kNN kernel (knn_tc.cu); the assignment kernel (assign_tc.cu) carries its
-// own copies of the same wrappers.
+// waits. Used by the exact kNN kernel (knn_tc.cu) and the assignment kernels (assign_tc.cu).
 #pragma once
 
 #include <cstdint>
