@@ -654,6 +654,7 @@ def run_ours(args):
             "recall_at_10": round(recall, 4),
             "build": {"seconds": round(res.total_seconds, 4), "wall_seconds": round(build_wall, 3),
                       "stages": {k: round(v, 4) for k, v in res.seconds.items()}, "nnd_rounds": res.nnd_rounds,
+                      "tc_knn_fallbacks": ctx.tc_knn_fallbacks,
                       "ground_truth_seconds": round(gt_seconds, 4), "sharded_graph": sharded_check},
             "recall_curve": curve,
             "e2e": {"value": pipe_qps, "unit": "queries/s", "h2d_bytes_per_step": Q * spec.dim * 4,

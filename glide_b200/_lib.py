@@ -64,6 +64,7 @@ SIGNATURES = {
     "glide_refine_waves": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, P(SearchParamsC), f32, i32, u32]),
     "glide_search": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
     "glide_search_host": (i32, [vp, vp, u32, u32, vp, u32, vp, u32, vp, vp, u32, P(SearchParamsC), i32, vp, vp]),
+    "glide_tc_knn_fallbacks": (u32, [vp]),
     "glide_matrix_file_info": (i32, [C.c_char_p, u32, P(u32), P(u32)]),
     "glide_load_rows": (i32, [vp, C.c_char_p, u32, u64, u64, vp, u32, u32, vp, u32, i32, vp, P(C.c_double)]),
     "glide_search_pipe_create": (i32, [vp, u32, u32, u32, u32, P(vp)]),

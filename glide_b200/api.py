@@ -92,6 +92,11 @@ class Context:
     def last_kernel_seconds(self) -> float:
         return float(self.lib.glide_last_kernel_ms(self.handle)) / 1000.0
 
+    @property
+    def tc_knn_fallbacks(self) -> int:
+        """kNN stages the tensor-core kernel handed back to the fp32 kernels (0 in normal operation)."""
+        return int(self.lib.glide_tc_knn_fallbacks(self.handle))
+
     def empty(self, shape, dtype) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype, device=self.torch_device)
 

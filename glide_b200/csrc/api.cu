@@ -513,13 +513,23 @@ int glide_build_nnd_range(glide_ctx *ctx, const float *d_reorder_data, uint32_t 
                 ctx->last_ms += tc_ms;
                 return rc0;
             }
-            // no tensor map, or a wait ran out: the fp32 kernels redo everything
+            // no tensor map, a wait that ran out, or a candidate buffer that overflowed: the fp32
+            // kernels redo everything; the time of the attempt stays in the stage's time
             if (exact_max_rows > 16384) exact_max_rows = 16384;
+            const float tc_ms = ctx->last_ms;
+            rc0 = build_nnd_simt(ctx, d_reorder_data, rows, dim, h_segment_start, h_segment_length, S, knn_degree, K,
+                                 max_iterations, termination_threshold, sample, exact_max_rows, seed, metric, row_base, d_knn,
+                                 iterations_run, false);
+            ctx->last_ms += tc_ms;
+            ctx->tc_knn_fallbacks++;
+            return rc0;
         }
     }
     return build_nnd_simt(ctx, d_reorder_data, rows, dim, h_segment_start, h_segment_length, S, knn_degree, K, max_iterations,
                           termination_threshold, sample, exact_max_rows, seed, metric, row_base, d_knn, iterations_run, false);
 }
+
+uint32_t glide_tc_knn_fallbacks(const glide_ctx *ctx) { return ctx ? ctx->tc_knn_fallbacks : 0; }
 
 // The fp32 kernels of the kNN stage: the register-tile all-pairs kernel for partitions of at most
 // exact_max_rows rows (unless skip_exact: the tensor-core kernel has done them) and NN-descent for the rest.

@@ -23,6 +23,7 @@ struct glide_ctx {
     uint32_t *start_point_word = nullptr;    // one word: the start point of a per-partition refine
     uint32_t last_launches = 0;              // kernels enqueued by the last glide_search
     float *tc_norms = nullptr;               // centroid norms for the assignment's tensor-core prefilter (up to 4096 centroids)
+    uint32_t tc_knn_fallbacks = 0;           // kNN stages the tensor-core kernel handed back to the fp32 kernels
     bool counters_on = false;
     glide_comm_state *comm = nullptr;        // NCCL communicator (glide_comm_init), or nullptr
 };

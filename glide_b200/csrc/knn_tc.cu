@@ -10,8 +10,10 @@
 //            partition in tiles of 128 rows. Operand tiles arrive by TMA (one 2-D tensor map over the
 //            whole reordered matrix, boxes of 32 floats x 128 rows, 128-byte swizzle, no multicast),
 //            tcgen05.mma kind::tf32 accumulates the 128 x 128 dot products in tensor memory (two
-//            buffers), and eight epilogue warps read them back (tcgen05.ld): thread (row, half) turns
-//            64 dot products of a tile into |a|^2 + |b|^2 - 2 a.b.
+//            buffers), and sixteen epilogue warps read them back (tcgen05.ld): thread (row, part)
+//            turns 32 dot products of a tile into |a|^2 + |b|^2 - 2 a.b (four threads per row; with
+//            two, the tile loop was bound by the latency of eight warps' dependent instruction chains:
+//            31 % of the issue slots and 26 % of the tensor pipe busy).
 //   select   two passes over the partition: the first finds per row a threshold that at least L
 //            columns meet (from minima over groups of columns), the second stores every column at or
 //            below it in a buffer private to the storing thread: no sorting, no atomics and no
@@ -40,8 +42,11 @@ using namespace umma;
 
 constexpr uint32_t kRows = 128;            // rows per CTA = columns per tile
 constexpr uint32_t kTmemCols = 256;        // two accumulator buffers of 128 columns
-constexpr uint32_t kEpiWarps = 8;
+constexpr uint32_t kSplit = 4;             // epilogue threads per row: each owns kCols columns of every tile
+constexpr uint32_t kCols = kRows / kSplit;
+constexpr uint32_t kEpiWarps = 4 * kSplit; // a warp reads the 32 tensor-memory lanes of its quadrant (warp % 4)
 constexpr uint32_t kThreads = (kEpiWarps + 1) * 32;
+static_assert(kCols == 32 || kCols == 64, "the epilogue reads 32 columns per tcgen05.ld");
 constexpr u64 kNoKey = ~0ull;
 
 struct KnnTile {
@@ -54,8 +59,8 @@ struct KnnTcArgs {
     const float *norms;        // per row of data
     const KnnTile *tiles;      // one per CTA
     u64 *cand;                 // launch rows x cap
-    uint32_t *cand_count;      // launch rows x 2 (written when a CTA is done)
-    float *gmin;               // launch rows x 2 x groups: group minima of pass 1
+    uint32_t *cand_count;      // launch rows x kSplit (written when a CTA is done)
+    float *gmin;               // launch rows x 2 x groups (kSplit threads x part_groups each): group minima of pass 1
     uint32_t *fail_flag;
 };
 
@@ -76,11 +81,11 @@ __global__ void row_norms_kernel(const float *__restrict__ data, uint64_t rows, 
 
 // Selection without sorting inside the tile loop. The partition is walked TWICE:
 //
-//   pass 1  every thread (row, half: the left or right 64 columns of each tile) splits the columns it
-//           sees into `groups` consecutive groups and keeps the minimum distance of each. The row's
-//           threshold is the `keep`-th smallest of its 2 x groups group minima: at least `keep`
-//           columns lie at or below it (the minima themselves), and for rows in no particular order
-//           about 1.4 x keep do, whatever the partition's size.
+//   pass 1  every thread (row, part: kCols of the 128 columns of each tile) splits the columns it
+//           sees into `part_groups` consecutive groups and keeps the minimum distance of each. The row's
+//           threshold is the `keep`-th smallest of its group minima: at least `keep` columns lie at
+//           or below it (the minima themselves), and for rows in no particular order 1.15 to 1.4 x
+//           keep do, whatever the partition's size.
 //   pass 2  the same tiles again; every column at or below the threshold is stored in the thread's
 //           private candidate buffer (a plain store at the thread's own counter: no atomics, no
 //           compaction, no barrier between warps).
@@ -88,13 +93,19 @@ __global__ void row_norms_kernel(const float *__restrict__ data, uint64_t rows, 
 // The second pass costs a second round of MMAs, which are a small part of a tile's time; in exchange
 // the epilogue is a few instructions per column in both passes. NL = 1: lists of 32 (out_degree <=
 // 32), keep = 64 candidates re-ranked exactly; NL = 2: lists of 64, keep = 128. A thread's buffer
-// holds half_cap keys; a row that would need more (hundreds of rows at exactly the threshold
+// holds part_cap keys; a row that would need more (hundreds of rows at exactly the threshold
 // distance, or near neighbours stored next to one another so that few groups hold them all) raises
 // the overflow flag and the host recomputes with the fp32 kernels.
 template<int NL> struct Sizes {
-    static constexpr uint32_t keep = 64u * NL, groups = 64u * NL, half_cap = 128u * NL, cap = 2u * half_cap;
+    // 2 x groups = 4 x keep group slots per row: the group size is rounded up to a power of two, so
+    // a row ends up with between 2 x keep and 4 x keep groups, and the keep-th smallest minimum then
+    // lets 1.15 to 1.4 x keep columns through. (With only 2 x keep slots a partition of nine tiles
+    // had 72 groups for keep = 64; its threshold sat near the largest minimum and let 150 to 200
+    // columns through, more than the buffers hold.)
+    static constexpr uint32_t keep = 64u * NL, groups = 128u * NL, cap = 256u * NL;
+    static constexpr uint32_t part_cap = cap / kSplit, part_groups = 2u * groups / kSplit;
     static constexpr int sort_n = 8 * NL;    // keys per lane when a warp sorts a row's candidates (32 * sort_n = cap)
-    static constexpr int thr_n = 4 * NL;     // values per lane when a warp sorts a row's 2 x groups minima
+    static constexpr int thr_n = 8 * NL;     // values per lane when a warp sorts a row's 2 x groups minima
 };
 
 __host__ __device__ inline uint32_t pow2_ceil(uint32_t x) {
@@ -128,7 +139,7 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
     uint8_t *As = base;
     uint8_t *Bs = As + tile_bytes;                            // two stages
     float *cn_w = reinterpret_cast<float *>(Bs + 2 * tile_bytes);       // 8 warps x 64 column norms
-    float *thr_s = cn_w + kEpiWarps * 64;                               // 128 row thresholds
+    float *thr_s = cn_w + kEpiWarps * kCols;                            // 128 row thresholds
     uint64_t *bars = reinterpret_cast<uint64_t *>(thr_s + kRows);       // a_full, b_full[2], mma_done[2], tmem_free[2]
     uint64_t *a_full = bars, *b_full = bars + 1, *mma_done = bars + 3, *tmem_free = bars + 5;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
@@ -188,21 +199,21 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             }
         }
     } else {
-        // ================= epilogue warps: thread (row, half) owns 64 columns of every tile =================
-        const uint32_t quad = warp & 3u, half = warp >> 2;
+        // ================= epilogue warps: thread (row, part) owns kCols columns of every tile =================
+        const uint32_t quad = warp & 3u, part = warp >> 2;
         const uint32_t row = quad * 32u + lane;
         const uint32_t rl = tile.first + row;                      // the row's partition-local id
         const bool active = rl < tile.seg_len;
         const float pnr = active ? __ldg(a.norms + tile.seg_start + rl) : 0.0f;
-        float *cn = cn_w + warp * 64;                              // this warp's 64 column norms of the current tile
-        constexpr uint32_t G = Sizes<NL>::groups;
-        float *my_gmin = a.gmin + ((launch_row0 + row) * 2 + half) * G;
-        u64 *my_cand = a.cand + (launch_row0 + row) * Sizes<NL>::cap + half * Sizes<NL>::half_cap;
+        float *cn = cn_w + warp * kCols;                           // this warp's column norms of the current tile
+        constexpr uint32_t G = Sizes<NL>::part_groups;
+        float *my_gmin = a.gmin + ((launch_row0 + row) * kSplit + part) * G;
+        u64 *my_cand = a.cand + (launch_row0 + row) * Sizes<NL>::cap + part * Sizes<NL>::part_cap;
         // groups: whole tiles when the partition has more tiles than groups, else runs of gs columns
-        // inside a tile (gs a power of two, at least tiles * 64 / G, so that at most G groups arise)
+        // inside a tile (gs a power of two, at least tiles * kCols / G, so that at most G groups arise)
         const bool by_tile = tiles > G;
-        const uint32_t gs = by_tile ? 128u : min(64u, pow2_ceil((tiles * 64u + G - 1) / G));
-        const uint32_t gs_shift = 31u - (uint32_t) __clz(gs), per_tile = by_tile ? 0u : 64u / gs;
+        const uint32_t gs = by_tile ? 2u * kCols : min(kCols, pow2_ceil((tiles * kCols + G - 1) / G));
+        const uint32_t gs_shift = 31u - (uint32_t) __clz(gs), per_tile = by_tile ? 0u : kCols / gs;
         if (active)
             for (uint32_t g = 0; g < G; g++) my_gmin[g] = FLT_MAX;
         float m = FLT_MAX, thr = 0.0f;
@@ -214,15 +225,16 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             if (t == tiles) {
                 // ---- between the passes: every row's threshold from its group minima ----
                 named_barrier_sync(1, kEpiWarps * 32);
-                for (uint32_t r = warp * 16; r < warp * 16 + 16; r++) {
+                constexpr uint32_t kRowsPerWarp = kRows / kEpiWarps;
+                for (uint32_t r = warp * kRowsPerWarp; r < (warp + 1) * kRowsPerWarp; r++) {
                     constexpr int N = Sizes<NL>::thr_n;
-                    const float *g = a.gmin + (launch_row0 + r) * 2 * G;
+                    const float *g = a.gmin + (launch_row0 + r) * 2 * Sizes<NL>::groups;
                     float k[N];
                     uint32_t v[N];
 #pragma unroll
                     for (int i = 0; i < N; i++) { k[i] = g[lane + 32u * i]; v[i] = 0u; }
                     warp_sort<N>(k, v);                              // ascending over e = N * lane + i
-                    const float kth = __shfl_sync(kFullMask, k[N - 1], 15);   // e = 16 N - 1 = keep - 1
+                    const float kth = __shfl_sync(kFullMask, k[N - 1], 7);    // e = 8 N - 1 = keep - 1
                     if (lane == 0) thr_s[r] = kth;
                 }
                 named_barrier_sync(1, kEpiWarps * 32);
@@ -230,8 +242,8 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             }
             __syncwarp();
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const uint32_t c = tt * kRows + half * 64u + lane + 32u * h;
+            for (uint32_t h = 0; h < kCols / 32u; h++) {
+                const uint32_t c = tt * kRows + part * kCols + lane + 32u * h;
                 cn[lane + 32u * h] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
             }
             __syncwarp();
@@ -239,14 +251,14 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             ok = __all_sync(kFullMask, ok);   // tcgen05.ld is a warp-wide instruction
             if (!ok) continue;
             fence_after();
-            const uint32_t c0 = tt * kRows + half * 64u;
+            const uint32_t c0 = tt * kRows + part * kCols;
             // A tile needs the per-column checks only when it holds a column beyond the partition's end
             // or the row itself; the 32 rows of a warp are consecutive, so that is the same for all lanes
             // up to a tile or two.
-            const bool checks = __any_sync(kFullMask, c0 + 64u > tile.seg_len || (rl >= c0 && rl < c0 + 64u));
-            for (uint32_t cb = 0; cb < 64; cb += 32) {
+            const bool checks = __any_sync(kFullMask, c0 + kCols > tile.seg_len || (rl >= c0 && rl < c0 + kCols));
+            for (uint32_t cb = 0; cb < kCols; cb += 32) {
                 uint32_t r[32];
-                tmem_load32(tmem_base + ((quad * 32u) << 16) + s * kRows + half * 64u + cb, r);
+                tmem_load32(tmem_base + ((quad * 32u) << 16) + s * kRows + part * kCols + cb, r);
                 float e[32];   // |b|^2 - 2 a.b: the distance without the row's own |a|^2, which shifts a row's values alike
 #pragma unroll
                 for (int j4 = 0; j4 < 32; j4 += 4) {
@@ -271,10 +283,10 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
                         case 3: m = group_minima<8>(e, m, my_gmin + tt * per_tile + (cb >> 3), active); break;
                         case 4: m = group_minima<16>(e, m, my_gmin + tt * per_tile + (cb >> 4), active); break;
                         case 5: m = group_minima<32>(e, m, my_gmin + tt * per_tile + (cb >> 5), active); break;
-                        default: {   // 64 columns or whole tiles: the run ends with the tile's second half, or later
+                        default: {   // a thread's whole share of the tile (when that is 64 columns), or whole tiles: the run ends later
 #pragma unroll
                             for (int j = 0; j < 32; j++) m = fminf(m, e[j]);
-                            if (gs_shift == 6 && cb == 32) {
+                            if (!by_tile && cb + 32u == kCols) {
                                 if (active) my_gmin[tt] = m;
                                 m = FLT_MAX;
                             }
@@ -285,7 +297,7 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
                     for (int j = 0; j < 32; j++) {
                         if (e[j] <= thr && active) {
                             // the key carries the full distance, clamped at zero (rounding can leave it just below)
-                            if (mine < Sizes<NL>::half_cap)
+                            if (mine < Sizes<NL>::part_cap)
                                 my_cand[mine] = ((u64) __float_as_uint(fmaxf(e[j] + pnr, 0.0f)) << 32) | (c0 + cb + j);
                             mine++;
                         }
@@ -303,8 +315,8 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
                 }
             }
         }
-        if (active) a.cand_count[2 * (launch_row0 + row) + half] = min(mine, Sizes<NL>::half_cap);
-        if (mine > Sizes<NL>::half_cap) atomicExch(a.fail_flag, 2u);    // more candidates than a buffer holds
+        if (active) a.cand_count[kSplit * (launch_row0 + row) + part] = min(mine, Sizes<NL>::part_cap);
+        if (mine > Sizes<NL>::part_cap) atomicExch(a.fail_flag, 2u);    // more candidates than a buffer holds
         if (*failed && lane == 0) atomicExch(a.fail_flag, 1u);          // a bounded wait ran out
     }
     fence_before();
@@ -334,15 +346,20 @@ __global__ void __launch_bounds__(256) knn_rerank_kernel(const KnnTcArgs a, uint
     uint32_t *ids = strip + dim_pad4(a.dim);
     float *dist = reinterpret_cast<float *>(ids + keep);
     const float *seg = a.data + (uint64_t) tile.seg_start * a.dim;
-    const uint32_t n0 = min(a.cand_count[2 * (uint64_t) lr], Sizes<NL>::half_cap);
-    const uint32_t n1 = min(a.cand_count[2 * (uint64_t) lr + 1], Sizes<NL>::half_cap);
-    const uint32_t cnt = min(n0 + n1, 32u * N);
+    // the row's candidates: kSplit buffers of part_cap keys, the first count[p] of each valid
     const u64 *buf = a.cand + (uint64_t) lr * Sizes<NL>::cap;
+    uint32_t count[kSplit], cnt = 0;
+#pragma unroll
+    for (uint32_t p = 0; p < kSplit; p++) {
+        count[p] = min(a.cand_count[kSplit * (uint64_t) lr + p], Sizes<NL>::part_cap);
+        cnt += count[p];
+    }
     u64 k[N];
 #pragma unroll
     for (int i = 0; i < N; i++) {
-        const uint32_t e = lane + 32u * i;
-        k[i] = e < n0 ? buf[e] : (e < cnt ? buf[Sizes<NL>::half_cap + (e - n0)] : kNoKey);
+        const uint32_t e = lane + 32u * i;            // slot e of the row's cap = 32 N slots
+        const uint32_t p = e / Sizes<NL>::part_cap, off = e % Sizes<NL>::part_cap;
+        k[i] = off < count[p] ? buf[e] : kNoKey;
     }
     sort_u64<N>(k);
     const uint32_t n = min(cnt, keep);
@@ -386,7 +403,7 @@ cudaError_t run(const float *data, uint64_t rows_total, uint32_t dim, const std:
     float *norms = reinterpret_cast<float *>(scratch); scratch += align256(rows_total * 4);
     uint32_t *fail_flag = reinterpret_cast<uint32_t *>(scratch); scratch += 256;
     KnnTile *d_tiles = reinterpret_cast<KnnTile *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * sizeof(KnnTile));
-    uint32_t *cand_count = reinterpret_cast<uint32_t *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * kRows * 8);
+    uint32_t *cand_count = reinterpret_cast<uint32_t *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * kRows * kSplit * 4);
     float *gmin = reinterpret_cast<float *>(scratch); scratch += align256((size_t) kMaxCtasPerLaunch * kRows * 2 * Sizes<NL>::groups * 4);
     u64 *cand = reinterpret_cast<u64 *>(scratch);
     CUtensorMap tm;
@@ -394,7 +411,7 @@ cudaError_t run(const float *data, uint64_t rows_total, uint32_t dim, const std:
     cudaError_t e = cudaMemsetAsync(fail_flag, 0, 4, stream);
     if (e != cudaSuccess) return e;
     row_norms_kernel<<<(unsigned) ((rows_total * 32 + 255) / 256), 256, 0, stream>>>(data, rows_total, dim, norms);
-    const size_t smem_main = 1024 + (size_t) 3 * kRows * dim * 4 + (kEpiWarps * 64 + kRows) * 4 + 7 * 8 + 16;
+    const size_t smem_main = 1024 + (size_t) 3 * kRows * dim * 4 + (kEpiWarps * kCols + kRows) * 4 + 7 * 8 + 16;
     if ((e = cudaFuncSetAttribute(knn_umma_kernel<NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_main)) != cudaSuccess) return e;
     const uint32_t rr_warps = 8;
     const size_t smem_rr = (size_t) rr_warps * (dim_pad4(dim) + 2 * Sizes<NL>::keep) * 4;
@@ -423,7 +440,7 @@ bool knn_tc_eligible(const float *data, uint32_t dim, uint32_t out_degree) {
 
 size_t knn_tc_scratch_bytes(uint64_t rows_total, uint32_t out_degree) {
     const size_t nl = out_degree <= 32 ? 1 : 2;
-    const size_t per_row = 8 /* counts */ + 2 * 64 * nl * 4 /* group minima */ + 256 * nl * 8 /* candidates */;
+    const size_t per_row = 4 * kSplit /* counts */ + 2 * 128 * nl * 4 /* group minima */ + 256 * nl * 8 /* candidates */;
     return align256(rows_total * 4) + 256 + align256((size_t) kMaxCtasPerLaunch * sizeof(KnnTile)) +
            (size_t) kMaxCtasPerLaunch * kRows * per_row + 4 * 256;
 }

@@ -215,6 +215,11 @@ int glide_comm_all_reduce_u64(glide_ctx *ctx, uint64_t *d_buf, uint64_t count, i
 /* Waits for everything enqueued on the context's stream (kernels, copies, collectives). */
 int glide_ctx_synchronize(glide_ctx *ctx);
 
+/* How many kNN stages of this context the tensor-core kernel gave back to the fp32 kernels (no
+ * tensor map, a bounded wait that ran out, or more candidates at a row's threshold than its buffers
+ * hold): 0 in normal operation; the results are correct either way. */
+uint32_t glide_tc_knn_fallbacks(const glide_ctx *ctx);
+
 /* ---- matrix files ----------------------------------------------------------------------- */
 /* load_matrix_data, load.cuh:10-30 (u32 rows, u32 dim, then the rows; the reference reads row by
  * row into pageable memory). elem_bytes 4 (fp32, .fbin) or 1 (uint8). GLIDE_ERR_IO for a missing

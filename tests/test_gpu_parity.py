@@ -386,15 +386,17 @@ def test_tensor_core_knn_equals_exact_knn(gpu_ctx, dim, degree, kind):
     the rows must equal the brute-force rows with ties by ascending id; elsewhere the exact re-rank of
     twice the list width leaves nothing but near-ties to differ."""
     base, _ = helpers.small_dataset(kind, 6000, dim, 10, seed=29)
-    lens = [1, 2, 40, 129, 700, 2100]
+    lens = [1, 2, 40, 129, 700, 1100, 2100]     # 1100 rows: nine tiles, a group size just past a power of two
     lens.append(6000 - sum(lens))
     seg_len = np.array(lens, np.uint32)
     seg_start = np.concatenate([[0], np.cumsum(seg_len)[:-1]]).astype(np.uint32)
     metric = oracle.COSINE if kind == "unit" else oracle.EUCLIDEAN
+    fallbacks = gpu_ctx.tc_knn_fallbacks
     d_knn, rounds, seconds = api.build_nnd(gpu_ctx, NNDescentParameter(degree), dev(gpu_ctx, base), seg_start, seg_len,
                                            Metric(metric))
     knn = d_knn.cpu().numpy()
     assert rounds == 0 and knn.shape == (6000, degree) and seconds > 0
+    assert gpu_ctx.tc_knn_fallbacks == fallbacks       # the rows below come from the tensor-core kernel, not from its fallback
     exact = helpers.exact_partition_knn(base, seg_start, seg_len, degree, metric)
     for s, l in zip(seg_start, seg_len):
         s, l = int(s), int(l)
@@ -629,7 +631,10 @@ def test_full_size_cfg1_properties(gpu_ctx):
     base, queries = datasets.make(spec)
     d_base, d_q = dev(gpu_ctx, base), dev(gpu_ctx, queries)
     cfg = pipeline.BuildConfig(centroid_num=1024, sample_factor=0.1, seed=spec.seed)
+    before = gpu_ctx.tc_knn_fallbacks
     res = pipeline.build_small(gpu_ctx, d_base, cfg)
+    # the kNN stage stayed on the tensor-core kernel (partitions of 9 tiles once overflowed its buffers)
+    assert gpu_ctx.tc_knn_fallbacks == before
     graph = api.to_u32(res.index.graph_view())
     n = base.shape[0]
     valid = graph != INVALID

@@ -372,6 +372,7 @@ def _at_scale(ctx, config, centroid_num, rows, capsys):
     report = {"config": spec.name, "rows": n, "dim": dim, "partitions": centroid_num, "degree": deg,
               "boundary_points": int(seg_len[-1]),
               "knn_stage": {"ours_s": res.seconds["knn"], "nn_descent_rounds": res.nnd_rounds,
+                            "tensor_core_kernel_fallbacks": ctx.tc_knn_fallbacks,
                             "largest_partition": int(seg_len.max()),
                             "graph_recall_at_10_on_a_sample": round(_knn_graph_recall(ctx, res, dim), 4)},
               "preprocess_s": res.seconds["preprocess"]}
