@@ -377,11 +377,13 @@ __global__ void __launch_bounds__(256) ff_update_kernel(const float *__restrict_
 }
 
 // The farthest row becomes centre number `next`; cc[j] = its squared distance to centre j < next.
-__global__ void __launch_bounds__(256) ff_pick_kernel(const float *__restrict__ sample, uint32_t dim,
-                                                      const u64 *__restrict__ block_best, uint32_t blocks,
-                                                      float *centroids, uint32_t next, float *cc) {
+// 1,024 threads: the distances to the earlier centres are a chain of dependent loads per team, and
+// one CTA has to get through up to 4,095 of them between two scans of the sample.
+__global__ void __launch_bounds__(1024) ff_pick_kernel(const float *__restrict__ sample, uint32_t dim,
+                                                       const u64 *__restrict__ block_best, uint32_t blocks,
+                                                       float *centroids, uint32_t next, float *cc) {
     extern __shared__ __align__(16) uint32_t smem[];
-    __shared__ u64 warp_best[8];
+    __shared__ u64 warp_best[32];
     __shared__ uint32_t winner;
     float *c = reinterpret_cast<float *>(smem);
     u64 best = 0;
@@ -393,10 +395,14 @@ __global__ void __launch_bounds__(256) ff_pick_kernel(const float *__restrict__ 
     }
     if (lane_id() == 0) warp_best[threadIdx.x >> 5] = best;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        u64 b = warp_best[0];
-        for (int w = 1; w < 8; w++) if (warp_best[w] > b) b = warp_best[w];
-        winner = 0xffffffffu - (uint32_t) b;
+    if (threadIdx.x < 32) {
+        u64 b = threadIdx.x < (blockDim.x >> 5) ? warp_best[threadIdx.x] : 0;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const u64 o = __shfl_xor_sync(kFullMask, b, off);
+            if (o > b) b = o;
+        }
+        if (threadIdx.x == 0) winner = 0xffffffffu - (uint32_t) b;
     }
     __syncthreads();
     float *next_centre = centroids + (uint64_t) next * dim;
@@ -598,7 +604,7 @@ cudaError_t launch_farthest_first(const float *sample, uint32_t n, uint32_t dim,
     for (uint32_t t = 0; t < C; t++) {
         ff_update_kernel<<<blocks, 256, smem, stream>>>(sample, n, dim, centroids + (uint64_t) t * dim, t, cc, mind2, owner,
                                                         block_best);
-        if (t + 1 < C) ff_pick_kernel<<<1, 256, smem, stream>>>(sample, dim, block_best, blocks, centroids, t + 1, cc);
+        if (t + 1 < C) ff_pick_kernel<<<1, 1024, smem, stream>>>(sample, dim, block_best, blocks, centroids, t + 1, cc);
     }
     return cudaGetLastError();
 }
