@@ -326,17 +326,8 @@ __device__ __forceinline__ u64 ff_key(float v, uint32_t row) {
     return ((u64) __float_as_uint(v) << 32) | (u64) (0xffffffffu - row);
 }
 
-// One farthest-first step: every sample row's squared distance to the newest centre (number t),
-// folded into its running minimum; the block's farthest row goes to block_best.
-// A row is not even read when the triangle inequality already rules the new centre out: with a =
-// the centre the row is nearest to so far, |c_t - c_a| >= 2 |x - c_a| implies |x - c_t| >= |x - c_a|.
-// The test is made on squared distances with a 1 % margin (cc[a] >= 4.01 * mind2), far more than
-// the rounding of either side, so a skipped row is one whose minimum the computed distance could
-// not have lowered: the result is that of the plain scan, bit for bit. On clustered data a new
-// centre then costs the rows of its own cluster instead of the whole sample.
 __global__ void __launch_bounds__(256) ff_update_kernel(const float *__restrict__ sample, uint32_t n, uint32_t dim,
-                                                        const float *__restrict__ centre, uint32_t t,
-                                                        const float *__restrict__ cc, float *mind2, uint32_t *owner,
+                                                        const float *__restrict__ centre, float *mind2,
                                                         u64 *block_best) {
     extern __shared__ __align__(16) uint32_t smem[];
     __shared__ u64 warp_best[8];
@@ -349,15 +340,12 @@ __global__ void __launch_bounds__(256) ff_update_kernel(const float *__restrict_
     for (uint32_t r = warp * kTeamsPerWarp; r < kFfRowsPerBlock; r += 8 * kTeamsPerWarp) {
         const uint32_t row = row0 + r + team;
         const bool active = row < n;
-        float m = active ? mind2[row] : 0.0f;
-        const bool scan = active && (t == 0 || !(__ldg(cc + owner[row]) >= 4.01f * m));
-        const float part = team_partial(c, sample + (uint64_t) (scan ? row : 0) * dim, dim, scan);
+        const float part = team_partial(c, sample + (uint64_t) (active ? row : 0) * dim, dim, active);
         const float d = team_fold(part);
         if (active) {
-            if (scan && d < m) {
-                m = d;
-                if ((lane & (kTeam - 1)) == 0) { mind2[row] = m; owner[row] = t; }
-            }
+            float m = mind2[row];
+            if (d < m) m = d;
+            if ((lane & (kTeam - 1)) == 0) mind2[row] = m;
             const u64 k = ff_key(m, row);
             if (k > best) best = k;
         }
@@ -376,16 +364,11 @@ __global__ void __launch_bounds__(256) ff_update_kernel(const float *__restrict_
     }
 }
 
-// The farthest row becomes centre number `next`; cc[j] = its squared distance to centre j < next.
-// 1,024 threads: the distances to the earlier centres are a chain of dependent loads per team, and
-// one CTA has to get through up to 4,095 of them between two scans of the sample.
-__global__ void __launch_bounds__(1024) ff_pick_kernel(const float *__restrict__ sample, uint32_t dim,
-                                                       const u64 *__restrict__ block_best, uint32_t blocks,
-                                                       float *centroids, uint32_t next, float *cc) {
-    extern __shared__ __align__(16) uint32_t smem[];
-    __shared__ u64 warp_best[32];
+__global__ void __launch_bounds__(256) ff_pick_kernel(const float *__restrict__ sample, uint32_t dim,
+                                                      const u64 *__restrict__ block_best, uint32_t blocks,
+                                                      float *next_centre) {
+    __shared__ u64 warp_best[8];
     __shared__ uint32_t winner;
-    float *c = reinterpret_cast<float *>(smem);
     u64 best = 0;
     for (uint32_t i = threadIdx.x; i < blocks; i += blockDim.x) if (block_best[i] > best) best = block_best[i];
 #pragma unroll
@@ -395,30 +378,13 @@ __global__ void __launch_bounds__(1024) ff_pick_kernel(const float *__restrict__
     }
     if (lane_id() == 0) warp_best[threadIdx.x >> 5] = best;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        u64 b = threadIdx.x < (blockDim.x >> 5) ? warp_best[threadIdx.x] : 0;
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            const u64 o = __shfl_xor_sync(kFullMask, b, off);
-            if (o > b) b = o;
-        }
-        if (threadIdx.x == 0) winner = 0xffffffffu - (uint32_t) b;
+    if (threadIdx.x == 0) {
+        u64 b = warp_best[0];
+        for (int w = 1; w < 8; w++) if (warp_best[w] > b) b = warp_best[w];
+        winner = 0xffffffffu - (uint32_t) b;
     }
     __syncthreads();
-    float *next_centre = centroids + (uint64_t) next * dim;
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float v = sample[(uint64_t) winner * dim + i];
-        next_centre[i] = v;
-        c[i] = v;
-    }
-    __syncthreads();
-    const uint32_t team = threadIdx.x / kTeam, teams = blockDim.x / kTeam;
-    for (uint32_t j0 = 0; j0 < next; j0 += teams) {   // every thread takes every trip: the fold is a warp-wide shuffle
-        const uint32_t j = j0 + team;
-        const bool active = j < next;
-        const float d = team_fold(team_partial(c, centroids + (uint64_t) (active ? j : 0) * dim, dim, active));
-        if (active && (threadIdx.x & (kTeam - 1)) == 0) cc[j] = d;
-    }
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) next_centre[i] = sample[(uint64_t) winner * dim + i];
 }
 
 __global__ void fill_f32_kernel(float *p, uint32_t n, float v) {
@@ -579,32 +545,22 @@ cudaError_t launch_count_changed(const uint32_t *a, const uint32_t *b, uint32_t 
     return cudaGetLastError();
 }
 
-// running minima [n], nearest centre so far [n], centre-to-centre distances [4096], block results
 size_t farthest_first_scratch_bytes(uint32_t n) {
-    const size_t per_row = ((size_t) n * 4 + 255) & ~(size_t) 255;
-    return 2 * per_row + 4096 * 4 + (size_t) ((n + kFfRowsPerBlock - 1) / kFfRowsPerBlock) * 8 + 256;
+    return (size_t) n * 4 + 256 + (size_t) ((n + kFfRowsPerBlock - 1) / kFfRowsPerBlock) * 8 + 256;
 }
 
 cudaError_t launch_farthest_first(const float *sample, uint32_t n, uint32_t dim, uint32_t C, float *centroids,
                                   void *scratch, cudaStream_t stream) {
-    if (C > 4096) return cudaErrorInvalidValue;
-    const size_t per_row = ((size_t) n * 4 + 255) & ~(size_t) 255;
-    char *base = static_cast<char *>(scratch);
-    float *mind2 = reinterpret_cast<float *>(base);
-    uint32_t *owner = reinterpret_cast<uint32_t *>(base + per_row);
-    float *cc = reinterpret_cast<float *>(base + 2 * per_row);
-    u64 *block_best = reinterpret_cast<u64 *>(base + 2 * per_row + 4096 * 4);
+    float *mind2 = static_cast<float *>(scratch);
+    u64 *block_best = reinterpret_cast<u64 *>(static_cast<char *>(scratch) + (((size_t) n * 4 + 255) & ~(size_t) 255));
     const uint32_t blocks = (n + kFfRowsPerBlock - 1) / kFfRowsPerBlock;
     fill_f32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(mind2, n, FLT_MAX);
-    cudaError_t e = cudaMemsetAsync(owner, 0, (size_t) n * 4, stream);
-    if (e != cudaSuccess) return e;
-    e = cudaMemcpyAsync(centroids, sample, (size_t) dim * 4, cudaMemcpyDeviceToDevice, stream);
+    cudaError_t e = cudaMemcpyAsync(centroids, sample, (size_t) dim * 4, cudaMemcpyDeviceToDevice, stream);
     if (e != cudaSuccess) return e;
     const size_t smem = (size_t) dim_pad4(dim) * 4;
     for (uint32_t t = 0; t < C; t++) {
-        ff_update_kernel<<<blocks, 256, smem, stream>>>(sample, n, dim, centroids + (uint64_t) t * dim, t, cc, mind2, owner,
-                                                        block_best);
-        if (t + 1 < C) ff_pick_kernel<<<1, 1024, smem, stream>>>(sample, dim, block_best, blocks, centroids, t + 1, cc);
+        ff_update_kernel<<<blocks, 256, smem, stream>>>(sample, n, dim, centroids + (uint64_t) t * dim, mind2, block_best);
+        if (t + 1 < C) ff_pick_kernel<<<1, 256, 0, stream>>>(sample, dim, block_best, blocks, centroids + (uint64_t) (t + 1) * dim);
     }
     return cudaGetLastError();
 }
