@@ -16,7 +16,6 @@ struct SearchDev {
     uint32_t max_centroid;
     uint32_t max_topk;
     uint32_t strip_words;
-    uint32_t static_first;   // a warp's first ticket is its position in the grid (see search_body)
 };
 
 // Last bitonic phase on a shared array of 32*n pairs (the input must be bitonic).
@@ -163,16 +162,11 @@ __device__ __forceinline__ void search_body(const SearchDev &d) {
         if (q < a.Q) search_one<NB, NC, LANES>(d, s, p, q, whole, true);
         return;
     }
-    // The first ticket of a warp is its position in the grid, so that the warps of a CTA start on
-    // consecutive tickets (queries of one partition, when the tickets are grouped by partition: they
-    // then share the partition's rows in the SM's L1 as well); later tickets come from the counter.
-    auto draw = [&]() {
-        uint32_t t = 0;
-        if (lane == 0) t = atomicAdd(a.ticket, 1u) + (d.static_first ? gridDim.x * (blockDim.x >> 5) : 0u);
-        return __shfl_sync(kFullMask, t, 0);
-    };
-    for (uint32_t ticket = d.static_first ? blockIdx.x * warps_per_cta + warp : draw(); ticket < a.Q; ticket = draw()) {
-        uint32_t q = ticket;
+    while (true) {
+        uint32_t q = 0;
+        if (lane == 0) q = atomicAdd(a.ticket, 1u);
+        q = __shfl_sync(kFullMask, q, 0);
+        if (q >= a.Q) break;
         if (a.order) q = a.order[q];
         if constexpr (!PARTS) {
             search_one<NB, NC, LANES>(d, s, p, q, whole, true);
@@ -287,10 +281,7 @@ cudaError_t launch_search_t(const SearchDev &d, uint32_t warps_per_cta, size_t s
         if (grid > resident) grid = resident;
         if ((e = cudaMemsetAsync(d.a.ticket, 0, sizeof(uint32_t), stream)) != cudaSuccess) return e;
     }
-    SearchDev dd = d;
-    static const bool drawn_only = [] { const char *v = getenv("GLIDE_B200_DRAWN_TICKETS"); return v && v[0] == '1'; }();
-    dd.static_first = (d.a.ticket != nullptr && !drawn_only) ? 1u : 0u;
-    kernel<<<grid, warps_per_cta * 32, smem_bytes, stream>>>(dd);
+    kernel<<<grid, warps_per_cta * 32, smem_bytes, stream>>>(d);
     return cudaGetLastError();
 }
 
