@@ -687,7 +687,8 @@ def run_ours(args):
 # --------------------------------------------------------------------------------------------
 # large path (cfg3: 10M x 96 cosine in 64 partitions; cfg4: 100M x 128 in 512 partitions)
 # --------------------------------------------------------------------------------------------
-LARGE = {"cfg3": dict(partitions=64, sample_rows=1 << 18), "cfg4": dict(partitions=512, sample_rows=1 << 19)}
+LARGE = {"cfg3": dict(partitions=64, sample_rows=1 << 18), "cfg4": dict(partitions=512, sample_rows=1 << 19),
+         "cfg3c64": dict(partitions=64, sample_rows=1 << 18), "cfg4c512": dict(partitions=512, sample_rows=1 << 19)}
 LARGE_BLOCK = 1 << 22   # rows generated and assigned at a time
 
 
@@ -761,7 +762,7 @@ def run_large(args):
         d_mine[p[keep] - r_lo] = rows[keep]
         del rows
     del pos
-    use_u8 = args.rows_u8 and spec.kind == "int_mixture"
+    use_u8 = args.rows_u8 and spec.kind in ("int_mixture", "int_lowrank_mixture")
     h_rows = large.pinned_empty((mine, dim), np.uint8 if use_u8 else np.float32)
     t_rows = large._PINNED[id(h_rows)]
     t_rows.copy_(d_mine.to(torch.uint8) if use_u8 else d_mine)

@@ -22,7 +22,7 @@ class DatasetSpec:
     n: int
     dim: int
     n_queries: int
-    kind: str            # "uniform" | "int_mixture" | "int_lowrank_mixture" | "scaled_mixture" | "unit_mixture"
+    kind: str            # "uniform" | "int_mixture" | "int_lowrank_mixture" | "scaled_mixture" | "unit_mixture" | "unit_lowrank_mixture"
     centres: int
     metric: str          # "Euclidean" | "Cosine"
     graph_degree: int
@@ -49,6 +49,14 @@ CONFIGS = {
     "cfg1c32": DatasetSpec("cfg1c32", 1_000_000, 128, 10_000, "int_lowrank_mixture", 32, "Euclidean", 32, 11),
     # 100M x 128: as cfg1 with 16,384 centres
     "cfg4": DatasetSpec("cfg4", 100_000_000, 128, 10_000, "int_mixture", 16384, "Euclidean", 32, 4),
+    # The two large configs with as many mixture components as BASELINE.json gives them partitions (64
+    # and 512) and the low intrinsic dimension of cfg1c32: a partition's kNN graph is then connected and
+    # recall@10 >= 0.95 is reachable at those partition counts, which the isotropic 4,096- and
+    # 16,384-component sets above cannot give (a partition there spans dozens of separate clusters).
+    # cfg3c64: unit vectors; a component varies in its own 24-dimensional subspace (per-coordinate sigma
+    # 0.5 before normalisation) plus isotropic noise of sigma 0.15. cfg4c512: as cfg1c32.
+    "cfg3c64": DatasetSpec("cfg3c64", 10_000_000, 96, 10_000, "unit_lowrank_mixture", 64, "Cosine", 32, 13),
+    "cfg4c512": DatasetSpec("cfg4c512", 100_000_000, 128, 10_000, "int_lowrank_mixture", 512, "Euclidean", 32, 14),
 }
 
 
@@ -63,8 +71,9 @@ def _rng(seed: int, stream: int, chunk: int) -> np.random.Generator:
     return np.random.Generator(np.random.Philox(key=[seed, stream], counter=[0, chunk, 0, 0]))
 
 
-_LATENT = 24          # int_lowrank_mixture: dimension of a component's own subspace
-_LOWRANK_NOISE = 6.0  # and the sigma of the isotropic noise around it
+_LATENT = 24          # low-rank mixtures: dimension of a component's own subspace
+_LOWRANK_NOISE = 6.0  # int_lowrank_mixture: sigma of the isotropic noise around it (latent: 20 per coordinate)
+_UNIT_LATENT_SIGMA, _UNIT_LOWRANK_NOISE = 0.5, 0.15   # unit_lowrank_mixture, before normalisation
 
 _basis_cache: dict = {}
 
@@ -79,14 +88,15 @@ def centres(spec: DatasetSpec) -> np.ndarray | None:
 
 
 def _subspaces(spec: DatasetSpec) -> np.ndarray:
-    """int_lowrank_mixture: per component _LATENT unit directions (centres x _LATENT x dim), scaled so that
-    a standard normal latent vector gives a per-coordinate sigma of 20."""
-    key = (spec.seed, spec.centres, spec.dim)
+    """Low-rank mixtures: per component _LATENT unit directions (centres x _LATENT x dim), scaled so that
+    a standard normal latent vector gives the kind's per-coordinate sigma (20, or 0.5 for unit vectors)."""
+    key = (spec.seed, spec.centres, spec.dim, spec.kind)
     if key not in _basis_cache:
         g = _rng(spec.seed, 3, 0)
         a = g.standard_normal(size=(spec.centres, _LATENT, spec.dim), dtype=np.float32)
         a /= np.linalg.norm(a, axis=2, keepdims=True)
-        _basis_cache[key] = a * np.float32(20.0 * np.sqrt(spec.dim / _LATENT))
+        sigma = 20.0 if spec.kind == "int_lowrank_mixture" else _UNIT_LATENT_SIGMA
+        _basis_cache[key] = a * np.float32(sigma * np.sqrt(spec.dim / _LATENT))
     return _basis_cache[key]
 
 
@@ -126,6 +136,14 @@ def _rows(spec: DatasetSpec, cent: np.ndarray | None, stream: int, first: int, c
                 block = (cent[comp] + np.float32(0.3) * noise) * scale[:, None]
             elif spec.kind == "unit_mixture":
                 block = cent[comp] + np.float32(0.5) * noise
+                block /= np.linalg.norm(block, axis=1, keepdims=True).astype(np.float32)
+            elif spec.kind == "unit_lowrank_mixture":
+                z = g.standard_normal(size=(_CHUNK, _LATENT), dtype=np.float32)[off:off + take]
+                basis = _subspaces(spec)
+                block = cent[comp] + np.float32(_UNIT_LOWRANK_NOISE) * noise
+                for k in np.unique(comp):
+                    rows = np.nonzero(comp == k)[0]
+                    block[rows] += z[rows] @ basis[k]
                 block /= np.linalg.norm(block, axis=1, keepdims=True).astype(np.float32)
             else:
                 raise ValueError(spec.kind)
@@ -167,6 +185,8 @@ def device_rows(spec: DatasetSpec, first: int, count: int, device, cent=None, st
     import torch
     if cent is None:
         cent = torch.from_numpy(centres(spec)).to(device)
+    lowrank = spec.kind in ("int_lowrank_mixture", "unit_lowrank_mixture")
+    basis = torch.from_numpy(_subspaces(spec)).to(device) if lowrank else None
     out = torch.empty((count, spec.dim), dtype=torch.float32, device=device)
     done = 0
     while done < count:
@@ -177,7 +197,20 @@ def device_rows(spec: DatasetSpec, first: int, count: int, device, cent=None, st
         g.manual_seed(((spec.seed * 7 + stream) << 32) + block)
         comp = torch.randint(0, spec.centres, (DEVICE_BLOCK,), generator=g, device=device)[off:off + take]
         noise = torch.randn((DEVICE_BLOCK, spec.dim), generator=g, device=device, dtype=torch.float32)[off:off + take]
-        if spec.kind == "int_mixture":
+        if lowrank:
+            # the row's component's subspace applied to its latent vector, 65,536 rows at a time (the
+            # gathered bases of a chunk are 0.8 GB)
+            z = torch.randn((DEVICE_BLOCK, _LATENT), generator=g, device=device, dtype=torch.float32)[off:off + take]
+            sigma = _LOWRANK_NOISE if spec.kind == "int_lowrank_mixture" else _UNIT_LOWRANK_NOISE
+            blockv = cent[comp] + sigma * noise
+            for lo in range(0, take, 65536):
+                hi = min(take, lo + 65536)
+                blockv[lo:hi] += torch.bmm(z[lo:hi, None, :], basis[comp[lo:hi]])[:, 0, :]
+            if spec.kind == "int_lowrank_mixture":
+                blockv = torch.clamp(torch.round(blockv), 0.0, 218.0)
+            else:
+                blockv = blockv / blockv.norm(dim=1, keepdim=True)
+        elif spec.kind == "int_mixture":
             blockv = torch.clamp(torch.round(cent[comp] + 20.0 * noise), 0.0, 218.0)
         elif spec.kind == "unit_mixture":
             blockv = cent[comp] + 0.5 * noise
