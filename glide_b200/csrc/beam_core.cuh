@@ -36,7 +36,13 @@ struct WarpStrip {
     uint32_t *work;      // 32*NC: slots of the candidates to score
     uint32_t *work_id;   // 32*NC: their ids
     uint32_t *extra;     // mode-specific scratch (pool, rows, merge buffers)
+    uint32_t *tail;      // the last kTwoWarpScratch words of the strip: present (and set by the kernel) only for beams
+                         // above 256 slots, whose merge runs on shared arrays (merge_beam_two_warps)
 };
+
+// beam keys [512], beam ids [512], one sorted candidate row of the lane-resident kernels: keys [32], ids [32]
+constexpr uint32_t kTwoWarpScratch = 2 * 512 + 64;
+__host__ __device__ inline uint32_t two_warp_scratch_words(uint32_t max_beam) { return max_beam > 256 ? kTwoWarpScratch : 0u; }
 
 __host__ __device__ inline uint32_t dim_pad4(uint32_t dim) { return (dim + 3u) & ~3u; }
 
@@ -53,6 +59,7 @@ __device__ __forceinline__ WarpStrip make_strip(uint32_t *base, uint32_t dim, ui
     s.work = s.visited + visited_words(hash_bit);
     s.work_id = s.work + max_cand;
     s.extra = s.work_id + max_cand;
+    s.tail = nullptr;
     return s;
 }
 
@@ -207,6 +214,142 @@ __device__ __forceinline__ uint32_t nearest_centroid(const float *q_smem, const 
     return cv[0];
 }
 
+// search_kernel.cuh:148-233: for MAX_BEAM = 512 the reference merges with two warps and ends up with
+// its own order among equal distances. One warp replays both here on shared arrays: candidates
+// (ascending, cand_k / cand_v, the first min(degree, beam) valid) replace mirrored beam slots where
+// they are strictly smaller, the two halves of the beam exchange pairwise, and each half is merged
+// after being loaded around its turning point (the first slot that changed), which makes the loaded
+// sequence bitonic. sk / sv: 512 words each. The beam comes in and leaves in registers (position
+// j = 16 * lane + i).
+__device__ __forceinline__ void merge_beam_two_warps(float (&bk)[16], uint32_t (&bv)[16], uint32_t beam, uint32_t degree,
+                                                     const float *cand_k, const uint32_t *cand_v, float *sk, uint32_t *sv) {
+    const uint32_t lane = lane_id(), half = beam >> 1;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const uint32_t j = 16u * lane + i;
+        if (j < beam) { sk[j] = bk[i]; sv[j] = bv[i]; }
+    }
+    __syncwarp();
+    uint32_t t0 = half, t1 = half, t2 = half;
+    const uint32_t lim = degree < beam ? degree : beam;
+    for (uint32_t k = lane; k < lim; k += 32) {
+        const uint32_t j = beam - 1u - k;
+        const float c = cand_k[k];
+        if (sk[j] > c) {
+            sk[j] = c;
+            sv[j] = cand_v[k];
+            if (j < half) t2 = min(t2, j); else t1 = min(t1, j - half);
+        }
+    }
+    __syncwarp();
+    for (uint32_t j = lane; j < half; j += 32) {
+        const uint32_t k = j + half;
+        const float a = sk[j], b = sk[k];
+        if (a > b) {
+            sk[j] = b; sk[k] = a;
+            const uint32_t t = sv[j]; sv[j] = sv[k]; sv[k] = t;
+            t0 = min(t0, j);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        t0 = min(t0, __shfl_xor_sync(kFullMask, t0, off));
+        t1 = min(t1, __shfl_xor_sync(kFullMask, t1, off));
+        t2 = min(t2, __shfl_xor_sync(kFullMask, t2, off));
+    }
+    if (t2 < half) t1 = t2;
+    __syncwarp();
+#pragma unroll 1
+    for (uint32_t w = 0; w < 2; w++) {
+        const uint32_t turning = w == 0 ? t0 : t1;
+        float k8[8];
+        uint32_t v8[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            uint32_t k = beam, j = 8u * lane + i;
+            if (j < turning) {
+                k = j + half * w;
+            } else if (j >= 256u - half) {
+                j -= 256u - half;
+                if (turning <= j && j < half) k = j + half * w;
+            }
+            k8[i] = k < beam ? sk[k] : FLT_MAX;
+            v8[i] = k < beam ? sv[k] : kInvalid;
+        }
+        __syncwarp();
+        warp_merge_final<8>(k8, v8);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t j = 8u * lane + i;
+            if (j < half) { sk[j + half * w] = k8[i]; sv[j + half * w] = v8[i]; }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const uint32_t j = 16u * lane + i;
+        bk[i] = j < beam ? sk[j] : FLT_MAX;
+        bv[i] = j < beam ? sv[j] : kInvalid;
+    }
+    __syncwarp();
+}
+
+// search_kernel.cuh:38-95: for MAX_CANDIDATE = 256 the reference sorts the candidates with two warps:
+// each sorts its half of 128, the halves exchange mirrored elements (equal keys stay, the first half
+// keeps the smaller), and each merges its half again. Replayed by one warp with two register sets on
+// the candidate arrays in shared memory.
+__device__ __forceinline__ void sort_candidates_two_warps(float *cand_k, uint32_t *cand_v, uint32_t degree, uint32_t beam) {
+    const uint32_t lane = lane_id();
+    constexpr uint32_t per = 128;
+    float ka[2][4];
+    uint32_t va[2][4];
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t j = lane + 32u * i + per * w;
+            ka[w][i] = j < degree ? cand_k[j] : FLT_MAX;
+            va[w][i] = j < degree ? cand_v[j] : kInvalid;
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+        warp_sort<4>(ka[w], va[w]);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t jl = 4u * lane + i, j = jl + per * w;
+            if (j < degree && jl < beam) { cand_k[j] = ka[w][i]; cand_v[j] = va[w][i]; }
+        }
+    }
+    __syncwarp();
+    const uint32_t used = (beam + per - 1) / per;
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+        if ((uint32_t) w >= used) continue;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t jl = 4u * lane + i, kl = per - 1u - jl, j = jl + per * w, k = 256u - 1u - j;
+            if (j >= degree || k >= degree || kl >= beam) continue;
+            const float other = cand_k[k];
+            if (ka[w][i] == other) continue;
+            if ((w == 0) == (ka[w][i] > other)) { ka[w][i] = other; va[w][i] = cand_v[k]; }
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+        if ((uint32_t) w >= used) continue;
+        warp_merge_final<4>(ka[w], va[w]);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t j = 4u * lane + i + per * w;
+            if (j < degree && j < beam) { cand_k[j] = ka[w][i]; cand_v[j] = va[w][i]; }
+        }
+    }
+    __syncwarp();
+}
+
 // The search loop proper. On return bk/bv hold the beam (ascending, position
 // j = NB*lane + i, ids still carrying the explored flag). Returns the number of
 // expansions; *rows_read accumulates data rows fetched.
@@ -241,6 +384,8 @@ __device__ __forceinline__ uint32_t beam_loop(float (&bk)[NB], uint32_t (&bv)[NB
                 s.cand_id[lane] = cv[0];
             }
             __syncwarp();
+        } else if constexpr (NC == 8) {
+            sort_candidates_two_warps(s.cand_dist, s.cand_id, degree, p.beam);
         } else {
             float ck[NC];
             uint32_t cv[NC];
@@ -271,6 +416,8 @@ __device__ __forceinline__ uint32_t beam_loop(float (&bk)[NB], uint32_t (&bv)[NB
                 bk[i] = take ? s.cand_dist[j] : FLT_MAX;
                 bv[i] = take ? s.cand_id[j] : kInvalid;
             }
+        } else if constexpr (NB == 16) {
+            merge_beam_two_warps(bk, bv, p.beam, degree, s.cand_dist, s.cand_id, reinterpret_cast<float *>(s.tail), s.tail + 512);
         } else {
 #pragma unroll
             for (int i = 0; i < NB; i++) {
@@ -425,6 +572,13 @@ __device__ __forceinline__ uint32_t beam_loop_lanes(float (&bk)[NB], uint32_t (&
                 bk[i] = take ? c : FLT_MAX;
                 bv[i] = take ? id : kInvalid;
             }
+        } else if constexpr (NB == 16) {
+            float *row_k = reinterpret_cast<float *>(s.tail + 1024);
+            uint32_t *row_v = s.tail + 1024 + 32;
+            row_k[lane] = ck;          // the sorted candidate row, slot = lane
+            row_v[lane] = cv;
+            __syncwarp();
+            merge_beam_two_warps(bk, bv, p.beam, degree, row_k, row_v, reinterpret_cast<float *>(s.tail), s.tail + 512);
         } else {
 #pragma unroll
             for (int i = 0; i < NB; i++) {

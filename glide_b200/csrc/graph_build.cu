@@ -204,6 +204,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
     const uint32_t point = a.first + (a.order ? a.order[t] : t);
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
     WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLaneScratch : 32u * NC, p.hash_bit);
+    if constexpr (NB == 16) s.tail = smem + (size_t) (warp + 1) * d.strip_words - kTwoWarpScratch;
     PruneStrip ps = make_prune_strip(s.extra, d.max_degree);
     const uint32_t degree = a.out_degree;
 
@@ -494,7 +495,7 @@ cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
         const uint64_t inserts = (uint64_t) a.p.beam + (uint64_t) a.in_degree * (a.p.hash_reset_interval + 2ull) + 2;
         if (words <= (cap > 1024 ? cap : 1024) && inserts <= cap) d.a.p.hash_bit = a.p.hash_bit | ((uint32_t) words << 8);
     }
-    d.strip_words = (strip_words_base(a.dim, lanes ? kLaneScratch : max_cand, d.a.p.hash_bit) + extra + 3u) & ~3u;
+    d.strip_words = (strip_words_base(a.dim, lanes ? kLaneScratch : max_cand, d.a.p.hash_bit) + extra + two_warp_scratch_words(max_beam) + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;
     while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;

@@ -155,7 +155,8 @@ __device__ __forceinline__ void search_body(const SearchDev &d) {
     const uint32_t warps_per_cta = blockDim.x >> 5;
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
-    const WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLaneScratch : 32u * NC, p.hash_bit);
+    WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLaneScratch : 32u * NC, p.hash_bit);
+    if constexpr (NB == 16) s.tail = smem + (size_t) (warp + 1) * d.strip_words - kTwoWarpScratch;
     const PartView whole{a.data, a.graph, a.map, a.start_point};
     if (a.ticket == nullptr) {
         const uint32_t q = blockIdx.x * warps_per_cta + warp;
@@ -308,7 +309,7 @@ cudaError_t launch_search(const SearchArgs &a, cudaStream_t stream) {
     const uint32_t max_cand = a.degree <= 64 ? 64 : (a.degree <= 128 ? 128 : 256);
     const uint32_t extra = a.segment_ids ? 4 * d.max_topk : 0;
     const bool lanes = a.degree <= 32;
-    d.strip_words = (strip_words_base(a.dim, lanes ? kLaneScratch : max_cand, a.p.hash_bit) + extra + 3u) & ~3u;
+    d.strip_words = (strip_words_base(a.dim, lanes ? kLaneScratch : max_cand, a.p.hash_bit) + extra + two_warp_scratch_words(max_beam) + 3u) & ~3u;
     const size_t strip_bytes = (size_t) d.strip_words * 4;
     uint32_t warps = 8;
     while (warps > 1 && strip_bytes * warps > 96 * 1024) warps >>= 1;

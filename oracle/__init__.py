@@ -261,6 +261,11 @@ def load_matrix_rowwise(path: str, dtype=np.float32) -> np.ndarray:
     return out
 
 
+def set_two_warps(on: bool) -> None:
+    """Tests only: False makes the search use the single-warp sort and merge at every size."""
+    lib().orc_set_two_warps(C.c_int(1 if on else 0))
+
+
 def recall(neighbors, truth, top_k) -> float:
     neighbors, truth = _u32(neighbors), _u32(truth)
     return float(lib().orc_recall(_p(neighbors), u32(neighbors.shape[1]), _p(truth), u32(truth.shape[1]),

@@ -240,6 +240,10 @@ uint32_t ladder_centroid(uint32_t c) {
     return m;
 }
 
+// Tests switch the two-warp sort and merge off to check them against the single-warp network
+// (same keys in the same order; only ids of equal keys may differ).
+bool g_two_warps = true;
+
 struct SearchCfg {
     uint32_t beam;            // already rounded to a multiple of 32 (params.cuh:94-98)
     uint32_t max_iterations;  // params.cuh:85-93
@@ -256,13 +260,123 @@ struct BeamState {
     VisitedSet visited;
     uint64_t n_dist = 0;  // distance evaluations against data rows
     uint32_t n_iter = 0;  // expansions
+    bool two_warps = g_two_warps;   // the reference's kernels run with at least 64 threads (two warps) per query or point
     BeamState(const SearchCfg &c, uint32_t degree)
         : beam(c.beam), max_beam(ladder_beam(c.beam)), deg(degree), max_cand(ladder_cand(degree)),
           beam_dist(c.beam, kMaxF), cand_dist(degree, kMaxF), beam_id(c.beam, kInvalid),
           cand_id(degree, kInvalid), visited(c.hash_bit) {}
 
+    // search_kernel.cuh:38-95: MAX_CANDIDATE > 128 splits the candidates over two warps. Each sorts its
+    // half of 128, the halves exchange mirrored elements (equal keys stay where they are, warp 0
+    // keeps the smaller), and each merges its half again. Restated as the reference's kernels run it:
+    // two register files, one candidate buffer.
+    void sort_candidates_two_warps() {
+        const uint32_t per = (max_cand + 1) / 2, N = (per + 31) / 32;
+        WarpRegs regs[2] = {WarpRegs(N), WarpRegs(N)};
+        for (uint32_t w = 0; w < 2; w++) {
+            WarpRegs &r = regs[w];
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t j = lane + 32 * i + per * w;
+                    r.K(lane, i) = (j < deg) ? cand_dist[j] : kMaxF;
+                    r.V(lane, i) = (j < deg) ? cand_id[j] : kInvalid;
+                }
+        }
+        for (uint32_t w = 0; w < 2; w++) {   // both warps have read before either writes (reads and writes touch its own half only)
+            WarpRegs &r = regs[w];
+            warp_sort(r);
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t jl = N * lane + i, j = jl + per * w;
+                    if (j < deg && jl < beam) {
+                        cand_dist[j] = r.K(lane, i);
+                        cand_id[j] = r.V(lane, i);
+                    }
+                }
+        }
+        const uint32_t used = (beam + per - 1) / per;
+        for (uint32_t w = 0; w < used && w < 2; w++) {   // reads of the buffer only: no order between the warps
+            WarpRegs &r = regs[w];
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t jl = N * lane + i, kl = per - 1 - jl, j = jl + per * w, k = max_cand - 1 - j;
+                    if (j >= deg || k >= deg || kl >= beam) continue;
+                    const float other = cand_dist[k];
+                    if (r.K(lane, i) == other) continue;
+                    if ((w == 0) == (r.K(lane, i) > other)) {
+                        r.K(lane, i) = other;
+                        r.V(lane, i) = cand_id[k];
+                    }
+                }
+        }
+        for (uint32_t w = 0; w < used && w < 2; w++) {
+            WarpRegs &r = regs[w];
+            warp_merge(r, 32);
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t j = N * lane + i + per * w;
+                    if (j < deg && j < beam) {
+                        cand_dist[j] = r.K(lane, i);
+                        cand_id[j] = r.V(lane, i);
+                    }
+                }
+        }
+    }
+    // search_kernel.cuh:148-233: MAX_BEAM > 256 merges with two warps. Candidates replace mirrored beam
+    // slots, the two halves of the beam exchange pairwise, and each warp merges its half, which it
+    // loads around a "turning point" (the first slot the exchange touched) so that the sequence is
+    // bitonic. The three minima the reference takes with atomics do not depend on thread order.
+    void merge_into_beam_two_warps() {
+        const uint32_t half = beam / 2, per = (max_beam + 1) / 2, N = (per + 31) / 32;
+        uint32_t ws[3] = {half, half, half};
+        const uint32_t lim = std::min(deg, beam);
+        for (uint32_t k = 0; k < lim; k++) {
+            const uint32_t j = beam - 1 - k;
+            if (beam_dist[j] > cand_dist[k]) {
+                beam_dist[j] = cand_dist[k];
+                beam_id[j] = cand_id[k];
+                if (j < half) ws[2] = std::min(ws[2], j);
+                else ws[1] = std::min(ws[1], j - half);
+            }
+        }
+        for (uint32_t j = 0; j < half; j++) {
+            const uint32_t k = j + half;
+            if (beam_dist[j] > beam_dist[k]) {
+                std::swap(beam_dist[j], beam_dist[k]);
+                std::swap(beam_id[j], beam_id[k]);
+                ws[0] = std::min(ws[0], j);
+            }
+        }
+        if (ws[2] < half) ws[1] = ws[2];
+        for (uint32_t w = 0; w < 2; w++) {
+            const uint32_t turning = ws[w];
+            WarpRegs r(N);
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    uint32_t k = beam, j = N * lane + i;
+                    if (j < turning) {
+                        k = j + half * w;
+                    } else if (j >= max_beam / 2 - half) {
+                        j -= max_beam / 2 - half;
+                        if (turning <= j && j < half) k = j + half * w;
+                    }
+                    r.K(lane, i) = (k < beam) ? beam_dist[k] : kMaxF;
+                    r.V(lane, i) = (k < beam) ? beam_id[k] : kInvalid;
+                }
+            warp_merge(r, 32);
+            for (uint32_t lane = 0; lane < 32; lane++)
+                for (uint32_t i = 0; i < N; i++) {
+                    const uint32_t j = N * lane + i;
+                    if (j < half) {
+                        beam_dist[j + half * w] = r.K(lane, i);
+                        beam_id[j + half * w] = r.V(lane, i);
+                    }
+                }
+        }
+    }
     // search_kernel.cuh:9-37 (single-warp branch).
     void sort_candidates() {
+        if (max_cand > 128 && two_warps) return sort_candidates_two_warps();
         const uint32_t N = max_cand / 32;
         WarpRegs r(N);
         for (uint32_t lane = 0; lane < 32; lane++)
@@ -290,6 +404,7 @@ struct BeamState {
             }
             return;
         }
+        if (max_beam > 256 && two_warps) return merge_into_beam_two_warps();
         const uint32_t N = max_beam / 32;
         WarpRegs r(N);
         for (uint32_t lane = 0; lane < 32; lane++)
@@ -1027,6 +1142,8 @@ int orc_load_matrix_rowwise(const char *path, uint32_t elem_bytes, void *out, ui
     }
     return 0;
 }
+
+void orc_set_two_warps(int on) { g_two_warps = on != 0; }
 
 // small_search.cu:14-36
 float orc_recall(const uint32_t *neighbors, uint32_t nb_stride, const uint32_t *truth,

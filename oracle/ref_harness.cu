@@ -69,7 +69,7 @@ int ref_search(const float *d_data, uint32_t dim, const uint32_t *d_graph, uint3
                uint32_t C, const uint32_t *d_start_points, const float *d_queries, uint32_t Q, uint32_t top_k,
                uint32_t beam, uint32_t max_iterations, uint32_t min_iterations, uint32_t hash_bit,
                uint32_t hash_reset_interval, int metric, uint32_t *d_ids, float *d_dists) {
-    if (degree > 64 || C > 64) return -2;
+    if (degree > 256 || beam > 512 || C > 64 || (C > 32 && (degree > 64 || beam > 256))) return -2;
     const uint32_t rbs = round_up32(beam + degree);
     if (C > rbs) return -2;  // the centroid lists alias the result buffers (search_kernel.cuh:424-427)
     const uint32_t smem = dim * sizeof(float) + rbs * (sizeof(uint32_t) + sizeof(float)) +
@@ -83,7 +83,25 @@ int ref_search(const float *d_data, uint32_t dim, const uint32_t *d_graph, uint3
         return 0;
     };
     int rc;
-    if (C <= 32)
+    if (C <= 32 && (degree > 64 || beam > 256)) {
+        // the wider ladders (kernel_config.cuh:40-60): MAX_CANDIDATE 128 / 256 and MAX_BEAM 512, the sizes at
+        // which the reference sorts and merges with two warps (search_kernel.cuh:38-95, 148-233)
+        auto by_beam4 = [&](auto k64, auto k128, auto k256, auto k512) {
+            if (beam <= 64) return launch(k64);
+            if (beam <= 128) return launch(k128);
+            if (beam <= 256) return launch(k256);
+            return launch(k512);
+        };
+        if (degree <= 64)
+            rc = by_beam4(search_kernel<64, 64, 32, float, uint32_t>, search_kernel<64, 128, 32, float, uint32_t>,
+                          search_kernel<64, 256, 32, float, uint32_t>, search_kernel<64, 512, 32, float, uint32_t>);
+        else if (degree <= 128)
+            rc = by_beam4(search_kernel<128, 64, 32, float, uint32_t>, search_kernel<128, 128, 32, float, uint32_t>,
+                          search_kernel<128, 256, 32, float, uint32_t>, search_kernel<128, 512, 32, float, uint32_t>);
+        else
+            rc = by_beam4(search_kernel<256, 64, 32, float, uint32_t>, search_kernel<256, 128, 32, float, uint32_t>,
+                          search_kernel<256, 256, 32, float, uint32_t>, search_kernel<256, 512, 32, float, uint32_t>);
+    } else if (C <= 32)
         rc = by_beam(beam, [&] { return launch(search_kernel<64, 64, 32, float, uint32_t>); },
                      [&] { return launch(search_kernel<64, 128, 32, float, uint32_t>); },
                      [&] { return launch(search_kernel<64, 256, 32, float, uint32_t>); });

@@ -49,7 +49,7 @@ def case(name):
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
-@pytest.mark.parametrize("beam", [32, 64, 100, 256])
+@pytest.mark.parametrize("beam", [32, 64, 100, 256, 300, 512])   # above 256: the reference's two-warp merge order
 def test_search_matches_oracle(gpu_ctx, name, beam):
     base, queries, P = case(name)
     metric = P["metric"]
@@ -91,7 +91,7 @@ def wide_case(name):
 
 
 @pytest.mark.parametrize("name", sorted(WIDE_CASES))
-@pytest.mark.parametrize("beam", [32, 64, 100, 256])
+@pytest.mark.parametrize("beam", [32, 64, 100, 256, 300, 512])
 def test_search_on_wide_adjacency_rows_matches_oracle(gpu_ctx, name, beam):
     base, queries, P = wide_case(name)
     metric, degree = P["metric"], P["graph"].shape[1]
@@ -107,6 +107,36 @@ def test_search_on_wide_adjacency_rows_matches_oracle(gpu_ctx, name, beam):
     same = (ref_ids == got_ids)
     assert same.mean() > 0.99
     assert np.allclose(got_d[same], ref_d[same], rtol=1e-5)
+
+
+def _widened_graph(graph, degree, seed=3):
+    """The case's graph with random further neighbours up to `degree` entries per row (for the search
+    any graph will do; rows stay free of duplicates and self loops)."""
+    n, d0 = graph.shape
+    rng = np.random.default_rng(seed)
+    out = np.full((n, degree), INVALID, np.uint32)
+    out[:, :d0] = graph
+    for r in range(n):
+        have = set(graph[r][graph[r] != INVALID].tolist()) | {r}
+        extra = [int(x) for x in rng.permutation(n)[:degree] if int(x) not in have][:degree - d0]
+        out[r, d0:d0 + len(extra)] = extra
+    return out
+
+
+@pytest.mark.parametrize("name,degree", [("int128_d64", 160), ("unit96_d48", 130), ("int128_d64", 256)])
+@pytest.mark.parametrize("beam", [64, 128, 300])
+def test_search_on_rows_wider_than_128_matches_oracle(gpu_ctx, name, degree, beam):
+    """Adjacency rows of more than 128 entries: the reference sorts the candidates with two warps
+    (search_kernel.cuh:38-95); with a beam above 256 it also merges with two (:148-233)."""
+    base, queries, P = wide_case(name)
+    metric = P["metric"]
+    graph = _widened_graph(P["graph"], degree)
+    o = oracle.SearchParams.derive(beam, degree, top_k=10)
+    want_ids, want_d = oracle.search(base, graph, P["centroids"], P["orig_sp"], queries, o, metric)
+    d_ids, d_d, _ = api.search(gpu_ctx, dev(gpu_ctx, base), dev(gpu_ctx, graph), dev(gpu_ctx, P["centroids"]),
+                               dev(gpu_ctx, P["orig_sp"]), dev(gpu_ctx, queries), sp_from(o), Metric(metric))
+    assert np.array_equal(api.to_u32(d_ids), want_ids)
+    assert np.array_equal(d_d.cpu().numpy(), want_d)
 
 
 @pytest.mark.parametrize("name", sorted(WIDE_CASES))

@@ -46,7 +46,7 @@ def dev(ctx, a):
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
-@pytest.mark.parametrize("beam", [32, 64, 100, 200])
+@pytest.mark.parametrize("beam", [32, 64, 100, 200, 300, 512])   # above 256: the reference merges with two warps
 def test_reference_search_kernel_equals_oracle(gpu_ctx, name, beam):
     base, queries, P = case(name)
     o = oracle.SearchParams.derive(beam, 16, top_k=10)
@@ -57,6 +57,34 @@ def test_reference_search_kernel_equals_oracle(gpu_ctx, name, beam):
     t = [dev(gpu_ctx, x) for x in (base, P["graph"], P["centroids"], P["orig_sp"], queries)]
     torch.cuda.synchronize()
     rc = ref.search(t[0].data_ptr(), base.shape[1], t[1].data_ptr(), 16, t[2].data_ptr(), P["centroids"].shape[0],
+                    t[3].data_ptr(), t[4].data_ptr(), queries.shape[0], o, P["metric"], d_ids.data_ptr(), d_d.data_ptr())
+    assert rc == 0
+    assert np.array_equal(api.to_u32(d_ids), want_ids)
+    assert np.array_equal(d_d.cpu().numpy(), want_d)
+
+
+@pytest.mark.parametrize("name,degree", [("int128", 160), ("unit96", 130), ("uniform32", 256)])
+@pytest.mark.parametrize("beam", [64, 128, 300])
+def test_reference_search_kernel_on_rows_wider_than_128_equals_oracle(gpu_ctx, name, degree, beam):
+    """MAX_CANDIDATE = 256: the reference sorts the candidates with two warps (search_kernel.cuh:38-95); the
+    graph is the case's own with random further neighbours (any graph serves a search)."""
+    base, queries, P = case(name)
+    n = base.shape[0]
+    rng = np.random.default_rng(7)
+    graph = np.full((n, degree), INVALID, np.uint32)
+    graph[:, :16] = P["graph"]
+    for r in range(n):
+        have = set(P["graph"][r][P["graph"][r] != INVALID].tolist()) | {r}
+        extra = [int(x) for x in rng.permutation(n)[:degree] if int(x) not in have][:degree - 16]
+        graph[r, 16:16 + len(extra)] = extra
+    o = oracle.SearchParams.derive(beam, degree, top_k=10)
+    want_ids, want_d = oracle.search(base, graph, P["centroids"], P["orig_sp"], queries, o, P["metric"],
+                                     order=oracle.ORDER_REF, route_order=oracle.ORDER_REF)
+    d_ids = api._u32_tensor(gpu_ctx, want_ids.shape)
+    d_d = gpu_ctx.empty(want_d.shape, torch.float32)
+    t = [dev(gpu_ctx, x) for x in (base, graph, P["centroids"], P["orig_sp"], queries)]
+    torch.cuda.synchronize()
+    rc = ref.search(t[0].data_ptr(), base.shape[1], t[1].data_ptr(), degree, t[2].data_ptr(), P["centroids"].shape[0],
                     t[3].data_ptr(), t[4].data_ptr(), queries.shape[0], o, P["metric"], d_ids.data_ptr(), d_d.data_ptr())
     assert rc == 0
     assert np.array_equal(api.to_u32(d_ids), want_ids)

@@ -177,3 +177,29 @@ def test_large_path_routing_and_merge():
     gt = oracle.bruteforce_knn(base, queries, 10, want_dists=False)
     assert np.all(np.diff(final_d, axis=1) >= 0)
     assert oracle.recall(final_ids, gt, 10) > 0.85
+
+
+@pytest.mark.parametrize("beam,degree", [(300, 16), (512, 16), (64, 160), (300, 200)])
+def test_two_warp_sort_and_merge_order_the_same_keys_as_the_single_warp_network(pipe, beam, degree):
+    """The reference's two-warp candidate sort (rows wider than 128) and two-warp beam merge (beams above
+    256) are other routes to the same sorted beam: on data without distance ties the search must return
+    exactly what the single-warp network returns; with ties only ids of equal distances may differ."""
+    base, queries, P = pipe
+    n = base.shape[0]
+    graph = np.full((n, degree), INVALID, np.uint32)
+    graph[:, :16] = P["graph"]
+    rng = np.random.default_rng(1)
+    for r in range(n):
+        have = set(P["graph"][r][P["graph"][r] != INVALID].tolist()) | {r}
+        extra = [int(x) for x in rng.permutation(n)[:degree] if int(x) not in have][:degree - 16]
+        graph[r, 16:16 + len(extra)] = extra
+    sp = oracle.SearchParams.derive(beam, degree, top_k=10)
+    try:
+        oracle.set_two_warps(False)
+        ids1, d1, c1 = oracle.search(base, graph, P["centroids"], P["orig_sp"], queries[:60], sp, want_counters=True)
+    finally:
+        oracle.set_two_warps(True)
+    ids2, d2, c2 = oracle.search(base, graph, P["centroids"], P["orig_sp"], queries[:60], sp, want_counters=True)
+    assert np.array_equal(d1, d2) and np.array_equal(ids1, ids2) and np.array_equal(c1, c2)
+    gt = oracle.bruteforce_knn(base, queries[:60], 10, want_dists=False)
+    assert oracle.recall(ids2, gt, 10) > 0.97
