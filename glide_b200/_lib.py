@@ -93,6 +93,9 @@ SIGNATURES = {
     "glide_large_make_resident": (i32, [vp, vp, u32, C.c_size_t, P(u32)]),
     "glide_large_search": (i32, [vp, vp, u32, vp, u32, u32, f32, P(SearchParamsC), vp, u32, vp, vp]),
     "glide_large_last_stats": (None, [vp, P(C.c_double)]),
+    "glide_large_merge": (i32, [vp, vp, u32, f32, u32, P(SearchParamsC), P(C.c_double)]),
+    "glide_large_search_merged": (i32, [vp, vp, u32, vp, u32, P(SearchParamsC), vp, vp]),
+    "glide_large_merged_graph": (i32, [vp, vp]),
     "glide_merge_results": (i32, [vp, vp, vp, u32, u32, u32, vp, vp]),
     "glide_malloc": (i32, [vp, C.c_size_t, P(vp)]),
     "glide_memcpy_h2d": (i32, [vp, vp, vp, C.c_size_t]),

@@ -130,6 +130,83 @@ __global__ void __launch_bounds__(128) merge_results_kernel(const uint32_t *__re
     }
 }
 
+// ---- merged index ------------------------------------------------------------------------------
+__global__ void iota_kernel(uint32_t *out, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = i;
+}
+
+// partition-local ids -> reorder ids
+__global__ void globalise_kernel(const uint32_t *__restrict__ local, size_t entries, uint32_t offset, uint32_t *__restrict__ out) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= entries) return;
+    const uint32_t v = local[i];
+    out[i] = v == 0xffffffffu ? v : v + offset;
+}
+
+// A data point's list of partitions within the boundary factor, without the partition it lives in
+// (row r of the chunk is reorder id first_row + r; lists end at the first 0xffffffff).
+__global__ void drop_own_kernel(uint32_t *routes, uint32_t rows, uint32_t S, uint32_t first_row, const uint32_t *__restrict__ seg_start) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const uint32_t id = first_row + r;
+    uint32_t lo = 0, hi = S;                       // last partition whose start is <= id
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (seg_start[mid] <= id) lo = mid; else hi = mid;
+    }
+    uint32_t *list = routes + (size_t) r * S;
+    uint32_t kept = 0;
+    for (uint32_t i = 0; i < S; i++) {
+        const uint32_t s = list[i];
+        if (s == 0xffffffffu) break;
+        if (s != lo) list[kept++] = s;
+    }
+    for (uint32_t i = kept; i < S && list[i] != 0xffffffffu; i++) list[i] = 0xffffffffu;
+}
+
+// Links into a row: every link id (nearest first, the list ends at 0xffffffff) that the row does not
+// hold yet goes into the row's first hole, or, when there is none, over the last entry that is not
+// itself a link of this pass (rows are in pick order, so the tail holds the least wanted edges).
+__global__ void link_merge_kernel(uint32_t *graph_rows, const uint32_t *__restrict__ links, uint32_t rows, uint32_t degree,
+                                  uint32_t link_count, uint32_t *rows_with_links) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    uint32_t *row = graph_rows + (size_t) r * degree;
+    const uint32_t *mine = links + (size_t) r * link_count;
+    uint32_t placed[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // positions written in this pass (degree <= 256)
+    uint32_t tail = degree, any = 0;
+    for (uint32_t l = 0; l < link_count; l++) {
+        const uint32_t id = mine[l];
+        if (id == 0xffffffffu) break;
+        bool have = false;
+        uint32_t hole = degree;
+        for (uint32_t i = 0; i < degree; i++) {
+            const uint32_t e = row[i];
+            if (e == id) { have = true; break; }
+            if (e == 0xffffffffu && hole == degree) hole = i;
+        }
+        if (have) continue;
+        uint32_t pos = hole;
+        if (pos == degree) {
+            while (tail > 0 && ((placed[(tail - 1) >> 5] >> ((tail - 1) & 31u)) & 1u)) tail--;
+            if (tail == 0) break;
+            pos = --tail;
+        }
+        row[pos] = id;
+        placed[pos >> 5] |= 1u << (pos & 31u);
+        any = 1;
+    }
+    if (any) atomicAdd(rows_with_links, 1u);
+}
+
+__global__ void map_ids_kernel(uint32_t *ids, const uint32_t *__restrict__ map, size_t count) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const uint32_t v = ids[i];
+    if (v != 0xffffffffu) ids[i] = map[v];
+}
+
 struct Slot {   // one partition's worth of device memory
     void *raw = nullptr;        // uint8 rows as uploaded (only for uint8 sets)
     float *rows = nullptr;      // fp32 rows the kernels read
@@ -160,6 +237,14 @@ struct glide_large {
     uint32_t *d_routed = nullptr;   // S counters
     uint32_t *d_routes = nullptr;   // Q x S
     size_t routes_capacity = 0;
+    // merged index (glide_large_merge): every partition in one piece of device memory, one graph over
+    // reorder ids with links across partition borders
+    float *arena_rows = nullptr;        // n x dim
+    uint32_t *merged_graph = nullptr;   // n x degree, reorder ids
+    uint32_t *arena_map = nullptr;      // n: reorder id -> original id
+    uint32_t *d_gid = nullptr;          // n: 0, 1, 2, ... (the id map of the link search: results in reorder ids)
+    uint32_t *d_start_global = nullptr; // S: every partition's start point as a reorder id
+    uint32_t *d_seg_start = nullptr;    // S
     double last_h2d_bytes = 0, last_h2d_seconds = 0;
     float last_stage_seconds[4] = {0, 0, 0, 0};   // kNN, build, reverse, refine (kernel time)
     uint32_t last_uploaded_partitions = 0, last_searched_partitions = 0;
@@ -303,6 +388,8 @@ void glide_large_destroy(glide_large *L) {
     if (L->d_routed) cudaFree(L->d_routed);
     if (L->d_parts) cudaFree(L->d_parts);
     if (L->d_routes) cudaFree(L->d_routes);
+    cudaFree(L->arena_rows); cudaFree(L->merged_graph); cudaFree(L->arena_map); cudaFree(L->d_gid);
+    cudaFree(L->d_start_global); cudaFree(L->d_seg_start);
     if (L->up) cudaStreamDestroy(L->up);
     if (L->down) cudaStreamDestroy(L->down);
     delete L;
@@ -616,6 +703,160 @@ int glide_large_search(glide_large *L, const float *d_queries, uint32_t q, const
     cudaEventDestroy(up_begin);
     cudaEventDestroy(up_end);
     ctx->last_ms = (L->last_stage_seconds[0] + L->last_stage_seconds[1]) * 1e3f;
+    return GLIDE_OK;
+}
+
+// ---- merged index ------------------------------------------------------------------------------
+// The reference declares GLIDE_large::build_with_merge (glide_large.cuh:96) and defines it nowhere;
+// what follows is this library's own reading of "one graph over the whole set instead of a search
+// per routed partition", made of the pieces the rest of the large path already has:
+//   * every partition in one piece of device memory (needs all of them resident), its subgraph
+//     rewritten from partition-local ids to reorder ids;
+//   * links: a point whose list of partitions within boundary_factor of its nearest holds other
+//     partitions than its own (select_segment_kernel's rule, the data points as queries) is searched
+//     for in those partitions (the routed multi-partition search, results as reorder ids) and its
+//     link_count nearest finds go into its row (link_merge_kernel);
+//   * reverse edges over the whole graph, so that the neighbouring partition points back;
+//   * search: the small path's kernel on that graph, entered at the nearest centroid's start point.
+int glide_large_merge(glide_large *L, const float *d_centroids, uint32_t centroid_num, float boundary_factor, uint32_t link_count,
+                      const glide_search_params *p_link, double *stats) {
+    if (!L) return GLIDE_ERR_BAD_ARG;
+    glide_ctx *ctx = L->ctx;
+    const uint32_t S = (uint32_t) L->seg_len.size();
+    if (!d_centroids || !p_link || centroid_num != S) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_merge: one centroid per partition expected");
+    if (link_count < 1 || link_count > 32 || link_count >= L->degree || p_link->top_k != link_count)
+        return fail(ctx, GLIDE_ERR_BAD_ARG, "large_merge: link_count must be in [1, 32], below the degree, and equal p_link->top_k");
+    if (p_link->beam < 32 || p_link->beam % 32 || p_link->beam > 512 || p_link->top_k > p_link->beam)
+        return fail(ctx, GLIDE_ERR_BAD_ARG, "large_merge: bad search parameters");
+    uint64_t n64 = 0;
+    for (uint32_t s = 0; s < S; s++) {
+        if (L->seg_len[s] && !L->resident[s].rows) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_merge: every partition must be resident (glide_large_make_resident)");
+        if (L->seg_start[s] != n64) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_merge: partitions must tile the rows in order");
+        n64 += L->seg_len[s];
+    }
+    if (n64 == 0 || n64 >= 0xffffffffull) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_merge: empty or too large");
+    const uint32_t n = (uint32_t) n64, dim = L->dim, degree = L->degree;
+    LG_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->stream;
+    if (!L->arena_rows) {
+        LG_CUDA(ctx, cudaMalloc(&L->arena_rows, (size_t) n * dim * 4));
+        LG_CUDA(ctx, cudaMalloc(&L->merged_graph, (size_t) n * degree * 4));
+        LG_CUDA(ctx, cudaMalloc(&L->arena_map, (size_t) n * 4));
+        LG_CUDA(ctx, cudaMalloc(&L->d_gid, (size_t) n * 4));
+        LG_CUDA(ctx, cudaMalloc(&L->d_start_global, (size_t) S * 4));
+        LG_CUDA(ctx, cudaMalloc(&L->d_seg_start, (size_t) S * 4));
+    }
+    std::vector<uint32_t> start_global(S);
+    for (uint32_t s = 0; s < S; s++) {
+        start_global[s] = L->seg_start[s] + L->start_points[s];
+        const uint32_t len = L->seg_len[s];
+        if (len == 0) continue;
+        const Slot &r = L->resident[s];
+        const size_t lo = L->seg_start[s];
+        LG_CUDA(ctx, cudaMemcpyAsync(L->arena_rows + lo * dim, r.rows, (size_t) len * dim * 4, cudaMemcpyDeviceToDevice, st));
+        LG_CUDA(ctx, cudaMemcpyAsync(L->arena_map + lo, r.map, (size_t) len * 4, cudaMemcpyDeviceToDevice, st));
+        const size_t entries = (size_t) len * degree;
+        globalise_kernel<<<(unsigned) ((entries + 255) / 256), 256, 0, st>>>(r.graph, entries, (uint32_t) lo, L->merged_graph + lo * degree);
+    }
+    LG_CUDA(ctx, cudaGetLastError());
+    iota_kernel<<<(n + 255) / 256, 256, 0, st>>>(L->d_gid, n);
+    LG_CUDA(ctx, cudaMemcpyAsync(L->d_start_global, start_global.data(), (size_t) S * 4, cudaMemcpyHostToDevice, st));
+    LG_CUDA(ctx, cudaMemcpyAsync(L->d_seg_start, L->seg_start.data(), (size_t) S * 4, cudaMemcpyHostToDevice, st));
+    // partition table of the link search: rows and local subgraph as they are resident, ids out as reorder ids
+    std::vector<glide::PartitionRef> refs(S, glide::PartitionRef{nullptr, nullptr, nullptr, 0, 0});
+    for (uint32_t s = 0; s < S; s++) {
+        if (L->seg_len[s] == 0) continue;
+        const Slot &r = L->resident[s];
+        refs[s] = glide::PartitionRef{r.rows, r.graph, L->d_gid + L->seg_start[s], L->start_points[s], L->seg_len[s]};
+    }
+    LG_CUDA(ctx, cudaMemcpyAsync(L->d_parts, refs.data(), (size_t) S * sizeof(glide::PartitionRef), cudaMemcpyHostToDevice, st));
+    LG_CUDA(ctx, cudaStreamSynchronize(st));   // start_global and refs are local vectors
+    // links, a chunk of points at a time
+    const uint32_t chunk = 1u << 18;
+    const uint32_t rows_cap = n < chunk ? n : chunk;
+    if ((size_t) rows_cap * S > L->routes_capacity) {
+        if (L->d_routes) cudaFree(L->d_routes);
+        L->d_routes = nullptr;
+        LG_CUDA(ctx, cudaMalloc(&L->d_routes, (size_t) rows_cap * S * 4));
+        L->routes_capacity = (size_t) rows_cap * S;
+    }
+    uint32_t *d_links = nullptr, *d_count = nullptr;
+    float *d_link_d = nullptr;
+    LG_CUDA(ctx, cudaMalloc(&d_links, (size_t) rows_cap * link_count * 4));
+    LG_CUDA(ctx, cudaMalloc(&d_link_d, (size_t) rows_cap * link_count * 4));
+    LG_CUDA(ctx, cudaMalloc(&d_count, 4));
+    LG_CUDA(ctx, cudaMemsetAsync(d_count, 0, 4, st));
+    std::vector<float> far((size_t) rows_cap * link_count, 3.402823466e+38f);
+    cudaEvent_t e0, e1, e2;
+    cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
+    cudaEventRecord(e0, st);
+    int rc = GLIDE_OK;
+    for (uint32_t lo = 0; lo < n && rc == GLIDE_OK; lo += chunk) {
+        const uint32_t cnt = n - lo < chunk ? n - lo : chunk;
+        const float *d_points = L->arena_rows + (size_t) lo * dim;
+        rc = glide_select_segments(ctx, d_points, cnt, dim, d_centroids, S, 1, boundary_factor, L->metric, L->d_routes);
+        if (rc) break;
+        drop_own_kernel<<<(cnt + 255) / 256, 256, 0, st>>>(L->d_routes, cnt, S, lo, L->d_seg_start);
+        cudaMemsetAsync(d_links, 0xff, (size_t) cnt * link_count * 4, st);
+        cudaMemcpyAsync(d_link_d, far.data(), (size_t) cnt * link_count * 4, cudaMemcpyHostToDevice, st);
+        glide::SearchArgs a{};
+        a.degree = degree; a.dim = dim; a.queries = d_points; a.Q = cnt; a.top_k = link_count; a.metric = L->metric;
+        a.p = glide::BeamParamsHost{p_link->beam, p_link->max_iterations, p_link->min_iterations, p_link->hash_bit, p_link->hash_reset_interval};
+        a.C = 1; a.out_ids = d_links; a.out_dists = d_link_d;
+        a.segment_ids = L->d_routes; a.segment_num = S; a.parts = L->d_parts;
+        a.ticket = ctx->ticket;
+        cudaError_t ce = glide::launch_search(a, st);
+        if (ce == cudaSuccess) {
+            link_merge_kernel<<<(cnt + 255) / 256, 256, 0, st>>>(L->merged_graph + (size_t) lo * degree, d_links, cnt, degree, link_count, d_count);
+            ce = cudaGetLastError();
+        }
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+        if (ce != cudaSuccess) rc = fail(ctx, GLIDE_ERR_CUDA, "large_merge: %s", cudaGetErrorString(ce));
+    }
+    cudaEventRecord(e1, st);
+    uint32_t with_links = 0;
+    if (rc == GLIDE_OK && cudaMemcpy(&with_links, d_count, 4, cudaMemcpyDeviceToHost) != cudaSuccess) rc = fail(ctx, GLIDE_ERR_CUDA, "large_merge: copy failed");
+    cudaFree(d_links); cudaFree(d_link_d); cudaFree(d_count);
+    if (rc == GLIDE_OK) rc = glide_reverse_graph(ctx, L->merged_graph, n, degree);
+    cudaEventRecord(e2, st);
+    cudaEventSynchronize(e2);
+    float ms_links = 0, ms_rev = 0;
+    cudaEventElapsedTime(&ms_links, e0, e1);
+    cudaEventElapsedTime(&ms_rev, e1, e2);
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    if (stats) { stats[0] = ms_links / 1e3; stats[1] = ms_rev / 1e3; stats[2] = with_links; }
+    return rc;
+}
+
+// One beam search per query over the merged graph, entered at the nearest centroid's start point
+// (glide_search on the arena); ids come back as original ids.
+int glide_large_search_merged(glide_large *L, const float *d_queries, uint32_t q, const float *d_centroids, uint32_t centroid_num,
+                              const glide_search_params *p, uint32_t *d_out_ids, float *d_out_dists) {
+    if (!L) return GLIDE_ERR_BAD_ARG;
+    glide_ctx *ctx = L->ctx;
+    if (!L->merged_graph) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_search_merged: no merged index (glide_large_merge)");
+    const uint32_t S = (uint32_t) L->seg_len.size();
+    if (centroid_num != S) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_search_merged: one centroid per partition expected");
+    const uint32_t n = L->seg_start[S - 1] + L->seg_len[S - 1];
+    int rc = glide_search(ctx, L->arena_rows, n, L->dim, L->merged_graph, L->degree, d_centroids, S, L->d_start_global, d_queries, q, p,
+                          L->metric, d_out_ids, d_out_dists);
+    if (rc || q == 0) return rc;
+    const size_t count = (size_t) q * p->top_k;
+    map_ids_kernel<<<(unsigned) ((count + 255) / 256), 256, 0, ctx->stream>>>(d_out_ids, L->arena_map, count);
+    LG_CUDA(ctx, cudaGetLastError());
+    LG_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return GLIDE_OK;
+}
+
+// The merged graph (rows x degree, reorder ids) into host memory, for files and tests.
+int glide_large_merged_graph(const glide_large *L, uint32_t *h_out) {
+    if (!L || !h_out) return GLIDE_ERR_BAD_ARG;
+    glide_ctx *ctx = L->ctx;
+    if (!L->merged_graph) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_merged_graph: no merged index (glide_large_merge)");
+    const uint32_t S = (uint32_t) L->seg_len.size();
+    const size_t n = (size_t) L->seg_start[S - 1] + L->seg_len[S - 1];
+    LG_CUDA(ctx, cudaSetDevice(ctx->device));
+    LG_CUDA(ctx, cudaMemcpy(h_out, L->merged_graph, n * L->degree * 4, cudaMemcpyDeviceToHost));
     return GLIDE_OK;
 }
 

@@ -301,6 +301,43 @@ class GLIDE_large:
                           partitions_uploaded=int(st[6]), partitions_searched=int(st[7]))
         return d_ids, d_d, st[0] + st[1]
 
+    def build_with_merge(self, boundary_factor: float, link_count: int = 8, link_beam: int = 32):
+        """The merged index (declared in the reference, glide_large.cuh:96, and defined nowhere: this
+        library's own design, see `glide_large_merge`): one graph over reorder ids with links across
+        partition borders, searched with one beam search per query. Every partition must be resident
+        (`make_resident`). Returns dict(link_seconds, reverse_seconds, rows_with_links)."""
+        import ctypes as C
+        p_link = SearchParameter(top_k=link_count, beam=link_beam).derive(self.graph_degree())
+        pc = api._params_c(p_link)
+        stats = (C.c_double * 3)()
+        self.ctx.sync_inputs()
+        self.ctx.check(self.ctx.lib.glide_large_merge(self.handle, self.d_centroids.data_ptr(), self.centroids_num(),
+                                                      float(boundary_factor), int(link_count), C.byref(pc), stats))
+        return dict(link_seconds=stats[0], reverse_seconds=stats[1], rows_with_links=int(stats[2]))
+
+    def merged_graph(self) -> np.ndarray:
+        """The merged graph in reorder ids (rows x graph_degree)."""
+        g = np.empty((self.h_data.shape[0], self.graph_degree()), np.uint32)
+        self.ctx.check(self.ctx.lib.glide_large_merged_graph(self.handle, g.ctypes.data))
+        return g
+
+    def search_merged_device(self, param: SearchParameter, d_query: torch.Tensor):
+        """One beam search per query over the merged graph; (ids tensor of original ids, dists, kernel seconds)."""
+        import ctypes as C
+        ctx = self.ctx
+        q = d_query.shape[0]
+        d_ids = api._u32_tensor(ctx, (q, param.top_k))
+        d_d = ctx.empty((q, param.top_k), torch.float32)
+        pc = api._params_c(param)
+        ctx.sync_inputs()
+        ctx.check(ctx.lib.glide_large_search_merged(self.handle, d_query.data_ptr(), q, self.d_centroids.data_ptr(),
+                                                    self.centroids_num(), C.byref(pc), d_ids.data_ptr(), d_d.data_ptr()))
+        return d_ids, d_d, ctx.last_kernel_seconds
+
+    def search_merged(self, param: SearchParameter, d_query: torch.Tensor):
+        d_ids, d_d, seconds = self.search_merged_device(param, d_query)
+        return api.to_u32(d_ids), d_d.cpu().numpy(), seconds
+
     def search(self, param: SearchParameter, min_segment_num: int, boundary_factor: float, d_query: torch.Tensor,
                partitions=None):
         """glide_large_impl.cuh:355-507. Returns (ids uint32 [Q,k] original ids, dists [Q,k], kernel seconds)."""

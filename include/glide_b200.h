@@ -362,6 +362,22 @@ int glide_large_search(glide_large *index, const float *d_queries, uint32_t q, c
                        uint32_t centroid_num, uint32_t min_segment_num, float boundary_factor,
                        const glide_search_params *p, const uint32_t *partition_ids, uint32_t partition_count,
                        uint32_t *d_final_ids, float *d_final_dists);
+/* Merged index. GLIDE_large::build_with_merge is declared in the reference (glide_large.cuh:96) and
+ * defined nowhere, so this is the library's own design, built from the large path's pieces: all
+ * partitions in one piece of device memory (they must be resident), their subgraphs rewritten to
+ * reorder ids, and links across partition borders: a point whose partitions within boundary_factor
+ * of its nearest centroid (select_segment_kernel's rule) include others than its own is searched for
+ * in those (p_link; p_link->top_k == link_count) and its link_count nearest finds enter its row
+ * (holes first, then over the row's tail); reverse edges follow. stats (may be null): [0] seconds of
+ * the link stage, [1] of the reverse edges, [2] rows that received links. */
+int glide_large_merge(glide_large *index, const float *d_centroids, uint32_t centroid_num, float boundary_factor,
+                      uint32_t link_count, const glide_search_params *p_link, double *stats);
+/* One beam search per query over the merged graph (glide_search on it), entered at the nearest
+ * centroid's start point; ids are original ids. */
+int glide_large_search_merged(glide_large *index, const float *d_queries, uint32_t q, const float *d_centroids,
+                              uint32_t centroid_num, const glide_search_params *p, uint32_t *d_out_ids, float *d_out_dists);
+/* The merged graph, rows x graph_degree reorder ids, into host memory. */
+int glide_large_merged_graph(const glide_large *index, uint32_t *h_out);
 /* Statistics of the last glide_large_build / glide_large_search: out[0..3] kernel seconds (build: kNN,
  * subgraph build, reverse edges, refine; search: routing, per-partition search, 0, 0), out[4] bytes
  * uploaded, out[5] seconds from the first to the last upload on the upload stream, out[6] partitions

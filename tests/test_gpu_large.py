@@ -161,6 +161,78 @@ def test_preprocess_from_a_file_equals_preprocess_of_the_loaded_array(gpu_ctx, b
         large.load_rows(gpu_ctx, str(tmp_path / "missing.bin"), dtype)
 
 
+def test_merged_index_equals_its_composition_from_oracle_pieces(gpu_ctx, built):
+    """The merged index is put together from pieces that each have an oracle: routing of the data
+    points (select_segments), the routed multi-partition search for the links (search_on_sub and its
+    running merge), the link rule (restated here), reverse edges, and the small path's search on the
+    result. Graph and search results must equal that composition bit for bit."""
+    pre, index, queries = built["pre"], built["index"], built["queries"]
+    rows, cent = pre["h_reorder_data"], pre["h_centroids"]
+    seg_start, seg_len = pre["h_segment_start"], pre["h_segment_length"]
+    n, deg, C, links, factor = rows.shape[0], 24, 6, 6, 1.3
+    assert index.make_resident(10 ** 9) == C
+    stats = index.build_with_merge(factor, link_count=links, link_beam=32)
+    got_graph = index.merged_graph()
+    # -- the composition --
+    local, starts = index.graph_view(), index.start_point_view()
+    owner = np.repeat(np.arange(C, dtype=np.uint32), seg_len)
+    want = local.copy()
+    for s in range(C):
+        lo, ln = int(seg_start[s]), int(seg_len[s])
+        blk = want[lo:lo + ln]
+        blk[blk != INVALID] += lo
+    routes = oracle.select_segments(rows, cent, 1, factor)
+    for r in range(n):                                   # the point's own partition leaves its list
+        keep = [int(x) for x in routes[r] if x != INVALID and x != owner[r]]
+        routes[r] = INVALID
+        routes[r, :len(keep)] = keep
+    p_link = SearchParameter(top_k=links, beam=32).derive(deg)
+    o = oracle.SearchParams(p_link.beam, p_link.max_iterations, 0, p_link.hash_bit, p_link.hash_reset_interval, links)
+    link_ids = np.full((n, links), INVALID, np.uint32)
+    link_d = np.full((n, links), np.finfo(np.float32).max, np.float32)
+    gid = np.arange(n, dtype=np.uint32)
+    for s in range(C):
+        lo, ln = int(seg_start[s]), int(seg_len[s])
+        oracle.search_on_sub(rows[lo:lo + ln], local[lo:lo + ln], gid[lo:lo + ln], int(starts[s]), rows, routes, s, o, link_ids, link_d)
+    with_links = 0
+    for r in range(n):
+        row, placed, tail, any_ = want[r], set(), deg, False
+        for lid in link_ids[r]:
+            if lid == INVALID:
+                break
+            if (row == lid).any():
+                continue
+            holes = np.nonzero(row == INVALID)[0]
+            if holes.size:
+                pos = int(holes[0])
+            else:
+                while tail > 0 and (tail - 1) in placed:
+                    tail -= 1
+                if tail == 0:
+                    break
+                tail -= 1
+                pos = tail
+            row[pos] = lid
+            placed.add(pos)
+            any_ = True
+        with_links += any_
+    assert with_links == stats["rows_with_links"] and 0.02 * n < with_links < n
+    oracle.reverse_graph(want)
+    assert np.array_equal(got_graph, want)
+    cross = owner[want[want != INVALID]] != np.repeat(owner, (want != INVALID).sum(axis=1))
+    assert cross.mean() > 0.005                          # edges across partition borders exist
+    # -- one search per query over the merged graph --
+    sp = SearchParameter(top_k=10, beam=64).derive(deg)
+    so = oracle.SearchParams(sp.beam, sp.max_iterations, 0, sp.hash_bit, sp.hash_reset_interval, 10)
+    start_global = (seg_start + starts).astype(np.uint32)
+    want_ids, want_d = oracle.search(rows, want, cent, start_global, queries, so)
+    valid = want_ids != INVALID
+    want_ids[valid] = pre["h_map"][want_ids[valid]]
+    d_q = torch.from_numpy(queries).to(gpu_ctx.torch_device)
+    ids, dists, seconds = index.search_merged(sp, d_q)
+    assert np.array_equal(ids, want_ids) and np.array_equal(dists, want_d) and seconds > 0
+
+
 def test_bad_arguments_are_refused(gpu_ctx, built):
     pre = built["pre"]
     import ctypes as C
