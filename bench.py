@@ -65,6 +65,7 @@ def parse_args():
     ap.add_argument("--rows", type=int, default=0, help="use only the first ROWS base rows (debugging; marks the run reduced)")
     ap.add_argument("--queries", type=int, default=0)
     ap.add_argument("--partitions", type=int, default=0, help="override the partition count")
+    ap.add_argument("--merged", action="store_true", help="large path, one GPU: also build and search the merged index")
     ap.add_argument("--loader-dir", default="/dev/shm", help="--config loader: where the synthetic matrix file is written")
     ap.add_argument("--rows-u8", action="store_true", help="large path: keep integer-valued rows as uint8 in host memory")
     ap.add_argument("--route-min", type=int, default=4, help="large path: partitions every query visits at least")
@@ -852,6 +853,33 @@ def run_large(args):
     if world > 1:
         dist.all_reduce(ts, op=dist.ReduceOp.MAX)
     kmax, wmax = float(ts[0]), float(ts[1])
+    # ---- the merged index on the same build (one GPU, sets whose two copies fit): links across partition
+    # borders, then ONE beam search per query instead of one per routed partition ----
+    merged = None
+    if world == 1 and args.merged and resident == len(my_parts) and (n * dim * 4 * 2 + n * degree * 4 * 5) < 120e9:
+        t_m = time.perf_counter()
+        mstats = index.build_with_merge(args.route_factor, link_count=8, link_beam=32)
+        torch.cuda.synchronize(dev)
+        merge_wall = time.perf_counter() - t_m
+        mchosen, mcurve = None, []
+        for mbeam in [b for b in BEAM_LADDER if b <= args.max_beam]:
+            msp = pipeline.derive_search_params(mbeam, degree, TOP_K)
+            d_i, _, ksec = index.search_merged_device(msp, d_queries)
+            rec = api.calculate_recall(api.to_u32(d_i), gt, TOP_K)
+            mcurve.append({"beam": mbeam, "recall": round(rec, 4), "qps": round(Q / ksec, 1)})
+            mchosen = (mbeam, msp, rec)
+            if rec >= TARGET_RECALL:
+                break
+        mbeam, msp, mrec = mchosen
+        for _ in range(args.warmup):
+            index.search_merged_device(msp, d_queries)
+        msum = 0.0
+        for _ in range(args.steps):
+            msum += index.search_merged_device(msp, d_queries)[2]
+        merged = {"merge_wall_seconds": round(merge_wall, 3), "link_seconds": round(mstats["link_seconds"], 4),
+                  "reverse_seconds": round(mstats["reverse_seconds"], 4), "rows_with_links": mstats["rows_with_links"],
+                  "link_rule": f"partitions within {args.route_factor} of the nearest centroid, 8 links per point, beam 32",
+                  "beam": mbeam, "recall_at_10": round(mrec, 4), "qps": Q * args.steps / msum, "recall_curve": mcurve}
     if rank == 0:
         line = {
             "metric": METRIC_NAME, "value": Q * args.steps / kmax, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
@@ -876,6 +904,8 @@ def run_large(args):
                     "note": "wall clock of the public call on device-resident queries, result ids read back to the host"},
             "gpu_launches": None, "clocks": clocks,
         }
+        if merged is not None:
+            line["merged_index"] = merged
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
