@@ -251,6 +251,49 @@ public:
         d_dists.download(result_dists.data_handle(), result_dists.size());
     }
 
+    // build_with_merge is declared in the reference (glide_large.cuh:96) and defined nowhere; here:
+    // the ordinary build without refine, every partition kept in device memory, then
+    // glide_large_merge (links across partition borders within boundary_factor, reverse edges over
+    // the whole graph). search_merged then runs one beam search per query on the merged graph.
+    void build_with_merge(const IndexParameter &build_param, const SearchParameter &search_param_knn,
+                          const HostMatrix<int> &h_knn_graph, const std::string &result_file, float boundary_factor = 1.2f,
+                          uint32_t link_count = 8, uint64_t seed = 0) {
+        SearchParameter no_refine;
+        no_refine.beam = 0;
+        build(build_param, search_param_knn, no_refine, h_knn_graph, "", seed);
+        std::vector<uint32_t> parts(seg_start_.size());
+        for (size_t i = 0; i < parts.size(); i++) parts[i] = (uint32_t) i;
+        glide_large *h = handle();
+        uint32_t kept = 0;
+        ctx_.check(glide_large_make_resident(h, parts.data(), (uint32_t) parts.size(), ~(size_t) 0, &kept));
+        SearchParameter link;
+        link.top_k = link_count;
+        link.beam = 32;
+        derive_search_params(link, degree_);
+        const glide_search_params pl = link.c();
+        DeviceBuffer<float> d_centroids(ctx_, centroids_.data_handle(), centroids_.size());
+        double st[3] = {0, 0, 0};
+        ctx_.check(glide_large_merge(h, d_centroids.data_handle(), centroids_.rows, boundary_factor, link_count, &pl, st));
+        std::printf("merge time: %g s (%u rows with links)\n", st[0] + st[1], (unsigned) st[2]);
+        if (!result_file.empty()) append_result(result_file, stream_text(st[0] + st[1]) + ",");
+    }
+
+    void search_merged(const SearchParameter &param, const HostMatrix<float> &h_query, HostMatrix<uint32_t> &result_ids,
+                       HostMatrix<float> &result_dists) {
+        const glide_search_params p = param.c();
+        const uint32_t q = h_query.rows;
+        DeviceBuffer<float> d_query(ctx_, h_query.data_handle(), h_query.size());
+        DeviceBuffer<float> d_centroids(ctx_, centroids_.data_handle(), centroids_.size());
+        DeviceBuffer<uint32_t> d_ids(ctx_, (size_t) q * param.top_k);
+        DeviceBuffer<float> d_dists(ctx_, (size_t) q * param.top_k);
+        ctx_.check(glide_large_search_merged(handle(), d_query.data_handle(), q, d_centroids.data_handle(), centroids_.rows, &p,
+                                             d_ids.data_handle(), d_dists.data_handle()));
+        result_ids = HostMatrix<uint32_t>(q, param.top_k);
+        result_dists = HostMatrix<float>(q, param.top_k);
+        d_ids.download(result_ids.data_handle(), result_ids.size());
+        d_dists.download(result_dists.data_handle(), result_dists.size());
+    }
+
     ~GLIDE_large() {
         if (large_) {
             glide_large_destroy(large_);
