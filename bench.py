@@ -856,7 +856,8 @@ def run_large(args):
     # ---- the merged index on the same build (one GPU, sets whose two copies fit): links across partition
     # borders, then ONE beam search per query instead of one per routed partition ----
     merged = None
-    if world == 1 and args.merged and resident == len(my_parts) and (n * dim * 4 * 2 + n * degree * 4 * 5) < 120e9:
+    if world == 1 and args.merged and resident == len(my_parts) and (n * dim * 4 * 2 + n * degree * 4 * 3) < 150e9:
+        torch.cuda.empty_cache()   # the arena is allocated by the library, outside torch's pool
         t_m = time.perf_counter()
         mstats = index.build_with_merge(args.route_factor, link_count=8, link_beam=32)
         torch.cuda.synchronize(dev)

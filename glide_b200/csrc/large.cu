@@ -214,6 +214,7 @@ struct Slot {   // one partition's worth of device memory
     uint32_t *map = nullptr;
     int32_t *knn = nullptr;
     cudaEvent_t uploaded = nullptr, computed = nullptr, downloaded = nullptr;
+    bool view = false;          // rows and map point into the merged index's arena and are not this slot's to free
 };
 
 }  // namespace
@@ -256,9 +257,9 @@ namespace {
 
 void free_slot(Slot &s) {
     if (s.raw) cudaFree(s.raw);
-    if (s.rows) cudaFree(s.rows);
+    if (s.rows && !s.view) cudaFree(s.rows);
     if (s.graph) cudaFree(s.graph);
-    if (s.map) cudaFree(s.map);
+    if (s.map && !s.view) cudaFree(s.map);
     if (s.knn) cudaFree(s.knn);
     if (s.uploaded) cudaEventDestroy(s.uploaded);
     if (s.computed) cudaEventDestroy(s.computed);
@@ -753,8 +754,10 @@ int glide_large_merge(glide_large *L, const float *d_centroids, uint32_t centroi
         if (len == 0) continue;
         const Slot &r = L->resident[s];
         const size_t lo = L->seg_start[s];
-        LG_CUDA(ctx, cudaMemcpyAsync(L->arena_rows + lo * dim, r.rows, (size_t) len * dim * 4, cudaMemcpyDeviceToDevice, st));
-        LG_CUDA(ctx, cudaMemcpyAsync(L->arena_map + lo, r.map, (size_t) len * 4, cudaMemcpyDeviceToDevice, st));
+        if (!r.view) {
+            LG_CUDA(ctx, cudaMemcpyAsync(L->arena_rows + lo * dim, r.rows, (size_t) len * dim * 4, cudaMemcpyDeviceToDevice, st));
+            LG_CUDA(ctx, cudaMemcpyAsync(L->arena_map + lo, r.map, (size_t) len * 4, cudaMemcpyDeviceToDevice, st));
+        }
         const size_t entries = (size_t) len * degree;
         globalise_kernel<<<(unsigned) ((entries + 255) / 256), 256, 0, st>>>(r.graph, entries, (uint32_t) lo, L->merged_graph + lo * degree);
     }
@@ -762,6 +765,17 @@ int glide_large_merge(glide_large *L, const float *d_centroids, uint32_t centroi
     iota_kernel<<<(n + 255) / 256, 256, 0, st>>>(L->d_gid, n);
     LG_CUDA(ctx, cudaMemcpyAsync(L->d_start_global, start_global.data(), (size_t) S * 4, cudaMemcpyHostToDevice, st));
     LG_CUDA(ctx, cudaMemcpyAsync(L->d_seg_start, L->seg_start.data(), (size_t) S * 4, cudaMemcpyHostToDevice, st));
+    // from here on the arena is the resident copy of rows and id maps: the per-partition copies go
+    LG_CUDA(ctx, cudaStreamSynchronize(st));
+    for (uint32_t s = 0; s < S; s++) {
+        Slot &r = L->resident[s];
+        if (L->seg_len[s] == 0 || r.view) continue;
+        cudaFree(r.rows);
+        cudaFree(r.map);
+        r.rows = L->arena_rows + (size_t) L->seg_start[s] * dim;
+        r.map = L->arena_map + L->seg_start[s];
+        r.view = true;
+    }
     // partition table of the link search: rows and local subgraph as they are resident, ids out as reorder ids
     std::vector<glide::PartitionRef> refs(S, glide::PartitionRef{nullptr, nullptr, nullptr, 0, 0});
     for (uint32_t s = 0; s < S; s++) {
