@@ -171,7 +171,14 @@ def test_merged_index_equals_its_composition_from_oracle_pieces(gpu_ctx, built):
     seg_start, seg_len = pre["h_segment_start"], pre["h_segment_length"]
     n, deg, C, links, factor = rows.shape[0], 24, 6, 6, 1.3
     assert index.make_resident(10 ** 9) == C
+    d_q = torch.from_numpy(queries).to(gpu_ctx.torch_device)
+    sp_multi = SearchParameter(top_k=10, beam=64).derive(deg)
+    before = index.search(sp_multi, 2, 1.2, d_q)
     stats = index.build_with_merge(factor, link_count=links, link_beam=32)
+    # the merge turns the arena into the resident copy of rows and id maps: the routed search still works on it
+    after = index.search(sp_multi, 2, 1.2, d_q)
+    assert np.array_equal(before[0], after[0]) and np.array_equal(before[1], after[1])
+    assert index.stats["partitions_uploaded"] == 0
     got_graph = index.merged_graph()
     # -- the composition --
     local, starts = index.graph_view(), index.start_point_view()
@@ -228,7 +235,6 @@ def test_merged_index_equals_its_composition_from_oracle_pieces(gpu_ctx, built):
     want_ids, want_d = oracle.search(rows, want, cent, start_global, queries, so)
     valid = want_ids != INVALID
     want_ids[valid] = pre["h_map"][want_ids[valid]]
-    d_q = torch.from_numpy(queries).to(gpu_ctx.torch_device)
     ids, dists, seconds = index.search_merged(sp, d_q)
     assert np.array_equal(ids, want_ids) and np.array_equal(dists, want_d) and seconds > 0
 
