@@ -837,11 +837,12 @@ def run_large(args):
     beam, sp, recall = chosen
     for _ in range(args.warmup):
         search(sp)
-    if world > 1:
-        dist.barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    if world > 1:
+        dist.barrier()   # after the sampler has started: a late rank 0 would make the others wait inside the first gather
+    torch.cuda.synchronize(dev)
     ksum = wsum = 0.0
     for _ in range(args.steps):
         _, ksec, wall = search(sp)
