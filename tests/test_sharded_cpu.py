@@ -126,3 +126,54 @@ def test_sharded_build_equals_single_process(tmp_path, world):
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert open(tmp_path / f"rank{r}.txt").read() == "ok"
+
+
+# ---- large path: partitions owned by ranks, per-rank top-k lists gathered and merged ----
+def _large_worker(rank, world, port, out_dir):
+    """What bench.py's large path does with more than one rank, over the oracle: every rank searches
+    the partitions it owns for all queries, the result sets are all-gathered in rank order and folded
+    with the reference's merge network; the fold must give the single-process search's distances, and
+    its ids wherever distances do not tie."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import golden_cases
+    import oracle
+    L = golden_cases.large_inputs()
+    q, C, top_k = L["queries"], L["C"], 10
+    Q = q.shape[0]
+    o = oracle.SearchParams.derive(64, golden_cases.LARGE_DEGREE, top_k=top_k)
+    routes = oracle.select_segments(q, L["centroids"], 2, 1.2)
+    INVALID, FAR = 0xFFFFFFFF, np.finfo(np.float32).max
+
+    def search(parts):
+        ids, d = np.full((Q, top_k), INVALID, np.uint32), np.full((Q, top_k), FAR, np.float32)
+        for s in parts:
+            p = L["parts"][s]
+            oracle.search_on_sub(p["rows"], p["graph"], p["map"], p["sp"], q, routes, s, o, ids, d)
+        return ids, d
+
+    lo, hi = sharded.owner_ranges(L["seg_len"][:C], world)[rank]
+    mine_ids, mine_d = search(range(lo, hi))
+    set_ids = torch.zeros((world * Q, top_k), dtype=torch.int32)
+    set_d = torch.zeros((world * Q, top_k), dtype=torch.float32)
+    set_ids[rank * Q:(rank + 1) * Q] = torch.from_numpy(mine_ids.view(np.int32))
+    set_d[rank * Q:(rank + 1) * Q] = torch.from_numpy(mine_d)
+    coll = sharded.TorchCollectives(dist, world, rank)
+    coll.all_gather_v(set_ids, [r * Q for r in range(world)], [Q] * world)
+    coll.all_gather_v(set_d, [r * Q for r in range(world)], [Q] * world)
+    got_ids, got_d = oracle.merge_results(set_ids.numpy().view(np.uint32).reshape(world, Q, top_k),
+                                          set_d.numpy().reshape(world, Q, top_k))
+    want_ids, want_d = search(range(C))
+    same_rows = (np.sort(got_ids, axis=1) == np.sort(want_ids, axis=1)).all(axis=1)
+    ok = np.array_equal(got_d, want_d) and same_rows.mean() > 0.97
+    open(os.path.join(out_dir, f"large{rank}.txt"), "w").write("ok" if ok else f"mismatch {same_rows.mean()}")
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_large_path_owner_search_and_merge_equal_single_process(tmp_path, world):
+    port = 31500 + (os.getpid() % 2000) + world
+    mp.spawn(_large_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / f"large{r}.txt").read() == "ok"
