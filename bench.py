@@ -854,6 +854,55 @@ def run_large(args):
     if world > 1:
         dist.all_reduce(ts, op=dist.ReduceOp.MAX)
     kmax, wmax = float(ts[0]), float(ts[1])
+    # ---- more than one rank: the same search with the QUERIES split over the ranks instead of the
+    # partitions. Every rank receives the partitions the others built (rows as fp32, graph rows, id
+    # maps: NCCL broadcasts into resident buffers), searches all partitions for its slice of the
+    # queries, and the slices are gathered; no merge is needed. ----
+    by_query = None
+    if world > 1 and (n * dim * 4 + n * degree * 4 + n * 4) < 150e9 and resident == len(my_parts):
+        owner_of = np.empty(S, np.int64)
+        for r, (lo_p, hi_p) in enumerate(owners):
+            owner_of[lo_p:hi_p] = r
+        sp_all = torch.from_numpy(index.start_point_view().astype(np.int64)).to(dev)
+        sp_all[torch.from_numpy(owner_of != rank).to(dev)] = 0
+        dist.all_reduce(sp_all)
+        index.set_start_points(sp_all.cpu().numpy().astype(np.uint32))
+        torch.cuda.synchronize(dev)
+        t_r = time.perf_counter()
+        received = index.replicate_partitions(owner_of.tolist(), rank)
+        replicate_wall = time.perf_counter() - t_r
+        q_lo, q_hi = sharded.split_range(Q, world, rank)
+        my_q = d_queries[q_lo:q_hi].contiguous()
+        full_ids = torch.zeros((Q, TOP_K), dtype=torch.int32, device=dev)
+        q_offs = [sharded.split_range(Q, world, r)[0] for r in range(world)]
+        q_cnts = [sharded.split_range(Q, world, r)[1] - sharded.split_range(Q, world, r)[0] for r in range(world)]
+
+        def search_by_query():
+            torch.cuda.synchronize(dev)
+            t1 = time.perf_counter()
+            d_i, _, ksec = index.search_device(sp, args.route_min, args.route_factor, my_q)
+            full_ids[q_lo:q_hi].copy_(d_i)
+            coll.all_gather_v(full_ids, q_offs, q_cnts)
+            coll.sync()
+            torch.cuda.synchronize(dev)
+            return ksec, time.perf_counter() - t1
+
+        for _ in range(max(args.warmup, 1)):
+            search_by_query()
+        rec_q = api.calculate_recall(api.to_u32(full_ids), gt, TOP_K)
+        dist.barrier()
+        kq = wq = 0.0
+        for _ in range(args.steps):
+            ksec, wall = search_by_query()
+            kq += ksec
+            wq += wall
+        tq = torch.tensor([kq, wq, replicate_wall], dtype=torch.float64, device=dev)
+        dist.all_reduce(tq, op=dist.ReduceOp.MAX)
+        by_query = {"recall_at_10": round(rec_q, 4), "kernel_qps": Q * args.steps / float(tq[0]),
+                    "wall_qps_with_gather": Q * args.steps / float(tq[1]),
+                    "replication": {"bytes_received_rank0": received, "wall_seconds": round(float(tq[2]), 3)},
+                    "note": "every rank holds every partition (rows, graph, id map received over NCCL) and searches its "
+                            "slice of the queries; beam as above"}
     # ---- the merged index on the same build (one GPU, sets whose two copies fit): links across partition
     # borders, then ONE beam search per query instead of one per routed partition ----
     merged = None
@@ -908,6 +957,8 @@ def run_large(args):
         }
         if merged is not None:
             line["merged_index"] = merged
+        if by_query is not None:
+            line["search_with_queries_split_over_ranks"] = by_query
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -93,6 +93,7 @@ SIGNATURES = {
     "glide_large_make_resident": (i32, [vp, vp, u32, C.c_size_t, P(u32)]),
     "glide_large_search": (i32, [vp, vp, u32, vp, u32, u32, f32, P(SearchParamsC), vp, u32, vp, vp]),
     "glide_large_last_stats": (None, [vp, P(C.c_double)]),
+    "glide_large_resident_buffers": (i32, [vp, u32, P(vp), P(vp), P(vp)]),
     "glide_large_merge": (i32, [vp, vp, u32, f32, u32, P(SearchParamsC), P(C.c_double)]),
     "glide_large_search_merged": (i32, [vp, vp, u32, vp, u32, P(SearchParamsC), vp, vp]),
     "glide_large_merged_graph": (i32, [vp, vp]),

@@ -562,6 +562,26 @@ int glide_large_make_resident(glide_large *L, const uint32_t *partition_ids, uin
     return GLIDE_OK;
 }
 
+// Device buffers of partition p as a resident partition, allocated here when it is not resident yet
+// and then left for the caller to fill: a rank that searches partitions another rank built receives
+// their rows (fp32), graph rows and id map over NCCL straight into these buffers.
+int glide_large_resident_buffers(glide_large *L, uint32_t p, float **d_rows, uint32_t **d_graph, uint32_t **d_map) {
+    if (!L || !d_rows || !d_graph || !d_map) return GLIDE_ERR_BAD_ARG;
+    glide_ctx *ctx = L->ctx;
+    if (p >= L->seg_len.size()) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_resident_buffers: partition id out of range");
+    LG_CUDA(ctx, cudaSetDevice(ctx->device));
+    Slot &s = L->resident[p];
+    const uint32_t len = L->seg_len[p];
+    if (!s.rows && len) {
+        int rc = alloc_slot(L, s, len, false, 0, false);
+        if (rc) { free_slot(s); return rc; }
+        if (s.raw) { cudaFree(s.raw); s.raw = nullptr; }   // the caller delivers fp32 rows
+        L->resident_bytes += (size_t) len * (L->dim * 4 + L->degree * 4 + 4);
+    }
+    *d_rows = s.rows; *d_graph = s.graph; *d_map = s.map;
+    return GLIDE_OK;
+}
+
 int glide_large_search(glide_large *L, const float *d_queries, uint32_t q, const float *d_centroids, uint32_t centroid_num,
                        uint32_t min_segment_num, float boundary_factor, const glide_search_params *p,
                        const uint32_t *partition_ids, uint32_t partition_count, uint32_t *d_final_ids,

@@ -233,6 +233,10 @@ class GLIDE_large:
         self.ctx.check(self.ctx.lib.glide_large_get_start_points(self.handle, out.ctypes.data))
         return out
 
+    def set_start_points(self, h_start_points) -> None:
+        sp = np.ascontiguousarray(h_start_points, np.uint32)
+        self.ctx.check(self.ctx.lib.glide_large_set_start_points(self.handle, sp.ctypes.data))
+
     def load(self, h_graph, h_start_points):
         np.copyto(self.h_graph, np.ascontiguousarray(h_graph, np.uint32))
         sp = np.ascontiguousarray(h_start_points, np.uint32)
@@ -281,6 +285,33 @@ class GLIDE_large:
         self.ctx.check(self.ctx.lib.glide_large_make_resident(self.handle, parts.ctypes.data, parts.size, int(budget_bytes),
                                                               C.byref(n)))
         return int(n.value)
+
+    def resident_buffers(self, partition: int):
+        """Device addresses (rows fp32, graph rows, id map) of a partition's resident buffers, allocated
+        uninitialised when the partition is not resident yet; see `glide_large_resident_buffers`."""
+        import ctypes as C
+        r, g, m = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        self.ctx.check(self.ctx.lib.glide_large_resident_buffers(self.handle, int(partition), C.byref(r), C.byref(g), C.byref(m)))
+        return r.value or 0, g.value or 0, m.value or 0
+
+    def replicate_partitions(self, owner_of_partition, rank: int) -> int:
+        """Every rank ends up with every partition in device memory: the owner's resident buffers are
+        broadcast over the context's NCCL communicator into buffers allocated here on the other ranks
+        (rows as fp32, graph rows, id map). Own partitions must be resident. Returns the bytes received."""
+        ctx = self.ctx
+        dim, deg = self.h_data.shape[1], self.graph_degree()
+        received = 0
+        for p, owner in enumerate(owner_of_partition):
+            ln = int(self.seg_len[p])
+            if ln == 0:
+                continue
+            rows, graph, idmap = self.resident_buffers(p)
+            for ptr, nbytes in ((rows, ln * dim * 4), (graph, ln * deg * 4), (idmap, ln * 4)):
+                ctx.check(ctx.lib.glide_comm_broadcast(ctx.handle, ptr, nbytes, int(owner)))
+                if owner != rank:
+                    received += nbytes
+        ctx.check(ctx.lib.glide_ctx_synchronize(ctx.handle))
+        return received
 
     def search_device(self, param: SearchParameter, min_segment_num: int, boundary_factor: float, d_query: torch.Tensor,
                       partitions=None):

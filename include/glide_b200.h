@@ -355,6 +355,10 @@ int glide_large_build(glide_large *index, const uint32_t *partition_ids, uint32_
  * query batch (glide_large_impl.cuh:424-438). */
 int glide_large_make_resident(glide_large *index, const uint32_t *partition_ids, uint32_t partition_count,
                               size_t budget_bytes, uint32_t *resident_count);
+/* The device buffers of partition p as a resident partition (rows x dim fp32, rows x graph_degree ids,
+ * rows ids), allocated uninitialised when p is not resident yet: for a rank that receives partitions
+ * another rank built (glide_comm_broadcast into these buffers) and then searches them. */
+int glide_large_resident_buffers(glide_large *index, uint32_t partition, float **d_rows, uint32_t **d_graph, uint32_t **d_map);
 /* GLIDE_large::search, glide_large_impl.cuh:355-507, over the listed partitions (ascending index
  * order): routing (select_segment_kernel), then search_on_sub_kernel per partition that some query
  * of the batch is routed to. d_final_*: q x top_k, overwritten. */
