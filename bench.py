@@ -636,8 +636,8 @@ def run_ours(args):
             dram_gbs = traffic / search_s / 1e9
             roofline.update({"achieved": round(dram_gbs, 1), "frac": round(dram_gbs / peak, 4),
                              "note": "achieved = DRAM bytes of one launch (ncu, see NCU_TRAFFIC) / the kernel's CUDA-event "
-                                     "time in this run; the kernel is bound by instruction issue and the dependent chain "
-                                     "of a query, not by HBM"})
+                                     "time in this run. The data set is read about three times per launch (the partitions "
+                                     "in flight exceed L2); the rest of the time is the dependent chain of a query"})
         else:
             roofline.update({"achieved": round(algo_gbs, 1), "frac": round(algo_gbs / peak, 4),
                              "note": "no ncu DRAM figure for this workload: achieved is the algorithmic figure, which "
