@@ -808,25 +808,40 @@ static int refine_common(glide_ctx *ctx, int mode, const float *d_data, uint32_t
     if (wave_rows == 0 || wave_rows > num) wave_rows = num;
     const size_t stage_bytes = (size_t) wave_rows * graph_degree * 4;
     const bool routed = mode == kModeRefine;
-    rc = ensure_ws(ctx, align256(stage_bytes) + align256((size_t) num * 4) + (routed ? order_scratch_bytes(wave_rows, C) : 0));
+    // work list of a wave: the rows with holes only (flags, list, count)
+    const size_t list_bytes = 2 * align256((size_t) wave_rows * 4) + 256;
+    rc = ensure_ws(ctx, align256(stage_bytes) + align256((size_t) num * 4) + list_bytes + (routed ? order_scratch_bytes(wave_rows, C) : 0));
     if (rc) return rc;
     uint32_t *staging = static_cast<uint32_t *>(ctx->ws);
     uint32_t *route = reinterpret_cast<uint32_t *>(static_cast<char *>(ctx->ws) + align256(stage_bytes));
+    char *list_base = reinterpret_cast<char *>(route) + align256((size_t) num * 4);
+    uint32_t *hole_flags = reinterpret_cast<uint32_t *>(list_base);
+    uint32_t *hole_list = reinterpret_cast<uint32_t *>(list_base + align256((size_t) wave_rows * 4));
+    uint32_t *hole_count = reinterpret_cast<uint32_t *>(list_base + 2 * align256((size_t) wave_rows * 4));
     Timed timer(ctx);
     OrderScratch o{};
     if (routed) {
         AssignArgs r{d_data, num, dim, d_centroids, C, -1.0f, metric, route, nullptr, C <= 4096 ? ctx->tc_norms : nullptr, nullptr};
         GL_CUDA(ctx, launch_assign(r, ctx->stream));
-        o = carve_order_scratch(reinterpret_cast<char *>(route) + align256((size_t) num * 4), wave_rows, C);
+        o = carve_order_scratch(list_base + list_bytes, wave_rows, C);
     }
     unsigned long long *counters = counters_or_null(ctx);
     for (uint32_t lo = 0; lo < num; lo += wave_rows) {
         const uint32_t count = num - lo < wave_rows ? num - lo : wave_rows;
         BuildArgs a{};
+        const uint32_t *grouped = nullptr;
         if (routed) {   // the wave's points grouped by partition: warps that run together share L2 lines
             GL_CUDA(ctx, make_partition_order(route + lo, count, C, o, ctx->stream));
-            a.order = o.order;
+            grouped = o.order;
         }
+        // Rows without holes are copied as they are; the kernel gets the rows with holes only, as a
+        // dense list, so that every warp of a CTA has a point to refine (with a warp per row of the
+        // wave, a CTA keeps its registers until its one or two busy warps are done).
+        GL_CUDA(ctx, cudaMemcpyAsync(staging, d_graph + (size_t) lo * graph_degree, (size_t) count * graph_degree * 4,
+                                     cudaMemcpyDeviceToDevice, ctx->stream));
+        GL_CUDA(ctx, launch_rows_with_holes(d_graph, lo, count, graph_degree, grouped, hole_flags, hole_list, hole_count, ctx->stream));
+        a.order = hole_list;
+        a.count_dev = hole_count;
         a.mode = mode;
         a.data = d_data; a.dim = dim; a.graph_in = d_graph; a.in_degree = graph_degree;
         a.graph_out = staging; a.out_first = lo; a.out_degree = graph_degree;
@@ -852,16 +867,26 @@ int glide_refine_rows(glide_ctx *ctx, const float *d_data, uint32_t num, uint32_
     if (rc) return rc;
     if (count == 0) { ctx->last_ms = 0.0f; return GLIDE_OK; }
     GL_CUDA(ctx, cudaSetDevice(ctx->device));
-    rc = ensure_ws(ctx, align256((size_t) count * 4) + order_scratch_bytes(count, C));
+    const size_t list_bytes = 2 * align256((size_t) count * 4) + 256;
+    rc = ensure_ws(ctx, align256((size_t) count * 4) + list_bytes + order_scratch_bytes(count, C));
     if (rc) return rc;
     uint32_t *route = static_cast<uint32_t *>(ctx->ws);
+    char *list_base = reinterpret_cast<char *>(route) + align256((size_t) count * 4);
+    uint32_t *hole_flags = reinterpret_cast<uint32_t *>(list_base);
+    uint32_t *hole_list = reinterpret_cast<uint32_t *>(list_base + align256((size_t) count * 4));
+    uint32_t *hole_count = reinterpret_cast<uint32_t *>(list_base + 2 * align256((size_t) count * 4));
     Timed timer(ctx);
     AssignArgs r{d_data + (size_t) first * dim, count, dim, d_centroids, C, -1.0f, metric, route, nullptr, ctx->tc_norms, nullptr};
     GL_CUDA(ctx, launch_assign(r, ctx->stream));
-    const OrderScratch o = carve_order_scratch(reinterpret_cast<char *>(route) + align256((size_t) count * 4), count, C);
+    const OrderScratch o = carve_order_scratch(list_base + list_bytes, count, C);
     GL_CUDA(ctx, make_partition_order(route, count, C, o, ctx->stream));
+    // as in refine_common: rows without holes are copied, the kernel works through the others as a dense list
+    GL_CUDA(ctx, cudaMemcpyAsync(d_rows_out, d_graph + (size_t) first * graph_degree, (size_t) count * graph_degree * 4,
+                                 cudaMemcpyDeviceToDevice, ctx->stream));
+    GL_CUDA(ctx, launch_rows_with_holes(d_graph, first, count, graph_degree, o.order, hole_flags, hole_list, hole_count, ctx->stream));
     BuildArgs a{};
-    a.order = o.order;
+    a.order = hole_list;
+    a.count_dev = hole_count;
     a.mode = kModeRefine;
     a.data = d_data; a.dim = dim; a.graph_in = d_graph; a.in_degree = graph_degree;
     a.graph_out = d_rows_out; a.out_first = first; a.out_degree = graph_degree;

@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(256, NB <= 4 ? 4 : 2) build_kernel(const Build
     const uint32_t warps_per_cta = blockDim.x >> 5;
     const uint32_t warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t t = blockIdx.x * warps_per_cta + warp;
-    if (t >= a.count) return;
+    if (t >= (a.count_dev ? __ldg(a.count_dev) : a.count)) return;
     const uint32_t point = a.first + (a.order ? a.order[t] : t);
     const BeamParams p{a.p.beam, a.p.max_iterations, a.p.min_iterations, a.p.hash_bit, a.p.hash_reset_interval};
     WarpStrip s = make_strip(smem + (size_t) warp * d.strip_words, a.dim, LANES ? kLaneScratch : 32u * NC, p.hash_bit);
@@ -474,6 +474,57 @@ __global__ void __launch_bounds__(256) reverse_insert_kernel(uint32_t *graph, ui
 }
 
 }  // namespace
+
+namespace {
+// flags[r] = 1 when row first + r has an empty slot: a warp per row, one coalesced read
+__global__ void hole_flags_kernel(const uint32_t *__restrict__ graph, uint32_t first, uint32_t count, uint32_t degree, uint32_t *flags) {
+    const uint32_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = lane_id();
+    if (r >= count) return;
+    const uint32_t *row = graph + (uint64_t) (first + r) * degree;
+    bool hole = false;
+    for (uint32_t i = lane; i < degree; i += 32) hole = hole || (__ldg(row + i) == kInvalid);
+    const uint32_t any = __ballot_sync(kFullMask, hole);
+    if (lane == 0) flags[r] = any != 0 ? 1u : 0u;
+}
+
+// Ordered compaction by one CTA: order_out = the entries of order_in (or 0, 1, 2, ...) whose flag is set
+__global__ void __launch_bounds__(1024) compact_flagged_kernel(const uint32_t *__restrict__ flags, const uint32_t *__restrict__ order_in,
+                                                               uint32_t count, uint32_t *order_out, uint32_t *count_out) {
+    __shared__ uint32_t warp_sums[32];
+    __shared__ uint32_t base;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (tid == 0) base = 0;
+    __syncthreads();
+    for (uint32_t i0 = 0; i0 < count; i0 += 1024) {
+        const uint32_t i = i0 + tid;
+        const uint32_t r = i < count ? (order_in ? order_in[i] : i) : 0u;
+        const bool keep = i < count && flags[r] != 0;
+        const uint32_t m = __ballot_sync(kFullMask, keep);
+        if (lane == 0) warp_sums[warp] = __popc(m);
+        __syncthreads();
+        uint32_t before = 0, total = 0;
+        for (uint32_t w = 0; w < 32; w++) {
+            const uint32_t c = warp_sums[w];
+            if (w < warp) before += c;
+            total += c;
+        }
+        if (keep) order_out[base + before + __popc(m & ((1u << lane) - 1u))] = r;
+        __syncthreads();
+        if (tid == 0) base += total;
+        __syncthreads();
+    }
+    if (tid == 0) *count_out = base;
+}
+}  // namespace
+
+cudaError_t launch_rows_with_holes(const uint32_t *graph, uint32_t first, uint32_t count, uint32_t degree,
+                                   const uint32_t *order_in, uint32_t *flags, uint32_t *order_out, uint32_t *count_out,
+                                   cudaStream_t stream) {
+    if (count == 0) return cudaMemsetAsync(count_out, 0, 4, stream);
+    hole_flags_kernel<<<(unsigned) (((uint64_t) count * 32 + 255) / 256), 256, 0, stream>>>(graph, first, count, degree, flags);
+    compact_flagged_kernel<<<1, 1024, 0, stream>>>(flags, order_in, count, order_out, count_out);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream) {
     if (a.count == 0) return cudaSuccess;

@@ -86,6 +86,8 @@ struct BuildArgs {
     const uint32_t *order;         // refine: warp t handles point first + order[t] (points grouped by partition so that
                                    // warps running together share L2 lines); nullptr: first + t
     uint32_t first, count;         // point range handled by this launch
+    const uint32_t *count_dev;     // when set: the number of entries of `order` to handle, read on the device (the
+                                   // grid still covers `count`; warps beyond *count_dev leave at once)
     uint32_t fixed_segment;        // boundary: the segment every point belongs to
     uint32_t max_seg_rows;         // build/boundary: rows of the largest partition this launch can touch (0: not known);
                                    // lets the launcher take the bitmap form of the visited set
@@ -96,6 +98,13 @@ struct BuildArgs {
 };
 cudaError_t launch_build(const BuildArgs &a, cudaStream_t stream);
 cudaError_t preload_build_kernels(cudaStream_t stream);
+// The rows of graph[first .. first + count) that hold at least one empty slot, as indices relative to
+// `first`, in the order of order_in (nullptr: ascending); *count_out receives how many. flags: count
+// words of scratch. A refine launch over that list keeps every warp of a CTA busy; one over all rows
+// leaves most CTAs with a warp or two at work when few rows have holes.
+cudaError_t launch_rows_with_holes(const uint32_t *graph, uint32_t first, uint32_t count, uint32_t degree,
+                                   const uint32_t *order_in, uint32_t *flags, uint32_t *order_out, uint32_t *count_out,
+                                   cudaStream_t stream);
 
 struct ReverseArgs {
     uint32_t *graph;   // num x degree, updated in place
