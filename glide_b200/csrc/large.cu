@@ -56,6 +56,14 @@ __global__ void widen_u8_kernel(const uint8_t *__restrict__ in, float *__restric
     reinterpret_cast<float4 *>(out)[i] = make_float4((float) b.x, (float) b.y, (float) b.z, (float) b.w);
 }
 
+// a null partition list means every partition of the index, in index order
+const uint32_t *every_partition(std::vector<uint32_t> &ids, uint32_t S, uint32_t *count) {
+    ids.resize(S);
+    for (uint32_t s = 0; s < S; s++) ids[s] = s;
+    *count = S;
+    return ids.data();
+}
+
 }  // namespace
 
 namespace glide {
@@ -424,10 +432,12 @@ int glide_large_build(glide_large *L, const uint32_t *partition_ids, uint32_t pa
                       uint32_t exact_max_rows, uint64_t seed, const int32_t *h_knn_in, int32_t *h_knn_out) {
     if (!L) return GLIDE_ERR_BAD_ARG;
     glide_ctx *ctx = L->ctx;
-    if (!partition_ids || !p_build) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_build: null pointer");
+    if (!p_build) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_build: null pointer");
     if (knn_degree == 0 || knn_degree > 64) return fail(ctx, GLIDE_ERR_UNSUPPORTED, "large_build: knn_degree must be <= 64");
     LG_CUDA(ctx, cudaSetDevice(ctx->device));
     const uint32_t S = (uint32_t) L->seg_len.size();
+    std::vector<uint32_t> every;
+    if (!partition_ids) partition_ids = every_partition(every, S, &partition_count);
     uint32_t max_rows = 0;
     for (uint32_t i = 0; i < partition_count; i++) {
         if (partition_ids[i] >= S) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_build: partition id out of range");
@@ -529,9 +539,11 @@ int glide_large_build(glide_large *L, const uint32_t *partition_ids, uint32_t pa
 // resident afterwards in *resident_count.
 int glide_large_make_resident(glide_large *L, const uint32_t *partition_ids, uint32_t partition_count, size_t budget_bytes,
                               uint32_t *resident_count) {
-    if (!L || !partition_ids) return GLIDE_ERR_BAD_ARG;
+    if (!L) return GLIDE_ERR_BAD_ARG;
     glide_ctx *ctx = L->ctx;
     LG_CUDA(ctx, cudaSetDevice(ctx->device));
+    std::vector<uint32_t> every;
+    if (!partition_ids) partition_ids = every_partition(every, (uint32_t) L->seg_len.size(), &partition_count);
     uint32_t n = 0;
     for (uint32_t i = 0; i < partition_count; i++) {
         const uint32_t p = partition_ids[i];
@@ -588,9 +600,11 @@ int glide_large_search(glide_large *L, const float *d_queries, uint32_t q, const
                        float *d_final_dists) {
     if (!L) return GLIDE_ERR_BAD_ARG;
     glide_ctx *ctx = L->ctx;
-    if (!d_queries || !d_centroids || !p || !partition_ids || !d_final_ids || !d_final_dists)
+    if (!d_queries || !d_centroids || !p || !d_final_ids || !d_final_dists)
         return fail(ctx, GLIDE_ERR_BAD_ARG, "large_search: null pointer");
     const uint32_t S = (uint32_t) L->seg_len.size();
+    std::vector<uint32_t> every;
+    if (!partition_ids) partition_ids = every_partition(every, S, &partition_count);
     if (centroid_num != S) return fail(ctx, GLIDE_ERR_BAD_ARG, "large_search: one centroid per partition expected");
     LG_CUDA(ctx, cudaSetDevice(ctx->device));
     for (auto &t : L->last_stage_seconds) t = 0;

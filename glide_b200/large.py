@@ -145,6 +145,15 @@ def preprocess_file_for_large(ctx: api.Context, path: str, dtype, centroid_num: 
                 h_centroids=d_centroids.cpu().numpy(), seconds=seconds, load=stats)
 
 
+def _partition_list(partitions):
+    """(array kept alive, pointer, count) for a partition list argument; None is the C side's null
+    list, which stands for every partition in index order."""
+    if partitions is None:
+        return None, None, 0
+    parts = np.ascontiguousarray(partitions, np.uint32)
+    return parts, parts.ctypes.data, parts.size
+
+
 def build_knn_for_large(ctx: api.Context, param: NNDescentParameter, h_reorder_data: np.ndarray, h_segment_start,
                         h_segment_length, metric: Metric = Metric.Euclidean, seed: int = 0,
                         exact_max_rows: int = 0xFFFFFFFF):
@@ -257,7 +266,7 @@ class GLIDE_large:
         all-pairs kernel) as part of the same streamed pass. Returns kernel seconds."""
         import ctypes as C
         ctx = self.ctx
-        parts = np.arange(self.segment_num(), dtype=np.uint32) if partitions is None else np.ascontiguousarray(partitions, np.uint32)
+        parts, parts_ptr, parts_n = _partition_list(partitions)
         nnd = nnd or NNDescentParameter(build_param.knn_degree)
         knn_degree = build_param.knn_degree if h_knn_graph is None else h_knn_graph.shape[1]
         pk = api._params_c(search_param_knn)
@@ -267,7 +276,7 @@ class GLIDE_large:
             knn_in = np.ascontiguousarray(h_knn_graph, np.int32)
         self.h_knn = pinned_empty((self.num(), knn_degree), np.int32) if want_knn else None
         ctx.sync_inputs()
-        ctx.check(ctx.lib.glide_large_build(self.handle, parts.ctypes.data, parts.size, knn_degree, C.byref(pk), C.byref(pr),
+        ctx.check(ctx.lib.glide_large_build(self.handle, parts_ptr, parts_n, knn_degree, C.byref(pk), C.byref(pr),
                                             build_param.relaxant_factor, nnd.max_iterations, nnd.termination_threshold, 0,
                                             exact_max_rows, seed,
                                             None if knn_in is None else knn_in.ctypes.data - self.row_offset * knn_degree * 4,
@@ -280,9 +289,9 @@ class GLIDE_large:
     def make_resident(self, budget_bytes: int, partitions=None) -> int:
         """Keep partitions in device memory for the searches that follow; returns how many fit."""
         import ctypes as C
-        parts = np.arange(self.segment_num(), dtype=np.uint32) if partitions is None else np.ascontiguousarray(partitions, np.uint32)
+        parts, parts_ptr, parts_n = _partition_list(partitions)
         n = C.c_uint32(0)
-        self.ctx.check(self.ctx.lib.glide_large_make_resident(self.handle, parts.ctypes.data, parts.size, int(budget_bytes),
+        self.ctx.check(self.ctx.lib.glide_large_make_resident(self.handle, parts_ptr, parts_n, int(budget_bytes),
                                                               C.byref(n)))
         return int(n.value)
 
@@ -319,14 +328,14 @@ class GLIDE_large:
         import ctypes as C
         ctx = self.ctx
         q = d_query.shape[0]
-        parts = np.arange(self.segment_num(), dtype=np.uint32) if partitions is None else np.ascontiguousarray(partitions, np.uint32)
+        parts, parts_ptr, parts_n = _partition_list(partitions)
         d_ids = api._u32_tensor(ctx, (q, param.top_k))
         d_d = ctx.empty((q, param.top_k), torch.float32)
         pc = api._params_c(param)
         ctx.sync_inputs()
         ctx.check(ctx.lib.glide_large_search(self.handle, d_query.data_ptr(), q, self.d_centroids.data_ptr(),
                                              self.centroids_num(), min_segment_num, boundary_factor, C.byref(pc),
-                                             parts.ctypes.data, parts.size, d_ids.data_ptr(), d_d.data_ptr()))
+                                             parts_ptr, parts_n, d_ids.data_ptr(), d_d.data_ptr()))
         st = self._stats()
         self.stats = dict(route_seconds=st[0], search_seconds=st[1], h2d_bytes=st[4], h2d_seconds=st[5],
                           partitions_uploaded=int(st[6]), partitions_searched=int(st[7]))

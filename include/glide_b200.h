@@ -345,7 +345,8 @@ int glide_large_get_start_points(const glide_large *index, uint32_t *h_out);
  * build lists its own): kNN graph (NN-descent or the exact all-pairs kernel, as glide_build_nnd;
  * skipped when h_knn_in, rows x knn_degree partition-local ids, is given), build_for_large, reverse
  * edges, refine_for_large (p_refine null or beam 0: none). h_knn_out (pinned, may be null) receives
- * the kNN rows. Partition p + 1 is uploaded while p is built. */
+ * the kNN rows. Partition p + 1 is uploaded while p is built. Here and in the two calls below a null
+ * partition_ids stands for every partition in index order (partition_count is then ignored). */
 int glide_large_build(glide_large *index, const uint32_t *partition_ids, uint32_t partition_count, uint32_t knn_degree,
                       const glide_search_params *p_build, const glide_search_params *p_refine, float relaxant_factor,
                       uint32_t nnd_max_iterations, float nnd_termination_threshold, uint32_t nnd_sample,
