@@ -3,6 +3,7 @@
 // (define_partition_kernel, :22-66), order-independent slot assignment replacing the
 // reference's atomics (:57-60), the permuted copy (reorder_kernel, :68-100) and the
 // Lloyd centroid update used in place of cuVS kmeans::fit (partition.cuh:48-54).
+#include <algorithm>
 #include <cstdlib>
 #include "beam_core.cuh"
 #include "kernels.h"
@@ -387,6 +388,164 @@ __global__ void __launch_bounds__(256) ff_pick_kernel(const float *__restrict__ 
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) next_centre[i] = sample[(uint64_t) winner * dim + i];
 }
 
+// ---- the same traversal as one launch --------------------------------------------------
+// One CTA per SM owns a fixed slice of the sample and keeps it on the chip for the whole
+// traversal: as many rows as fit in shared memory, then up to four rows per team of eight lanes
+// in registers (dimensions that are multiples of 32 up to 128), the rest re-read from L2. The
+// CTAs meet at one grid barrier per centre: update + block maximum, atomic maximum into the
+// centre's own slot, barrier, every CTA reads the slot and fetches the winning row as its next
+// centre. Same arithmetic and tie rule as the two kernels above, so the centres are the same
+// bits. The barrier's wait is bounded: a CTA that waits too long raises the error word, and
+// every CTA returns once it sees the word or runs out of patience itself.
+constexpr uint32_t kFfThreads = 512;
+constexpr uint32_t kFfWarps = kFfThreads / 32;
+constexpr uint32_t kFfTeams = kFfThreads / kTeam;
+constexpr uint32_t kFfTeamRows = 4;           // rows a team can hold in registers
+constexpr uint32_t kFfSpinLimit = 1u << 22;   // around a second of polling
+constexpr uint32_t kFfMaxCentres = 4096;
+
+struct FfArgs {
+    const float *sample;
+    uint32_t n, dim, C;
+    float *centroids;
+    u64 *step_best;        // one slot per centre, zero at launch
+    uint32_t *sync;        // [0] arrivals, [1] error
+    uint32_t rows_per_block, shared_rows;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// team lane's partial sum over a row held in shared memory; the order of team_partial
+__device__ __forceinline__ float team_partial_shared(const float *q, const float *row, uint32_t dim) {
+    const uint32_t t = threadIdx.x & (kTeam - 1);
+    const uint32_t chunks = dim >> 2;
+    const float4 *q4 = reinterpret_cast<const float4 *>(q);
+    const float4 *r4 = reinterpret_cast<const float4 *>(row);
+    float acc = 0.0f;
+#pragma unroll 4
+    for (uint32_t c = t; c < chunks; c += kTeam) acc = sq_acc4(q4[c], r4[c], acc);
+    return acc;
+}
+
+__device__ __forceinline__ u64 ff_block_max(u64 best, u64 *warp_best) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const u64 o = __shfl_xor_sync(kFullMask, best, off);
+        if (o > best) best = o;
+    }
+    if (lane_id() == 0) warp_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    u64 b = warp_best[0];
+    for (uint32_t w = 1; w < kFfWarps; w++) if (warp_best[w] > b) b = warp_best[w];
+    return b;
+}
+
+// CH: 16-byte chunks of a row per team lane (dim == 32 * CH) when rows are held in registers, else 0
+template<int CH>
+__global__ void __launch_bounds__(kFfThreads, 1) ff_persistent_kernel(const FfArgs a) {
+    extern __shared__ __align__(16) uint32_t smem[];
+    __shared__ u64 warp_best[kFfWarps];
+    __shared__ uint32_t gave_up;
+    __shared__ u64 step_winner;
+    const uint32_t dim = a.dim;
+    float *c = reinterpret_cast<float *>(smem);
+    float *mind2 = c + dim_pad4(dim);
+    float *held = mind2 + ((a.rows_per_block + 3u) & ~3u);
+    const uint32_t lo = min(a.n, blockIdx.x * a.rows_per_block), hi = min(a.n, lo + a.rows_per_block);
+    const uint32_t mine = hi - lo, in_shared = min(a.shared_rows, mine);
+    const uint32_t in_regs = CH > 0 ? min(mine - in_shared, kFfTeams * kFfTeamRows) : 0;
+    const uint32_t warp = threadIdx.x >> 5, team = lane_id() / kTeam, t8 = threadIdx.x & (kTeam - 1);
+    const uint32_t my_first = in_shared + (threadIdx.x / kTeam) * kFfTeamRows;   // this team's rows in registers
+    float4 hr[kFfTeamRows][CH > 0 ? CH : 1];
+    {
+        const float4 *src = reinterpret_cast<const float4 *>(a.sample + (uint64_t) lo * dim);   // in_shared > 0 only when dim % 4 == 0
+        float4 *dst = reinterpret_cast<float4 *>(held);
+        const uint32_t chunks = in_shared * (dim >> 2);
+        for (uint32_t i = threadIdx.x; i < chunks; i += kFfThreads) dst[i] = __ldg(src + i);
+        if (CH > 0) {
+#pragma unroll
+            for (uint32_t j = 0; j < kFfTeamRows; j++)
+#pragma unroll
+                for (int k = 0; k < CH; k++)
+                    hr[j][k] = my_first + j < in_shared + in_regs ? __ldg(src + (size_t) (my_first + j) * (dim >> 2) + t8 + k * kTeam)
+                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    for (uint32_t i = threadIdx.x; i < mine; i += kFfThreads) mind2[i] = FLT_MAX;
+    for (uint32_t i = threadIdx.x; i < dim; i += kFfThreads) {
+        const float v = __ldg(a.sample + i);   // the first centre is the first sample row
+        c[i] = v;
+        if (blockIdx.x == 0) a.centroids[i] = v;
+    }
+    if (threadIdx.x == 0) gave_up = 0;
+    __syncthreads();
+    for (uint32_t t = 0; t + 1 < a.C; t++) {
+        u64 best = 0;
+        auto settle = [&](uint32_t i, float part, bool active) {
+            const float d = team_fold(part);
+            if (active) {
+                float m = mind2[i];
+                if (d < m) m = d;
+                if (t8 == 0) mind2[i] = m;
+                const u64 k = ff_key(m, lo + i);
+                if (k > best) best = k;
+            }
+        };
+        for (uint32_t r = warp * kTeamsPerWarp; r < in_shared; r += kFfWarps * kTeamsPerWarp) {
+            const uint32_t i = r + team;
+            const bool active = i < in_shared;
+            settle(i, active ? team_partial_shared(c, held + (size_t) i * dim, dim) : 0.0f, active);
+        }
+        if (CH > 0) {
+            const float4 *q4 = reinterpret_cast<const float4 *>(c);
+#pragma unroll
+            for (uint32_t j = 0; j < kFfTeamRows; j++) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int k = 0; k < CH; k++) acc = sq_acc4(q4[t8 + k * kTeam], hr[j][k], acc);
+                settle(my_first + j, acc, my_first + j < in_shared + in_regs);
+            }
+        }
+        for (uint32_t r = in_shared + in_regs + warp * kTeamsPerWarp; r < mine; r += kFfWarps * kTeamsPerWarp) {
+            const uint32_t i = r + team;
+            const bool active = i < mine;
+            settle(i, team_partial(c, a.sample + (uint64_t) (lo + (active ? i : 0)) * dim, dim, active), active);
+        }
+        const u64 block_max = ff_block_max(best, warp_best);
+        // arrive with this CTA's maximum and wait for every CTA's
+        if (threadIdx.x == 0) {
+            atomicMax(reinterpret_cast<unsigned long long *>(a.step_best + t), (unsigned long long) block_max);
+            __threadfence();
+            atomicAdd(&a.sync[0], 1u);
+            const uint32_t target = (t + 1) * gridDim.x;
+            uint32_t spins = 0;
+            bool ok = true;
+            while (ld_acquire_u32(&a.sync[0]) < target) {
+                if (++spins > kFfSpinLimit || ((spins & 1023u) == 0 && ld_acquire_u32(&a.sync[1]) != 0)) {
+                    atomicExch(&a.sync[1], 1u);
+                    ok = false;
+                    break;
+                }
+            }
+            if (ok) step_winner = __ldcg(a.step_best + t);
+            else gave_up = 1;
+        }
+        __syncthreads();   // also: nobody reads the old centre or warp_best any more
+        if (gave_up) return;
+        const uint32_t winner = 0xffffffffu - (uint32_t) step_winner;
+        for (uint32_t i = threadIdx.x; i < dim; i += kFfThreads) {
+            const float v = __ldg(a.sample + (uint64_t) winner * dim + i);
+            c[i] = v;
+            if (blockIdx.x == 0) a.centroids[(uint64_t) (t + 1) * dim + i] = v;
+        }
+        __syncthreads();
+    }
+}
+
 __global__ void fill_f32_kernel(float *p, uint32_t n, float v) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
@@ -546,14 +705,69 @@ cudaError_t launch_count_changed(const uint32_t *a, const uint32_t *b, uint32_t 
 }
 
 size_t farthest_first_scratch_bytes(uint32_t n) {
-    return (size_t) n * 4 + 256 + (size_t) ((n + kFfRowsPerBlock - 1) / kFfRowsPerBlock) * 8 + 256;
+    // distances, block maxima of the launch-per-centre path, then the per-centre slots and the two
+    // barrier words of the one-launch path
+    return (size_t) n * 4 + 256 + (size_t) ((n + kFfRowsPerBlock - 1) / kFfRowsPerBlock) * 8 + 256 + kFfMaxCentres * 8 + 256;
+}
+
+// One persistent launch when the sample is small enough to stay on the chip and in L2 between
+// centres; returns cudaErrorNotSupported when this device or shape cannot take it.
+static cudaError_t launch_farthest_first_persistent(const float *sample, uint32_t n, uint32_t dim, uint32_t C,
+                                                    float *centroids, char *tail, cudaStream_t stream) {
+    int device = 0, sms = 0, coop = 0, smem_max = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if (e != cudaSuccess) return e;
+    if (!coop || sms <= 0 || C > kFfMaxCentres) return cudaErrorNotSupported;
+    const uint32_t G = std::max(1u, std::min<uint32_t>((uint32_t) sms, (n + 63) / 64));
+    const uint32_t rows_per_block = (n + G - 1) / G;
+    const size_t fixed_bytes = (size_t) dim_pad4(dim) * 4 + (size_t) ((rows_per_block + 3u) & ~3u) * 4;
+    const size_t budget = (size_t) smem_max - 1024;
+    if (fixed_bytes + 1024 > budget || rows_per_block > 16384) return cudaErrorNotSupported;
+    uint32_t shared_rows = 0;
+    if ((dim & 3u) == 0) shared_rows = (uint32_t) std::min<size_t>(rows_per_block, (budget - fixed_bytes) / ((size_t) dim * 4));
+    const size_t smem = fixed_bytes + (size_t) shared_rows * dim * 4;
+    const int ch = (dim % 32 == 0 && dim <= 128) ? (int) (dim / 32) : 0;
+    const void *kernel = ch == 1 ? (const void *) ff_persistent_kernel<1> : ch == 2 ? (const void *) ff_persistent_kernel<2>
+                       : ch == 3 ? (const void *) ff_persistent_kernel<3> : ch == 4 ? (const void *) ff_persistent_kernel<4>
+                                                                                     : (const void *) ff_persistent_kernel<0>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    int per_sm = 0;
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int) kFfThreads, smem);
+    if (e != cudaSuccess) return e;
+    if ((uint64_t) per_sm * (uint64_t) sms < G) return cudaErrorNotSupported;
+    FfArgs a{sample, n, dim, C, centroids, reinterpret_cast<u64 *>(tail), reinterpret_cast<uint32_t *>(tail + kFfMaxCentres * 8),
+             rows_per_block, shared_rows};
+    e = cudaMemsetAsync(tail, 0, kFfMaxCentres * 8 + 8, stream);
+    if (e != cudaSuccess) return e;
+    void *params[] = {&a};
+    e = cudaLaunchCooperativeKernel(kernel, dim3(G), dim3(kFfThreads), params, smem, stream);
+    if (e == cudaErrorCooperativeLaunchTooLarge) return cudaErrorNotSupported;   // fewer SMs than the device reports are ours
+    if (e != cudaSuccess) return e;
+    uint32_t words[2] = {0, 0};
+    e = cudaMemcpyAsync(words, a.sync, 8, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    return words[1] ? cudaErrorLaunchTimeout : cudaSuccess;   // a CTA ran out of patience at the barrier
 }
 
 cudaError_t launch_farthest_first(const float *sample, uint32_t n, uint32_t dim, uint32_t C, float *centroids,
                                   void *scratch, cudaStream_t stream) {
     float *mind2 = static_cast<float *>(scratch);
-    u64 *block_best = reinterpret_cast<u64 *>(static_cast<char *>(scratch) + (((size_t) n * 4 + 255) & ~(size_t) 255));
+    char *after = static_cast<char *>(scratch) + (((size_t) n * 4 + 255) & ~(size_t) 255);
+    u64 *block_best = reinterpret_cast<u64 *>(after);
     const uint32_t blocks = (n + kFfRowsPerBlock - 1) / kFfRowsPerBlock;
+    // GLIDE_B200_FF_LAUNCHES=1 keeps the launch-per-centre path (the tests compare both)
+    const char *env = std::getenv("GLIDE_B200_FF_LAUNCHES");
+    const bool per_centre = env && env[0] == '1';
+    if (!per_centre && n > 0 && C > 0 && (uint64_t) n * dim * 4 <= ((uint64_t) 96 << 20)) {
+        char *tail = after + (((size_t) blocks * 8 + 255) & ~(size_t) 255);
+        const cudaError_t e = launch_farthest_first_persistent(sample, n, dim, C, centroids, tail, stream);
+        if (e != cudaErrorNotSupported) return e;
+        (void) cudaGetLastError();
+    }
     fill_f32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(mind2, n, FLT_MAX);
     cudaError_t e = cudaMemcpyAsync(centroids, sample, (size_t) dim * 4, cudaMemcpyDeviceToDevice, stream);
     if (e != cudaSuccess) return e;

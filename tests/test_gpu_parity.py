@@ -233,6 +233,26 @@ def test_kmeans_matches_oracle(gpu_ctx, name, c, init):
     assert np.array_equal(d_c.cpu().numpy(), want_c)
 
 
+@pytest.mark.parametrize("n,dim,c", [(1200, 128, 40), (70000, 128, 48), (5000, 30, 33), (150, 64, 150), (100000, 128, 24),
+                                     (140000, 64, 20), (95000, 96, 20), (275000, 32, 12), (40000, 200, 16)])
+def test_farthest_first_in_one_launch_equals_a_launch_per_centre(gpu_ctx, monkeypatch, n, dim, c):
+    """The traversal runs as one persistent kernel (rows held in shared memory as far as they fit, then
+    in registers for dimensions 32, 64, 96 and 128, then left in L2: the larger shapes here overflow
+    shared memory, 40,000 x 200 has no register form) or as two launches per centre; both give the
+    oracle's centres. One Lloyd round follows, so labels and centres are functions of the traversal's
+    centres alone."""
+    rng = np.random.default_rng(n + dim)
+    sample = rng.integers(0, 50, (n, dim)).astype(np.float32)
+    sample[n // 2] = sample[n // 3]   # equal rows: the lower one wins a tie
+    want_c, want_l, _ = oracle.kmeans(sample, c, 1, init=1)
+    d_sample = dev(gpu_ctx, sample)
+    d_one, l_one, _ = api.kmeans_fit(gpu_ctx, d_sample, c, 1, Metric.Euclidean, 1)
+    monkeypatch.setenv("GLIDE_B200_FF_LAUNCHES", "1")
+    d_two, l_two, _ = api.kmeans_fit(gpu_ctx, d_sample, c, 1, Metric.Euclidean, 1)
+    assert np.array_equal(api.to_u32(l_one), want_l) and np.array_equal(d_one.cpu().numpy(), want_c)
+    assert np.array_equal(api.to_u32(l_two), want_l) and np.array_equal(d_two.cpu().numpy(), want_c)
+
+
 def test_get_centroids_uses_seeded_sample(gpu_ctx):
     base, _, _ = case("int128")
     ids = api.sample_ids(base.shape[0], 600, 3)
