@@ -487,33 +487,41 @@ __global__ void hole_flags_kernel(const uint32_t *__restrict__ graph, uint32_t f
     if (lane == 0) flags[r] = any != 0 ? 1u : 0u;
 }
 
-// Ordered compaction by one CTA: order_out = the entries of order_in (or 0, 1, 2, ...) whose flag is set
+// Ordered compaction by one CTA: order_out = the entries of order_in (or 0, 1, 2, ...) whose flag is set.
+// Every warp owns one contiguous run of the list and walks it 32 entries at a time, once to count its
+// kept entries and, after the 32 counts are scanned, once more to write them; the reads of a pass do
+// not depend on one another, so their latencies overlap.
 __global__ void __launch_bounds__(1024) compact_flagged_kernel(const uint32_t *__restrict__ flags, const uint32_t *__restrict__ order_in,
                                                                uint32_t count, uint32_t *order_out, uint32_t *count_out) {
     __shared__ uint32_t warp_sums[32];
-    __shared__ uint32_t base;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    if (tid == 0) base = 0;
-    __syncthreads();
-    for (uint32_t i0 = 0; i0 < count; i0 += 1024) {
-        const uint32_t i = i0 + tid;
-        const uint32_t r = i < count ? (order_in ? order_in[i] : i) : 0u;
-        const bool keep = i < count && flags[r] != 0;
-        const uint32_t m = __ballot_sync(kFullMask, keep);
-        if (lane == 0) warp_sums[warp] = __popc(m);
-        __syncthreads();
-        uint32_t before = 0, total = 0;
-        for (uint32_t w = 0; w < 32; w++) {
-            const uint32_t c = warp_sums[w];
-            if (w < warp) before += c;
-            total += c;
-        }
-        if (keep) order_out[base + before + __popc(m & ((1u << lane) - 1u))] = r;
-        __syncthreads();
-        if (tid == 0) base += total;
-        __syncthreads();
+    const uint32_t per_warp = ((count + 1023u) / 1024u) * 32u;   // a multiple of 32 entries per warp
+    const uint32_t lo = min(count, warp * per_warp), hi = min(count, lo + per_warp);
+    uint32_t kept = 0;
+#pragma unroll 8
+    for (uint32_t i0 = lo; i0 < hi; i0 += 32) {
+        const uint32_t i = i0 + lane;
+        const uint32_t r = i < hi ? (order_in ? __ldg(order_in + i) : i) : 0u;
+        kept += __popc(__ballot_sync(kFullMask, i < hi && flags[r] != 0));
     }
-    if (tid == 0) *count_out = base;
+    if (lane == 0) warp_sums[warp] = kept;
+    __syncthreads();
+    uint32_t at = 0, total = 0;
+    for (uint32_t w = 0; w < 32; w++) {
+        const uint32_t c = warp_sums[w];
+        if (w < warp) at += c;
+        total += c;
+    }
+#pragma unroll 8
+    for (uint32_t i0 = lo; i0 < hi; i0 += 32) {
+        const uint32_t i = i0 + lane;
+        const uint32_t r = i < hi ? (order_in ? __ldg(order_in + i) : i) : 0u;
+        const bool keep = i < hi && flags[r] != 0;
+        const uint32_t m = __ballot_sync(kFullMask, keep);
+        if (keep) order_out[at + __popc(m & ((1u << lane) - 1u))] = r;
+        at += __popc(m);
+    }
+    if (tid == 0) *count_out = total;
 }
 }  // namespace
 
