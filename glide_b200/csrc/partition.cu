@@ -765,7 +765,9 @@ cudaError_t launch_farthest_first(const float *sample, uint32_t n, uint32_t dim,
     if (!per_centre && n > 0 && C > 0 && (uint64_t) n * dim * 4 <= ((uint64_t) 96 << 20)) {
         char *tail = after + (((size_t) blocks * 8 + 255) & ~(size_t) 255);
         const cudaError_t e = launch_farthest_first_persistent(sample, n, dim, C, centroids, tail, stream);
-        if (e != cudaErrorNotSupported) return e;
+        // a barrier that ran out of patience (the CTAs were not all resident in time, say behind another
+        // stream's long kernel) leaves nothing behind that the launches below do not overwrite
+        if (e != cudaErrorNotSupported && e != cudaErrorLaunchTimeout) return e;
         (void) cudaGetLastError();
     }
     fill_f32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(mind2, n, FLT_MAX);
