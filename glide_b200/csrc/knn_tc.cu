@@ -24,7 +24,7 @@
 // kind::tf32 keeps 10 mantissa bits per operand, so integer-valued rows below 1024 give exact dot
 // products and the result is the exact kNN graph with ties by ascending id; elsewhere the approximate
 // order only has to bring the true neighbours into the L = 2 x list-width candidates, and the
-// re-rank orders them exactly. One producer thread issues copies and MMAs; every mbarrier wait is
+// re-rank orders them exactly. One thread issues the copies and another the MMAs; every mbarrier wait is
 // bounded, and a CTA whose wait runs out raises a flag that makes the host redo the rows with the
 // SIMT kernels.
 #include <cstdlib>
@@ -45,7 +45,7 @@ constexpr uint32_t kTmemCols = 256;        // two accumulator buffers of 128 col
 constexpr uint32_t kSplit = 4;             // epilogue threads per row: each owns kCols columns of every tile
 constexpr uint32_t kCols = kRows / kSplit;
 constexpr uint32_t kEpiWarps = 4 * kSplit; // a warp reads the 32 tensor-memory lanes of its quadrant (warp % 4)
-constexpr uint32_t kThreads = (kEpiWarps + 1) * 32;
+constexpr uint32_t kThreads = (kEpiWarps + 2) * 32;   // + the MMA warp and the copy warp (one thread of each works)
 static_assert(kCols == 32 || kCols == 64, "the epilogue reads 32 columns per tcgen05.ld");
 constexpr u64 kNoKey = ~0ull;
 
@@ -166,8 +166,10 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == kEpiWarps) {
-        // ================= producer: TMA copies and MMA issue, one thread =================
+    if (warp == kEpiWarps + 1) {
+        // ================= copy warp: operand tiles by TMA, one thread =================
+        // Stage s takes tile t + 2 as soon as the MMAs of tile t have read it; the MMA thread does not
+        // wait for that, so the MMAs of tile t + 1 are already queued behind those of tile t.
         if (lane == 0) {
             auto load_tile = [&](uint8_t *dst, uint32_t row0, uint64_t *bar) {
                 mbar_expect_tx(bar, tile_bytes);
@@ -176,6 +178,15 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             load_tile(As, tile.seg_start + tile.first, a_full);
             load_tile(Bs, tile.seg_start, b_full + 0);
             if (total > 1) load_tile(Bs + tile_bytes, tile.seg_start + (1u % tiles) * kRows, b_full + 1);
+            for (uint32_t t = 0; t + 2 < total; t++) {
+                const uint32_t s = t & 1u, use = t >> 1;
+                if (!mbar_wait(mma_done + s, use & 1u, failed)) break;
+                load_tile(Bs + s * tile_bytes, tile.seg_start + ((t + 2) % tiles) * kRows, b_full + s);
+            }
+        }
+    } else if (warp == kEpiWarps) {
+        // ================= MMA warp: one thread issues =================
+        if (lane == 0) {
             // instruction descriptor: D fp32, A and B TF32, both K-major, N = 128, M = 128
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kRows >> 3) << 17) | ((kRows >> 4) << 24);
             const uint32_t a_addr = smem_u32(As), b_addr = smem_u32(Bs);
@@ -192,10 +203,6 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
                              ks > 0 ? 1u : 0u);
                 }
                 commit_to(mma_done + s);
-                if (t + 2 < total) {   // stage s is free once these MMAs have read it
-                    ok = mbar_wait(mma_done + s, use & 1u, failed);
-                    if (ok) load_tile(Bs + s * tile_bytes, tile.seg_start + ((t + 2) % tiles) * kRows, b_full + s);
-                }
             }
         }
     } else {
@@ -217,7 +224,13 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
         if (active)
             for (uint32_t g = 0; g < G; g++) my_gmin[g] = FLT_MAX;
         float m = FLT_MAX, thr = 0.0f;
-        uint32_t mine = 0;
+        uint32_t mine = 0, grp = 0, grp_rem = 0;
+        float cn_ahead[kCols / 32u];
+#pragma unroll
+        for (uint32_t h = 0; h < kCols / 32u; h++) {
+            const uint32_t c = part * kCols + lane + 32u * h;
+            cn_ahead[h] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
+        }
         for (uint32_t t = 0; t < total; t++) {
             const uint32_t s = t & 1u, use = t >> 1;
             const bool second = t >= tiles;
@@ -241,10 +254,17 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
                 thr = thr_s[row];
             }
             __syncwarp();
+            // the column norms of this tile were requested a tile ago; those of the next are requested now,
+            // so their trip to L2 runs under this tile's work instead of in front of the next one's
 #pragma unroll
-            for (uint32_t h = 0; h < kCols / 32u; h++) {
-                const uint32_t c = tt * kRows + part * kCols + lane + 32u * h;
-                cn[lane + 32u * h] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
+            for (uint32_t h = 0; h < kCols / 32u; h++) cn[lane + 32u * h] = cn_ahead[h];
+            if (t + 1 < total) {
+                const uint32_t tn = (t + 1 == tiles) ? 0u : tt + 1;
+#pragma unroll
+                for (uint32_t h = 0; h < kCols / 32u; h++) {
+                    const uint32_t c = tn * kRows + part * kCols + lane + 32u * h;
+                    cn_ahead[h] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
+                }
             }
             __syncwarp();
             bool ok = !*failed && mbar_wait(mma_done + s, use & 1u, failed);
@@ -308,11 +328,15 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_free + s);
             if (!second && by_tile) {   // a group of whole tiles ends with this tile
-                const uint32_t g = (uint32_t) (((uint64_t) tt * G) / tiles), g_next = (uint32_t) (((uint64_t) (tt + 1) * G) / tiles);
-                if (tt + 1 == tiles || g_next != g) {
-                    if (active) my_gmin[g] = m;
+                // tile tt belongs to group floor(tt * G / tiles); stepped without dividing: tt * G = grp * tiles + grp_rem,
+                // and G < tiles here, so the group number grows by at most one per tile
+                grp_rem += G;
+                const bool last_of_group = grp_rem >= tiles;
+                if (tt + 1 == tiles || last_of_group) {
+                    if (active) my_gmin[grp] = m;
                     m = FLT_MAX;
                 }
+                if (last_of_group) { grp_rem -= tiles; grp++; }
             }
         }
         if (active) a.cand_count[kSplit * (launch_row0 + row) + part] = min(mine, Sizes<NL>::part_cap);
