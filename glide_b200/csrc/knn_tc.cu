@@ -41,7 +41,9 @@ namespace {
 using namespace umma;
 
 constexpr uint32_t kRows = 128;            // rows per CTA = columns per tile
-constexpr uint32_t kTmemCols = 256;        // two accumulator buffers of 128 columns
+constexpr uint32_t kTmemCols = 512;        // two accumulator buffers of 128 columns, then the CTA's own rows (up to 128 columns)
+constexpr uint32_t kTmemA = 2 * kRows;     // first column of the CTA's own rows
+constexpr uint32_t kStages = 3;            // tiles of the partition in flight in shared memory
 constexpr uint32_t kSplit = 4;             // epilogue threads per row: each owns kCols columns of every tile
 constexpr uint32_t kCols = kRows / kSplit;
 constexpr uint32_t kEpiWarps = 4 * kSplit; // a warp reads the 32 tensor-memory lanes of its quadrant (warp % 4)
@@ -56,6 +58,7 @@ struct KnnTile {
 struct KnnTcArgs {
     const float *data;
     uint32_t dim;
+    uint64_t rows_total;       // rows of data
     const float *norms;        // per row of data
     const KnnTile *tiles;      // one per CTA
     u64 *cand;                 // launch rows x cap
@@ -136,13 +139,12 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
     const uint32_t dim = a.dim, kblocks = dim >> 5, ksteps = dim >> 3;
     const uint32_t sub_bytes = kRows * 128u;                  // one 32-float column block of a tile
     const uint32_t tile_bytes = kblocks * sub_bytes;
-    uint8_t *As = base;
-    uint8_t *Bs = As + tile_bytes;                            // two stages
-    float *cn_w = reinterpret_cast<float *>(Bs + 2 * tile_bytes);       // 8 warps x 64 column norms
+    uint8_t *Bs = base;                                       // kStages tiles of the partition; the CTA's own rows live in tensor memory
+    float *cn_w = reinterpret_cast<float *>(Bs + kStages * tile_bytes); // a warp's column norms of the current tile
     float *thr_s = cn_w + kEpiWarps * kCols;                            // 128 row thresholds
-    uint64_t *bars = reinterpret_cast<uint64_t *>(thr_s + kRows);       // a_full, b_full[2], mma_done[2], tmem_free[2]
-    uint64_t *a_full = bars, *b_full = bars + 1, *mma_done = bars + 3, *tmem_free = bars + 5;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(thr_s + kRows);       // a_full, b_full[3], stage_free[3], mma_done[2], tmem_free[2]
+    uint64_t *a_full = bars, *b_full = bars + 1, *stage_free = b_full + kStages, *mma_done = stage_free + kStages, *tmem_free = mma_done + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_free + 2);
     volatile uint32_t *failed = tmem_slot + 1;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -151,8 +153,9 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
     const uint64_t launch_row0 = (uint64_t) blockIdx.x * kRows;
 
     if (tid == 0) {
-        mbar_init(a_full, 1);
-        for (int s = 0; s < 2; s++) { mbar_init(b_full + s, 1); mbar_init(mma_done + s, 1); mbar_init(tmem_free + s, kEpiWarps); }
+        mbar_init(a_full, 4 * kblocks);   // the warps that write the CTA's rows into tensor memory
+        for (uint32_t s = 0; s < kStages; s++) { mbar_init(b_full + s, 1); mbar_init(stage_free + s, 1); }
+        for (int c = 0; c < 2; c++) { mbar_init(mma_done + c, 1); mbar_init(tmem_free + c, kEpiWarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *failed = 0;
     }
@@ -175,13 +178,11 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
                 mbar_expect_tx(bar, tile_bytes);
                 for (uint32_t kb = 0; kb < kblocks; kb++) tma_load_2d(dst + kb * sub_bytes, &tm_rows, kb * 32u, row0, bar);
             };
-            load_tile(As, tile.seg_start + tile.first, a_full);
-            load_tile(Bs, tile.seg_start, b_full + 0);
-            if (total > 1) load_tile(Bs + tile_bytes, tile.seg_start + (1u % tiles) * kRows, b_full + 1);
-            for (uint32_t t = 0; t + 2 < total; t++) {
-                const uint32_t s = t & 1u, use = t >> 1;
-                if (!mbar_wait(mma_done + s, use & 1u, failed)) break;
-                load_tile(Bs + s * tile_bytes, tile.seg_start + ((t + 2) % tiles) * kRows, b_full + s);
+            for (uint32_t i = 0; i < kStages && i < total; i++) load_tile(Bs + i * tile_bytes, tile.seg_start + (i % tiles) * kRows, b_full + i);
+            for (uint32_t t = 0; t + kStages < total; t++) {
+                const uint32_t s = t % kStages, use = t / kStages;
+                if (!mbar_wait(stage_free + s, use & 1u, failed)) break;
+                load_tile(Bs + s * tile_bytes, tile.seg_start + ((t + kStages) % tiles) * kRows, b_full + s);
             }
         }
     } else if (warp == kEpiWarps) {
@@ -189,20 +190,21 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
         if (lane == 0) {
             // instruction descriptor: D fp32, A and B TF32, both K-major, N = 128, M = 128
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kRows >> 3) << 17) | ((kRows >> 4) << 24);
-            const uint32_t a_addr = smem_u32(As), b_addr = smem_u32(Bs);
+            const uint32_t b_addr = smem_u32(Bs);
             bool ok = mbar_wait(a_full, 0, failed);
             for (uint32_t t = 0; t < total && ok; t++) {   // t counts tiles over both passes
-                const uint32_t s = t & 1u, use = t >> 1;
+                const uint32_t s = t % kStages, use = t / kStages, acc = t & 1u, acc_use = t >> 1;
                 ok = mbar_wait(b_full + s, use & 1u, failed);
-                if (ok && t >= 2) ok = mbar_wait(tmem_free + s, (use - 1) & 1u, failed);
+                if (ok && t >= 2) ok = mbar_wait(tmem_free + acc, (acc_use - 1) & 1u, failed);
                 if (!ok) break;
                 fence_after();
-                for (uint32_t ks = 0; ks < ksteps; ks++) {
+                for (uint32_t ks = 0; ks < ksteps; ks++) {   // eight TF32 values of every row per step: eight columns of A
                     const uint32_t off = (ks >> 2) * sub_bytes + (ks & 3u) * 32u;
-                    mma_tf32(tmem_base + s * kRows, desc_sw128(a_addr + off), desc_sw128(b_addr + s * tile_bytes + off), idesc,
-                             ks > 0 ? 1u : 0u);
+                    mma_tf32_ts(tmem_base + acc * kRows, tmem_base + kTmemA + ks * 8u, desc_sw128(b_addr + s * tile_bytes + off), idesc,
+                                ks > 0 ? 1u : 0u);
                 }
-                commit_to(mma_done + s);
+                commit_to(stage_free + s);   // the stage may be refilled
+                commit_to(mma_done + acc);   // the accumulator may be read
             }
         }
     } else {
@@ -212,6 +214,23 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
         const uint32_t rl = tile.first + row;                      // the row's partition-local id
         const bool active = rl < tile.seg_len;
         const float pnr = active ? __ldg(a.norms + tile.seg_start + rl) : 0.0f;
+        // The CTA's own rows go into tensor memory once: warp (quad, part) writes columns part * 32 ... of the 32
+        // rows of its quadrant (lane = row), read straight from global memory; rows beyond the matrix are zeros.
+        if (part < kblocks) {
+            uint32_t v[32];
+            const uint64_t grow = (uint64_t) tile.seg_start + rl;
+            const float4 *src = reinterpret_cast<const float4 *>(a.data + grow * dim + part * 32u);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float4 x = grow < a.rows_total ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[4 * i] = __float_as_uint(x.x); v[4 * i + 1] = __float_as_uint(x.y);
+                v[4 * i + 2] = __float_as_uint(x.z); v[4 * i + 3] = __float_as_uint(x.w);
+            }
+            tmem_store32(tmem_base + ((quad * 32u) << 16) + kTmemA + part * 32u, v);
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_full);
+        }
         float *cn = cn_w + warp * kCols;                           // this warp's column norms of the current tile
         constexpr uint32_t G = Sizes<NL>::part_groups;
         float *my_gmin = a.gmin + ((launch_row0 + row) * kSplit + part) * G;
@@ -232,7 +251,7 @@ __global__ void __launch_bounds__(kThreads) knn_umma_kernel(const KnnTcArgs a, c
             cn_ahead[h] = c < tile.seg_len ? __ldg(a.norms + tile.seg_start + c) : 0.0f;
         }
         for (uint32_t t = 0; t < total; t++) {
-            const uint32_t s = t & 1u, use = t >> 1;
+            const uint32_t s = t & 1u, use = t >> 1;   // the accumulator buffer and its turn
             const bool second = t >= tiles;
             const uint32_t tt = second ? t - tiles : t;
             if (t == tiles) {
@@ -435,13 +454,13 @@ cudaError_t run(const float *data, uint64_t rows_total, uint32_t dim, const std:
     cudaError_t e = cudaMemsetAsync(fail_flag, 0, 4, stream);
     if (e != cudaSuccess) return e;
     row_norms_kernel<<<(unsigned) ((rows_total * 32 + 255) / 256), 256, 0, stream>>>(data, rows_total, dim, norms);
-    const size_t smem_main = 1024 + (size_t) 3 * kRows * dim * 4 + (kEpiWarps * kCols + kRows) * 4 + 7 * 8 + 16;
+    const size_t smem_main = 1024 + (size_t) 3 * kRows * dim * 4 + (kEpiWarps * kCols + kRows) * 4 + (1 + 2 * kStages + 4) * 8 + 16;
     if ((e = cudaFuncSetAttribute(knn_umma_kernel<NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_main)) != cudaSuccess) return e;
     const uint32_t rr_warps = 8;
     const size_t smem_rr = (size_t) rr_warps * (dim_pad4(dim) + 2 * Sizes<NL>::keep) * 4;
     if (smem_rr > 48 * 1024 &&
         (e = cudaFuncSetAttribute(knn_rerank_kernel<NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_rr)) != cudaSuccess) return e;
-    KnnTcArgs a{data, dim, norms, d_tiles, cand, cand_count, gmin, fail_flag};
+    KnnTcArgs a{data, dim, rows_total, norms, d_tiles, cand, cand_count, gmin, fail_flag};
     for (size_t first = 0; first < tiles.size(); first += kMaxCtasPerLaunch) {
         const uint32_t n = (uint32_t) std::min<size_t>(kMaxCtasPerLaunch, tiles.size() - first);
         // the table is pageable host memory: the copy has read it when the call returns
