@@ -7,10 +7,12 @@
 //
 //   norms    |x|^2 of every row, exact fp32.
 //   contract a CTA owns 128 rows of one partition (the M of a 128 x 128 x 8 TF32 MMA) and walks the
-//            partition in tiles of 128 rows. Operand tiles arrive by TMA (one 2-D tensor map over the
-//            whole reordered matrix, boxes of 32 floats x 128 rows, 128-byte swizzle, no multicast),
-//            tcgen05.mma kind::tf32 accumulates the 128 x 128 dot products in tensor memory (two
-//            buffers), and sixteen epilogue warps read them back (tcgen05.ld): thread (row, part)
+//            partition in tiles of 128 rows. The CTA's own rows are written into tensor memory once
+//            (tcgen05.st) and are the MMA's A operand from there; the partition's tiles arrive by TMA
+//            (one 2-D tensor map over the whole reordered matrix, boxes of 32 floats x 128 rows,
+//            128-byte swizzle, no multicast) into three stages of shared memory; tcgen05.mma
+//            kind::tf32 accumulates the 128 x 128 dot products in tensor memory (two buffers), and
+//            sixteen epilogue warps read them back (tcgen05.ld): thread (row, part)
 //            turns 32 dot products of a tile into |a|^2 + |b|^2 - 2 a.b (four threads per row; with
 //            two, the tile loop was bound by the latency of eight warps' dependent instruction chains:
 //            31 % of the issue slots and 26 % of the tensor pipe busy).
