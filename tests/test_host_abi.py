@@ -134,3 +134,25 @@ def test_no_product_module_imports_the_oracle():
             if fn.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, fn), errors="ignore").read()
                 assert "import oracle" not in text and "from oracle" not in text and "glide_oracle" not in text, fn
+
+
+def test_bench_reference_arm_prints_one_contract_line_without_a_gpu():
+    """`bench.py --impl reference` on a box without a CUDA device: one JSON line on stdout with the keys the
+    bench contract names (the CPU arm then runs exact brute force, there being no index to search)."""
+    import json
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("with a GPU this arm searches a GPU-built index: covered by the GPU bench itself")
+    run = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--rows", "20000",
+                          "--steps", "1", "--warmup", "0"], capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = [l for l in run.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["unit"] == "queries/s" and line["higher_is_better"] is True
+    assert line["steps"] == 1 and line["warmup"] == 0 and line["n_gpus"] == 1 and line["value"] > 0
+    assert set(line["cpu_baseline"]) >= {"value", "unit", "cores", "kind", "sample"}
+    assert line["e2e"] == {"value": line["value"], "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in line["config"]
